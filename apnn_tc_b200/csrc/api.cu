@@ -1,0 +1,201 @@
+// C ABI of the library (include/apnn_b200.h): argument checking, problem set-up and
+// dispatch.  No entry point allocates device memory except the host-buffer front end's
+// handle (host_front.cu), and none falls back to a CPU path.
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/apnn_b200.h"
+#include "api_internal.h"
+#include "core_launch.h"
+#include "tc5_gemm.h"
+
+namespace apnn {
+
+static thread_local char g_cuda_err[256] = "";
+
+apnn_status cuda_fail(cudaError_t e, const char* where) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", where, cudaGetErrorString(e));
+  return APNN_ERR_CUDA;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int device_sm_count() {
+  static int sms[16] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev < 16 && sms[dev]) return sms[dev];
+  int n = 148;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (dev < 16) sms[dev] = n;
+  return n;
+}
+
+apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, int abits_signed_w, int abits_signed_x) {
+  if (!e) return APNN_OK;
+  if (e->out_mode < APNN_OUT_INT32 || e->out_mode > APNN_OUT_THRESHOLDS) return APNN_ERR_INVALID_ARG;
+  if (e->out_mode != APNN_OUT_INT32) {
+    if (e->out_bits < 1 || e->out_bits > 8) return APNN_ERR_INVALID_ARG;
+    if (channels % 32 != 0) return APNN_ERR_UNSUPPORTED;
+    if (e->out_mode == APNN_OUT_THRESHOLDS && !e->thresholds) return APNN_ERR_INVALID_ARG;
+  }
+  if (e->signed_operand < APNN_SIGN_NONE || e->signed_operand > APNN_SIGN_X) return APNN_ERR_INVALID_ARG;
+  if (e->signed_operand == APNN_SIGN_W && abits_signed_w != 1) return APNN_ERR_UNSUPPORTED;
+  if (e->signed_operand == APNN_SIGN_X && abits_signed_x != 1) return APNN_ERR_UNSUPPORTED;
+  if (e->pool < APNN_POOL_NONE || e->pool > APNN_POOL_MAX2) return APNN_ERR_INVALID_ARG;
+  if (!is_conv && (e->pool != APNN_POOL_NONE || e->out_halo != 0)) return APNN_ERR_INVALID_ARG;
+  if (e->out_halo < 0 || e->out_halo > 8) return APNN_ERR_INVALID_ARG;
+  return APNN_OK;
+}
+
+}  // namespace apnn
+
+using namespace apnn;
+
+extern "C" {
+
+const char* apnn_status_string(apnn_status s) {
+  switch (s) {
+    case APNN_OK: return "ok";
+    case APNN_ERR_INVALID_ARG: return "invalid argument";
+    case APNN_ERR_UNSUPPORTED: return "unsupported bit widths or shape";
+    case APNN_ERR_ALIGNMENT: return "pointer not 16-byte aligned or K not a multiple of 128";
+    case APNN_ERR_WORKSPACE: return "workspace missing or too small";
+    case APNN_ERR_CUDA: return "CUDA error";
+    case APNN_ERR_NO_DEVICE: return "no sm_100 device";
+    case APNN_ERR_TIMEOUT: return "a bounded device-side wait expired";
+  }
+  return "unknown status";
+}
+
+const char* apnn_last_cuda_error(void) { return g_cuda_err; }
+
+int apnn_version(void) { return 100; }
+
+size_t apnn_gemm_workspace_bytes(int algo, int wbits, int xbits, int M, int N, int K) {
+  (void)wbits;
+  (void)xbits;
+  if (algo != APNN_ALGO_TCGEN05) return 0;
+  return tc5_workspace_bytes(M, N, K);
+}
+
+apnn_status apnn_gemm_check(void* stream, const void* workspace, int M, int N, int K) {
+  if (!workspace || M <= 0 || N <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
+  int flag = tc5_read_error_flag(reinterpret_cast<cudaStream_t>(stream), workspace, M, N, K);
+  if (flag < 0) return cuda_fail(cudaGetLastError(), "apnn_gemm_check");
+  return flag == 0 ? APNN_OK : APNN_ERR_TIMEOUT;
+}
+
+apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const void* W, const void* X, void* D, int M,
+                         int N, int K, const apnn_epilogue* epi, void* workspace, size_t workspace_bytes) {
+  if (!W || !X || !D) return APNN_ERR_INVALID_ARG;
+  if (M <= 0 || N <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
+  if (algo < APNN_ALGO_AUTO || algo > APNN_ALGO_TCGEN05) return APNN_ERR_INVALID_ARG;
+  if (K % 128 != 0) return APNN_ERR_ALIGNMENT;
+  if (!aligned16(W) || !aligned16(X) || !aligned16(D)) return APNN_ERR_ALIGNMENT;
+  if (!core_supports(wbits, xbits)) return APNN_ERR_UNSUPPORTED;
+  apnn_status st = check_epilogue(epi, N, false, wbits, xbits);
+  if (st != APNN_OK) return st;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+
+  if (algo == APNN_ALGO_AUTO) {
+    bool ws_ok = workspace && workspace_bytes >= tc5_workspace_bytes(M, N, K);
+    algo = (ws_ok && tc5_worthwhile(M, N, K)) ? APNN_ALGO_TCGEN05 : APNN_ALGO_IMMA;
+  }
+  if (algo == APNN_ALGO_TCGEN05) {
+    if (!workspace || workspace_bytes < tc5_workspace_bytes(M, N, K)) return APNN_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return APNN_ERR_ALIGNMENT;
+    return tc5_gemm(s, wbits, xbits, (const uint32_t*)W, (const uint32_t*)X, D, M, N, K, epi, workspace);
+  }
+
+  CoreParams p;
+  memset(&p, 0, sizeof(p));
+  p.A = (const uint32_t*)W;
+  p.B = (const uint32_t*)X;
+  p.a_plane_words = (long long)M * (K / 32);
+  p.b_plane_words = (long long)N * (K / 32);
+  p.M = M;
+  p.N = N;
+  p.kchunks = K / 128;
+  p.a_row_words = K / 32;
+  p.b_row_words = K / 32;
+  p.out = D;
+  p.out_mode = APNN_OUT_INT32;
+  if (epi) {
+    p.out_mode = epi->out_mode;
+    p.out_bits = epi->out_bits;
+    p.thresholds = epi->thresholds;
+    p.sign = epi->signed_operand == APNN_SIGN_W ? SIGN_A : epi->signed_operand == APNN_SIGN_X ? SIGN_B : SIGN_NONE;
+    p.out_plane_words = (long long)M * (N / 32);
+  }
+  int kind = algo == APNN_ALGO_BMMA ? CORE_B1 : CORE_U8;
+  cudaError_t e = launch_core(kind, wbits, xbits, p, s, core_pick_tile(p, device_sm_count()));
+  if (e != cudaSuccess) return cuda_fail(e, "apnn_gemm launch");
+  return APNN_OK;
+}
+
+apnn_status apnn_gemm(void* stream, int wbits, int xbits, const void* W, const void* X, int32_t* D, int M, int N,
+                      int K) {
+  return apnn_gemm_ex(stream, APNN_ALGO_AUTO, wbits, xbits, W, X, D, M, N, K, nullptr, nullptr, 0);
+}
+
+apnn_status apnn_conv2d(void* stream, int wbits, int xbits, const void* Wt, const void* X, void* Out, int B, int H,
+                        int Wd, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi) {
+  if (!Wt || !X || !Out) return APNN_ERR_INVALID_ARG;
+  if (B <= 0 || H <= 0 || Wd <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
+  if (R != 1 && R != 3) return APNN_ERR_UNSUPPORTED;
+  if (stride != 1 && stride != 2) return APNN_ERR_UNSUPPORTED;
+  if (CIN % 128 != 0) return APNN_ERR_ALIGNMENT;
+  if (!aligned16(Wt) || !aligned16(X) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
+  // core operand A = activations (xbits), B = filter (wbits)
+  if (!core_supports(xbits, wbits)) return APNN_ERR_UNSUPPORTED;
+  apnn_status st = check_epilogue(epi, COUT, true, wbits, xbits);
+  if (st != APNN_OK) return st;
+  const int pad = (R - 1) / 2;
+  const int Ho = (H - 1) / stride + 1, Wo = (Wd - 1) / stride + 1;
+  const int pool = epi ? epi->pool : APNN_POOL_NONE;
+  if (pool != APNN_POOL_NONE && ((Ho & 1) || (Wo & 1))) return APNN_ERR_UNSUPPORTED;
+  const long long pixels = (long long)B * Ho * Wo;
+  if (pixels > 0x7fffffffLL) return APNN_ERR_UNSUPPORTED;
+
+  CoreParams p;
+  memset(&p, 0, sizeof(p));
+  p.A = (const uint32_t*)X;
+  p.B = (const uint32_t*)Wt;
+  p.Hp = H + 2 * pad;
+  p.Wp = Wd + 2 * pad;
+  p.cin_words = CIN / 32;
+  p.cin_chunks = CIN / 128;
+  p.a_plane_words = (long long)B * p.Hp * p.Wp * p.cin_words;
+  p.b_row_words = R * R * p.cin_words;
+  p.b_plane_words = (long long)COUT * p.b_row_words;
+  p.M = (int)pixels;
+  p.N = COUT;
+  p.kchunks = R * R * p.cin_chunks;
+  p.is_conv = 1;
+  p.Ho = Ho;
+  p.Wo = Wo;
+  p.R = R;
+  p.stride = stride;
+  p.out = Out;
+  p.out_mode = APNN_OUT_INT32;
+  p.pool = pool;
+  p.out_h = pool ? Ho / 2 : Ho;
+  p.out_w = pool ? Wo / 2 : Wo;
+  if (epi) {
+    p.out_mode = epi->out_mode;
+    p.out_bits = epi->out_bits;
+    p.thresholds = epi->thresholds;
+    // the filter is core operand B, the activations core operand A
+    p.sign = epi->signed_operand == APNN_SIGN_W ? SIGN_B : epi->signed_operand == APNN_SIGN_X ? SIGN_A : SIGN_NONE;
+    p.out_halo = epi->out_halo;
+  }
+  p.out_plane_words =
+      (long long)B * (p.out_h + 2 * p.out_halo) * (p.out_w + 2 * p.out_halo) * (COUT / 32);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_core(CORE_U8, xbits, wbits, p, s, core_pick_tile(p, device_sm_count()));
+  if (e != cudaSuccess) return cuda_fail(e, "apnn_conv2d launch");
+  return APNN_OK;
+}
+
+}  // extern "C"

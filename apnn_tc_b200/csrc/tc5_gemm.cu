@@ -1,0 +1,454 @@
+// tcgen05 path for large GEMMs.
+//
+// Step 1 (expand_planes_kernel): every operand is rewritten once from bit planes to one
+// int8 per element, value = sum_p bit_p << p (or -1/+1 for a signed 1-bit operand), rows of
+// K bytes in the caller's workspace.  Within each group of 32 k the byte order is the
+// "spread" order (bit q+8j of the word -> byte 4q+j); both operands use it, so the dot
+// product is unchanged.
+//
+// Step 2 (tc5_gemm_kernel): persistent, warp-specialised int8 GEMM.  One CTA per SM walks
+// over 128 x 256 output tiles.  Warp 0 streams K blocks of 128 bytes per row with TMA
+// (128-byte swizzle) through a 4-stage shared-memory ring; warp 1 issues tcgen05.mma
+// kind::i8 (M=128, N=256, K=32) from shared-memory descriptors into one of two 256-column
+// TMEM accumulators; warps 2-5 drain the other accumulator with tcgen05.ld and run the
+// epilogue (int32 stores, or requantise + bit-plane pack: a thread owns one row and 32
+// consecutive columns, i.e. exactly one output word per plane).  No cluster, no multicast.
+//
+// Every mbarrier wait is bounded: on expiry the kernel raises a flag in global memory,
+// stops issuing work, and falls through to the common tear-down (TMEM is released).
+#include <cuda.h>
+
+#include "api_internal.h"
+#include "apnn_device.cuh"
+#include "tc5_gemm.h"
+
+namespace apnn {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;  // bytes of K per stage = one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK;
+constexpr int B_STAGE_BYTES = BN * BK;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 16;  // tiles are walked in bands of 16 row-tiles for L2 reuse
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // a wait that lasts 2 s is a bug, not a delay
+
+// ------------------------------------------------------------------ expand kernel
+__global__ void __launch_bounds__(256) expand_planes_kernel(const uint32_t* __restrict__ planes,
+                                                            uint8_t* __restrict__ out, long long rows, int kwords,
+                                                            int bits, int is_signed) {
+  const long long total = rows * kwords;
+  const long long plane_words = total;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    uint32_t w[8];
+#pragma unroll
+    for (int p = 0; p < 8; p++) w[p] = p < bits ? __ldg(planes + p * plane_words + i) : 0u;
+    uint32_t r[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      uint32_t v = 0;
+#pragma unroll
+      for (int p = 0; p < 8; p++) {
+        uint32_t s = (q >= p) ? (w[p] >> (q - p)) : (w[p] << (p - q));
+        v |= s & (0x01010101u << p);
+      }
+      // signed 1-bit operand: bit 1 -> +1 (0x01), bit 0 -> -1 (0xFF)
+      r[q] = is_signed ? (0xFFFFFFFFu ^ (v * 0xFEu)) : v;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + i * 32);
+    dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
+    dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
+  }
+}
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: returns false when the time limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  unsigned long long t0 = 0;
+  for (uint32_t spin = 0;; spin++) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 255u) == 255u) {
+      unsigned long long now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+  return d;
+}
+
+struct Tc5Params {
+  void* out;
+  const int32_t* thresholds;
+  int M, N, kblocks;
+  int tiles_m, tiles_n;
+  int out_mode, out_bits;
+  uint32_t idesc;
+  long long out_plane_words;
+  int* error_flag;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int band = GROUP_M * tiles_n;
+  const int g = tile / band;
+  const int first = g * GROUP_M;
+  const int rows = min(GROUP_M, tiles_m - first);
+  const int r = tile - g * band;
+  tm = first + r % rows;
+  tn = r / rows;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const Tc5Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t bars = base + STAGES * STAGE_BYTES;
+  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM pointer
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        for (int kb = 0; kb < p.kblocks; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const uint32_t sa = base + s * STAGE_BYTES;
+          tma_load_2d(sa, &map_a, kb * BK, tm * BM, full_bar(s));
+          tma_load_2d(sa + A_STAGE_BYTES, &map_b, kb * BK, tn * BN, full_bar(s));
+        }
+      }
+      if (!ok) atomicExch(p.error_flag, 1);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t tl = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
+        const uint32_t acc = tl & 1u;
+        const uint32_t aph = (tl >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.kblocks; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + s * STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + A_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 32; k++) {
+            // advancing 32 bytes along K inside the swizzle row = +2 in 16-byte units
+            tc_mma_i8(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));  // frees the stage when these MMAs have read it
+        }
+        if (ok) tc_commit(tfull_bar(acc));  // accumulator complete
+      }
+      if (!ok) atomicExch(p.error_flag, 2);
+    }
+  } else {
+    // ---------------- epilogue warps (2..5) ----------------
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
+    uint32_t tl = 0;
+    bool ok = true;
+    const int nl = (1 << p.out_bits) - 1;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const uint32_t acc = tl & 1u;
+      const uint32_t aph = (tl >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
+      tc_fence_after();
+      const long long row = (long long)tm * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        if (p.out_mode == OUT_INT32) {
+          int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
+          if ((p.N & 3) == 0 && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+              reinterpret_cast<uint4*>(D)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < p.N) D[j] = (int32_t)v[j];
+          }
+        } else {
+          // packed modes need N % 32 == 0, so this word is whole
+          uint32_t lv[32];
+          if (p.out_mode == OUT_LOWBITS) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) lv[j] = v[j] & (uint32_t)nl;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              const int32_t* T = p.thresholds + (long long)(col0 + j) * nl;
+              uint32_t l = 0;
+              for (int t = 0; t < nl; t++) l += ((int32_t)v[j] >= __ldg(T + t)) ? 1u : 0u;
+              lv[j] = l;
+            }
+          }
+          uint32_t* O = reinterpret_cast<uint32_t*>(p.out);
+          for (int b = 0; b < p.out_bits; b++) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < 32; j++) word |= ((lv[j] >> b) & 1u) << (31 - j);
+            O[b * p.out_plane_words + row * (p.N >> 5) + (col0 >> 5)] = word;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+    if (!ok && lane == 0) atomicExch(p.error_flag, 3);
+  }
+
+  // ---------------- tear-down ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// rows x K bytes, row-major; box = box_rows x 128 bytes, 128-byte swizzle, zero fill outside
+bool make_operand_map(CUtensorMap* map, const void* base, long long rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+size_t tc5_workspace_bytes(int M, int N, int K) {
+  // int8 copies of both operands + a 256-byte slot for the kernel's error flag
+  return align_up((size_t)M * K, 256) + align_up((size_t)N * K, 256) + 256;
+}
+
+bool tc5_worthwhile(int M, int N, int K) {
+  long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return tiles >= 64 && K >= 1024;
+}
+
+apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, const uint32_t* X, void* D, int M,
+                     int N, int K, const apnn_epilogue* epi, void* workspace) {
+  uint8_t* wa = reinterpret_cast<uint8_t*>(workspace);
+  uint8_t* wb = wa + align_up((size_t)M * K, 256);
+  int* err = reinterpret_cast<int*>(wb + align_up((size_t)N * K, 256));
+  const int sign = epi ? epi->signed_operand : APNN_SIGN_NONE;
+
+  cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), s);
+  if (e != cudaSuccess) return cuda_fail(e, "tc5 flag reset");
+  const int sms = device_sm_count();
+  {
+    long long total = (long long)M * (K / 32);
+    int blocks = (int)((total + 255) / 256 < (long long)sms * 16 ? (total + 255) / 256 : (long long)sms * 16);
+    expand_planes_kernel<<<blocks, 256, 0, s>>>(W, wa, M, K / 32, wbits, sign == APNN_SIGN_W);
+    total = (long long)N * (K / 32);
+    blocks = (int)((total + 255) / 256 < (long long)sms * 16 ? (total + 255) / 256 : (long long)sms * 16);
+    expand_planes_kernel<<<blocks, 256, 0, s>>>(X, wb, N, K / 32, xbits, sign == APNN_SIGN_X);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "expand_planes launch");
+  }
+
+  CUtensorMap map_a, map_b;
+  if (!make_operand_map(&map_a, wa, M, K, BM) || !make_operand_map(&map_b, wb, N, K, BN)) {
+    return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  }
+
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !attr_set[dev]) {
+    e = cudaFuncSetAttribute(tc5_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return cuda_fail(e, "tc5 smem attribute");
+    if (dev < 16) attr_set[dev] = true;
+  }
+
+  Tc5Params p;
+  p.out = D;
+  p.thresholds = epi ? epi->thresholds : nullptr;
+  p.M = M;
+  p.N = N;
+  p.kblocks = K / BK;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
+  p.out_bits = epi ? epi->out_bits : 0;
+  p.out_plane_words = (long long)M * (N / 32);
+  p.error_flag = err;
+  // instruction descriptor: D = s32, A/B = u8 or s8, both K-major, N = 256, M = 128
+  const uint32_t afmt = sign == APNN_SIGN_W ? 1u : 0u, bfmt = sign == APNN_SIGN_X ? 1u : 0u;
+  p.idesc = (2u << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+  long long tiles = (long long)p.tiles_m * p.tiles_n;
+  int grid = (int)(tiles < sms ? tiles : sms);
+  tc5_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm launch");
+  return APNN_OK;
+}
+
+// Reads back the flag a bounded wait raises; 0 means the last tc5_gemm on this workspace
+// ran to completion.  Synchronises the stream.
+int tc5_read_error_flag(cudaStream_t s, const void* workspace, int M, int N, int K) {
+  const uint8_t* wa = reinterpret_cast<const uint8_t*>(workspace);
+  const uint8_t* wb = wa + align_up((size_t)M * K, 256);
+  const int* err = reinterpret_cast<const int*>(wb + align_up((size_t)N * K, 256));
+  int v = -1;
+  if (cudaMemcpyAsync(&v, err, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace apnn

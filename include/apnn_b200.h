@@ -1,0 +1,154 @@
+/*
+ * apnn_b200.h -- C ABI of the B200 (sm_100a) arbitrary-precision GEMM / convolution
+ * library.  Plain pointers and sizes only; every device pointer is memory the
+ * caller allocated (cudaMalloc or equivalent) and still owns, as in the reference,
+ * where kernels allocate nothing.  Every entry point returns a status code and
+ * never aborts.  `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ *
+ * Reference interfaces cited below are paths inside the APNN-TC project;
+ * LIB = APNN-TC-lib/bmmaTensorCoreGemm/src, NN = APNN-TC-nn/src.
+ *
+ * Tensor layouts (identical to the reference, uint32 words, planes outermost,
+ * K / channel fastest, 16-byte aligned):
+ *   GEMM  W[wbits][M][K/32]   X[xbits][N][K/32]   D[M][N] int32
+ *         D = sum_wb sum_xb 2^(wb+xb) popcount(W[wb][m] & X[xb][n])
+ *         packed D[out_bits][M][N/32], column n in bit 31-(n%32)
+ *   conv  X[xbits][B][H+2p][W+2p][CIN/32] (halo of p=(R-1)/2 pixels stored with
+ *         every image), Wt[wbits][COUT][R][R][CIN/32],
+ *         Out[B][Ho][Wo][COUT] int32 or packed Out[out_bits][B][Ho][Wo][COUT/32]
+ */
+#ifndef APNN_B200_H
+#define APNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum apnn_status {
+  APNN_OK = 0,
+  APNN_ERR_INVALID_ARG = 1, /* null pointer, non-positive size, bad enum */
+  APNN_ERR_UNSUPPORTED = 2, /* bit-width pair or shape rule not supported */
+  APNN_ERR_ALIGNMENT = 3,   /* pointer not 16-byte aligned / K not a multiple of 128 */
+  APNN_ERR_WORKSPACE = 4,   /* workspace missing or too small for the chosen algorithm */
+  APNN_ERR_CUDA = 5,        /* a CUDA call failed; see apnn_last_cuda_error() */
+  APNN_ERR_NO_DEVICE = 6,   /* no sm_100 device available */
+  APNN_ERR_TIMEOUT = 7      /* a bounded device-side wait expired; the output is incomplete */
+} apnn_status;
+
+/* What the fused epilogue writes. */
+enum {
+  APNN_OUT_INT32 = 0,     /* int32 value per output element */
+  APNN_OUT_LOWBITS = 1,   /* low out_bits bits of the value, plane-split and packed (the
+                             reference's fused kernels) */
+  APNN_OUT_THRESHOLDS = 2 /* level = number of per-channel int32 thresholds the value reaches
+                             (batch-norm + quantiser folded on the host), packed */
+};
+/* Which operand's bits mean -1/+1 instead of 0/1 (that operand must be 1-bit). */
+enum { APNN_SIGN_NONE = 0, APNN_SIGN_W = 1, APNN_SIGN_X = 2 };
+/* 2x2 pooling applied to the int32 value before requantisation (conv only). */
+enum { APNN_POOL_NONE = 0, APNN_POOL_AVG2 = 1, APNN_POOL_MAX2 = 2 };
+/* Contraction path. */
+enum {
+  APNN_ALGO_AUTO = 0,    /* TCGEN05 when a large enough workspace is given and the problem is
+                            big enough to fill the device, else IMMA */
+  APNN_ALGO_BMMA = 1,    /* 1-bit and-popcount mma.sync per plane pair (emulated on sm_100a;
+                            kept as the measured comparison), no workspace */
+  APNN_ALGO_IMMA = 2,    /* planes spread to u8 in registers, mma.sync m16n8k32, no workspace */
+  APNN_ALGO_TCGEN05 = 3  /* planes expanded to int8 in the workspace, TMA-fed tcgen05 kind::i8
+                            with TMEM accumulators */
+};
+
+typedef struct apnn_epilogue {
+  int32_t out_mode;          /* APNN_OUT_* */
+  int32_t out_bits;          /* 1..8 for the packed modes */
+  int32_t signed_operand;    /* APNN_SIGN_*: value = 2*acc - (sum of the other operand's row) */
+  int32_t pool;              /* APNN_POOL_* (conv only; H and W even) */
+  int32_t out_halo;          /* conv only: write the output inside a zeroed ring of this many
+                                pixels, so it can feed the next conv directly */
+  int32_t reserved;
+  const int32_t *thresholds; /* device, [channels][2^out_bits - 1] ascending; channel = n
+                                (GEMM) or output channel (conv) */
+} apnn_epilogue;
+
+const char *apnn_status_string(apnn_status s);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char *apnn_last_cuda_error(void);
+int apnn_version(void);
+
+/* ---- GEMM ----------------------------------------------------------------------
+ * apnn_gemm replaces the int32-output kernels
+ *   apmm_w1a2 (LIB/71_bmmaTensorCoreGemm.cu:80), apmm_w2a2 (LIB/72_...cu:80),
+ *   apmm_w1a4 (LIB/78_...cu:80) and the w1a3 binary the README runs,
+ * launched there as <<<SMs, 256, 65536>>>(W, X, D, M, N, K, wb, xb).
+ * Supported (wbits, xbits): (1,2) (1,3) (1,4) (2,2) and their transposes.
+ * Rules: K % 128 == 0; W, X, D 16-byte aligned; M, N >= 1 (ragged edges handled). */
+apnn_status apnn_gemm(void *stream, int wbits, int xbits, const void *W, const void *X,
+                      int32_t *D, int M, int N, int K);
+
+/* apnn_gemm_ex adds the fused epilogue and the algorithm / workspace choice; with
+ * APNN_OUT_LOWBITS it replaces apmm_w1a2_decompose (LIB/66_bmmaTensorCoreGemm.cuh:81-280)
+ * and apmm_w2a2_decompose (LIB/73_bmmaTensorCoreGemm.cuh:81-297), which FC_new_global /
+ * Output_new_global call (NN/kernel.cuh:299-318).  Packed modes need N % 32 == 0.
+ * epi == NULL means int32 output.  workspace may be NULL for every algorithm but APNN_ALGO_TCGEN05. */
+apnn_status apnn_gemm_ex(void *stream, int algo, int wbits, int xbits, const void *W,
+                         const void *X, void *D, int M, int N, int K,
+                         const apnn_epilogue *epi, void *workspace, size_t workspace_bytes);
+
+/* Bytes of device workspace `algo` needs for this problem (0 unless APNN_ALGO_TCGEN05). */
+size_t apnn_gemm_workspace_bytes(int algo, int wbits, int xbits, int M, int N, int K);
+
+/* The tcgen05 kernel bounds every barrier wait (2 s) and raises a flag in the workspace
+ * instead of hanging.  This call synchronises `stream` and returns APNN_ERR_TIMEOUT if the
+ * last APNN_ALGO_TCGEN05 GEMM that used this workspace with these sizes gave up, APNN_OK
+ * otherwise.  No counterpart in the reference (its kernels have no waits). */
+apnn_status apnn_gemm_check(void *stream, const void *workspace, int M, int N, int K);
+
+/* ---- convolution ---------------------------------------------------------------
+ * Implicit-GEMM RxR convolution, R in {1, 3}, stride in {1, 2}, symmetric padding
+ * carried by the input.  With B = 1, R = 3, stride = 1:
+ *   epi NULL / APNN_OUT_INT32      -> compute_conv_imma (LIB/51_...cu:58 w1a2, LIB/48_...cu:58
+ *                                     w2a2, LIB/53_...cu:58 w1a4, LIB/59_...cu:58 w1a3)
+ *   APNN_OUT_LOWBITS               -> APConv_w1a2_pack (LIB/67_bmmaTensorCoreGemm.cu:58),
+ *                                     APConv_w2a2_pack (LIB/70_...cu:58)
+ *   APNN_OUT_LOWBITS + POOL_AVG2   -> APConv_w1a2_pack_pool (LIB/68_...cu:58),
+ *                                     APConv_w2a2_pack_pool (LIB/69_...cuh:59)
+ * which Conv_new_global calls (NN/kernel.cuh:285-289).
+ * Rules: CIN % 128 == 0; packed modes need COUT % 32 == 0; pooling needs even Ho, Wo. */
+apnn_status apnn_conv2d(void *stream, int wbits, int xbits, const void *Wt, const void *X,
+                        void *Out, int B, int H, int W, int CIN, int COUT, int R, int stride,
+                        const apnn_epilogue *epi);
+
+/* ---- packers -------------------------------------------------------------------
+ * apnn_bit_compress replaces Bit_compression (NN/kernel.cuh:46-77): one uint32 level per
+ * element, levels[rows][C] -> planes[bits][rows][PAD128(C)/32], channel c in bit 31-(c%32);
+ * channels C..PAD128(C)-1 are written as zero.
+ * apnn_quantize_pack fuses Quantize_val (NN/kernel.cuh:29-44: clip to [-10,10], affine to
+ * 2^bits steps, round to nearest even, clamped to 2^bits-1) in front of it, replacing the
+ * kernel pair images_quantization launches (NN/kernel.cuh:129-161). */
+apnn_status apnn_bit_compress(void *stream, const uint32_t *levels, uint32_t *planes, long rows,
+                              int C, int bits);
+apnn_status apnn_quantize_pack(void *stream, const float *values, uint32_t *planes, long rows,
+                               int C, int bits);
+
+/* ---- host-buffer front end -----------------------------------------------------
+ * For callers that hold operands in host memory (the reference's main() programs:
+ * malloc + cudaMemcpy around every launch, LIB/71_bmmaTensorCoreGemm.cu:498-571).
+ * A handle owns a stream and a grow-only device arena; apnn_gemm_host copies W and X
+ * in, runs apnn_gemm_ex, copies D out and synchronises. */
+typedef struct apnn_handle_s *apnn_handle;
+apnn_status apnn_create(apnn_handle *h, int device);
+apnn_status apnn_destroy(apnn_handle h);
+apnn_status apnn_gemm_host(apnn_handle h, int algo, int wbits, int xbits, const void *W_host,
+                           const void *X_host, void *D_host, int M, int N, int K,
+                           const apnn_epilogue *epi_host_thresholds);
+apnn_status apnn_conv2d_host(apnn_handle h, int wbits, int xbits, const void *Wt_host,
+                             const void *X_host, void *Out_host, int B, int H, int W, int CIN,
+                             int COUT, int R, int stride, const apnn_epilogue *epi_host_thresholds);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* APNN_B200_H */

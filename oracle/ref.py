@@ -145,7 +145,11 @@ def _conv_args(Wt, X):
 def conv_ref(prog, Wt, X):
     Wa, Xa, H, Wd, CIN, COUT, wbits, xbits = _conv_args(Wt, X)
     out = _aligned((1, H, Wd, COUT), np.int32)
-    getattr(_lib(prog), _CONV_REF)(_ptr(Wa), _ptr(Xa), _ptr(out), H, Wd, CIN, COUT, wbits, xbits)
+    fn = getattr(_lib(prog), _CONV_REF)
+    if prog in (48, 70):  # these two programs declare compute_ref(X, W, ..., X_BIT, W_BIT)
+        fn(_ptr(Xa), _ptr(Wa), _ptr(out), H, Wd, CIN, COUT, xbits, wbits)
+    else:                 # 67, 68: compute_ref(W, X, ..., W_BIT, X_BIT)
+        fn(_ptr(Wa), _ptr(Xa), _ptr(out), H, Wd, CIN, COUT, wbits, xbits)
     return np.array(out)
 
 

@@ -1,0 +1,74 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the header
+declares, and rejects bad arguments with status codes before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from apnn_tc_b200 import _cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_functions():
+    text = open(os.path.join(ROOT, "include", "apnn_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(apnn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = _cabi.lib()
+    declared = _header_functions()
+    assert set(declared) == set(_cabi.EXPORTS)
+    for name in declared:
+        assert hasattr(L, name), name
+
+
+def test_status_strings_and_version():
+    L = _cabi.lib()
+    assert L.apnn_version() >= 100
+    assert L.apnn_status_string(0) == b"ok"
+    for s in range(1, 8):
+        assert L.apnn_status_string(s) not in (b"ok", b"unknown status")
+
+
+def test_argument_validation_returns_status_codes():
+    L = _cabi.lib()
+    buf = (ctypes.c_uint32 * 64)()
+    base = ctypes.addressof(buf)
+    p = base + (-base % 16)
+    # null pointers / sizes
+    assert L.apnn_gemm_ex(None, 0, 1, 2, None, p, p, 64, 64, 128, None, None, 0) == 1
+    assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 0, 64, 128, None, None, 0) == 1
+    # K not a multiple of 128, misaligned pointer
+    assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 96, None, None, 0) == 3
+    assert L.apnn_gemm_ex(None, 0, 1, 2, p + 4, p, p, 64, 64, 128, None, None, 0) == 3
+    # unsupported widths, packed output with N % 32 != 0, signed operand wider than 1 bit
+    assert L.apnn_gemm_ex(None, 0, 3, 3, p, p, p, 64, 64, 128, None, None, 0) == 2
+    e = _cabi.Epilogue(out_mode=1, out_bits=2)
+    assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 48, 128, ctypes.byref(e), None, 0) == 2
+    e = _cabi.Epilogue(out_mode=0, signed_operand=2)
+    assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 128, ctypes.byref(e), None, 0) == 2
+    e = _cabi.Epilogue(out_mode=2, out_bits=2)  # thresholds missing
+    assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 128, ctypes.byref(e), None, 0) == 1
+    # tcgen05 path without a workspace
+    assert L.apnn_gemm_ex(None, 3, 1, 2, p, p, p, 128, 256, 128, None, None, 0) == 4
+    assert L.apnn_gemm_workspace_bytes(3, 1, 2, 128, 256, 128) >= (128 + 256) * 128
+    assert L.apnn_gemm_workspace_bytes(2, 1, 2, 128, 256, 128) == 0
+    # conv rules
+    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 96, 64, 3, 1, None) == 3
+    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 128, 64, 5, 1, None) == 2
+    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 128, 64, 3, 3, None) == 2
+    e = _cabi.Epilogue(out_mode=1, out_bits=2, pool=1)
+    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 7, 8, 128, 64, 3, 1, ctypes.byref(e)) == 2
+    # packers
+    assert L.apnn_bit_compress(None, p, p, 0, 3, 2) == 1
+    assert L.apnn_quantize_pack(None, p, p, 4, 3, 9) == 1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_cabi, "_lib", None)
+    monkeypatch.setattr(_cabi, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError):
+        _cabi.lib()

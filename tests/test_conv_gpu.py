@@ -1,0 +1,119 @@
+"""GPU parity of the implicit-GEMM convolution against the CPU oracle, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_host_loops.npz"))
+
+
+@pytest.mark.parametrize("wb,xb", [(1, 2), (2, 2), (1, 4)])
+def test_reference_inputs(cuda_device, wb, xb):
+    """The reference's conv operands (random halo ring included) on 8x8x128 -> 64 against the
+    committed outputs of its compute_ref / compute_ref_pack / compute_ref_pack_pool."""
+    import apnn_tc_b200 as ap
+    X, Wt = oracle.fill_conv(8, 8, 128, 64, xb, wb)
+    key = f"conv_w{wb}a{xb}_8x8x128x64"
+    acc = to_host(ap.apconv(to_dev(Wt), to_dev(X)), np.int32)
+    assert np.array_equal(acc, GOLD[key])
+    pk = to_host(ap.apconv(to_dev(Wt), to_dev(X), epilogue=ap.make_epilogue("lowbits", 2)))
+    assert np.array_equal(pk, GOLD[key + "_pack"])
+    pl = to_host(ap.apconv(to_dev(Wt), to_dev(X), epilogue=ap.make_epilogue("lowbits", 2, pool="avg")))
+    assert np.array_equal(pl, GOLD[key + "_pool"])
+
+
+def test_reference_named_wrappers(cuda_device):
+    import apnn_tc_b200 as ap
+    X, Wt = oracle.fill_conv(8, 8, 128, 64, 2, 1)
+    # reference shapes: X[xb][H+2][W+2][CIN/32], W[wb][COUT][9*CIN/32]
+    out = ap.APConv_w1a2_pack(to_dev(Wt.reshape(1, 64, -1)), to_dev(X[:, 0]))
+    assert np.array_equal(to_host(out), GOLD["conv_w1a2_8x8x128x64_pack"])
+    out = ap.APConv_w1a2_pack_pool(to_dev(Wt.reshape(1, 64, -1)), to_dev(X[:, 0]))
+    assert np.array_equal(to_host(out), GOLD["conv_w1a2_8x8x128x64_pool"])
+
+
+def make_conv(rng, B, H, Wd, CIN, COUT, R, wb, xb):
+    p = (R - 1) // 2
+    xl = rng.integers(0, 1 << xb, size=(B, H + 2 * p, Wd + 2 * p, CIN), dtype=np.uint32)
+    if p:
+        xl[:, 0] = xl[:, -1] = 0
+        xl[:, :, 0] = xl[:, :, -1] = 0
+    wl = rng.integers(0, 1 << wb, size=(COUT, R, R, CIN), dtype=np.uint32)
+    return oracle.pack_levels(xl, xb), oracle.pack_levels(wl, wb)
+
+
+@pytest.mark.parametrize("wb,xb", [(1, 2), (1, 4), (2, 2), (1, 3)])
+@pytest.mark.parametrize("C", [128, 256, 384, 512, 1024])
+def test_config3_batch8_16x16(cuda_device, wb, xb, C):
+    """Batch 8, 16x16, C=O, 3x3, stride 1, pad 1, BN thresholds -> 2-bit packed output,
+    with +-1 weights for the 1-bit filters."""
+    import apnn_tc_b200 as ap
+    if C > 512 and (wb, xb) != (1, 2):
+        pytest.skip("largest size checked on w1a2 only to bound oracle time")
+    rng = np.random.default_rng(0xA9117C + 3)
+    X, Wt = make_conv(rng, 8, 16, 16, C, C, 3, wb, xb)
+    acc = oracle.conv_popc(Wt, X, threads=8)
+    got = to_host(ap.apconv(to_dev(Wt), to_dev(X)), np.int32)
+    assert np.array_equal(got, acc)
+    signed = "w" if wb == 1 else "none"
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, 3), 0) if wb == 1 else acc
+    scale = rng.uniform(0.5, 1.5, C).astype(np.float32)
+    bias = rng.uniform(-1, 1, C).astype(np.float32)
+    T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, 2)
+    epi = ap.make_epilogue("thresholds", 2, signed=signed, thresholds=to_dev(T))
+    pk = to_host(ap.apconv(to_dev(Wt), to_dev(X), epilogue=epi))
+    assert np.array_equal(pk, oracle.requant_pack(v, 2, 2, T))
+
+
+@pytest.mark.parametrize("R,stride", [(3, 1), (3, 2), (1, 1), (1, 2)])
+@pytest.mark.parametrize("pool", ["none", "avg", "max"])
+def test_filters_strides_pools(cuda_device, R, stride, pool):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(R * 10 + stride)
+    B, H, Wd, CIN, COUT = 3, 12, 20, 256, 96
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, R, 1, 2)
+    acc = oracle.conv_popc(Wt, X, stride=stride, threads=4)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R, stride), 0)
+    if pool != "none":
+        v = oracle.pool2x2(v, 1 if pool == "avg" else 2)
+    out = ap.apconv(to_dev(Wt), to_dev(X), stride=stride, epilogue=ap.make_epilogue("int32", signed="w", pool=pool))
+    assert np.array_equal(to_host(out, np.int32), v)
+    T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
+    out = ap.apconv(to_dev(Wt), to_dev(X), stride=stride,
+                    epilogue=ap.make_epilogue("thresholds", 2, signed="w", pool=pool, thresholds=to_dev(T)))
+    assert np.array_equal(to_host(out), oracle.requant_pack(v, 2, 2, T))
+
+
+def test_output_halo_chains_into_next_conv(cuda_device):
+    """A conv that writes its packed output inside a zero ring feeds the next conv directly."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(41)
+    B, H, Wd, C = 2, 8, 8, 128
+    X, W1 = make_conv(rng, B, H, Wd, C, C, 3, 1, 2)
+    _, W2 = make_conv(rng, B, H, Wd, C, 64, 3, 1, 2)
+    acc1 = oracle.conv_popc(W1, X)
+    l1 = oracle.levels(acc1, 2, 1)
+    mid = ap.apconv(to_dev(W1), to_dev(X), epilogue=ap.make_epilogue("lowbits", 2, out_halo=1))
+    assert mid.shape == (2, B, H + 2, Wd + 2, C // 32)
+    padded = np.zeros((B, H + 2, Wd + 2, C), dtype=np.uint32)
+    padded[:, 1:-1, 1:-1] = l1
+    assert np.array_equal(to_host(mid), oracle.pack_levels(padded, 2))
+    acc2 = to_host(ap.apconv(to_dev(W2), mid), np.int32)
+    assert np.array_equal(acc2, oracle.conv_popc(W2, oracle.pack_levels(padded, 2)))
+
+
+def test_conv_host_front_end(cuda_device):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(43)
+    X, Wt = make_conv(rng, 2, 8, 8, 128, 64, 3, 1, 2)
+    out = np.zeros((2, 2, 8, 8, 2), dtype=np.uint32)
+    h = ap.HostHandle(0)
+    h.conv2d(Wt, X, out, 1, 2, 2, 8, 8, 128, 64, epilogue=ap.make_epilogue("lowbits", 2))
+    h.close()
+    assert np.array_equal(out, oracle.requant_pack(oracle.conv_popc(Wt, X), 2, 1))

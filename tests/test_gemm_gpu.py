@@ -1,0 +1,260 @@
+"""GPU parity of the GEMM path against the CPU oracle, through the C ABI.  Bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_host_loops.npz"))
+PAIRS = [(1, 2), (1, 3), (1, 4), (2, 2)]
+
+
+def run_gemm(W, X, **kw):
+    import apnn_tc_b200 as ap
+    out = ap.apmm(to_dev(W), to_dev(X), **kw)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("algo", ["imma", "bmma"])
+@pytest.mark.parametrize("wb,xb", PAIRS)
+def test_reference_inputs_small(cuda_device, wb, xb, algo):
+    """The reference's own operands (default-seed rand stream), M=64, N=K=128/256, against
+    the committed outputs of the reference's compute_ref."""
+    for n in (128, 256):
+        W, X = oracle.fill_gemm(64, n, n, wb, xb)
+        D = to_host(run_gemm(W, X, algo=algo), np.int32)
+        assert np.array_equal(D, GOLD[f"gemm_w{wb}a{xb}_64x{n}x{n}"])
+
+
+@pytest.mark.parametrize("algo", ["imma", "bmma"])
+def test_config1_w1a2_64x1024x1024(cuda_device, algo):
+    W, X = oracle.fill_gemm(64, 1024, 1024, 1, 2)
+    D = to_host(run_gemm(W, X, algo=algo), np.int32)
+    assert int(D.astype(np.int64).sum()) == 49072252 and int(D[0, 0]) == 722
+    assert np.array_equal(D, oracle.gemm_popc(W, X, threads=4))
+
+
+@pytest.mark.parametrize("wb,xb", PAIRS + [(2, 1), (4, 1), (1, 1)])
+def test_m64_sweep(cuda_device, wb, xb):
+    """M=64, N=K in 128..1024 (the reference's sweep), value-level seeded operands."""
+    rng = np.random.default_rng(0xA9117C + 2)
+    for n in range(128, 1025, 128):
+        W, _ = oracle.value_planes(rng, 64, n, wb)
+        X, _ = oracle.value_planes(rng, n, n, xb)
+        D = to_host(run_gemm(W, X, algo="imma"), np.int32)
+        assert np.array_equal(D, oracle.gemm_popc(W, X, threads=4)), (wb, xb, n)
+
+
+@pytest.mark.parametrize("algo", ["imma", "bmma"])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 128), (5, 3, 128), (64, 40, 384), (130, 257, 640), (300, 520, 1152),
+                                   (128, 128, 8192)])
+def test_ragged_shapes(cuda_device, M, N, K, algo):
+    rng = np.random.default_rng(M * 1000 + N)
+    W, wl = oracle.value_planes(rng, M, K, 1)
+    X, xl = oracle.value_planes(rng, N, K, 2)
+    D = to_host(run_gemm(W, X, algo=algo), np.int32)
+    assert np.array_equal(D, wl.astype(np.int64) @ xl.astype(np.int64).T)
+
+
+def test_big_tile_all_pairs(cuda_device):
+    """Shapes large enough to select the 128x128 tile class."""
+    rng = np.random.default_rng(99)
+    for wb, xb in PAIRS + [(2, 1), (3, 1), (4, 1), (1, 1)]:
+        W, wl = oracle.value_planes(rng, 1100, 512, wb)
+        X, xl = oracle.value_planes(rng, 1300, 512, xb)
+        D = to_host(run_gemm(W, X, algo="imma"), np.int32)
+        assert np.array_equal(D, wl.astype(np.int64) @ xl.astype(np.int64).T), (wb, xb)
+
+
+def test_extreme_values(cuda_device):
+    """All-ones operands (the reference's known-answer fill): D = (2^w-1)(2^x-1) K."""
+    for wb, xb in PAIRS:
+        K = 1024
+        W = np.full((wb, 64, K // 32), 0xFFFFFFFF, dtype=np.uint32)
+        X = np.full((xb, 96, K // 32), 0xFFFFFFFF, dtype=np.uint32)
+        D = to_host(run_gemm(W, X, algo="imma"), np.int32)
+        assert (D == ((1 << wb) - 1) * ((1 << xb) - 1) * K).all()
+        D0 = to_host(run_gemm(np.zeros_like(W), X, algo="imma"), np.int32)
+        assert not D0.any()
+
+
+@pytest.mark.parametrize("wb,xb", [(1, 2), (2, 2)])
+def test_lowbit_pack_against_reference_golden(cuda_device, wb, xb):
+    import apnn_tc_b200 as ap
+    W, X = oracle.fill_gemm(64, 128, 128, wb, xb)
+    fn = ap.apmm_w1a2_decompose if wb == 1 else ap.apmm_w2a2_decompose
+    P = to_host(fn(to_dev(W), to_dev(X)))
+    assert np.array_equal(P, GOLD[f"gemm_pack_w{wb}a{xb}_64x128x128"])
+
+
+@pytest.mark.parametrize("algo", ["imma", "bmma"])
+@pytest.mark.parametrize("signed", ["none", "w", "x"])
+@pytest.mark.parametrize("mode", ["int32", "lowbits", "thresholds"])
+def test_fused_epilogues(cuda_device, mode, signed, algo):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(17)
+    M, N, K = 200, 352, 768
+    wb, xb = (1, 2) if signed != "x" else (2, 1)
+    W, wl = oracle.value_planes(rng, M, K, wb)
+    X, xl = oracle.value_planes(rng, N, K, xb)
+    acc = oracle.gemm_popc(W, X, threads=4)
+    if signed == "w":
+        v = oracle.signed_correct(acc, oracle.row_sums(X), 1)
+        assert np.array_equal(v, (2 * wl.astype(np.int64) - 1) @ xl.astype(np.int64).T)
+    elif signed == "x":
+        v = oracle.signed_correct(acc, oracle.row_sums(W), 0)
+    else:
+        v = acc
+    T = None
+    if mode == "thresholds":
+        scale = rng.uniform(0.5, 1.5, N).astype(np.float32)
+        bias = rng.uniform(-1, 1, N).astype(np.float32)
+        T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, 2)
+    epi = ap.make_epilogue(mode, 2 if mode != "int32" else 0, signed=signed,
+                           thresholds=to_dev(T) if T is not None else None)
+    out = ap.apmm(to_dev(W), to_dev(X), epilogue=epi, algo=algo)
+    if mode == "int32":
+        assert np.array_equal(to_host(out, np.int32), v)
+    else:
+        want = oracle.requant_pack(v, 2, 1 if mode == "lowbits" else 2, T)
+        assert np.array_equal(to_host(out), want)
+        if mode == "thresholds":
+            assert len(np.unique(oracle.levels(v, 2, 2, T))) == 4  # all four levels occur
+
+
+def test_three_bit_requant(cuda_device):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(23)
+    W, _ = oracle.value_planes(rng, 64, 256, 1)
+    X, _ = oracle.value_planes(rng, 128, 256, 3)
+    acc = oracle.gemm_popc(W, X)
+    out = ap.apmm(to_dev(W), to_dev(X), epilogue=ap.make_epilogue("lowbits", 3))
+    assert np.array_equal(to_host(out), oracle.requant_pack(acc, 3, 1))
+
+
+def test_host_buffer_front_end(cuda_device):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(31)
+    M, N, K = 64, 1024, 1024
+    W, _ = oracle.value_planes(rng, M, K, 1)
+    X, _ = oracle.value_planes(rng, N, K, 2)
+    h = ap.HostHandle(0)
+    D = np.zeros((M, N), dtype=np.int32)
+    h.gemm(W, X, D, 1, 2, M, N, K, algo="imma")
+    assert np.array_equal(D, oracle.gemm_popc(W, X, threads=4))
+    P = np.zeros((2, M, N // 32), dtype=np.uint32)
+    h.gemm(W, X, P, 1, 2, M, N, K, algo="imma", epilogue=ap.make_epilogue("lowbits", 2))
+    assert np.array_equal(P, oracle.requant_pack(D, 2, 1))
+    h.close()
+
+
+def test_errors_raise(cuda_device):
+    import apnn_tc_b200 as ap
+    W = torch.zeros((1, 64, 3), dtype=torch.int32, device="cuda")  # K = 96
+    X = torch.zeros((2, 64, 3), dtype=torch.int32, device="cuda")
+    with pytest.raises(ap.ApnnError):
+        ap.apmm(W, X)
+    with pytest.raises(ValueError):
+        ap.apmm(W.cpu(), X)
+
+
+# ------------------------------------------------------------------ tcgen05 kind::i8 path
+def run_tc5(W, X, epilogue=None):
+    import apnn_tc_b200 as ap
+    wb, M, kw = W.shape
+    xb, N, _ = X.shape
+    ws = torch.empty(ap.gemm_workspace_bytes(M, N, kw * 32), dtype=torch.uint8, device="cuda")
+    out = ap.apmm(to_dev(W), to_dev(X), algo="tcgen05", workspace=ws, epilogue=epilogue)
+    ap.gemm_check(ws, M, N, kw * 32)  # synchronises; raises if a bounded wait expired
+    return out
+
+
+@pytest.mark.parametrize("wb,xb", PAIRS + [(2, 1), (4, 1)])
+def test_tcgen05_all_pairs(cuda_device, wb, xb):
+    rng = np.random.default_rng(wb * 10 + xb)
+    W, wl = oracle.value_planes(rng, 384, 1024, wb)
+    X, xl = oracle.value_planes(rng, 768, 1024, xb)
+    D = to_host(run_tc5(W, X), np.int32)
+    assert np.array_equal(D, wl.astype(np.int64) @ xl.astype(np.int64).T)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 128), (64, 1024, 1024), (130, 257, 640), (1000, 1000, 2048), (128, 256, 8192)])
+def test_tcgen05_ragged_shapes(cuda_device, M, N, K):
+    rng = np.random.default_rng(M + N + K)
+    W, wl = oracle.value_planes(rng, M, K, 1)
+    X, xl = oracle.value_planes(rng, N, K, 2)
+    D = to_host(run_tc5(W, X), np.int32)
+    assert np.array_equal(D, wl.astype(np.int64) @ xl.astype(np.int64).T)
+
+
+def test_tcgen05_many_tiles_per_cta(cuda_device):
+    """More tiles than SMs: every CTA walks several tiles and both TMEM accumulators."""
+    rng = np.random.default_rng(77)
+    W, _ = oracle.value_planes(rng, 2560, 512, 1)
+    X, _ = oracle.value_planes(rng, 4096 + 96, 512, 2)
+    D = to_host(run_tc5(W, X), np.int32)
+    assert np.array_equal(D, oracle.gemm_popc(W, X, threads=8))
+
+
+def test_tcgen05_reference_inputs_config1(cuda_device):
+    W, X = oracle.fill_gemm(64, 1024, 1024, 1, 2)
+    D = to_host(run_tc5(W, X), np.int32)
+    assert int(D.astype(np.int64).sum()) == 49072252 and int(D[0, 0]) == 722
+
+
+@pytest.mark.parametrize("signed", ["none", "w", "x"])
+@pytest.mark.parametrize("mode", ["int32", "lowbits", "thresholds"])
+def test_tcgen05_fused_epilogues(cuda_device, mode, signed):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(19)
+    M, N, K = 200, 352, 768
+    wb, xb = (1, 2) if signed != "x" else (2, 1)
+    W, _ = oracle.value_planes(rng, M, K, wb)
+    X, _ = oracle.value_planes(rng, N, K, xb)
+    acc = oracle.gemm_popc(W, X, threads=4)
+    v = acc
+    if signed == "w":
+        v = oracle.signed_correct(acc, oracle.row_sums(X), 1)
+    elif signed == "x":
+        v = oracle.signed_correct(acc, oracle.row_sums(W), 0)
+    T = None
+    if mode == "thresholds":
+        scale = rng.uniform(0.5, 1.5, N).astype(np.float32)
+        bias = rng.uniform(-1, 1, N).astype(np.float32)
+        T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, 2)
+    epi = ap.make_epilogue(mode, 2 if mode != "int32" else 0, signed=signed,
+                           thresholds=to_dev(T) if T is not None else None)
+    out = run_tc5(W, X, epi)
+    if mode == "int32":
+        assert np.array_equal(to_host(out, np.int32), v)
+    else:
+        assert np.array_equal(to_host(out), oracle.requant_pack(v, 2, 1 if mode == "lowbits" else 2, T))
+
+
+def test_large_shape_properties(cuda_device):
+    """M=N=K=8192 (the compute-bound configuration): the three contraction paths agree
+    bit for bit, sampled rows equal the oracle, and the result is linear in the planes
+    (D(w1a2) = D(plane0) + 2 D(plane1))."""
+    import apnn_tc_b200 as ap
+    M = N = K = 8192
+    g = torch.Generator(device="cuda").manual_seed(5)
+    W = torch.randint(-2**31, 2**31 - 1, (1, M, K // 32), dtype=torch.int32, device="cuda", generator=g)
+    X = torch.randint(-2**31, 2**31 - 1, (2, N, K // 32), dtype=torch.int32, device="cuda", generator=g)
+    ws = torch.empty(ap.gemm_workspace_bytes(M, N, K), dtype=torch.uint8, device="cuda")
+    D = ap.apmm(W, X, algo="tcgen05", workspace=ws)
+    ap.gemm_check(ws, M, N, K)
+    assert torch.equal(D, ap.apmm(W, X, algo="imma"))
+    rows = np.array([0, 1, 127, 128, 4095, 4096, 8191])
+    want = oracle.gemm_popc(np.ascontiguousarray(to_host(W)[:, rows]), to_host(X), threads=8)
+    assert np.array_equal(to_host(D[torch.from_numpy(rows).cuda()], np.int32), want)
+    D0 = ap.apmm(W, X[0:1].contiguous(), algo="tcgen05", workspace=ws)
+    D1 = ap.apmm(W, X[1:2].contiguous(), algo="tcgen05", workspace=ws)
+    assert torch.equal(D, D0 + 2 * D1)
+    del D0, D1
+    assert torch.equal(D, ap.apmm(W, X, algo="bmma"))
