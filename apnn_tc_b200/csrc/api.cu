@@ -86,6 +86,29 @@ apnn_status apnn_gemm_check(void* stream, const void* workspace, int M, int N, i
   return flag == 0 ? APNN_OK : APNN_ERR_TIMEOUT;
 }
 
+apnn_status apnn_expand_planes(void* stream, const void* planes, void* out_i8, long rows, int K, int bits,
+                               int is_signed) {
+  if (!planes || !out_i8 || rows <= 0 || K <= 0 || bits < 1 || bits > 8) return APNN_ERR_INVALID_ARG;
+  if (is_signed && bits != 1) return APNN_ERR_UNSUPPORTED;
+  if (K % 128 != 0 || !aligned16(planes) || !aligned16(out_i8)) return APNN_ERR_ALIGNMENT;
+  return tc5_expand(reinterpret_cast<cudaStream_t>(stream), (const uint32_t*)planes, (uint8_t*)out_i8, rows, K, bits,
+                    is_signed != 0);
+}
+
+apnn_status apnn_gemm_i8(void* stream, const void* W8, const void* X8, void* D, int M, int N, int K, int w_signed,
+                         int x_signed, const apnn_epilogue* epi, int* status_flag) {
+  if (!W8 || !X8 || !D || !status_flag || M <= 0 || N <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
+  if (K % 128 != 0 || !aligned16(W8) || !aligned16(X8) || !aligned16(D)) return APNN_ERR_ALIGNMENT;
+  if (epi) {
+    // the sign lives in the expanded bytes; the epilogue must not correct again
+    if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;
+    apnn_status st = check_epilogue(epi, N, false, 1, 1);
+    if (st != APNN_OK) return st;
+  }
+  return tc5_gemm_i8(reinterpret_cast<cudaStream_t>(stream), (const uint8_t*)W8, (const uint8_t*)X8, D, M, N, K,
+                     w_signed != 0, x_signed != 0, epi, status_flag);
+}
+
 apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const void* W, const void* X, void* D, int M,
                          int N, int K, const apnn_epilogue* epi, void* workspace, size_t workspace_bytes) {
   if (!W || !X || !D) return APNN_ERR_INVALID_ARG;

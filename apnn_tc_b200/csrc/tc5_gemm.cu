@@ -380,32 +380,26 @@ bool tc5_worthwhile(int M, int N, int K) {
   return tiles >= 64 && K >= 1024;
 }
 
-apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, const uint32_t* X, void* D, int M,
-                     int N, int K, const apnn_epilogue* epi, void* workspace) {
-  uint8_t* wa = reinterpret_cast<uint8_t*>(workspace);
-  uint8_t* wb = wa + align_up((size_t)M * K, 256);
-  int* err = reinterpret_cast<int*>(wb + align_up((size_t)N * K, 256));
-  const int sign = epi ? epi->signed_operand : APNN_SIGN_NONE;
-
-  cudaError_t e = cudaMemsetAsync(err, 0, sizeof(int), s);
-  if (e != cudaSuccess) return cuda_fail(e, "tc5 flag reset");
+apnn_status tc5_expand(cudaStream_t s, const uint32_t* planes, uint8_t* out, long long rows, int K, int bits,
+                       bool is_signed) {
   const int sms = device_sm_count();
-  {
-    long long total = (long long)M * (K / 32);
-    int blocks = (int)((total + 255) / 256 < (long long)sms * 16 ? (total + 255) / 256 : (long long)sms * 16);
-    expand_planes_kernel<<<blocks, 256, 0, s>>>(W, wa, M, K / 32, wbits, sign == APNN_SIGN_W);
-    total = (long long)N * (K / 32);
-    blocks = (int)((total + 255) / 256 < (long long)sms * 16 ? (total + 255) / 256 : (long long)sms * 16);
-    expand_planes_kernel<<<blocks, 256, 0, s>>>(X, wb, N, K / 32, xbits, sign == APNN_SIGN_X);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "expand_planes launch");
-  }
+  long long total = rows * (K / 32);
+  long long want = (total + 255) / 256, cap = (long long)sms * 16;
+  int blocks = (int)(want < cap ? want : cap);
+  expand_planes_kernel<<<blocks, 256, 0, s>>>(planes, out, rows, K / 32, bits, is_signed ? 1 : 0);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "expand_planes launch");
+  return APNN_OK;
+}
 
+apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
+                        bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
+  cudaError_t e = cudaMemsetAsync(status_flag, 0, sizeof(int), s);
+  if (e != cudaSuccess) return cuda_fail(e, "tc5 flag reset");
   CUtensorMap map_a, map_b;
-  if (!make_operand_map(&map_a, wa, M, K, BM) || !make_operand_map(&map_b, wb, N, K, BN)) {
+  if (!make_operand_map(&map_a, A8, M, K, BM) || !make_operand_map(&map_b, B8, N, K, BN)) {
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   }
-
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -414,7 +408,6 @@ apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, co
     if (e != cudaSuccess) return cuda_fail(e, "tc5 smem attribute");
     if (dev < 16) attr_set[dev] = true;
   }
-
   Tc5Params p;
   p.out = D;
   p.thresholds = epi ? epi->thresholds : nullptr;
@@ -426,17 +419,30 @@ apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, co
   p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
   p.out_bits = epi ? epi->out_bits : 0;
   p.out_plane_words = (long long)M * (N / 32);
-  p.error_flag = err;
+  p.error_flag = status_flag;
   // instruction descriptor: D = s32, A/B = u8 or s8, both K-major, N = 256, M = 128
-  const uint32_t afmt = sign == APNN_SIGN_W ? 1u : 0u, bfmt = sign == APNN_SIGN_X ? 1u : 0u;
+  const uint32_t afmt = a_signed ? 1u : 0u, bfmt = b_signed ? 1u : 0u;
   p.idesc = (2u << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
   long long tiles = (long long)p.tiles_m * p.tiles_n;
+  const int sms = device_sm_count();
   int grid = (int)(tiles < sms ? tiles : sms);
   tc5_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm launch");
   return APNN_OK;
+}
+
+apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, const uint32_t* X, void* D, int M,
+                     int N, int K, const apnn_epilogue* epi, void* workspace) {
+  uint8_t* wa = reinterpret_cast<uint8_t*>(workspace);
+  uint8_t* wb = wa + align_up((size_t)M * K, 256);
+  int* err = reinterpret_cast<int*>(wb + align_up((size_t)N * K, 256));
+  const int sign = epi ? epi->signed_operand : APNN_SIGN_NONE;
+  apnn_status st = tc5_expand(s, W, wa, M, K, wbits, sign == APNN_SIGN_W);
+  if (st != APNN_OK) return st;
+  st = tc5_expand(s, X, wb, N, K, xbits, sign == APNN_SIGN_X);
+  if (st != APNN_OK) return st;
+  return tc5_gemm_i8(s, wa, wb, D, M, N, K, sign == APNN_SIGN_W, sign == APNN_SIGN_X, epi, err);
 }
 
 // Reads back the flag a bounded wait raises; 0 means the last tc5_gemm on this workspace

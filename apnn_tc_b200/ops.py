@@ -66,6 +66,39 @@ def gemm_check(workspace: torch.Tensor, M: int, N: int, K: int) -> None:
     _cabi.check(_cabi.lib().apnn_gemm_check(_stream_ptr(), workspace.data_ptr(), M, N, K), "apnn_gemm_check")
 
 
+def expand_planes(planes: torch.Tensor, signed: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """planes [bits, rows, K/32] -> int8 [rows, K] (one byte per element) for ``gemm_i8``."""
+    planes = _dev_words(planes, "planes")
+    bits, rows, kw = planes.shape
+    if out is None:
+        out = torch.empty((rows, kw * 32), dtype=torch.uint8, device=planes.device)
+    st = _cabi.lib().apnn_expand_planes(_stream_ptr(), planes.data_ptr(), out.data_ptr(), rows, kw * 32, bits,
+                                        1 if signed else 0)
+    _cabi.check(st, "apnn_expand_planes")
+    return out
+
+
+def gemm_i8(W8: torch.Tensor, X8: torch.Tensor, out: Optional[torch.Tensor] = None, *, w_signed: bool = False,
+            x_signed: bool = False, epilogue: Optional[Epilogue] = None,
+            status_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """tcgen05 kind::i8 GEMM over operands produced by ``expand_planes``."""
+    M, K = W8.shape
+    N, K2 = X8.shape
+    if K != K2:
+        raise ValueError("operands disagree on K")
+    packed = epilogue is not None and epilogue.out_mode != 0
+    if out is None:
+        shape = (epilogue.out_bits, M, N // 32) if packed else (M, N)
+        out = torch.empty(shape, dtype=torch.int32, device=W8.device)
+    if status_flag is None:
+        status_flag = torch.empty(1, dtype=torch.int32, device=W8.device)
+    st = _cabi.lib().apnn_gemm_i8(_stream_ptr(), W8.data_ptr(), X8.data_ptr(), out.data_ptr(), M, N, K,
+                                  1 if w_signed else 0, 1 if x_signed else 0,
+                                  ctypes.byref(epilogue) if epilogue is not None else None, status_flag.data_ptr())
+    _cabi.check(st, "apnn_gemm_i8")
+    return out
+
+
 def apmm(W: torch.Tensor, X: torch.Tensor, out: Optional[torch.Tensor] = None, *, epilogue: Optional[Epilogue] = None,
          algo: str = "auto", workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """D[m][n] = sum_wb sum_xb 2^(wb+xb) popcount(W[wb][m] & X[xb][n]).

@@ -106,6 +106,21 @@ size_t apnn_gemm_workspace_bytes(int algo, int wbits, int xbits, int M, int N, i
  * otherwise.  No counterpart in the reference (its kernels have no waits). */
 apnn_status apnn_gemm_check(void *stream, const void *workspace, int M, int N, int K);
 
+/* The two stages of APNN_ALGO_TCGEN05 as entry points of their own, so that a static
+ * operand (the weights of a layer) is expanded once and reused.  No counterpart in the
+ * reference, whose kernels read the planes directly.
+ * apnn_expand_planes: planes[bits][rows][K/32] -> out_i8[rows][K], one byte per element,
+ *   value = sum_p bit_p << p, or -1/+1 for a 1-bit operand with is_signed != 0.  The byte
+ *   order inside each group of 32 k is a fixed permutation shared by both operands.
+ * apnn_gemm_i8: D = W8 * X8^T over operands produced by apnn_expand_planes, same epilogue
+ *   (signed_operand must be APNN_SIGN_NONE: the sign is in the bytes; pass w_signed /
+ *   x_signed to say which operand holds -1/+1).  status_flag: 4 bytes of device memory,
+ *   written 0 at launch and non-zero if a bounded wait expires. */
+apnn_status apnn_expand_planes(void *stream, const void *planes, void *out_i8, long rows, int K,
+                               int bits, int is_signed);
+apnn_status apnn_gemm_i8(void *stream, const void *W8, const void *X8, void *D, int M, int N, int K,
+                         int w_signed, int x_signed, const apnn_epilogue *epi, int *status_flag);
+
 /* ---- convolution ---------------------------------------------------------------
  * Implicit-GEMM RxR convolution, R in {1, 3}, stride in {1, 2}, symmetric padding
  * carried by the input.  With B = 1, R = 3, stride = 1:
@@ -132,6 +147,16 @@ apnn_status apnn_bit_compress(void *stream, const uint32_t *levels, uint32_t *pl
                               int C, int bits);
 apnn_status apnn_quantize_pack(void *stream, const float *values, uint32_t *planes, long rows,
                                int C, int bits);
+
+/* ---- measurement aid ------------------------------------------------------------
+ * Launches an operand-resident issue loop of one contraction instruction on every SM and
+ * returns the operations one launch performs; the caller times the launch with events to
+ * get the device's peak for that path (the roofline denominator).  kind 0: tcgen05.mma
+ * kind::i8 (128x256x32, operands fixed in shared memory), 1: mma.sync m16n8k32 u8,
+ * 2: mma.sync m16n8k256 b1 and.popc (bit operations).  scratch_flag: 4 bytes of device
+ * memory.  No counterpart in the reference. */
+apnn_status apnn_probe_peak(void *stream, int kind, int iters, int *scratch_flag,
+                            double *ops_per_launch);
 
 /* ---- host-buffer front end -----------------------------------------------------
  * For callers that hold operands in host memory (the reference's main() programs:
