@@ -21,7 +21,7 @@ ALGOS = {"auto": ALGO_AUTO, "bmma": ALGO_BMMA, "imma": ALGO_IMMA, "tcgen05": ALG
 # every symbol the header declares; the CPU test-suite checks the library exports them all
 EXPORTS = (
     "apnn_status_string", "apnn_last_cuda_error", "apnn_version", "apnn_gemm", "apnn_gemm_ex",
-    "apnn_gemm_workspace_bytes", "apnn_gemm_check", "apnn_expand_planes", "apnn_gemm_i8", "apnn_conv2d", "apnn_bit_compress", "apnn_quantize_pack", "apnn_create",
+    "apnn_gemm_workspace_bytes", "apnn_gemm_check", "apnn_expand_planes", "apnn_gemm_i8", "apnn_gemm_static_scratch", "apnn_conv2d", "apnn_bit_compress", "apnn_quantize_pack", "apnn_create",
     "apnn_destroy", "apnn_gemm_host", "apnn_conv2d_host", "apnn_probe_peak",
 )
 
@@ -68,6 +68,7 @@ def lib() -> ctypes.CDLL:
     L.apnn_gemm_check.argtypes = [vp, vp, i, i, i]
     L.apnn_expand_planes.argtypes = [vp, vp, vp, lg, i, i, i]
     L.apnn_gemm_i8.argtypes = [vp, vp, vp, vp, i, i, i, i, i, ep, vp]
+    L.apnn_gemm_static_scratch.argtypes = [vp, i, i, vp, vp, vp, i, i, i, ep, vp]
     L.apnn_conv2d.argtypes = [vp, i, i, vp, vp, vp, i, i, i, i, i, i, i, ep]
     L.apnn_bit_compress.argtypes = [vp, vp, vp, lg, i, i]
     L.apnn_quantize_pack.argtypes = [vp, vp, vp, lg, i, i]

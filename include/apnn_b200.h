@@ -121,6 +121,27 @@ apnn_status apnn_expand_planes(void *stream, const void *planes, void *out_i8, l
 apnn_status apnn_gemm_i8(void *stream, const void *W8, const void *X8, void *D, int M, int N, int K,
                          int w_signed, int x_signed, const apnn_epilogue *epi, int *status_flag);
 
+/* A tcgen05 GEMM that allocates nothing and needs no workspace argument.  No counterpart
+ * in the reference.  It exists for callers that cannot cudaMalloc a workspace: code running
+ * inside a host application whose own memory pool already owns the device's memory, or a
+ * latency-critical loop that cannot afford the device-wide synchronisation of cudaMalloc /
+ * cudaFree and has no spare buffer to pass.  The int8 images of W and X are written to a
+ * fixed array inside the library image (APNN_STATIC_SCRATCH_BYTES of device memory on every
+ * GPU that loads the library, held until the process exits).
+ *   - Limit: align256(M*K) + align256(N*K) <= APNN_STATIC_SCRATCH_BYTES (e.g. 2048x2048x8192,
+ *     4096x4096x4096); anything larger returns APNN_ERR_WORKSPACE and launches nothing.
+ *   - All calls on a device share the one array: calls whose kernels may overlap on the GPU
+ *     race on it, so keep them on one stream or order them with events.  The array is not
+ *     cleared between calls and does not need to be; the status flag (4 bytes of caller
+ *     device memory, 0 = completed, non-zero = a bounded wait expired) is reset by each call.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) and caches it; make that first call outside stream capture.
+ * Arguments and results are those of apnn_gemm_ex (wbits, xbits in 1..4, same epilogue). */
+#define APNN_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+apnn_status apnn_gemm_static_scratch(void *stream, int wbits, int xbits, const void *W, const void *X,
+                                     void *D, int M, int N, int K, const apnn_epilogue *epi,
+                                     int *status_flag);
+
 /* ---- convolution ---------------------------------------------------------------
  * Implicit-GEMM RxR convolution, R in {1, 3}, stride in {1, 2}, symmetric padding
  * carried by the input.  With B = 1, R = 3, stride = 1:
