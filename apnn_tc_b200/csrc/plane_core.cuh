@@ -39,7 +39,7 @@ struct CoreCfg {
   static constexpr int A_SLOTS = A_ROWS / RPP;
   static constexpr int B_SLOTS = B_ROWS / RPP;
   static_assert(A_ROWS % RPP == 0 && B_ROWS % RPP == 0, "tile rows must divide over the copy passes");
-  static_assert(NT % 2 == 0, "B fragments are fetched two n-tiles at a time");
+  static_assert(NT % 4 == 0 && MT % 2 == 0, "fragments are fetched four 8-row matrices at a time");
 };
 
 // Spread bit (q + 8j) of every plane word into byte j: value = sum_p bit_p << p.
@@ -59,34 +59,36 @@ struct RowSrc {
   long long off;  // word offset of the row's first K word inside one plane
 };
 
-// Source row of tile-local A row r.
+// Source row of tile-local A row r.  Row, pixel and window counts fit 32 bits (the host
+// checks), so the index arithmetic uses 32-bit unsigned division; only the final word
+// offset is 64-bit.
 template <int BM>
 __device__ __forceinline__ RowSrc a_row_source(const CoreParams& p, int tile_m, int r) {
   RowSrc s;
   if (!p.is_conv) {
-    long long m = (long long)tile_m * BM + r;
-    s.valid = m < p.M;
-    s.off = m * p.a_row_words;
+    const unsigned m = (unsigned)tile_m * BM + r;
+    s.valid = m < (unsigned)p.M;
+    s.off = (long long)m * p.a_row_words;
     return s;
   }
-  int b, ho, wo;
+  unsigned b, ho, wo;
   if (p.pool == POOL_NONE) {
-    long long m = (long long)tile_m * BM + r;
-    s.valid = m < p.M;
-    wo = (int)(m % p.Wo);
-    long long t = m / p.Wo;
-    ho = (int)(t % p.Ho);
-    b = (int)(t / p.Ho);
+    const unsigned m = (unsigned)tile_m * BM + r;
+    s.valid = m < (unsigned)p.M;
+    const unsigned t = m / (unsigned)p.Wo;
+    wo = m - t * p.Wo;
+    b = t / (unsigned)p.Ho;
+    ho = t - b * p.Ho;
   } else {
     // rows r, r+8, r+16, r+24 of every 32-row group are the four pixels of one window
-    long long u = (long long)tile_m * (BM / 4) + (r >> 5) * 8 + (r & 7);
-    int quad = (r >> 3) & 3;
-    s.valid = u < p.M / 4;
-    int wh = p.Wo >> 1, hh = p.Ho >> 1;
-    int wp = (int)(u % wh);
-    long long t = u / wh;
-    int hp = (int)(t % hh);
-    b = (int)(t / hh);
+    const unsigned u = (unsigned)tile_m * (BM / 4) + (r >> 5) * 8 + (r & 7);
+    const unsigned quad = (r >> 3) & 3;
+    s.valid = u < (unsigned)p.M / 4;
+    const unsigned wh = p.Wo >> 1, hh = p.Ho >> 1;
+    const unsigned t = u / wh;
+    const unsigned wp = u - t * wh;
+    b = t / hh;
+    const unsigned hp = t - b * hh;
     ho = 2 * hp + (quad >> 1);
     wo = 2 * wp + (quad & 1);
   }
@@ -96,15 +98,15 @@ __device__ __forceinline__ RowSrc a_row_source(const CoreParams& p, int tile_m, 
 
 // Output row (in units of output rows of N channels) of logical row index idx, where
 // idx counts GEMM rows, conv pixels, or pooled windows.  Returns -1 when out of range.
-__device__ __forceinline__ long long out_row_of(const CoreParams& p, long long idx, long long limit) {
+__device__ __forceinline__ long long out_row_of(const CoreParams& p, unsigned idx, unsigned limit) {
   if (idx >= limit) return -1;
   if (!p.is_conv) return idx;
-  int w = (int)(idx % p.out_w);
-  long long t = idx / p.out_w;
-  int h = (int)(t % p.out_h);
-  long long b = t / p.out_h;
-  int hh = p.out_halo;
-  return (b * (p.out_h + 2 * hh) + h + hh) * (p.out_w + 2 * hh) + w + hh;
+  const unsigned t = idx / (unsigned)p.out_w;
+  const unsigned w = idx - t * p.out_w;
+  const unsigned b = t / (unsigned)p.out_h;
+  const unsigned h = t - b * p.out_h;
+  const int hh = p.out_halo;
+  return ((long long)b * (p.out_h + 2 * hh) + h + hh) * (p.out_w + 2 * hh) + w + hh;
 }
 
 template <class Cfg>
@@ -184,6 +186,12 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
   const uint32_t b_row_off = (uint32_t)((A_ROWS + warp_n * NT * 8 + (mi >> 1) * 8 + r8) * 64);
   const uint32_t b_chunk0 = (uint32_t)(((mi & 1) ^ sw) << 4);
 
+  // u8 path, one chunk at a time:
+  //   A matrices (m-tile i rows 0-7) (i rows 8-15) (i+1 rows 0-7) (i+1 rows 8-15)
+  //   B matrices (n-tile j) (j+1) (j+2) (j+3)
+  const uint32_t a1_row_off = (uint32_t)((warp_m * MT * 16 + mi * 8 + r8) * 64);
+  const uint32_t b1_row_off = (uint32_t)((A_ROWS + warp_n * NT * 8 + mi * 8 + r8) * 64);
+
   int acc[NACC][MT][NT][4];
 #pragma unroll
   for (int s = 0; s < NACC; s++)
@@ -219,39 +227,38 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
     }
     const uint32_t st = sbase + (ks % STAGES) * STAGE_BYTES;
 
-#pragma unroll
-    for (int sub = 0; sub < 2; sub++) {
-      uint32_t aw[ABITS][MT][4];
-      uint32_t bw[BBITS][NT][2];
-#pragma unroll
-      for (int pa = 0; pa < ABITS; pa++)
-#pragma unroll
-        for (int i = 0; i < MT; i++)
-          ldmatrix_x4(st + a_row_off + (pa * BM + i * 16) * 64 + (a_chunk0 ^ (sub << 5)), aw[pa][i][0], aw[pa][i][1],
-                      aw[pa][i][2], aw[pa][i][3]);
-#pragma unroll
-      for (int pb = 0; pb < BBITS; pb++)
-#pragma unroll
-        for (int j = 0; j < NT; j += 2)
-          ldmatrix_x4(st + b_row_off + (pb * BN + j * 8) * 64 + (b_chunk0 ^ (sub << 5)), bw[pb][j][0], bw[pb][j][1],
-                      bw[pb][j + 1][0], bw[pb][j + 1][1]);
-
-      if (p.sign == SIGN_B) {
+    if constexpr (KIND == KIND_B1) {
+      // two 128-bit chunks per m16n8k256 MMA
+#pragma unroll 1
+      for (int sub = 0; sub < 2; sub++) {
+        uint32_t aw[ABITS][MT][4];
+        uint32_t bw[BBITS][NT][2];
 #pragma unroll
         for (int pa = 0; pa < ABITS; pa++)
 #pragma unroll
-          for (int i = 0; i < MT; i++) {
-            sum_a[i][0] += (__popc(aw[pa][i][0]) + __popc(aw[pa][i][2])) << pa;
-            sum_a[i][1] += (__popc(aw[pa][i][1]) + __popc(aw[pa][i][3])) << pa;
-          }
-      } else if (p.sign == SIGN_A) {
+          for (int i = 0; i < MT; i++)
+            ldmatrix_x4(st + a_row_off + (pa * BM + i * 16) * 64 + (a_chunk0 ^ (sub << 5)), aw[pa][i][0],
+                        aw[pa][i][1], aw[pa][i][2], aw[pa][i][3]);
 #pragma unroll
         for (int pb = 0; pb < BBITS; pb++)
 #pragma unroll
-          for (int j = 0; j < NT; j++) sum_b[j] += (__popc(bw[pb][j][0]) + __popc(bw[pb][j][1])) << pb;
-      }
-
-      if constexpr (KIND == KIND_B1) {
+          for (int j = 0; j < NT; j += 2)
+            ldmatrix_x4(st + b_row_off + (pb * BN + j * 8) * 64 + (b_chunk0 ^ (sub << 5)), bw[pb][j][0],
+                        bw[pb][j][1], bw[pb][j + 1][0], bw[pb][j + 1][1]);
+        if (p.sign == SIGN_B) {
+#pragma unroll
+          for (int pa = 0; pa < ABITS; pa++)
+#pragma unroll
+            for (int i = 0; i < MT; i++) {
+              sum_a[i][0] += (__popc(aw[pa][i][0]) + __popc(aw[pa][i][2])) << pa;
+              sum_a[i][1] += (__popc(aw[pa][i][1]) + __popc(aw[pa][i][3])) << pa;
+            }
+        } else if (p.sign == SIGN_A) {
+#pragma unroll
+          for (int pb = 0; pb < BBITS; pb++)
+#pragma unroll
+            for (int j = 0; j < NT; j++) sum_b[j] += (__popc(bw[pb][j][0]) + __popc(bw[pb][j][1])) << pb;
+        }
 #pragma unroll
         for (int pa = 0; pa < ABITS; pa++)
 #pragma unroll
@@ -262,51 +269,82 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
               for (int j = 0; j < NT; j++)
                 mma_b1(acc[pa + pb][i][j], aw[pa][i][0], aw[pa][i][1], aw[pa][i][2], aw[pa][i][3], bw[pb][j][0],
                        bw[pb][j][1]);
-      } else {
+      }
+    } else {
+      // one 128-bit chunk per iteration: a compact body (four k32 steps) that stays in the
+      // instruction cache, executed four times per stage
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t aw[ABITS][MT][2];  // [plane][m-tile][rows g / g+8]: word t4 of the chunk
+        uint32_t bw[BBITS][NT];     // [plane][n-tile]: word t4 of row g
+        const uint32_t a_ch = (uint32_t)((c ^ sw) << 4);
 #pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
+        for (int pa = 0; pa < ABITS; pa++)
 #pragma unroll
-          for (int kk = 0; kk < 4; kk++) {
-            uint32_t ea[MT][4];
-            uint32_t eb[NT][2];
+          for (int i = 0; i < MT; i += 2)
+            ldmatrix_x4(st + a1_row_off + (pa * BM + i * 16) * 64 + a_ch, aw[pa][i][0], aw[pa][i][1],
+                        aw[pa][i + 1][0], aw[pa][i + 1][1]);
+#pragma unroll
+        for (int pb = 0; pb < BBITS; pb++)
+#pragma unroll
+          for (int j = 0; j < NT; j += 4)
+            ldmatrix_x4(st + b1_row_off + (pb * BN + j * 8) * 64 + a_ch, bw[pb][j], bw[pb][j + 1], bw[pb][j + 2],
+                        bw[pb][j + 3]);
+        if (p.sign == SIGN_B) {
+#pragma unroll
+          for (int pa = 0; pa < ABITS; pa++)
 #pragma unroll
             for (int i = 0; i < MT; i++) {
-              uint32_t lo[ABITS], hi[ABITS];
-#pragma unroll
-              for (int pa = 0; pa < ABITS; pa++) {
-                lo[pa] = aw[pa][i][cc * 2 + 0];
-                hi[pa] = aw[pa][i][cc * 2 + 1];
-              }
-              // kk is a compile-time constant after unrolling; dispatch the shift amounts
-              switch (kk) {
-                case 0: ea[i][0] = spread<ABITS, 0>(lo); ea[i][1] = spread<ABITS, 0>(hi);
-                        ea[i][2] = spread<ABITS, 1>(lo); ea[i][3] = spread<ABITS, 1>(hi); break;
-                case 1: ea[i][0] = spread<ABITS, 2>(lo); ea[i][1] = spread<ABITS, 2>(hi);
-                        ea[i][2] = spread<ABITS, 3>(lo); ea[i][3] = spread<ABITS, 3>(hi); break;
-                case 2: ea[i][0] = spread<ABITS, 4>(lo); ea[i][1] = spread<ABITS, 4>(hi);
-                        ea[i][2] = spread<ABITS, 5>(lo); ea[i][3] = spread<ABITS, 5>(hi); break;
-                default: ea[i][0] = spread<ABITS, 6>(lo); ea[i][1] = spread<ABITS, 6>(hi);
-                         ea[i][2] = spread<ABITS, 7>(lo); ea[i][3] = spread<ABITS, 7>(hi); break;
-              }
+              sum_a[i][0] += __popc(aw[pa][i][0]) << pa;
+              sum_a[i][1] += __popc(aw[pa][i][1]) << pa;
             }
+        } else if (p.sign == SIGN_A) {
 #pragma unroll
-            for (int j = 0; j < NT; j++) {
-              uint32_t wv[BBITS];
+          for (int pb = 0; pb < BBITS; pb++)
 #pragma unroll
-              for (int pb = 0; pb < BBITS; pb++) wv[pb] = bw[pb][j][cc];
-              switch (kk) {
-                case 0: eb[j][0] = spread<BBITS, 0>(wv); eb[j][1] = spread<BBITS, 1>(wv); break;
-                case 1: eb[j][0] = spread<BBITS, 2>(wv); eb[j][1] = spread<BBITS, 3>(wv); break;
-                case 2: eb[j][0] = spread<BBITS, 4>(wv); eb[j][1] = spread<BBITS, 5>(wv); break;
-                default: eb[j][0] = spread<BBITS, 6>(wv); eb[j][1] = spread<BBITS, 7>(wv); break;
-              }
+            for (int j = 0; j < NT; j++) sum_b[j] += __popc(bw[pb][j]) << pb;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) {
+          uint32_t ea[MT][4];
+          uint32_t eb[NT][2];
+#pragma unroll
+          for (int i = 0; i < MT; i++) {
+            uint32_t lo[ABITS], hi[ABITS];
+#pragma unroll
+            for (int pa = 0; pa < ABITS; pa++) {
+              lo[pa] = aw[pa][i][0];
+              hi[pa] = aw[pa][i][1];
             }
-#pragma unroll
-            for (int i = 0; i < MT; i++)
-#pragma unroll
-              for (int j = 0; j < NT; j++)
-                mma_u8(acc[0][i][j], ea[i][0], ea[i][1], ea[i][2], ea[i][3], eb[j][0], eb[j][1]);
+            // kk is a compile-time constant after unrolling; dispatch the shift amounts
+            switch (kk) {
+              case 0: ea[i][0] = spread<ABITS, 0>(lo); ea[i][1] = spread<ABITS, 0>(hi);
+                      ea[i][2] = spread<ABITS, 1>(lo); ea[i][3] = spread<ABITS, 1>(hi); break;
+              case 1: ea[i][0] = spread<ABITS, 2>(lo); ea[i][1] = spread<ABITS, 2>(hi);
+                      ea[i][2] = spread<ABITS, 3>(lo); ea[i][3] = spread<ABITS, 3>(hi); break;
+              case 2: ea[i][0] = spread<ABITS, 4>(lo); ea[i][1] = spread<ABITS, 4>(hi);
+                      ea[i][2] = spread<ABITS, 5>(lo); ea[i][3] = spread<ABITS, 5>(hi); break;
+              default: ea[i][0] = spread<ABITS, 6>(lo); ea[i][1] = spread<ABITS, 6>(hi);
+                       ea[i][2] = spread<ABITS, 7>(lo); ea[i][3] = spread<ABITS, 7>(hi); break;
+            }
           }
+#pragma unroll
+          for (int j = 0; j < NT; j++) {
+            uint32_t wv[BBITS];
+#pragma unroll
+            for (int pb = 0; pb < BBITS; pb++) wv[pb] = bw[pb][j];
+            switch (kk) {
+              case 0: eb[j][0] = spread<BBITS, 0>(wv); eb[j][1] = spread<BBITS, 1>(wv); break;
+              case 1: eb[j][0] = spread<BBITS, 2>(wv); eb[j][1] = spread<BBITS, 3>(wv); break;
+              case 2: eb[j][0] = spread<BBITS, 4>(wv); eb[j][1] = spread<BBITS, 5>(wv); break;
+              default: eb[j][0] = spread<BBITS, 6>(wv); eb[j][1] = spread<BBITS, 7>(wv); break;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < MT; i++)
+#pragma unroll
+            for (int j = 0; j < NT; j++)
+              mma_u8(acc[0][i][j], ea[i][0], ea[i][1], ea[i][2], ea[i][3], eb[j][0], eb[j][1]);
         }
       }
     }
@@ -421,8 +459,8 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
     for (int i = 0; i < MT; i++)
 #pragma unroll
       for (int h = 0; h < 2; h++) {
-        long long idx = (long long)tile_m * BM + warp_m * MT * 16 + i * 16 + h * 8 + g;
-        long long orow = out_row_of(p, idx, p.M);
+        unsigned idx = (unsigned)tile_m * BM + warp_m * MT * 16 + i * 16 + h * 8 + g;
+        long long orow = out_row_of(p, idx, (unsigned)p.M);
         int vals[NT][2];
 #pragma unroll
         for (int j = 0; j < NT; j++) {
@@ -435,8 +473,8 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
     if constexpr (MT % 2 == 0) {
 #pragma unroll
       for (int i = 0; i < MT; i += 2) {
-        long long u = (long long)tile_m * (BM / 4) + ((warp_m * MT * 16 + i * 16) >> 5) * 8 + g;
-        long long orow = out_row_of(p, u, p.M / 4);
+        unsigned u = (unsigned)tile_m * (BM / 4) + ((warp_m * MT * 16 + i * 16) >> 5) * 8 + g;
+        long long orow = out_row_of(p, u, (unsigned)p.M / 4);
         int vals[NT][2];
 #pragma unroll
         for (int j = 0; j < NT; j++)
