@@ -162,9 +162,46 @@ apnn_status apnn_gemm(void* stream, int wbits, int xbits, const void* W, const v
   return apnn_gemm_ex(stream, APNN_ALGO_AUTO, wbits, xbits, W, X, D, M, N, K, nullptr, nullptr, 0);
 }
 
+size_t apnn_conv2d_workspace_bytes(int algo, int B, int H, int W, int CIN, int COUT, int R) {
+  if (algo != APNN_ALGO_TCGEN05 || B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0 || (R != 1 && R != 3)) return 0;
+  return tc5_conv_workspace_bytes(B, H, W, CIN, COUT, R);
+}
+
+apnn_status apnn_conv2d_check(void* stream, const void* workspace, int B, int H, int W, int CIN, int COUT, int R) {
+  if (!workspace || B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
+  int flag = tc5_conv_read_error_flag(reinterpret_cast<cudaStream_t>(stream), workspace, B, H, W, CIN, COUT, R);
+  if (flag < 0) return cuda_fail(cudaGetLastError(), "apnn_conv2d_check");
+  return flag == 0 ? APNN_OK : APNN_ERR_TIMEOUT;
+}
+
+apnn_status apnn_conv2d_i8(void* stream, const void* W8, const void* X8, void* Out, int B, int H, int W, int CIN,
+                           int COUT, int R, int w_signed, const apnn_epilogue* epi, int* status_flag) {
+  if (!W8 || !X8 || !Out || !status_flag) return APNN_ERR_INVALID_ARG;
+  if (B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
+  if (R != 1 && R != 3) return APNN_ERR_UNSUPPORTED;
+  if (CIN % 128 != 0 || !aligned16(W8) || !aligned16(X8) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
+  if (epi) {
+    if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;  // the sign is in the bytes
+    apnn_status st = check_epilogue(epi, COUT, true, 1, 1);
+    if (st != APNN_OK) return st;
+    if (epi->pool != APNN_POOL_NONE && ((H & 1) || (W & 1))) return APNN_ERR_UNSUPPORTED;
+  }
+  if (!tc5_conv_supported(H, W, R, 1, epi ? epi->pool : APNN_POOL_NONE)) return APNN_ERR_UNSUPPORTED;
+  return tc5_conv_i8(reinterpret_cast<cudaStream_t>(stream), (const uint8_t*)X8, (const uint8_t*)W8, Out, B, H, W,
+                     CIN, COUT, R, w_signed != 0, epi, status_flag);
+}
+
 apnn_status apnn_conv2d(void* stream, int wbits, int xbits, const void* Wt, const void* X, void* Out, int B, int H,
                         int Wd, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi) {
+  return apnn_conv2d_ex(stream, APNN_ALGO_IMMA, wbits, xbits, Wt, X, Out, B, H, Wd, CIN, COUT, R, stride, epi, nullptr,
+                        0);
+}
+
+apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const void* Wt, const void* X, void* Out,
+                           int B, int H, int Wd, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi,
+                           void* workspace, size_t workspace_bytes) {
   if (!Wt || !X || !Out) return APNN_ERR_INVALID_ARG;
+  if (algo != APNN_ALGO_AUTO && algo != APNN_ALGO_IMMA && algo != APNN_ALGO_TCGEN05) return APNN_ERR_INVALID_ARG;
   if (B <= 0 || H <= 0 || Wd <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
   if (R != 1 && R != 3) return APNN_ERR_UNSUPPORTED;
   if (stride != 1 && stride != 2) return APNN_ERR_UNSUPPORTED;
@@ -180,6 +217,21 @@ apnn_status apnn_conv2d(void* stream, int wbits, int xbits, const void* Wt, cons
   if (pool != APNN_POOL_NONE && ((Ho & 1) || (Wo & 1))) return APNN_ERR_UNSUPPORTED;
   const long long pixels = (long long)B * Ho * Wo;
   if (pixels > 0x7fffffffLL) return APNN_ERR_UNSUPPORTED;
+
+  if (algo == APNN_ALGO_AUTO) {
+    // the tcgen05 path pays two expand launches; worth it once the contraction is sizeable
+    const bool ws_ok = workspace && workspace_bytes >= tc5_conv_workspace_bytes(B, H, Wd, CIN, COUT, R);
+    const double flops = 2.0 * (double)pixels * COUT * R * R * CIN;
+    algo = (ws_ok && tc5_conv_supported(H, Wd, R, stride, pool) && flops >= 2e9) ? APNN_ALGO_TCGEN05 : APNN_ALGO_IMMA;
+  }
+  if (algo == APNN_ALGO_TCGEN05) {
+    if (!tc5_conv_supported(H, Wd, R, stride, pool)) return APNN_ERR_UNSUPPORTED;
+    if (epi && epi->signed_operand == APNN_SIGN_X) return APNN_ERR_UNSUPPORTED;
+    if (!workspace || workspace_bytes < tc5_conv_workspace_bytes(B, H, Wd, CIN, COUT, R)) return APNN_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return APNN_ERR_ALIGNMENT;
+    return tc5_conv(reinterpret_cast<cudaStream_t>(stream), wbits, xbits, (const uint32_t*)Wt, (const uint32_t*)X, Out,
+                    B, H, Wd, CIN, COUT, R, epi, workspace);
+  }
 
   CoreParams p;
   memset(&p, 0, sizeof(p));

@@ -401,8 +401,32 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
   const int ncol0 = n0 + warp_n * NT * 8;  // first column of this warp
   const int nl = (1 << p.out_bits) - 1;
 
+  // Thresholds of up to 2-bit outputs are staged once per CTA in the (now idle) pipeline
+  // buffers, one int4 per column with unused slots at INT_MAX: one shared-memory load per
+  // value instead of nl global loads.
+  const bool thr_staged = p.out_mode == OUT_THRESHOLDS && nl <= 3;
+  const int4* thr_s = reinterpret_cast<const int4*>(smem);
+  if (thr_staged) {
+    __syncthreads();  // every warp is done with the last stage
+    for (int cidx = tid; cidx < BN; cidx += Cfg::THREADS) {
+      const int col = n0 + cidx;
+      int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
+      if (col < p.N) {
+        const int32_t* T = p.thresholds + (long long)col * nl;
+        t4.x = __ldg(T);
+        if (nl > 1) { t4.y = __ldg(T + 1); t4.z = __ldg(T + 2); }
+      }
+      reinterpret_cast<int4*>(smem)[cidx] = t4;
+    }
+    __syncthreads();
+  }
+
   auto level_of = [&](int v, int col) -> uint32_t {
     if (p.out_mode == OUT_LOWBITS) return (uint32_t)v & (uint32_t)nl;
+    if (thr_staged) {
+      const int4 t4 = thr_s[col - n0];
+      return (v >= t4.x ? 1u : 0u) + (v >= t4.y ? 1u : 0u) + (v >= t4.z ? 1u : 0u);
+    }
     uint32_t l = 0;
     const int32_t* T = p.thresholds + (long long)col * nl;
     for (int j2 = 0; j2 < nl; j2++) l += (v >= __ldg(T + j2)) ? 1u : 0u;

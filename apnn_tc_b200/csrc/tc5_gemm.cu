@@ -1,4 +1,4 @@
-// tcgen05 path for large GEMMs.
+// tcgen05 path for large GEMMs and 3x3 / 1x1 stride-1 convolutions.
 //
 // Step 1 (expand_planes_kernel): every operand is rewritten once from bit planes to one
 // int8 per element, value = sum_p bit_p << p (or -1/+1 for a signed 1-bit operand), rows of
@@ -14,9 +14,19 @@
 // epilogue (int32 stores, or requantise + bit-plane pack: a thread owns one row and 32
 // consecutive columns, i.e. exactly one output word per plane).  No cluster, no multicast.
 //
+// Convolution reuses the same kernel as an implicit GEMM: the activations are expanded to
+// int8 NHWC (halo included), and the A tile of a K block is one 4-D TMA box -- 128 bytes of
+// channels x (bw x bh x bb) output pixels -- fetched at the halo offset of the filter tap,
+// which lands in shared memory as the same 128-byte-swizzled row block a GEMM tile would.
+// K runs over (tap_i, tap_j, 128-channel block), matching the filter rows' K order.  A
+// 2x2 pooling window lies inside one warp (the box is at most 16 pixels wide), so the
+// epilogue pools with three lane shuffles before requantising.
+//
 // Every mbarrier wait is bounded: on expiry the kernel raises a flag in global memory,
 // stops issuing work, and falls through to the common tear-down (TMEM is released).
 #include <cuda.h>
+
+#include <cstring>
 
 #include "api_internal.h"
 #include "apnn_device.cuh"
@@ -27,14 +37,24 @@ namespace apnn {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BN = 256;
 constexpr int BK = 128;  // bytes of K per stage = one 128-byte swizzle row
-constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK;
-constexpr int B_STAGE_BYTES = BN * BK;
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 192;
+constexpr int MAX_STAGES = 6;
+
+// Tile width N is 256 (4 stages of 48 KiB) when that still fills the device, else 128
+// (6 stages of 32 KiB): twice as many tiles for mid-sized problems.
+template <int BN>
+struct TileCfg {
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int B_STAGE_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  // each epilogue warp keeps the tile's thresholds as one 16-byte entry per column
+  static constexpr int THR_BYTES_PER_WARP = BN * 16;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * THR_BYTES_PER_WARP;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
 constexpr int GROUP_M = 16;  // tiles are walked in bands of 16 row-tiles for L2 reuse
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // a wait that lasts 2 s is a bug, not a delay
 
@@ -108,6 +128,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], "
+      "[%6];" ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -157,7 +184,49 @@ struct Tc5Params {
   uint32_t idesc;
   long long out_plane_words;
   int* error_flag;
+  // convolution (is_conv != 0): an A tile is a box of bw x bh x bb output pixels
+  int is_conv;
+  int bw, bh, bb;
+  int tiles_w, tiles_h;  // boxes per image along w and h
+  int Bn, Ho, Wo;        // batch and conv output extent (before pooling)
+  int cblocks, R;        // CIN / 128, filter size
+  int pool, out_h, out_w, out_halo;
+  uint32_t a_box_bytes;  // bytes one A box deposits
 };
+
+// Output row (units of N channels) and validity of tile row r; for pooled outputs only the
+// top-left pixel of a window is a writer.
+struct RowDst {
+  long long row;
+  bool valid;
+};
+__device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, int r) {
+  RowDst d;
+  if (!p.is_conv) {
+    d.row = (long long)tm * BM + r;
+    d.valid = d.row < p.M;
+    return d;
+  }
+  const int tw = tm % p.tiles_w;
+  const int t2 = tm / p.tiles_w;
+  const int th = t2 % p.tiles_h;
+  const int bg = t2 / p.tiles_h;
+  const int wi = r % p.bw;
+  const int r2 = r / p.bw;
+  const int hi = r2 % p.bh;
+  const int bi = r2 / p.bh;
+  const int b = bg * p.bb + bi, ho = th * p.bh + hi, wo = tw * p.bw + wi;
+  d.valid = bi < p.bb && b < p.Bn && ho < p.Ho && wo < p.Wo;
+  int oh = ho, ow = wo;
+  if (p.pool != POOL_NONE) {
+    d.valid = d.valid && ((hi | wi) & 1) == 0;
+    oh = ho >> 1;
+    ow = wo >> 1;
+  }
+  const int hh = p.out_halo;
+  d.row = ((long long)b * (p.out_h + 2 * hh) + oh + hh) * (p.out_w + 2 * hh) + ow + hh;
+  return d;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int band = GROUP_M * tiles_n;
@@ -169,9 +238,13 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / rows;
 }
 
+template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Tc5Params p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -184,11 +257,13 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
   volatile uint32_t* tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+  uint8_t* thr_stage = smem_raw + (bars + 256u - raw);  // 4 x THR_BYTES_PER_WARP
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) *p.error_flag = 0;  // only ever raised after a 2 s wait, long after this store
     for (int s = 0; s < STAGES; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -200,7 +275,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                 "r"(Cfg::TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   tc_fence_before();
@@ -218,13 +294,28 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        int w0 = 0, h0 = 0, b0 = 0;
+        if (p.is_conv) {
+          w0 = (tm % p.tiles_w) * p.bw;
+          const int t2 = tm / p.tiles_w;
+          h0 = (t2 % p.tiles_h) * p.bh;
+          b0 = (t2 / p.tiles_h) * p.bb;
+        }
+        int tap = 0, cb = 0;  // conv: K block = (filter tap, 128-channel block)
         for (int kb = 0; kb < p.kblocks; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t sa = base + s * STAGE_BYTES;
-          tma_load_2d(sa, &map_a, kb * BK, tm * BM, full_bar(s));
+          if (!p.is_conv) {
+            mbar_expect_tx(full_bar(s), STAGE_BYTES);
+            tma_load_2d(sa, &map_a, kb * BK, tm * BM, full_bar(s));
+          } else {
+            mbar_expect_tx(full_bar(s), p.a_box_bytes + Cfg::B_STAGE_BYTES);
+            const int ti = tap / p.R, tj = tap - ti * p.R;
+            tma_load_4d(sa, &map_a, cb * BK, w0 + tj, h0 + ti, b0, full_bar(s));
+            if (++cb == p.cblocks) { cb = 0; tap++; }
+          }
           tma_load_2d(sa + A_STAGE_BYTES, &map_b, kb * BK, tn * BN, full_bar(s));
         }
       }
@@ -267,15 +358,37 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t tl = 0;
     bool ok = true;
     const int nl = (1 << p.out_bits) - 1;
+    // thresholds of up to 2-bit outputs are staged per tile in this warp's shared-memory
+    // slice, one int4 per column (unused slots = INT_MAX), so a value costs one broadcast
+    // 16-byte load instead of nl global loads
+    const bool thr_staged = p.out_mode == OUT_THRESHOLDS && nl <= 3;
+    int4* thr_s = reinterpret_cast<int4*>(thr_stage + (warp - 2) * Cfg::THR_BYTES_PER_WARP);
+    int staged_tn = -1;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      if (thr_staged && tn != staged_tn) {
+        __syncwarp();
+        for (int cidx = lane; cidx < BN; cidx += 32) {
+          const int col = tn * BN + cidx;
+          int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
+          if (col < p.N) {
+            const int32_t* T = p.thresholds + (long long)col * nl;
+            t4.x = __ldg(T);
+            if (nl > 1) { t4.y = __ldg(T + 1); t4.z = __ldg(T + 2); }
+          }
+          thr_s[cidx] = t4;
+        }
+        __syncwarp();
+        staged_tn = tn;
+      }
       const uint32_t acc = tl & 1u;
       const uint32_t aph = (tl >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
       tc_fence_after();
-      const long long row = (long long)tm * BM + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
+      const RowDst dst = row_destination(p, tm, quarter * 32 + lane);
+      const long long row = dst.row;
+      const bool row_ok = dst.valid;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
@@ -283,7 +396,19 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tmem_ld32(taddr + c * 32, v);
         tmem_ld_wait();
         const int col0 = tn * BN + c * 32;
-        if (!row_ok || col0 >= p.N) continue;
+        if (col0 >= p.N) continue;  // uniform over the warp
+        if (p.pool != POOL_NONE) {
+          // the four pixels of a window are lanes l, l^1 (next column) and l^bw, l^bw^1 (next row)
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int a0 = (int)v[j];
+            const int a1 = __shfl_xor_sync(0xffffffffu, a0, 1);
+            const int a2 = __shfl_xor_sync(0xffffffffu, a0, p.bw);
+            const int a3 = __shfl_xor_sync(0xffffffffu, a1, p.bw);
+            v[j] = (uint32_t)(p.pool == POOL_AVG2 ? (a0 + a1 + a2 + a3) / 4 : max(max(a0, a1), max(a2, a3)));
+          }
+        }
+        if (!row_ok) continue;
         if (p.out_mode == OUT_INT32) {
           int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
           if ((p.N & 3) == 0 && col0 + 32 <= p.N) {
@@ -301,6 +426,13 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (p.out_mode == OUT_LOWBITS) {
 #pragma unroll
             for (int j = 0; j < 32; j++) lv[j] = v[j] & (uint32_t)nl;
+          } else if (thr_staged) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              const int4 t4 = thr_s[c * 32 + j];
+              const int x = (int)v[j];
+              lv[j] = (x >= t4.x ? 1u : 0u) + (x >= t4.y ? 1u : 0u) + (x >= t4.z ? 1u : 0u);
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) {
@@ -331,7 +463,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS));
   }
 }
 
@@ -353,7 +485,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // rows x K bytes, row-major; box = box_rows x 128 bytes, 128-byte swizzle, zero fill outside
-bool make_operand_map(CUtensorMap* map, const void* base, long long rows, int K, int box_rows) {
+bool make_operand_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -366,7 +498,53 @@ bool make_operand_map(CUtensorMap* map, const void* base, long long rows, int K,
   return r == CUDA_SUCCESS;
 }
 
+// int8 NHWC activations [B][Hp][Wp][CIN]; box = 128 channels x bw x bh x bb pixels
+bool make_activation_map(CUtensorMap* map, const void* base, int B, int Hp, int Wp, int CIN, int bw, int bh, int bb) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)CIN, (cuuint64_t)Wp, (cuuint64_t)Hp, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)CIN, (cuuint64_t)Wp * CIN, (cuuint64_t)Hp * Wp * CIN};
+  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bb};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+template <int BN>
+cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const Tc5Params& p,
+                       int grid) {
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(tc5_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TileCfg<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    if (dev < 16) attr_set[dev] = true;
+  }
+  tc5_gemm_kernel<BN><<<grid, THREADS, TileCfg<BN>::SMEM_BYTES, s>>>(map_a, map_b, p);
+  return cudaGetLastError();
+}
+
+// Tile width: 256 unless that leaves the device under-filled and 128 does better.
+int pick_bn(long long tiles_m, int N, int sms) {
+  long long t256 = tiles_m * ((N + 255) / 256), t128 = tiles_m * ((N + 127) / 128);
+  if (t256 >= sms) return 256;
+  // waves needed with each width, in units of a 256-wide tile's work
+  double w256 = (double)((t256 + sms - 1) / sms);
+  double w128 = 0.5 * (double)((t128 + sms - 1) / sms);
+  return w128 < w256 ? 128 : 256;
+}
+
+uint32_t make_idesc(bool a_signed, bool b_signed, int bn) {
+  // D = s32, A/B = u8 or s8, both K-major, N = bn, M = 128
+  return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(bn >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
 
 }  // namespace
 
@@ -376,7 +554,7 @@ size_t tc5_workspace_bytes(int M, int N, int K) {
 }
 
 bool tc5_worthwhile(int M, int N, int K) {
-  long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  long long tiles = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
   return tiles >= 64 && K >= 1024;
 }
 
@@ -394,40 +572,30 @@ apnn_status tc5_expand(cudaStream_t s, const uint32_t* planes, uint8_t* out, lon
 
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
-  cudaError_t e = cudaMemsetAsync(status_flag, 0, sizeof(int), s);
-  if (e != cudaSuccess) return cuda_fail(e, "tc5 flag reset");
+  cudaError_t e;
+  const int sms = device_sm_count();
+  Tc5Params p;
+  memset(&p, 0, sizeof(p));
+  p.tiles_m = (M + BM - 1) / BM;
+  const int bn = pick_bn(p.tiles_m, N, sms);
   CUtensorMap map_a, map_b;
-  if (!make_operand_map(&map_a, A8, M, K, BM) || !make_operand_map(&map_b, B8, N, K, BN)) {
+  if (!make_operand_map(&map_a, A8, M, K, BM) || !make_operand_map(&map_b, B8, N, K, bn)) {
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   }
-  static bool attr_set[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 16 || !attr_set[dev]) {
-    e = cudaFuncSetAttribute(tc5_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return cuda_fail(e, "tc5 smem attribute");
-    if (dev < 16) attr_set[dev] = true;
-  }
-  Tc5Params p;
   p.out = D;
   p.thresholds = epi ? epi->thresholds : nullptr;
   p.M = M;
   p.N = N;
   p.kblocks = K / BK;
-  p.tiles_m = (M + BM - 1) / BM;
-  p.tiles_n = (N + BN - 1) / BN;
+  p.tiles_n = (N + bn - 1) / bn;
   p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
   p.out_bits = epi ? epi->out_bits : 0;
   p.out_plane_words = (long long)M * (N / 32);
   p.error_flag = status_flag;
-  // instruction descriptor: D = s32, A/B = u8 or s8, both K-major, N = 256, M = 128
-  const uint32_t afmt = a_signed ? 1u : 0u, bfmt = b_signed ? 1u : 0u;
-  p.idesc = (2u << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  p.idesc = make_idesc(a_signed, b_signed, bn);
   long long tiles = (long long)p.tiles_m * p.tiles_n;
-  const int sms = device_sm_count();
   int grid = (int)(tiles < sms ? tiles : sms);
-  tc5_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
-  e = cudaGetLastError();
+  e = bn == 256 ? launch_tc5<256>(s, map_a, map_b, p, grid) : launch_tc5<128>(s, map_a, map_b, p, grid);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm launch");
   return APNN_OK;
 }
@@ -443,6 +611,126 @@ apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, co
   st = tc5_expand(s, X, wb, N, K, xbits, sign == APNN_SIGN_X);
   if (st != APNN_OK) return st;
   return tc5_gemm_i8(s, wa, wb, D, M, N, K, sign == APNN_SIGN_W, sign == APNN_SIGN_X, epi, err);
+}
+
+// ------------------------------------------------------------------ convolution
+// Pixel box of an A tile: bw x bh (x bb whole images when an image is smaller than a tile),
+// at most 128 pixels, chosen for the fewest wasted MMA rows.  With pooling the box is a
+// power of two wide (<= 16) and even high, so a 2x2 window never straddles warps.
+bool tc5_conv_box(int Ho, int Wo, int pool, int* bw_out, int* bh_out, int* bb_out) {
+  double best = -1.0;
+  for (int bw = 1; bw <= 128 && bw <= Wo; bw++) {
+    if (pool && !(bw == 2 || bw == 4 || bw == 8 || bw == 16)) continue;
+    int bh = 128 / bw;
+    if (bh > Ho) bh = Ho;
+    if (pool) bh &= ~1;
+    if (bh < 1) continue;
+    int bb = 1;
+    if (bw == Wo && bh == Ho) bb = 128 / (bw * bh);
+    if (bb < 1) bb = 1;
+    // TMA box extents are limited to 256 per dimension; all are <= 128 here
+    double covered = (double)Wo * Ho;
+    double spent = (double)((Wo + bw - 1) / bw) * ((Ho + bh - 1) / bh) * 128.0 / bb;
+    double util = covered / spent;
+    if (util > best + 1e-9) {
+      best = util;
+      *bw_out = bw;
+      *bh_out = bh;
+      *bb_out = bb;
+    }
+  }
+  return best > 0;
+}
+
+size_t tc5_conv_workspace_bytes(int B, int H, int W, int CIN, int COUT, int R) {
+  const int pad = (R - 1) / 2;
+  return align_up((size_t)B * (H + 2 * pad) * (W + 2 * pad) * CIN, 256) + align_up((size_t)COUT * R * R * CIN, 256) +
+         256;
+}
+
+bool tc5_conv_supported(int H, int W, int R, int stride, int pool) {
+  if (stride != 1) return false;
+  int bw, bh, bb;
+  return tc5_conv_box(H, W, pool, &bw, &bh, &bb);
+}
+
+apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int H, int W,
+                        int CIN, int COUT, int R, bool w_signed, const apnn_epilogue* epi, int* status_flag) {
+  const int pad = (R - 1) / 2;
+  const int Hp = H + 2 * pad, Wp = W + 2 * pad;
+  const int pool = epi ? epi->pool : APNN_POOL_NONE;
+  int bw = 0, bh = 0, bb = 0;
+  if (!tc5_conv_box(H, W, pool, &bw, &bh, &bb)) return APNN_ERR_UNSUPPORTED;
+  cudaError_t e;
+  const int sms = device_sm_count();
+  Tc5Params p;
+  memset(&p, 0, sizeof(p));
+  p.is_conv = 1;
+  p.bw = bw;
+  p.bh = bh;
+  p.bb = bb;
+  p.tiles_w = (W + bw - 1) / bw;
+  p.tiles_h = (H + bh - 1) / bh;
+  p.tiles_m = ((B + bb - 1) / bb) * p.tiles_h * p.tiles_w;
+  p.Bn = B;
+  p.Ho = H;
+  p.Wo = W;
+  p.cblocks = CIN / BK;
+  p.R = R;
+  p.pool = pool;
+  p.out_h = pool ? H / 2 : H;
+  p.out_w = pool ? W / 2 : W;
+  p.out_halo = epi ? epi->out_halo : 0;
+  p.a_box_bytes = (uint32_t)(bw * bh * bb * BK);
+  const int bn = pick_bn(p.tiles_m, COUT, sms);
+  CUtensorMap map_a, map_b;
+  if (!make_activation_map(&map_a, X8, B, Hp, Wp, CIN, bw, bh, bb) ||
+      !make_operand_map(&map_b, W8, COUT, (long long)R * R * CIN, bn)) {
+    return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  }
+  p.out = Out;
+  p.thresholds = epi ? epi->thresholds : nullptr;
+  p.M = B * H * W;
+  p.N = COUT;
+  p.kblocks = R * R * p.cblocks;
+  p.tiles_n = (COUT + bn - 1) / bn;
+  p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
+  p.out_bits = epi ? epi->out_bits : 0;
+  p.out_plane_words =
+      (long long)B * (p.out_h + 2 * p.out_halo) * (p.out_w + 2 * p.out_halo) * (COUT / 32);
+  p.error_flag = status_flag;
+  p.idesc = make_idesc(false, w_signed, bn);  // A = activations (unsigned), B = filter
+  long long tiles = (long long)p.tiles_m * p.tiles_n;
+  int grid = (int)(tiles < sms ? tiles : sms);
+  e = bn == 256 ? launch_tc5<256>(s, map_a, map_b, p, grid) : launch_tc5<128>(s, map_a, map_b, p, grid);
+  if (e != cudaSuccess) return cuda_fail(e, "tc5_conv launch");
+  return APNN_OK;
+}
+
+apnn_status tc5_conv(cudaStream_t s, int wbits, int xbits, const uint32_t* Wt, const uint32_t* X, void* Out, int B,
+                     int H, int W, int CIN, int COUT, int R, const apnn_epilogue* epi, void* workspace) {
+  const int pad = (R - 1) / 2;
+  const long long pixels = (long long)B * (H + 2 * pad) * (W + 2 * pad);
+  uint8_t* x8 = reinterpret_cast<uint8_t*>(workspace);
+  uint8_t* w8 = x8 + align_up((size_t)pixels * CIN, 256);
+  int* err = reinterpret_cast<int*>(w8 + align_up((size_t)COUT * R * R * CIN, 256));
+  const bool w_signed = epi && epi->signed_operand == APNN_SIGN_W;
+  apnn_status st = tc5_expand(s, X, x8, pixels, CIN, xbits, false);
+  if (st != APNN_OK) return st;
+  st = tc5_expand(s, Wt, w8, COUT, R * R * CIN, wbits, w_signed);
+  if (st != APNN_OK) return st;
+  return tc5_conv_i8(s, x8, w8, Out, B, H, W, CIN, COUT, R, w_signed, epi, err);
+}
+
+int tc5_conv_read_error_flag(cudaStream_t s, const void* workspace, int B, int H, int W, int CIN, int COUT, int R) {
+  const int pad = (R - 1) / 2;
+  const uint8_t* x8 = reinterpret_cast<const uint8_t*>(workspace);
+  const uint8_t* w8 = x8 + align_up((size_t)B * (H + 2 * pad) * (W + 2 * pad) * CIN, 256);
+  const int* err = reinterpret_cast<const int*>(w8 + align_up((size_t)COUT * R * R * CIN, 256));
+  int v = -1;
+  if (cudaMemcpyAsync(&v, err, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+  return v;
 }
 
 // Reads back the flag a bounded wait raises; 0 means the last tc5_gemm on this workspace

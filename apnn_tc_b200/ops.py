@@ -158,8 +158,19 @@ def apmm_w2a2_decompose(W, X, D=None, **kw):
     return apmm(W, X, D, epilogue=make_epilogue("lowbits", 2), **kw)
 
 
+def conv_workspace_bytes(B: int, H: int, W: int, CIN: int, COUT: int, R: int = 3) -> int:
+    return int(_cabi.lib().apnn_conv2d_workspace_bytes(_cabi.ALGO_TCGEN05, B, H, W, CIN, COUT, R))
+
+
+def conv_check(workspace: torch.Tensor, B: int, H: int, W: int, CIN: int, COUT: int, R: int = 3) -> None:
+    """Synchronise and raise if the tcgen05 conv that last used ``workspace`` gave up on a wait."""
+    _cabi.check(_cabi.lib().apnn_conv2d_check(_stream_ptr(), workspace.data_ptr(), B, H, W, CIN, COUT, R),
+                "apnn_conv2d_check")
+
+
 def apconv(Wt: torch.Tensor, X: torch.Tensor, out: Optional[torch.Tensor] = None, *, stride: int = 1,
-           epilogue: Optional[Epilogue] = None) -> torch.Tensor:
+           epilogue: Optional[Epilogue] = None, algo: str = "imma",
+           workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Implicit-GEMM convolution over packed NHWC planes.
 
     X: [xbits, B, H+2p, W+2p, CIN/32] (halo stored), Wt: [wbits, COUT, R, R, CIN/32].
@@ -186,9 +197,13 @@ def apconv(Wt: torch.Tensor, X: torch.Tensor, out: Optional[torch.Tensor] = None
         else:
             shape = shape + (COUT,)
         out = (torch.zeros if halo else torch.empty)(shape, dtype=torch.int32, device=X.device)
-    st = _cabi.lib().apnn_conv2d(_stream_ptr(), wbits, xbits, Wt.data_ptr(), X.data_ptr(), out.data_ptr(), B, H, Wd,
-                                 cw * 32, COUT, R, stride, ctypes.byref(epilogue) if epilogue is not None else None)
-    _cabi.check(st, "apnn_conv2d")
+    ws_ptr, ws_bytes = None, 0
+    if workspace is not None:
+        ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    st = _cabi.lib().apnn_conv2d_ex(_stream_ptr(), _cabi.ALGOS[algo], wbits, xbits, Wt.data_ptr(), X.data_ptr(),
+                                    out.data_ptr(), B, H, Wd, cw * 32, COUT, R, stride,
+                                    ctypes.byref(epilogue) if epilogue is not None else None, ws_ptr, ws_bytes)
+    _cabi.check(st, "apnn_conv2d_ex")
     return out
 
 

@@ -100,13 +100,17 @@ def sweep_conv():
                                dim=1).values.contiguous()
                 epi = ap.make_epilogue("thresholds", 2, signed="w" if wb == 1 else "none", thresholds=T)
                 out = torch.empty((2, B, H, Wd, C // 32), dtype=torch.int32, device="cuda")
-                gus, pus = time_call(lambda: ap.apconv(Wt, X, out, epilogue=epi))
+                ws = torch.empty(ap.conv_workspace_bytes(B, H, Wd, C, C, 3), dtype=torch.uint8, device="cuda")
                 flops = 2.0 * B * H * Wd * C * 9 * C
                 byts = xb * B * 18 * 18 * C / 8 + wb * 9 * C * C / 8 + 2 * B * 256 * C / 8 + 12 * C
-                print(json.dumps({"op": "conv3x3_bn_requant2", "w": wb, "a": xb, "B": B, "HW": 16, "C": C,
-                                  "graph_us": round(gus, 3), "plain_us": round(pus, 3),
-                                  "tops": round(flops / gus / 1e6, 2), "algorithmic_bytes": int(byts),
-                                  "gbps": round(byts / gus / 1e3, 1)}), flush=True)
+                for algo in ("imma", "tcgen05"):
+                    if not _keep(algo=algo):
+                        continue
+                    gus, pus = time_call(lambda: ap.apconv(Wt, X, out, epilogue=epi, algo=algo, workspace=ws))
+                    print(json.dumps({"op": "conv3x3_bn_requant2", "w": wb, "a": xb, "B": B, "HW": 16, "C": C,
+                                      "algo": algo, "graph_us": round(gus, 3), "plain_us": round(pus, 3),
+                                      "tops": round(flops / gus / 1e6, 2), "algorithmic_bytes": int(byts),
+                                      "gbps": round(byts / gus / 1e3, 1)}), flush=True)
 
 
 def sweep_big():

@@ -117,3 +117,78 @@ def test_conv_host_front_end(cuda_device):
     h.conv2d(Wt, X, out, 1, 2, 2, 8, 8, 128, 64, epilogue=ap.make_epilogue("lowbits", 2))
     h.close()
     assert np.array_equal(out, oracle.requant_pack(oracle.conv_popc(Wt, X), 2, 1))
+
+
+# ------------------------------------------------------------------ tcgen05 implicit-GEMM path
+def run_tc5_conv(Wt, X, epilogue=None):
+    import apnn_tc_b200 as ap
+    xb, B, Hp, Wp, cw = X.shape
+    wb, COUT, R = Wt.shape[0], Wt.shape[1], Wt.shape[2]
+    p = (R - 1) // 2
+    H, Wd, CIN = Hp - 2 * p, Wp - 2 * p, cw * 32
+    ws = torch.empty(ap.conv_workspace_bytes(B, H, Wd, CIN, COUT, R), dtype=torch.uint8, device="cuda")
+    out = ap.apconv(to_dev(Wt), to_dev(X), epilogue=epilogue, algo="tcgen05", workspace=ws)
+    ap.conv_check(ws, B, H, Wd, CIN, COUT, R)  # synchronises; raises if a bounded wait expired
+    return out
+
+
+@pytest.mark.parametrize("wb,xb", [(1, 2), (2, 2), (1, 4)])
+def test_tcgen05_reference_inputs(cuda_device, wb, xb):
+    import apnn_tc_b200 as ap
+    X, Wt = oracle.fill_conv(8, 8, 128, 64, xb, wb)
+    key = f"conv_w{wb}a{xb}_8x8x128x64"
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X), np.int32), GOLD[key])
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X, ap.make_epilogue("lowbits", 2))), GOLD[key + "_pack"])
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X, ap.make_epilogue("lowbits", 2, pool="avg"))), GOLD[key + "_pool"])
+
+
+@pytest.mark.parametrize("C", [128, 256, 512, 1024])
+def test_tcgen05_config3_batch8_16x16(cuda_device, C):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(0xA9117C + 3)
+    X, Wt = make_conv(rng, 8, 16, 16, C, C, 3, 1, 2)
+    acc = oracle.conv_popc(Wt, X, threads=8)
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X), np.int32), acc)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, 3), 0)
+    scale = rng.uniform(0.5, 1.5, C).astype(np.float32)
+    bias = rng.uniform(-1, 1, C).astype(np.float32)
+    T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, 2)
+    epi = ap.make_epilogue("thresholds", 2, signed="w", thresholds=to_dev(T))
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X, epi)), oracle.requant_pack(v, 2, 2, T))
+
+
+@pytest.mark.parametrize("B,H,Wd", [(3, 12, 20), (5, 8, 8), (2, 56, 56), (1, 4, 4), (2, 6, 130)])
+@pytest.mark.parametrize("R", [3, 1])
+@pytest.mark.parametrize("pool", ["none", "avg", "max"])
+def test_tcgen05_shapes_filters_pools(cuda_device, B, H, Wd, R, pool):
+    """Boxes that do not divide the image, images smaller than a tile, ragged batch."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(B * 100 + H + R)
+    CIN, COUT = 128, 96
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, R, 1, 2)
+    acc = oracle.conv_popc(Wt, X, threads=4)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R, 1), 0)
+    if pool != "none":
+        v = oracle.pool2x2(v, 1 if pool == "avg" else 2)
+    out = run_tc5_conv(Wt, X, ap.make_epilogue("int32", signed="w", pool=pool))
+    assert np.array_equal(to_host(out, np.int32), v)
+    T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
+    out = run_tc5_conv(Wt, X, ap.make_epilogue("thresholds", 2, signed="w", pool=pool, out_halo=1, thresholds=to_dev(T)))
+    want = oracle.requant_pack(v, 2, 2, T)
+    got = to_host(out)
+    assert got.shape[2] == want.shape[2] + 2 and got.shape[3] == want.shape[3] + 2
+    assert np.array_equal(got[:, :, 1:-1, 1:-1], want)
+    assert not got[:, :, 0].any() and not got[:, :, -1].any() and not got[:, :, :, 0].any() and not got[:, :, :, -1].any()
+
+
+def test_tcgen05_many_tiles_and_auto(cuda_device):
+    """More tiles than SMs (both TMEM accumulators, several tiles per CTA) and the AUTO choice."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(57)
+    B, H, Wd, CIN, COUT = 16, 32, 32, 256, 512
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, 3, 2, 2)
+    want = oracle.conv_popc(Wt, X, threads=8)
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X), np.int32), want)
+    ws = torch.empty(ap.conv_workspace_bytes(B, H, Wd, CIN, COUT, 3), dtype=torch.uint8, device="cuda")
+    out = ap.apconv(to_dev(Wt), to_dev(X), algo="auto", workspace=ws)
+    assert np.array_equal(to_host(out, np.int32), want)
