@@ -36,6 +36,8 @@ class Epilogue(ctypes.Structure):
         ("out_halo", ctypes.c_int32),
         ("reserved", ctypes.c_int32),
         ("thresholds", ctypes.c_void_p),
+        ("residual_in", ctypes.c_void_p),
+        ("residual_out", ctypes.c_void_p),
     ]
 
 

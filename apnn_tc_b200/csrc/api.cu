@@ -150,6 +150,8 @@ apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const voi
     p.thresholds = epi->thresholds;
     p.sign = epi->signed_operand == APNN_SIGN_W ? SIGN_A : epi->signed_operand == APNN_SIGN_X ? SIGN_B : SIGN_NONE;
     p.out_plane_words = (long long)M * (N / 32);
+    p.residual_in = epi->residual_in;
+    p.residual_out = epi->residual_out;
   }
   int kind = algo == APNN_ALGO_BMMA ? CORE_B1 : CORE_U8;
   cudaError_t e = launch_core(kind, wbits, xbits, p, s, core_pick_tile(p, device_sm_count()));
@@ -163,7 +165,7 @@ apnn_status apnn_gemm(void* stream, int wbits, int xbits, const void* W, const v
 }
 
 size_t apnn_conv2d_workspace_bytes(int algo, int B, int H, int W, int CIN, int COUT, int R) {
-  if (algo != APNN_ALGO_TCGEN05 || B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0 || (R != 1 && R != 3)) return 0;
+  if (algo != APNN_ALGO_TCGEN05 || B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0 || (R < 1 || R > 11 || (R & 1) == 0)) return 0;
   return tc5_conv_workspace_bytes(B, H, W, CIN, COUT, R);
 }
 
@@ -178,7 +180,7 @@ apnn_status apnn_conv2d_i8(void* stream, const void* W8, const void* X8, void* O
                            int COUT, int R, int w_signed, const apnn_epilogue* epi, int* status_flag) {
   if (!W8 || !X8 || !Out || !status_flag) return APNN_ERR_INVALID_ARG;
   if (B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
-  if (R != 1 && R != 3) return APNN_ERR_UNSUPPORTED;
+  if (R < 1 || R > 11 || (R & 1) == 0) return APNN_ERR_UNSUPPORTED;
   if (CIN % 128 != 0 || !aligned16(W8) || !aligned16(X8) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
   if (epi) {
     if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;  // the sign is in the bytes
@@ -203,8 +205,8 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
   if (!Wt || !X || !Out) return APNN_ERR_INVALID_ARG;
   if (algo != APNN_ALGO_AUTO && algo != APNN_ALGO_IMMA && algo != APNN_ALGO_TCGEN05) return APNN_ERR_INVALID_ARG;
   if (B <= 0 || H <= 0 || Wd <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
-  if (R != 1 && R != 3) return APNN_ERR_UNSUPPORTED;
-  if (stride != 1 && stride != 2) return APNN_ERR_UNSUPPORTED;
+  if (R < 1 || R > 11 || (R & 1) == 0) return APNN_ERR_UNSUPPORTED;
+  if (stride < 1 || stride > 4) return APNN_ERR_UNSUPPORTED;
   if (CIN % 128 != 0) return APNN_ERR_ALIGNMENT;
   if (!aligned16(Wt) || !aligned16(X) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
   // core operand A = activations (xbits), B = filter (wbits)
@@ -264,6 +266,8 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
     // the filter is core operand B, the activations core operand A
     p.sign = epi->signed_operand == APNN_SIGN_W ? SIGN_B : epi->signed_operand == APNN_SIGN_X ? SIGN_A : SIGN_NONE;
     p.out_halo = epi->out_halo;
+    p.residual_in = epi->residual_in;
+    p.residual_out = epi->residual_out;
   }
   p.out_plane_words =
       (long long)B * (p.out_h + 2 * p.out_halo) * (p.out_w + 2 * p.out_halo) * (COUT / 32);

@@ -38,6 +38,8 @@ struct CoreParams {
   int out_mode, out_bits, sign, pool;
   int out_h, out_w, out_halo;   // conv: output spatial size after pooling, ring width
   long long out_plane_words;    // packed: words between output bit planes
+  const int32_t* residual_in;   // optional dense int32 [rows][N] added before requantisation
+  int32_t* residual_out;        // optional dense int32 [rows][N]: the value after the add
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -119,6 +119,8 @@ apnn_status apnn_gemm_host(apnn_handle h, int algo, int wbits, int xbits, const 
   if (epi) {
     dev_epi = *epi;
     dev_epi.thresholds = (const int32_t*)dT;
+    dev_epi.residual_in = nullptr;  // residual tensors are device-side only
+    dev_epi.residual_out = nullptr;
     pe = &dev_epi;
   }
   st = apnn_gemm_ex(h->stream, use_algo, wbits, xbits, dW, dX, dD, M, N, K, pe, ws ? dWs : nullptr, ws);
@@ -134,8 +136,8 @@ apnn_status apnn_conv2d_host(apnn_handle h, int wbits, int xbits, const void* Wt
                              const apnn_epilogue* epi) {
   if (!h || !Wt_host || !X_host || !Out_host) return APNN_ERR_INVALID_ARG;
   if (B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0 || wbits < 1 || xbits < 1) return APNN_ERR_INVALID_ARG;
-  if (R != 1 && R != 3) return APNN_ERR_UNSUPPORTED;
-  if (stride != 1 && stride != 2) return APNN_ERR_UNSUPPORTED;
+  if (R < 1 || R > 11 || (R & 1) == 0) return APNN_ERR_UNSUPPORTED;
+  if (stride < 1 || stride > 4) return APNN_ERR_UNSUPPORTED;
   if (CIN % 128 != 0) return APNN_ERR_ALIGNMENT;
   cudaError_t e = cudaSetDevice(h->device);
   if (e != cudaSuccess) return apnn::cuda_fail(e, "cudaSetDevice");
@@ -170,6 +172,8 @@ apnn_status apnn_conv2d_host(apnn_handle h, int wbits, int xbits, const void* Wt
   if (epi) {
     dev_epi = *epi;
     dev_epi.thresholds = (const int32_t*)dT;
+    dev_epi.residual_in = nullptr;  // residual tensors are device-side only
+    dev_epi.residual_out = nullptr;
     pe = &dev_epi;
   }
   st = apnn_conv2d(h->stream, wbits, xbits, dW, dX, dO, B, H, W, CIN, COUT, R, stride, pe);

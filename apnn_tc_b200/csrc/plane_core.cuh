@@ -434,7 +434,24 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
   };
 
   // Emits one output row: vals[j][e] is the value at column ncol0 + j*8 + 2*t4 + e.
-  auto emit_row = [&](long long orow, int (&vals)[NT][2]) {
+  // orow: output row including the optional ring; dense: row index without it (the index of
+  // the residual tensors); both negative when the row is out of range.
+  auto emit_row = [&](long long orow, long long dense, int (&vals)[NT][2]) {
+    if (p.residual_in != nullptr || p.residual_out != nullptr) {
+      if (dense >= 0) {
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const int col = ncol0 + j * 8 + 2 * t4 + e;
+            if (col < p.N) {
+              const long long at = dense * (long long)p.N + col;
+              if (p.residual_in != nullptr) vals[j][e] += __ldg(p.residual_in + at);
+              if (p.residual_out != nullptr) p.residual_out[at] = vals[j][e];
+            }
+          }
+      }
+    }
     if (p.out_mode == OUT_INT32) {
       if (orow < 0) return;
       int32_t* D = reinterpret_cast<int32_t*>(p.out) + orow * (long long)p.N;
@@ -485,13 +502,14 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
       for (int h = 0; h < 2; h++) {
         unsigned idx = (unsigned)tile_m * BM + warp_m * MT * 16 + i * 16 + h * 8 + g;
         long long orow = out_row_of(p, idx, (unsigned)p.M);
+        long long dense = orow < 0 ? -1 : (long long)idx;
         int vals[NT][2];
 #pragma unroll
         for (int j = 0; j < NT; j++) {
           vals[j][0] = acc[0][i][j][h * 2 + 0];
           vals[j][1] = acc[0][i][j][h * 2 + 1];
         }
-        emit_row(orow, vals);
+        emit_row(orow, dense, vals);
       }
   } else {
     if constexpr (MT % 2 == 0) {
@@ -499,6 +517,7 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
       for (int i = 0; i < MT; i += 2) {
         unsigned u = (unsigned)tile_m * (BM / 4) + ((warp_m * MT * 16 + i * 16) >> 5) * 8 + g;
         long long orow = out_row_of(p, u, (unsigned)p.M / 4);
+        long long dense = orow < 0 ? -1 : (long long)u;
         int vals[NT][2];
 #pragma unroll
         for (int j = 0; j < NT; j++)
@@ -508,7 +527,7 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
             int v2 = acc[0][i + 1][j][e], v3 = acc[0][i + 1][j][2 + e];
             vals[j][e] = (p.pool == POOL_AVG2) ? (v0 + v1 + v2 + v3) / 4 : max(max(v0, v1), max(v2, v3));
           }
-        emit_row(orow, vals);
+        emit_row(orow, dense, vals);
       }
     }
   }

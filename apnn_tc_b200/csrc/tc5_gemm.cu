@@ -192,18 +192,22 @@ struct Tc5Params {
   int cblocks, R;        // CIN / 128, filter size
   int pool, out_h, out_w, out_halo;
   uint32_t a_box_bytes;  // bytes one A box deposits
+  const int32_t* residual_in;  // optional dense int32 [rows][N], added before requantisation
+  int32_t* residual_out;       // optional dense int32 [rows][N], the value after the add
 };
 
 // Output row (units of N channels) and validity of tile row r; for pooled outputs only the
 // top-left pixel of a window is a writer.
 struct RowDst {
-  long long row;
+  long long row;    // output row, ring included
+  long long dense;  // output row without the ring (index of the residual tensors)
   bool valid;
 };
 __device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, int r) {
   RowDst d;
   if (!p.is_conv) {
     d.row = (long long)tm * BM + r;
+    d.dense = d.row;
     d.valid = d.row < p.M;
     return d;
   }
@@ -225,6 +229,7 @@ __device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, in
   }
   const int hh = p.out_halo;
   d.row = ((long long)b * (p.out_h + 2 * hh) + oh + hh) * (p.out_w + 2 * hh) + ow + hh;
+  d.dense = ((long long)b * p.out_h + oh) * p.out_w + ow;
   return d;
 }
 
@@ -409,6 +414,15 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
         if (!row_ok) continue;
+        if (p.residual_in != nullptr || p.residual_out != nullptr) {
+          const long long at = dst.dense * (long long)p.N + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (col0 + j < p.N) {
+              if (p.residual_in != nullptr) v[j] = (uint32_t)((int)v[j] + __ldg(p.residual_in + at + j));
+              if (p.residual_out != nullptr) p.residual_out[at + j] = (int32_t)v[j];
+            }
+        }
         if (p.out_mode == OUT_INT32) {
           int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
           if ((p.N & 3) == 0 && col0 + 32 <= p.N) {
@@ -592,6 +606,8 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.out_bits = epi ? epi->out_bits : 0;
   p.out_plane_words = (long long)M * (N / 32);
   p.error_flag = status_flag;
+  p.residual_in = epi ? epi->residual_in : nullptr;
+  p.residual_out = epi ? epi->residual_out : nullptr;
   p.idesc = make_idesc(a_signed, b_signed, bn);
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < sms ? tiles : sms);
@@ -699,6 +715,8 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.out_plane_words =
       (long long)B * (p.out_h + 2 * p.out_halo) * (p.out_w + 2 * p.out_halo) * (COUT / 32);
   p.error_flag = status_flag;
+  p.residual_in = epi ? epi->residual_in : nullptr;
+  p.residual_out = epi ? epi->residual_out : nullptr;
   p.idesc = make_idesc(false, w_signed, bn);  // A = activations (unsigned), B = filter
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < sms ? tiles : sms);

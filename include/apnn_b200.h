@@ -71,6 +71,13 @@ typedef struct apnn_epilogue {
   int32_t reserved;
   const int32_t *thresholds; /* device, [channels][2^out_bits - 1] ascending; channel = n
                                 (GEMM) or output channel (conv) */
+  const int32_t *residual_in; /* optional, device, dense int32 [rows][channels] (rows = M, or
+                                 B*Ho*Wo after pooling, no ring): added to the value before
+                                 requantisation -- the residual injection of a ResNet block
+                                 (semantics of NN/kernel.cuh:779-831) */
+  int32_t *residual_out;      /* optional, same shape: receives the int32 value (after the
+                                 residual add) next to the requantised output, i.e. the
+                                 "save_residual" output of NN/param.h:943-945 */
 } apnn_epilogue;
 
 const char *apnn_status_string(apnn_status s);
@@ -143,7 +150,7 @@ apnn_status apnn_gemm_static_scratch(void *stream, int wbits, int xbits, const v
                                      int *status_flag);
 
 /* ---- convolution ---------------------------------------------------------------
- * Implicit-GEMM RxR convolution, R in {1, 3}, stride in {1, 2}, symmetric padding
+ * Implicit-GEMM RxR convolution, R odd in 1..11, stride in 1..4, symmetric padding (R-1)/2
  * carried by the input.  With B = 1, R = 3, stride = 1:
  *   epi NULL / APNN_OUT_INT32      -> compute_conv_imma (LIB/51_...cu:58 w1a2, LIB/48_...cu:58
  *                                     w2a2, LIB/53_...cu:58 w1a4, LIB/59_...cu:58 w1a3)
@@ -157,7 +164,7 @@ apnn_status apnn_conv2d(void *stream, int wbits, int xbits, const void *Wt, cons
                         void *Out, int B, int H, int W, int CIN, int COUT, int R, int stride,
                         const apnn_epilogue *epi);
 
-/* apnn_conv2d_ex adds the algorithm / workspace choice.  APNN_ALGO_TCGEN05 (stride 1 only)
+/* apnn_conv2d_ex adds the algorithm / workspace choice.  APNN_ALGO_TCGEN05 (stride 1 only, any supported R)
  * expands activations and filter to int8 in the workspace and runs the implicit GEMM on
  * tcgen05 kind::i8, each A tile a 4-D TMA box of output pixels; APNN_ALGO_AUTO picks it when
  * the workspace is large enough and the contraction is at least ~2 GFLOP, else the

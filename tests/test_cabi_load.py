@@ -58,8 +58,9 @@ def test_argument_validation_returns_status_codes():
     assert L.apnn_gemm_workspace_bytes(2, 1, 2, 128, 256, 128) == 0
     # conv rules
     assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 96, 64, 3, 1, None) == 3
-    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 128, 64, 5, 1, None) == 2
-    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 128, 64, 3, 3, None) == 2
+    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 128, 64, 4, 1, None) == 2
+    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 128, 64, 13, 1, None) == 2
+    assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 8, 8, 128, 64, 3, 5, None) == 2
     e = _cabi.Epilogue(out_mode=1, out_bits=2, pool=1)
     assert L.apnn_conv2d(None, 1, 2, p, p, p, 1, 7, 8, 128, 64, 3, 1, ctypes.byref(e)) == 2
     # packers

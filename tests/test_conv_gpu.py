@@ -192,3 +192,44 @@ def test_tcgen05_many_tiles_and_auto(cuda_device):
     ws = torch.empty(ap.conv_workspace_bytes(B, H, Wd, CIN, COUT, 3), dtype=torch.uint8, device="cuda")
     out = ap.apconv(to_dev(Wt), to_dev(X), algo="auto", workspace=ws)
     assert np.array_equal(to_host(out, np.int32), want)
+
+
+# ------------------------------------------------------------------ wider filters, residuals
+@pytest.mark.parametrize("R,stride", [(5, 1), (7, 2), (7, 4), (11, 4), (5, 3)])
+def test_wide_filters_and_strides(cuda_device, R, stride):
+    """First-layer shapes of the model lists (11x11 s4, 7x7 s4, 5x5) on the warp-level kernel."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(R * 7 + stride)
+    X, Wt = make_conv(rng, 2, 24, 20, 128, 64, R, 1, 2)
+    acc = oracle.conv_popc(Wt, X, stride=stride, threads=4)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R, stride), 0)
+    out = ap.apconv(to_dev(Wt), to_dev(X), stride=stride, epilogue=ap.make_epilogue("int32", signed="w"))
+    assert np.array_equal(to_host(out, np.int32), v)
+    if stride == 1:
+        assert np.array_equal(to_host(run_tc5_conv(Wt, X, ap.make_epilogue("int32", signed="w")), np.int32), v)
+
+
+@pytest.mark.parametrize("algo", ["imma", "tcgen05"])
+@pytest.mark.parametrize("pool", ["none", "max"])
+def test_residual_in_and_out(cuda_device, algo, pool):
+    """value = conv + residual_in; residual_out receives it; the requantised output uses it."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(71)
+    B, H, Wd, CIN, COUT = 3, 12, 8, 128, 160
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, 3, 1, 2)
+    acc = oracle.conv_popc(Wt, X, threads=4)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, 3), 0)
+    if pool != "none":
+        v = oracle.pool2x2(v, 2)
+    res = rng.integers(-500, 500, size=v.shape).astype(np.int32)
+    v = v + res
+    T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
+    res_out = torch.zeros(v.shape, dtype=torch.int32, device="cuda")
+    epi = ap.make_epilogue("thresholds", 2, signed="w", pool=pool, out_halo=1, thresholds=to_dev(T),
+                           residual_in=to_dev(res), residual_out=res_out)
+    if algo == "tcgen05":
+        out = run_tc5_conv(Wt, X, epi)
+    else:
+        out = ap.apconv(to_dev(Wt), to_dev(X), epilogue=epi)
+    assert np.array_equal(to_host(res_out, np.int32), v)
+    assert np.array_equal(to_host(out)[:, :, 1:-1, 1:-1], oracle.requant_pack(v, 2, 2, T))

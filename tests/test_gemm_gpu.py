@@ -258,3 +258,23 @@ def test_large_shape_properties(cuda_device):
     assert torch.equal(D, D0 + 2 * D1)
     del D0, D1
     assert torch.equal(D, ap.apmm(W, X, algo="bmma"))
+
+
+@pytest.mark.parametrize("algo", ["imma", "bmma", "tcgen05"])
+def test_gemm_residual(cuda_device, algo):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(83)
+    M, N, K = 150, 288, 512
+    W, _ = oracle.value_planes(rng, M, K, 2)
+    X, _ = oracle.value_planes(rng, N, K, 1)
+    v = oracle.signed_correct(oracle.gemm_popc(W, X, threads=4), oracle.row_sums(W), 0)
+    res = rng.integers(-300, 300, size=v.shape).astype(np.int32)
+    v = v + res
+    res_out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    epi = ap.make_epilogue("lowbits", 2, signed="x", residual_in=to_dev(res), residual_out=res_out)
+    if algo == "tcgen05":
+        out = run_tc5(W, X, epi)
+    else:
+        out = ap.apmm(to_dev(W), to_dev(X), epilogue=epi, algo=algo)
+    assert np.array_equal(to_host(res_out, np.int32), v)
+    assert np.array_equal(to_host(out), oracle.requant_pack(v, 2, 1))
