@@ -34,7 +34,7 @@ class Epilogue(ctypes.Structure):
         ("signed_operand", ctypes.c_int32),
         ("pool", ctypes.c_int32),
         ("out_halo", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("in_halo", ctypes.c_int32),
         ("thresholds", ctypes.c_void_p),
         ("residual_in", ctypes.c_void_p),
         ("residual_out", ctypes.c_void_p),

@@ -45,6 +45,7 @@ apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, i
   if (e->pool < APNN_POOL_NONE || e->pool > APNN_POOL_MAX2) return APNN_ERR_INVALID_ARG;
   if (!is_conv && (e->pool != APNN_POOL_NONE || e->out_halo != 0)) return APNN_ERR_INVALID_ARG;
   if (e->out_halo < 0 || e->out_halo > 8) return APNN_ERR_INVALID_ARG;
+  if (e->in_halo < 0 || e->in_halo > 8 || (!is_conv && e->in_halo != 0)) return APNN_ERR_INVALID_ARG;
   return APNN_OK;
 }
 
@@ -187,6 +188,7 @@ apnn_status apnn_conv2d_i8(void* stream, const void* W8, const void* X8, void* O
     apnn_status st = check_epilogue(epi, COUT, true, 1, 1);
     if (st != APNN_OK) return st;
     if (epi->pool != APNN_POOL_NONE && ((H & 1) || (W & 1))) return APNN_ERR_UNSUPPORTED;
+    if (epi->in_halo != 0 && epi->in_halo < (R - 1) / 2) return APNN_ERR_INVALID_ARG;
   }
   if (!tc5_conv_supported(H, W, R, 1, epi ? epi->pool : APNN_POOL_NONE)) return APNN_ERR_UNSUPPORTED;
   return tc5_conv_i8(reinterpret_cast<cudaStream_t>(stream), (const uint8_t*)X8, (const uint8_t*)W8, Out, B, H, W,
@@ -224,10 +226,13 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
     // the tcgen05 path pays two expand launches; worth it once the contraction is sizeable
     const bool ws_ok = workspace && workspace_bytes >= tc5_conv_workspace_bytes(B, H, Wd, CIN, COUT, R);
     const double flops = 2.0 * (double)pixels * COUT * R * R * CIN;
-    algo = (ws_ok && tc5_conv_supported(H, Wd, R, stride, pool) && flops >= 2e9) ? APNN_ALGO_TCGEN05 : APNN_ALGO_IMMA;
+    const bool exact_ring = !epi || epi->in_halo == 0 || epi->in_halo == pad;
+    algo = (ws_ok && exact_ring && tc5_conv_supported(H, Wd, R, stride, pool) && flops >= 2e9) ? APNN_ALGO_TCGEN05
+                                                                                               : APNN_ALGO_IMMA;
   }
   if (algo == APNN_ALGO_TCGEN05) {
     if (!tc5_conv_supported(H, Wd, R, stride, pool)) return APNN_ERR_UNSUPPORTED;
+    if (epi && epi->in_halo != 0 && epi->in_halo != pad) return APNN_ERR_UNSUPPORTED;  // use apnn_conv2d_i8
     if (epi && epi->signed_operand == APNN_SIGN_X) return APNN_ERR_UNSUPPORTED;
     if (!workspace || workspace_bytes < tc5_conv_workspace_bytes(B, H, Wd, CIN, COUT, R)) return APNN_ERR_WORKSPACE;
     if (!aligned16(workspace)) return APNN_ERR_ALIGNMENT;
@@ -239,8 +244,11 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
   memset(&p, 0, sizeof(p));
   p.A = (const uint32_t*)X;
   p.B = (const uint32_t*)Wt;
-  p.Hp = H + 2 * pad;
-  p.Wp = Wd + 2 * pad;
+  const int in_halo = (epi && epi->in_halo) ? epi->in_halo : pad;
+  if (in_halo < pad) return APNN_ERR_INVALID_ARG;
+  p.Hp = H + 2 * in_halo;
+  p.Wp = Wd + 2 * in_halo;
+  p.in_off = in_halo - pad;
   p.cin_words = CIN / 32;
   p.cin_chunks = CIN / 128;
   p.a_plane_words = (long long)B * p.Hp * p.Wp * p.cin_words;

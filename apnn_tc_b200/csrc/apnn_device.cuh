@@ -32,6 +32,7 @@ struct CoreParams {
   int cin_words;            // CIN / 32
   int cin_chunks;           // CIN / 128
   int R, stride;
+  int in_off;               // stored ring width minus (R-1)/2: extra offset of pixel (0,0)
   // epilogue
   void* out;
   const int32_t* thresholds;

@@ -92,7 +92,8 @@ __device__ __forceinline__ RowSrc a_row_source(const CoreParams& p, int tile_m, 
     ho = 2 * hp + (quad >> 1);
     wo = 2 * wp + (quad & 1);
   }
-  s.off = (((long long)b * p.Hp + (long long)ho * p.stride) * p.Wp + (long long)wo * p.stride) * p.cin_words;
+  s.off = (((long long)b * p.Hp + (long long)ho * p.stride + p.in_off) * p.Wp + (long long)wo * p.stride + p.in_off) *
+          p.cin_words;
   return s;
 }
 

@@ -190,6 +190,7 @@ struct Tc5Params {
   int tiles_w, tiles_h;  // boxes per image along w and h
   int Bn, Ho, Wo;        // batch and conv output extent (before pooling)
   int cblocks, R;        // CIN / 128, filter size
+  int in_off;            // stored ring width minus (R-1)/2
   int pool, out_h, out_w, out_halo;
   uint32_t a_box_bytes;  // bytes one A box deposits
   const int32_t* residual_in;  // optional dense int32 [rows][N], added before requantisation
@@ -318,7 +319,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           } else {
             mbar_expect_tx(full_bar(s), p.a_box_bytes + Cfg::B_STAGE_BYTES);
             const int ti = tap / p.R, tj = tap - ti * p.R;
-            tma_load_4d(sa, &map_a, cb * BK, w0 + tj, h0 + ti, b0, full_bar(s));
+            tma_load_4d(sa, &map_a, cb * BK, w0 + tj + p.in_off, h0 + ti + p.in_off, b0, full_bar(s));
             if (++cb == p.cblocks) { cb = 0; tap++; }
           }
           tma_load_2d(sa + A_STAGE_BYTES, &map_b, kb * BK, tn * BN, full_bar(s));
@@ -673,7 +674,8 @@ bool tc5_conv_supported(int H, int W, int R, int stride, int pool) {
 apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int H, int W,
                         int CIN, int COUT, int R, bool w_signed, const apnn_epilogue* epi, int* status_flag) {
   const int pad = (R - 1) / 2;
-  const int Hp = H + 2 * pad, Wp = W + 2 * pad;
+  const int in_halo = (epi && epi->in_halo) ? epi->in_halo : pad;
+  const int Hp = H + 2 * in_halo, Wp = W + 2 * in_halo;
   const int pool = epi ? epi->pool : APNN_POOL_NONE;
   int bw = 0, bh = 0, bb = 0;
   if (!tc5_conv_box(H, W, pool, &bw, &bh, &bb)) return APNN_ERR_UNSUPPORTED;
@@ -693,6 +695,7 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.Wo = W;
   p.cblocks = CIN / BK;
   p.R = R;
+  p.in_off = in_halo - pad;
   p.pool = pool;
   p.out_h = pool ? H / 2 : H;
   p.out_w = pool ? W / 2 : W;

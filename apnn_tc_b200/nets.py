@@ -1,0 +1,388 @@
+"""Layer descriptors and model runners over the C-ABI operators.
+
+Mirrors the reference's network layer (paths inside the APNN-TC project):
+
+* ``Conv128LayerParam`` -- ``APNN-TC-nn/src/param.h:877-1083`` (shape math ``:915-924``),
+* ``Fc128LayerParam`` -- ``param.h:219-385``, ``Out128LayerParam`` -- ``param.h:388-531``,
+* the layer lists of ``APNN-TC-nn/src/alexnet.cu:43-81``, ``vgg.cu:49-127``, ``resnet18.cu:40-142``.
+
+What a layer computes is fixed by ``LayerSpec`` below and restated on the CPU in
+``tests/net_reference.py`` (the reference's programs never check a network output, so this
+is project-defined): activations are ``a_bit`` levels in packed NHWC planes with a zero ring
+for the next convolution, weights are 1-bit meaning -1/+1, every hidden layer requantises
+through per-channel int32 thresholds (batch-norm folded on the host), pooling is a 2x2
+maximum on the int32 value, a residual is the int32 value saved by an earlier layer, and
+the output layer returns int32 logits.  Channel counts are padded to multiples of 128 with
+zero activations (padded output channels get thresholds no value reaches).
+
+Everything here is host plumbing: every tensor operation is a call into ``libapnn_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from . import _cabi
+from .ops import _stream_ptr, make_epilogue
+
+INT_MAX = 2**31 - 1
+
+
+def pad128(c: int) -> int:
+    return (c + 127) // 128 * 128
+
+
+@dataclass
+class LayerSpec:
+    """One layer of a model list.  kind: 'conv' | 'fc' | 'out'."""
+    name: str
+    kind: str
+    cin: int                      # real input channels / features
+    cout: int                     # real output channels / features
+    R: int = 1                    # filter size (conv)
+    stride: int = 1
+    pool: int = 1                 # 2 = 2x2 max pool after the conv
+    save_residual: bool = False   # keep the int32 value for a later layer
+    residual_from: Optional[str] = None   # name of the layer whose saved value is added
+    src: Optional[str] = None     # input layer (default: the previous one)
+    quantise: bool = True         # False: int32 output only (shortcut convs, logits)
+
+
+@dataclass
+class ModelSpec:
+    name: str
+    image_hw: int
+    image_channels: int
+    layers: List[LayerSpec]
+    a_bit: int = 2
+    w_bit: int = 1
+
+
+def alexnet_spec(n_classes: int = 1000) -> ModelSpec:
+    """APNN-TC-nn/src/alexnet.cu:43-81: 64c11s4+pool, 192c5+pool, 384c3, 256c3, 256c3+pool, 4096, 4096, out."""
+    L = [
+        LayerSpec("Conv1", "conv", 3, 64, 11, 4, pool=2),
+        LayerSpec("Conv2", "conv", 64, 192, 5, 1, pool=2),
+        LayerSpec("Conv3", "conv", 192, 384, 3),
+        LayerSpec("Conv4", "conv", 384, 256, 3),
+        LayerSpec("Conv5", "conv", 256, 256, 3, pool=2),
+        LayerSpec("Fc1", "fc", 0, 4096),
+        LayerSpec("Fc2", "fc", 4096, 4096),
+        LayerSpec("Fout", "out", 4096, n_classes, quantise=False),
+    ]
+    return ModelSpec("alexnet", 224, 3, L)
+
+
+def vgg_variant_spec(n_classes: int = 1000) -> ModelSpec:
+    """The VGG-variant: 3x3 stacks of 128 / 256 / 512 channels with 2x2 pools, then 4096, 4096, out
+    (layer plan of APNN-TC-nn/src/vgg.cu:49-127 with the 128/256/512 channel plan)."""
+    L = [
+        LayerSpec("Conv1", "conv", 3, 128, 3, 2, pool=2),
+        LayerSpec("Conv2", "conv", 128, 256, 3), LayerSpec("Conv3", "conv", 256, 256, 3),
+        LayerSpec("Conv4", "conv", 256, 256, 3, pool=2),
+        LayerSpec("Conv5", "conv", 256, 512, 3), LayerSpec("Conv6", "conv", 512, 512, 3),
+        LayerSpec("Conv7", "conv", 512, 512, 3, pool=2),
+        LayerSpec("Conv8", "conv", 512, 512, 3), LayerSpec("Conv9", "conv", 512, 512, 3),
+        LayerSpec("Conv10", "conv", 512, 512, 3, pool=2),
+        LayerSpec("Fc1", "fc", 0, 4096), LayerSpec("Fc2", "fc", 4096, 4096),
+        LayerSpec("Fout", "out", 4096, n_classes, quantise=False),
+    ]
+    return ModelSpec("vgg_variant", 224, 3, L)
+
+
+def resnet18_spec(n_classes: int = 1000) -> ModelSpec:
+    """APNN-TC-nn/src/resnet18.cu:40-142: 64c7s4, four stages of two basic blocks (64/128/256/512,
+    stride 2 entering stages 2-4), FC 512, out.  The residual of a block is the saved int32 value
+    of its input; where the shape changes it is a 1x1 stride-2 convolution of the block input."""
+    L = [LayerSpec("Conv1", "conv", 3, 64, 7, 4, save_residual=True)]
+    prev, cin = "Conv1", 64
+    for stage, c in enumerate((64, 128, 256, 512), start=1):
+        for blk in (1, 2):
+            tag = f"L{stage}B{blk}"
+            down = stage > 1 and blk == 1
+            L.append(LayerSpec(tag + "C1", "conv", cin, c, 3, 2 if down else 1, src=prev))
+            res = prev
+            if down:
+                L.append(LayerSpec(tag + "S", "conv", cin, c, 1, 2, src=prev, save_residual=True, quantise=False))
+                res = tag + "S"
+            L.append(LayerSpec(tag + "C2", "conv", c, c, 3, 1, src=tag + "C1", residual_from=res, save_residual=True))
+            prev, cin = tag + "C2", c
+    L += [LayerSpec("Fc1", "fc", 0, 512, src=prev), LayerSpec("Fout", "out", 512, n_classes, quantise=False)]
+    return ModelSpec("resnet18", 224, 3, L)
+
+
+MODELS = {"alexnet": alexnet_spec, "vgg_variant": vgg_variant_spec, "resnet18": resnet18_spec}
+
+
+# ----------------------------------------------------------------------------- parameters (host, seeded)
+@dataclass
+class LayerParams:
+    """Seeded random parameters of one layer in the library's layouts (numpy, host)."""
+    weight_planes: np.ndarray     # conv: [1][COUTp][R][R][CINp/32]; fc/out: [1][Np][Kp/32]
+    thresholds: Optional[np.ndarray]   # [COUTp][2^a_bit - 1] int32, or None when not quantised
+    shape: Dict[str, int] = field(default_factory=dict)
+
+
+def _pack_bits_msb(bits: np.ndarray) -> np.ndarray:
+    """[..., K] of 0/1 -> [..., K/32] uint32, element k in bit 31 - k%32."""
+    K = bits.shape[-1]
+    by = np.packbits(bits.astype(np.uint8).reshape(*bits.shape[:-1], K // 32, 32), axis=-1, bitorder="big")
+    return (by[..., 0].astype(np.uint32) << 24) | (by[..., 1].astype(np.uint32) << 16) | \
+        (by[..., 2].astype(np.uint32) << 8) | by[..., 3].astype(np.uint32)
+
+
+def fold_thresholds(scale: np.ndarray, bias: np.ndarray, mu: float, sigma: float, out_bits: int) -> np.ndarray:
+    """y = scale*(v-mu)/sigma + bias; level >= j exactly when y >= (j-0.5)*20/2^bits - 10 (the clip /
+    round quantiser of APNN-TC-nn/src/kernel.cuh:29-44), so T[c][j-1] = ceil(mu + sigma*(edge_j - bias)/scale).
+    Computed in double; the table is what host checker and kernels share."""
+    nl = (1 << out_bits) - 1
+    j = np.arange(1, nl + 1, dtype=np.float64)
+    edge = (j - 0.5) * 20.0 / float(1 << out_bits) - 10.0
+    t = mu + sigma * (edge[None, :] - bias.astype(np.float64)[:, None]) / scale.astype(np.float64)[:, None]
+    return np.clip(np.ceil(t), -2**31, INT_MAX).astype(np.int64).astype(np.int32)
+
+
+def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[int] = None) -> Dict[str, LayerParams]:
+    """Random +-1 weights (uniform bits), BN scale U[0.5,1.5] and bias U[-1,1] folded to thresholds with
+    mu = 0 and sigma = sqrt(3.5 * fan_in)/4 (variance of a +-1 x uniform-level dot product)."""
+    rng = np.random.default_rng(seed)
+    hw = image_hw or spec.image_hw
+    out: Dict[str, LayerParams] = {}
+    dims: Dict[str, tuple] = {}   # layer -> (H, W, C real) of its quantised output
+    prev = None
+    for ls in spec.layers:
+        src = ls.src or prev
+        if ls.kind == "conv":
+            H, W, _ = dims[src] if src else (hw, hw, spec.image_channels)
+            cinp, coutp = pad128(ls.cin), pad128(ls.cout)
+            bits = np.zeros((coutp, ls.R, ls.R, cinp), dtype=np.uint8)
+            bits[: ls.cout, :, :, : ls.cin] = rng.integers(0, 2, size=(ls.cout, ls.R, ls.R, ls.cin), dtype=np.uint8)
+            planes = _pack_bits_msb(bits)[None]
+            Ho, Wo = (H - 1) // ls.stride + 1, (W - 1) // ls.stride + 1
+            if ls.pool == 2:
+                Ho, Wo = Ho // 2, Wo // 2
+            fan_in = ls.R * ls.R * ls.cin
+            dims[ls.name] = (Ho, Wo, ls.cout)
+            shape = {"H": H, "W": W, "Ho": Ho, "Wo": Wo, "cinp": cinp, "coutp": coutp}
+        else:
+            if ls.kind == "fc" and ls.cin == 0:
+                H, W, C = dims[src]
+                K = H * W * pad128(C)
+                fan_in = H * W * C
+                kbits = np.zeros((pad128(ls.cout), H, W, pad128(C)), dtype=np.uint8)
+                kbits[: ls.cout, :, :, :C] = rng.integers(0, 2, size=(ls.cout, H, W, C), dtype=np.uint8)
+                kbits = kbits.reshape(pad128(ls.cout), K)
+            else:
+                K = pad128(ls.cin)
+                fan_in = ls.cin
+                kbits = np.zeros((pad128(ls.cout), K), dtype=np.uint8)
+                kbits[: ls.cout, : ls.cin] = rng.integers(0, 2, size=(ls.cout, ls.cin), dtype=np.uint8)
+            planes = _pack_bits_msb(kbits)[None]
+            coutp = pad128(ls.cout)
+            dims[ls.name] = (1, 1, ls.cout)
+            shape = {"K": K, "coutp": coutp}
+        thr = None
+        if ls.quantise:
+            scale = rng.uniform(0.5, 1.5, ls.cout).astype(np.float32)
+            bias = rng.uniform(-1.0, 1.0, ls.cout).astype(np.float32)
+            extra = 2.0 if ls.residual_from else 1.0
+            sigma = math.sqrt(3.5 * fan_in * extra) / 4.0
+            thr = np.full((coutp, (1 << spec.a_bit) - 1), INT_MAX, dtype=np.int32)
+            thr[: ls.cout] = fold_thresholds(scale, bias, 0.0, sigma, spec.a_bit)
+        out[ls.name] = LayerParams(np.ascontiguousarray(planes), thr, shape)
+        prev = ls.name
+    return out
+
+
+# ----------------------------------------------------------------------------- device runtime
+def _dev_words(a: np.ndarray, device) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int32)).to(device)
+
+
+class Network:
+    """A model list bound to device buffers: weights (packed planes, and their int8 images for the
+    tcgen05 path, expanded once), one output buffer per layer (packed planes inside the zero ring
+    its consumers need), int32 residual buffers, and one shared int8 scratch for activations.
+
+    ``forward(images)`` launches one packer and then, per layer, at most an activation expand and
+    one contraction kernel, all on the current stream; ``capture()`` records that sequence in a
+    CUDA graph for replay.
+    """
+
+    def __init__(self, spec: ModelSpec, batch: int, params: Optional[Dict[str, LayerParams]] = None,
+                 device: Optional[torch.device] = None, image_hw: Optional[int] = None, use_tcgen05: bool = True):
+        self.spec, self.batch = spec, batch
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.hw = image_hw or spec.image_hw
+        self.params = params if params is not None else make_params(spec, image_hw=self.hw)
+        self.use_tcgen05 = use_tcgen05
+        self.L = _cabi.lib()
+        self.by_name = {ls.name: ls for ls in spec.layers}
+        a = spec.a_bit
+        # ring each layer's output needs = the widest padding among its conv consumers
+        prev = None
+        self.src_of: Dict[str, Optional[str]] = {}
+        halo: Dict[Optional[str], int] = {None: 0}
+        for ls in spec.layers:
+            src = ls.src or prev
+            self.src_of[ls.name] = src
+            halo.setdefault(ls.name, 0)
+            if ls.kind == "conv":
+                halo[src] = max(halo.get(src, 0), (ls.R - 1) // 2)
+            prev = ls.name
+        self.halo = halo
+        B = batch
+        cp = pad128(spec.image_channels)
+        h0 = halo[None]
+        self.image_planes = torch.zeros((a, B, self.hw + 2 * h0, self.hw + 2 * h0, cp // 32), dtype=torch.int32,
+                                        device=self.device)
+        self.image_levels = torch.zeros((a, B, self.hw, self.hw, cp // 32), dtype=torch.int32, device=self.device)
+        self.out: Dict[str, torch.Tensor] = {}
+        self.res: Dict[str, torch.Tensor] = {}
+        self.w_planes: Dict[str, torch.Tensor] = {}
+        self.w8: Dict[str, torch.Tensor] = {}
+        self.thr: Dict[str, Optional[torch.Tensor]] = {}
+        self.tc5_ok: Dict[str, bool] = {}
+        x8_bytes = 0
+        for ls in spec.layers:
+            p = self.params[ls.name]
+            sh = p.shape
+            self.w_planes[ls.name] = _dev_words(p.weight_planes, self.device)
+            self.thr[ls.name] = _dev_words(p.thresholds, self.device) if p.thresholds is not None else None
+            src = self.src_of[ls.name]
+            if ls.kind == "conv":
+                hh = halo[ls.name]
+                if ls.quantise:
+                    self.out[ls.name] = torch.zeros((a, B, sh["Ho"] + 2 * hh, sh["Wo"] + 2 * hh, sh["coutp"] // 32),
+                                                    dtype=torch.int32, device=self.device)
+                if ls.save_residual or not ls.quantise:
+                    self.res[ls.name] = torch.zeros((B * sh["Ho"] * sh["Wo"], sh["coutp"]), dtype=torch.int32,
+                                                    device=self.device)
+                Hc, Wc = (sh["H"] - 1) // ls.stride + 1, (sh["W"] - 1) // ls.stride + 1
+                ok = use_tcgen05 and ls.stride == 1 and not (ls.pool == 2 and (Hc % 2 or Wc % 2))
+                self.tc5_ok[ls.name] = ok
+                if ok:
+                    ih = halo[src]
+                    x8_bytes = max(x8_bytes, B * (sh["H"] + 2 * ih) * (sh["W"] + 2 * ih) * sh["cinp"])
+            else:
+                self.tc5_ok[ls.name] = use_tcgen05
+                if ls.quantise:
+                    self.out[ls.name] = torch.zeros((a, B, sh["coutp"] // 32), dtype=torch.int32, device=self.device)
+                else:
+                    self.out[ls.name] = torch.zeros((B, sh["coutp"]), dtype=torch.int32, device=self.device)
+                if use_tcgen05:
+                    x8_bytes = max(x8_bytes, B * sh["K"])
+            if self.tc5_ok[ls.name]:
+                wp = self.w_planes[ls.name]
+                rows = wp.shape[1]
+                k = int(np.prod(wp.shape[2:])) * 32
+                w8 = torch.empty((rows, k), dtype=torch.uint8, device=self.device)
+                _cabi.check(self.L.apnn_expand_planes(_stream_ptr(), wp.data_ptr(), w8.data_ptr(), rows, k, 1, 1),
+                            "expand weights")
+                self.w8[ls.name] = w8
+        self.x8 = torch.empty(max(x8_bytes, 256), dtype=torch.uint8, device=self.device)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.graph = None
+        self.static_images = None
+        self.launches_per_forward = 0
+        torch.cuda.synchronize(self.device)
+
+    # -- one layer -------------------------------------------------------------------
+    def _input_of(self, name: str) -> torch.Tensor:
+        src = self.src_of[name]
+        return self.image_planes if src is None else self.out[src]
+
+    def _epilogue(self, ls: LayerSpec, conv: bool):
+        mode = "thresholds" if ls.quantise else "int32"
+        res_in = self.res[ls.residual_from] if ls.residual_from else None
+        res_out = self.res.get(ls.name) if (ls.save_residual and ls.quantise) else None
+        return make_epilogue(mode, self.spec.a_bit if ls.quantise else 0, signed="none",
+                             pool="max" if ls.pool == 2 else "none", out_halo=self.halo[ls.name] if conv else 0,
+                             in_halo=self.halo[self.src_of[ls.name]] if conv else 0, thresholds=self.thr[ls.name],
+                             residual_in=res_in, residual_out=res_out)
+
+    def _run_conv(self, ls: LayerSpec) -> int:
+        sh = self.params[ls.name].shape
+        X = self._input_of(ls.name)
+        a, B = self.spec.a_bit, self.batch
+        epi = self._epilogue(ls, True)
+        out = self.out[ls.name] if ls.quantise else self.res[ls.name]
+        s = _stream_ptr()
+        if self.tc5_ok[ls.name]:
+            rows = X.shape[1] * X.shape[2] * X.shape[3]
+            _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), rows, sh["cinp"], a, 0), "expand")
+            _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), self.x8.data_ptr(), out.data_ptr(), B,
+                                              sh["H"], sh["W"], sh["cinp"], sh["coutp"], ls.R, 1, ctypes.byref(epi),
+                                              self.flag.data_ptr()), "apnn_conv2d_i8 " + ls.name)
+            return 2
+        epi.signed_operand = _cabi.SIGN_W
+        _cabi.check(self.L.apnn_conv2d_ex(s, _cabi.ALGO_IMMA, 1, a, self.w_planes[ls.name].data_ptr(), X.data_ptr(),
+                                          out.data_ptr(), B, sh["H"], sh["W"], sh["cinp"], sh["coutp"], ls.R, ls.stride,
+                                          ctypes.byref(epi), None, 0), "apnn_conv2d_ex " + ls.name)
+        return 1
+
+    def _run_fc(self, ls: LayerSpec) -> int:
+        sh = self.params[ls.name].shape
+        X = self._input_of(ls.name)       # [a][B][...] packed, no ring
+        a, B, K, N = self.spec.a_bit, self.batch, sh["K"], sh["coutp"]
+        epi = self._epilogue(ls, False)
+        out = self.out[ls.name]
+        s = _stream_ptr()
+        if self.tc5_ok[ls.name]:
+            _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), B, K, a, 0), "expand")
+            _cabi.check(self.L.apnn_gemm_i8(s, self.x8.data_ptr(), self.w8[ls.name].data_ptr(), out.data_ptr(), B, N, K,
+                                            0, 1, ctypes.byref(epi), self.flag.data_ptr()), "apnn_gemm_i8 " + ls.name)
+            return 2
+        epi.signed_operand = _cabi.SIGN_X
+        _cabi.check(self.L.apnn_gemm_ex(s, _cabi.ALGO_IMMA, a, 1, X.data_ptr(), self.w_planes[ls.name].data_ptr(),
+                                        out.data_ptr(), B, N, K, ctypes.byref(epi), None, 0), "apnn_gemm_ex " + ls.name)
+        return 1
+
+    # -- whole model -----------------------------------------------------------------
+    def forward(self, images: torch.Tensor) -> torch.Tensor:
+        """images: float32 [B, H, W, C] on the device.  Returns int32 logits [B, PAD128(classes)]."""
+        a = self.spec.a_bit
+        s = _stream_ptr()
+        rows = self.batch * self.hw * self.hw
+        n = 1
+        h0 = self.halo[None]
+        target = self.image_levels if h0 else self.image_planes
+        _cabi.check(self.L.apnn_quantize_pack(s, images.data_ptr(), target.data_ptr(), rows, self.spec.image_channels, a),
+                    "apnn_quantize_pack")
+        if h0:
+            # place the packed image inside its zero ring (device-side strided copy)
+            self.image_planes[:, :, h0:-h0, h0:-h0].copy_(self.image_levels)
+            n += 1
+        for ls in self.spec.layers:
+            n += self._run_conv(ls) if ls.kind == "conv" else self._run_fc(ls)
+        self.launches_per_forward = n
+        return self.out[self.spec.layers[-1].name]
+
+    def capture(self, images: torch.Tensor) -> None:
+        """Record forward(images) in a CUDA graph; ``replay()`` reruns it on the same buffers."""
+        self.static_images = images
+        self.forward(images)  # warm-up: function attributes, descriptor caches
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        st = torch.cuda.Stream(device=self.device)
+        st.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(g, stream=st):
+                self.forward(images)
+        torch.cuda.synchronize(self.device)
+        self.graph = g
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.out[self.spec.layers[-1].name]
+
+    def check(self) -> None:
+        """Synchronise and raise if a tcgen05 kernel gave up on a bounded wait."""
+        torch.cuda.synchronize(self.device)
+        if int(self.flag.item()) != 0:
+            raise _cabi.ApnnError(7, "a bounded device-side wait expired")

@@ -39,7 +39,7 @@ def _dev_words(t: torch.Tensor, name: str) -> torch.Tensor:
 
 
 def make_epilogue(out_mode: str = "int32", out_bits: int = 0, signed: str = "none", pool: str = "none",
-                  out_halo: int = 0, thresholds: Optional[torch.Tensor] = None,
+                  out_halo: int = 0, in_halo: int = 0, thresholds: Optional[torch.Tensor] = None,
                   residual_in: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None) -> Epilogue:
     """Build the fused-epilogue descriptor.
 
@@ -54,6 +54,7 @@ def make_epilogue(out_mode: str = "int32", out_bits: int = 0, signed: str = "non
     e.signed_operand = {"none": 0, "w": 1, "x": 2}[signed]
     e.pool = {"none": 0, "avg": 1, "max": 2}[pool]
     e.out_halo = out_halo
+    e.in_halo = in_halo
     e.thresholds = thresholds.data_ptr() if thresholds is not None else None
     e.residual_in = residual_in.data_ptr() if residual_in is not None else None
     e.residual_out = residual_out.data_ptr() if residual_out is not None else None

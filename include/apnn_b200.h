@@ -68,7 +68,9 @@ typedef struct apnn_epilogue {
   int32_t pool;              /* APNN_POOL_* (conv only; H and W even) */
   int32_t out_halo;          /* conv only: write the output inside a zeroed ring of this many
                                 pixels, so it can feed the next conv directly */
-  int32_t reserved;
+  int32_t in_halo;           /* conv only: the stored input carries a ring of in_halo pixels;
+                                0 means exactly (R-1)/2.  Lets a 1x1 shortcut read a tensor
+                                that was written with the ring a 3x3 consumer needs. */
   const int32_t *thresholds; /* device, [channels][2^out_bits - 1] ascending; channel = n
                                 (GEMM) or output channel (conv) */
   const int32_t *residual_in; /* optional, device, dense int32 [rows][channels] (rows = M, or
@@ -169,7 +171,8 @@ apnn_status apnn_conv2d(void *stream, int wbits, int xbits, const void *Wt, cons
  * tcgen05 kind::i8, each A tile a 4-D TMA box of output pixels; APNN_ALGO_AUTO picks it when
  * the workspace is large enough and the contraction is at least ~2 GFLOP, else the
  * warp-level kernel.  apnn_conv2d_check is apnn_gemm_check for this workspace layout.
- * apnn_conv2d_i8 runs on operands already expanded by apnn_expand_planes: X8[B][H+2p][W+2p][CIN]
+ * apnn_conv2d_i8 runs on operands already expanded by apnn_expand_planes: X8[B][H+2h][W+2h][CIN]
+ * (h = epi->in_halo, or (R-1)/2 when that is 0)
  * and W8[COUT][R*R*CIN] (expand the filter once per model, the activations once per layer). */
 apnn_status apnn_conv2d_ex(void *stream, int algo, int wbits, int xbits, const void *Wt, const void *X,
                            void *Out, int B, int H, int W, int CIN, int COUT, int R, int stride,

@@ -1,0 +1,53 @@
+"""GPU parity of the model runners (AlexNet, VGG-variant, ResNet-18 layer lists) against the CPU
+restatement in net_reference.py, on reduced image sizes so the oracle finishes in seconds."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import to_host
+from net_reference import forward_reference
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("use_tcgen05", [False, True])
+@pytest.mark.parametrize("model,hw,batch", [("resnet18", 32, 3), ("alexnet", 64, 2), ("vgg_variant", 32, 2)])
+def test_model_logits_match_reference(cuda_device, model, hw, batch, use_tcgen05):
+    from apnn_tc_b200 import nets
+    spec = nets.MODELS[model](n_classes=200)
+    params = nets.make_params(spec, image_hw=hw)
+    rng = np.random.default_rng(123)
+    images = rng.uniform(-10, 10, size=(batch, hw, hw, 3)).astype(np.float32)
+    want, levels, values = forward_reference(spec, params, images)
+    net = nets.Network(spec, batch, params, image_hw=hw, use_tcgen05=use_tcgen05)
+    logits = net.forward(torch.from_numpy(images).cuda())
+    net.check()
+    assert np.array_equal(to_host(logits, np.int32), want)
+    # every hidden layer too: packed planes (inside their ring) and saved residuals
+    for ls in spec.layers:
+        if ls.kind == "conv" and ls.quantise:
+            h = net.halo[ls.name]
+            got = to_host(net.out[ls.name])
+            if h:
+                got = got[:, :, h:-h, h:-h]
+            assert np.array_equal(oracle.unpack_levels(got), levels[ls.name]), ls.name
+        if ls.name in net.res:
+            assert np.array_equal(to_host(net.res[ls.name], np.int32).reshape(values[ls.name].shape), values[ls.name]), ls.name
+    # the quantiser is exercised: more than one level occurs in the last hidden layer
+    assert len(np.unique(levels[spec.layers[-2].name])) > 1
+
+
+def test_graph_replay_matches_eager(cuda_device):
+    from apnn_tc_b200 import nets
+    spec = nets.resnet18_spec(n_classes=100)
+    net = nets.Network(spec, 4, image_hw=32)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    images = (torch.rand((4, 32, 32, 3), device="cuda", generator=g) * 20 - 10).contiguous()
+    eager = net.forward(images).clone()
+    net.capture(images)
+    images.copy_((torch.rand((4, 32, 32, 3), device="cuda", generator=g) * 20 - 10))
+    second = net.forward(images).clone()
+    replayed = net.replay().clone()
+    net.check()
+    assert torch.equal(replayed, second) and not torch.equal(eager, second)
