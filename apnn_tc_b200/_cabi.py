@@ -22,7 +22,7 @@ ALGOS = {"auto": ALGO_AUTO, "bmma": ALGO_BMMA, "imma": ALGO_IMMA, "tcgen05": ALG
 EXPORTS = (
     "apnn_status_string", "apnn_last_cuda_error", "apnn_version", "apnn_gemm", "apnn_gemm_ex",
     "apnn_gemm_workspace_bytes", "apnn_gemm_check", "apnn_expand_planes", "apnn_gemm_i8", "apnn_gemm_static_scratch", "apnn_conv2d", "apnn_conv2d_ex",
-    "apnn_conv2d_workspace_bytes", "apnn_conv2d_check", "apnn_conv2d_i8", "apnn_bit_compress", "apnn_quantize_pack", "apnn_create",
+    "apnn_conv2d_workspace_bytes", "apnn_conv2d_check", "apnn_conv2d_i8", "apnn_bit_compress", "apnn_quantize_pack", "apnn_quantize_im2col", "apnn_create",
     "apnn_destroy", "apnn_gemm_host", "apnn_conv2d_host", "apnn_probe_peak",
 )
 
@@ -81,6 +81,7 @@ def lib() -> ctypes.CDLL:
     L.apnn_bit_compress.argtypes = [vp, vp, vp, lg, i, i]
     L.apnn_quantize_pack.argtypes = [vp, vp, vp, lg, i, i]
     L.apnn_probe_peak.argtypes = [vp, i, i, vp, ctypes.POINTER(ctypes.c_double)]
+    L.apnn_quantize_im2col.argtypes = [vp, vp, vp, i, i, i, i, i, i, i]
     L.apnn_create.argtypes = [ctypes.POINTER(vp), i]
     L.apnn_destroy.argtypes = [vp]
     L.apnn_gemm_host.argtypes = [vp, i, i, i, vp, vp, vp, i, i, i, ep]

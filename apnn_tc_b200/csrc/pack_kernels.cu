@@ -71,14 +71,88 @@ __global__ void __launch_bounds__(256) pack_planes_kernel(const void* __restrict
   }
 }
 
+// Rows of at most 32 channels (the 3-channel image of a first layer): one thread per row
+// builds the single non-zero word of every plane and stores the row's four words at once.
+template <bool FROM_FLOAT>
+__global__ void __launch_bounds__(256) pack_narrow_rows_kernel(const void* __restrict__ in,
+                                                               uint32_t* __restrict__ planes, long long rows, int C,
+                                                               int bits) {
+  const float steps = (float)(1 << bits);
+  const uint32_t maxlv = (1u << bits) - 1u;
+  for (long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x; row < rows;
+       row += (long long)gridDim.x * blockDim.x) {
+    uint32_t word[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    for (int c = 0; c < C; c++) {
+      uint32_t lv;
+      if (FROM_FLOAT) lv = quantize_level(__ldg(reinterpret_cast<const float*>(in) + row * C + c), steps, maxlv);
+      else lv = __ldg(reinterpret_cast<const uint32_t*>(in) + row * C + c);
+#pragma unroll
+      for (int b = 0; b < 8; b++) word[b] |= ((lv >> b) & 1u) << (31 - c);
+    }
+#pragma unroll
+    for (int b = 0; b < 8; b++)
+      if (b < bits) reinterpret_cast<uint4*>(planes)[(long long)b * rows + row] = make_uint4(word[b], 0u, 0u, 0u);
+  }
+}
+
+// First-layer re-layout: quantise a float NHWC image and gather every output pixel's R x R x C
+// window into channels, k = (i*R + j)*C + c, zero outside the image and beyond R*R*C up to the
+// next multiple of 128.  The convolution then becomes a 1x1 convolution over R*R*C "channels"
+// instead of one over C padded to 128 (42x less contraction work for a 3-channel image).
+// One thread builds one 32-k word of every plane of one output pixel.
+__global__ void __launch_bounds__(256) quantize_im2col_kernel(const float* __restrict__ img,
+                                                              uint32_t* __restrict__ planes, int B, int H, int W,
+                                                              int C, int R, int stride, int bits, int Ho, int Wo,
+                                                              int kwords) {
+  const float steps = (float)(1 << bits);
+  const uint32_t maxlv = (1u << bits) - 1u;
+  const int pad = (R - 1) / 2;
+  const int kreal = R * R * C;
+  const long long pixels = (long long)B * Ho * Wo;
+  const long long total = pixels * kwords;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+       t += (long long)gridDim.x * blockDim.x) {
+    const long long pix = t / kwords;
+    const int w = (int)(t - pix * kwords);
+    const int wo = (int)(pix % Wo);
+    const long long t2 = pix / Wo;
+    const int ho = (int)(t2 % Ho);
+    const int b = (int)(t2 / Ho);
+    uint32_t word[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    for (int e = 0; e < 32; e++) {
+      const int k = w * 32 + e;
+      if (k >= kreal) break;
+      const int tap = k / C, c = k - tap * C;
+      const int i = tap / R, j = tap - i * R;
+      const int hi = ho * stride + i - pad, wi = wo * stride + j - pad;
+      if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
+      const uint32_t lv = quantize_level(__ldg(img + (((long long)b * H + hi) * W + wi) * C + c), steps, maxlv);
+#pragma unroll
+      for (int p = 0; p < 8; p++) word[p] |= ((lv >> p) & 1u) << (31 - e);
+    }
+#pragma unroll
+    for (int p = 0; p < 8; p++)
+      if (p < bits) planes[(long long)p * total + t] = word[p];
+  }
+}
+
 template <bool FROM_FLOAT>
 apnn_status launch_pack(void* stream, const void* in, uint32_t* planes, long rows, int C, int bits) {
   if (!in || !planes) return APNN_ERR_INVALID_ARG;
   if (rows <= 0 || C <= 0 || bits < 1 || bits > 8) return APNN_ERR_INVALID_ARG;
   if ((reinterpret_cast<uintptr_t>(in) & 15u) || (reinterpret_cast<uintptr_t>(planes) & 15u)) return APNN_ERR_ALIGNMENT;
+  long long cap = (long long)device_sm_count() * 8;
+  if (C <= 32) {
+    long long nb = (rows + 255) / 256;
+    if (nb > cap) nb = cap;
+    pack_narrow_rows_kernel<FROM_FLOAT><<<(unsigned)nb, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(in, planes, rows,
+                                                                                                        C, bits);
+    cudaError_t e0 = cudaGetLastError();
+    if (e0 != cudaSuccess) return cuda_fail(e0, "pack_narrow_rows launch");
+    return APNN_OK;
+  }
   long long tasks = (long long)rows * ((C + 127) / 128);
   long long blocks = (tasks + 7) / 8;
-  long long cap = (long long)device_sm_count() * 8;
   if (blocks > cap) blocks = cap;
   pack_planes_kernel<FROM_FLOAT><<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(in, planes, rows,
                                                                                                      C, bits);
@@ -98,6 +172,25 @@ apnn_status apnn_bit_compress(void* stream, const uint32_t* levels, uint32_t* pl
 
 apnn_status apnn_quantize_pack(void* stream, const float* values, uint32_t* planes, long rows, int C, int bits) {
   return apnn::launch_pack<true>(stream, values, planes, rows, C, bits);
+}
+
+apnn_status apnn_quantize_im2col(void* stream, const float* images, uint32_t* planes, int B, int H, int W, int C,
+                                 int R, int stride, int bits) {
+  using namespace apnn;
+  if (!images || !planes) return APNN_ERR_INVALID_ARG;
+  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || bits < 1 || bits > 8) return APNN_ERR_INVALID_ARG;
+  if (R < 1 || R > 11 || (R & 1) == 0 || stride < 1 || stride > 4) return APNN_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(images) & 15u) || (reinterpret_cast<uintptr_t>(planes) & 15u)) return APNN_ERR_ALIGNMENT;
+  const int Ho = (H - 1) / stride + 1, Wo = (W - 1) / stride + 1;
+  const int kwords = (R * R * C + 127) / 128 * 4;
+  const long long total = (long long)B * Ho * Wo * kwords;
+  long long nb = (total + 255) / 256, cap = (long long)device_sm_count() * 16;
+  if (nb > cap) nb = cap;
+  quantize_im2col_kernel<<<(unsigned)nb, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(images, planes, B, H, W, C, R,
+                                                                                          stride, bits, Ho, Wo, kwords);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "quantize_im2col launch");
+  return APNN_OK;
 }
 
 }  // extern "C"

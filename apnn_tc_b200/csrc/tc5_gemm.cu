@@ -417,12 +417,30 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (!row_ok) continue;
         if (p.residual_in != nullptr || p.residual_out != nullptr) {
           const long long at = dst.dense * (long long)p.N + col0;
+          if ((p.N & 3) == 0 && col0 + 32 <= p.N) {
+            // this thread's 32 columns are 128 contiguous bytes: 16-byte accesses
+            if (p.residual_in != nullptr) {
+              const int4* R4 = reinterpret_cast<const int4*>(p.residual_in + at);
 #pragma unroll
-          for (int j = 0; j < 32; j++)
-            if (col0 + j < p.N) {
-              if (p.residual_in != nullptr) v[j] = (uint32_t)((int)v[j] + __ldg(p.residual_in + at + j));
-              if (p.residual_out != nullptr) p.residual_out[at + j] = (int32_t)v[j];
+              for (int j = 0; j < 8; j++) {
+                const int4 r = __ldg(R4 + j);
+                v[4 * j] += (uint32_t)r.x; v[4 * j + 1] += (uint32_t)r.y;
+                v[4 * j + 2] += (uint32_t)r.z; v[4 * j + 3] += (uint32_t)r.w;
+              }
             }
+            if (p.residual_out != nullptr) {
+              uint4* O4 = reinterpret_cast<uint4*>(p.residual_out + at);
+#pragma unroll
+              for (int j = 0; j < 8; j++) O4[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < p.N) {
+                if (p.residual_in != nullptr) v[j] = (uint32_t)((int)v[j] + __ldg(p.residual_in + at + j));
+                if (p.residual_out != nullptr) p.residual_out[at + j] = (int32_t)v[j];
+              }
+          }
         }
         if (p.out_mode == OUT_INT32) {
           int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;

@@ -126,6 +126,7 @@ class LayerParams:
     weight_planes: np.ndarray     # conv: [1][COUTp][R][R][CINp/32]; fc/out: [1][Np][Kp/32]
     thresholds: Optional[np.ndarray]   # [COUTp][2^a_bit - 1] int32, or None when not quantised
     shape: Dict[str, int] = field(default_factory=dict)
+    im2col_planes: Optional[np.ndarray] = None   # first layer only: [1][COUTp][PAD128(R*R*C)/32], k = (i*R+j)*C+c
 
 
 def _pack_bits_msb(bits: np.ndarray) -> np.ndarray:
@@ -163,6 +164,12 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
             bits = np.zeros((coutp, ls.R, ls.R, cinp), dtype=np.uint8)
             bits[: ls.cout, :, :, : ls.cin] = rng.integers(0, 2, size=(ls.cout, ls.R, ls.R, ls.cin), dtype=np.uint8)
             planes = _pack_bits_msb(bits)[None]
+            im2col = None
+            if src is None:   # the same filter with the real channels only, laid out for the im2col first layer
+                kp = pad128(ls.R * ls.R * ls.cin)
+                flat = np.zeros((coutp, kp), dtype=np.uint8)
+                flat[:, : ls.R * ls.R * ls.cin] = bits[:, :, :, : ls.cin].reshape(coutp, -1)
+                im2col = np.ascontiguousarray(_pack_bits_msb(flat)[None])
             Ho, Wo = (H - 1) // ls.stride + 1, (W - 1) // ls.stride + 1
             if ls.pool == 2:
                 Ho, Wo = Ho // 2, Wo // 2
@@ -195,6 +202,8 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
             thr = np.full((coutp, (1 << spec.a_bit) - 1), INT_MAX, dtype=np.int32)
             thr[: ls.cout] = fold_thresholds(scale, bias, 0.0, sigma, spec.a_bit)
         out[ls.name] = LayerParams(np.ascontiguousarray(planes), thr, shape)
+        if ls.kind == "conv" and src is None:
+            out[ls.name].im2col_planes = im2col
         prev = ls.name
     return out
 
@@ -239,15 +248,13 @@ class Network:
         B = batch
         cp = pad128(spec.image_channels)
         h0 = halo[None]
-        self.image_planes = torch.zeros((a, B, self.hw + 2 * h0, self.hw + 2 * h0, cp // 32), dtype=torch.int32,
-                                        device=self.device)
-        self.image_levels = torch.zeros((a, B, self.hw, self.hw, cp // 32), dtype=torch.int32, device=self.device)
         self.out: Dict[str, torch.Tensor] = {}
         self.res: Dict[str, torch.Tensor] = {}
         self.w_planes: Dict[str, torch.Tensor] = {}
         self.w8: Dict[str, torch.Tensor] = {}
         self.thr: Dict[str, Optional[torch.Tensor]] = {}
         self.tc5_ok: Dict[str, bool] = {}
+        self.first_im2col = None
         x8_bytes = 0
         for ls in spec.layers:
             p = self.params[ls.name]
@@ -264,9 +271,18 @@ class Network:
                     self.res[ls.name] = torch.zeros((B * sh["Ho"] * sh["Wo"], sh["coutp"]), dtype=torch.int32,
                                                     device=self.device)
                 Hc, Wc = (sh["H"] - 1) // ls.stride + 1, (sh["W"] - 1) // ls.stride + 1
-                ok = use_tcgen05 and ls.stride == 1 and not (ls.pool == 2 and (Hc % 2 or Wc % 2))
+                pool_ok = not (ls.pool == 2 and (Hc % 2 or Wc % 2))
+                ok = use_tcgen05 and ls.stride == 1 and pool_ok
+                if src is None and use_tcgen05 and pool_ok and p.im2col_planes is not None:
+                    # first layer: windows gathered into channels, then a 1x1 convolution on tcgen05
+                    kp = p.im2col_planes.shape[-1] * 32
+                    self.first_im2col = (ls.name, Hc, Wc, kp)
+                    self.im2col_planes = torch.zeros((a, B, Hc, Wc, kp // 32), dtype=torch.int32, device=self.device)
+                    self.w_planes[ls.name] = _dev_words(p.im2col_planes, self.device)
+                    x8_bytes = max(x8_bytes, B * Hc * Wc * kp)
+                    ok = True
                 self.tc5_ok[ls.name] = ok
-                if ok:
+                if ok and not (self.first_im2col and self.first_im2col[0] == ls.name):
                     ih = halo[src]
                     x8_bytes = max(x8_bytes, B * (sh["H"] + 2 * ih) * (sh["W"] + 2 * ih) * sh["cinp"])
             else:
@@ -285,6 +301,11 @@ class Network:
                 _cabi.check(self.L.apnn_expand_planes(_stream_ptr(), wp.data_ptr(), w8.data_ptr(), rows, k, 1, 1),
                             "expand weights")
                 self.w8[ls.name] = w8
+        if self.first_im2col is None:
+            self.image_planes = torch.zeros((a, B, self.hw + 2 * h0, self.hw + 2 * h0, cp // 32), dtype=torch.int32,
+                                            device=self.device)
+            self.image_levels = torch.zeros((a, B, self.hw, self.hw, cp // 32), dtype=torch.int32,
+                                            device=self.device) if h0 else None
         self.x8 = torch.empty(max(x8_bytes, 256), dtype=torch.uint8, device=self.device)
         self.flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.graph = None
@@ -295,7 +316,9 @@ class Network:
     # -- one layer -------------------------------------------------------------------
     def _input_of(self, name: str) -> torch.Tensor:
         src = self.src_of[name]
-        return self.image_planes if src is None else self.out[src]
+        if src is None:
+            return self.im2col_planes if self.first_im2col else self.image_planes
+        return self.out[src]
 
     def _epilogue(self, ls: LayerSpec, conv: bool):
         mode = "thresholds" if ls.quantise else "int32"
@@ -313,6 +336,15 @@ class Network:
         epi = self._epilogue(ls, True)
         out = self.out[ls.name] if ls.quantise else self.res[ls.name]
         s = _stream_ptr()
+        if self.first_im2col and self.first_im2col[0] == ls.name:
+            _, Hc, Wc, kp = self.first_im2col
+            epi.in_halo = 0
+            _cabi.check(self.L.apnn_expand_planes(s, self.im2col_planes.data_ptr(), self.x8.data_ptr(), B * Hc * Wc, kp,
+                                                  a, 0), "expand")
+            _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), self.x8.data_ptr(), out.data_ptr(), B,
+                                              Hc, Wc, kp, sh["coutp"], 1, 1, ctypes.byref(epi), self.flag.data_ptr()),
+                        "apnn_conv2d_i8 " + ls.name)
+            return 2
         if self.tc5_ok[ls.name]:
             rows = X.shape[1] * X.shape[2] * X.shape[3]
             _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), rows, sh["cinp"], a, 0), "expand")
@@ -351,13 +383,19 @@ class Network:
         rows = self.batch * self.hw * self.hw
         n = 1
         h0 = self.halo[None]
-        target = self.image_levels if h0 else self.image_planes
-        _cabi.check(self.L.apnn_quantize_pack(s, images.data_ptr(), target.data_ptr(), rows, self.spec.image_channels, a),
-                    "apnn_quantize_pack")
-        if h0:
-            # place the packed image inside its zero ring (device-side strided copy)
-            self.image_planes[:, :, h0:-h0, h0:-h0].copy_(self.image_levels)
-            n += 1
+        if self.first_im2col:
+            first = self.by_name[self.first_im2col[0]]
+            _cabi.check(self.L.apnn_quantize_im2col(s, images.data_ptr(), self.im2col_planes.data_ptr(), self.batch,
+                                                    self.hw, self.hw, self.spec.image_channels, first.R, first.stride, a),
+                        "apnn_quantize_im2col")
+        else:
+            target = self.image_levels if h0 else self.image_planes
+            _cabi.check(self.L.apnn_quantize_pack(s, images.data_ptr(), target.data_ptr(), rows,
+                                                  self.spec.image_channels, a), "apnn_quantize_pack")
+            if h0:
+                # place the packed image inside its zero ring (device-side strided copy)
+                self.image_planes[:, :, h0:-h0, h0:-h0].copy_(self.image_levels)
+                n += 1
         for ls in self.spec.layers:
             n += self._run_conv(ls) if ls.kind == "conv" else self._run_fc(ls)
         self.launches_per_forward = n

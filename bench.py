@@ -391,6 +391,91 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------- network workloads
+NET_BATCH = {"resnet18": 1024, "vgg_variant": 1024, "alexnet": 128}
+
+
+def run_net(args) -> None:
+    """images/s of a whole w1a2 network (BASELINE configs 4/5): global batch sharded over the ranks
+    (no collective), one CUDA-graph replay of the layer sequence per step."""
+    import numpy as np
+    import torch
+    from apnn_tc_b200 import nets
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    else:
+        torch.cuda.set_device(0)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gb = args.batch or NET_BATCH[args.workload]
+    batch = gb // world
+    spec = nets.MODELS[args.workload]()
+    net = nets.Network(spec, batch, device=dev, use_tcgen05=(args.algo == "tcgen05"))
+    g = torch.Generator(device=dev).manual_seed(0xA9117C + 5 + rank)
+    images = (torch.rand((batch, spec.image_hw, spec.image_hw, 3), device=dev, generator=g) * 20 - 10).contiguous()
+    net.capture(images)
+    for _ in range(args.warmup):
+        net.replay()
+    net.check()
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    net.replay()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    wall0 = time.perf_counter()
+    t0.record()
+    for _ in range(args.steps):
+        net.replay()
+    t1.record()
+    torch.cuda.synchronize()
+    wall1 = time.perf_counter()
+    if dist is not None:
+        dist.barrier()
+    net.check()
+    ms = t0.elapsed_time(t1) / args.steps
+    # end to end: pinned host images in, logits out, through the same layer sequence
+    himg = images.cpu().pin_memory()
+    hlog = torch.empty(net.out[spec.layers[-1].name].shape, dtype=torch.int32).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+    torch.cuda.synchronize()
+    c0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        images.copy_(himg, non_blocking=True)
+        net.replay()
+        hlog.copy_(net.out[spec.layers[-1].name], non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - c0) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([ms, e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+    clocks = sampler.stop(wall0, wall1) if sampler is not None else None
+    if rank == 0:
+        line = {
+            "metric": f"{args.workload}_w1a2_images_per_s", "value": batch * world / (ms * 1e-3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u8 operands, int32 accumulate (exact)",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}_w1a2_224x224x3", "global_batch": batch * world,
+                       "per_gpu_batch": batch, "algo": args.algo, "sharding": "batch-sharded, no collective",
+                       "l2": "activations of one step exceed L2 at this batch"},
+            "e2e": {"value": batch * world / e2e_s, "unit": "images/s", "h2d_bytes_per_step": himg.numel() * 4,
+                    "d2h_bytes_per_step": hlog.numel() * 4, "steps": e2e_steps},
+            "gpu_launches": net.launches_per_forward * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap_ = argparse.ArgumentParser()
     ap_.add_argument("--gpus", type=int, default=1)
@@ -400,10 +485,17 @@ def main() -> None:
     ap_.add_argument("--algo", default="tcgen05", choices=["tcgen05", "imma", "bmma"])
     ap_.add_argument("--profile", action="store_true",
                      help="timed steps only (no e2e, probe or CPU baseline): the command ncu captures")
+    ap_.add_argument("--workload", default="gemm", choices=["gemm", "resnet18", "vgg_variant", "alexnet"],
+                     help="gemm (default, the headline line) or a whole w1a2 network (images/s)")
+    ap_.add_argument("--batch", type=int, default=0, help="global batch of a network workload")
     args = ap_.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "gemm":
+        if args.steps == 200:
+            args.steps = 20
+        run_net(args)
     else:
         run_ours(args)
 

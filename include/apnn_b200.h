@@ -195,6 +195,14 @@ apnn_status apnn_bit_compress(void *stream, const uint32_t *levels, uint32_t *pl
                               int C, int bits);
 apnn_status apnn_quantize_pack(void *stream, const float *values, uint32_t *planes, long rows,
                                int C, int bits);
+/* First-layer variant of the pair above: quantises a float NHWC image [B][H][W][C] and lays
+ * every output pixel's RxRxC window (symmetric padding (R-1)/2, given stride) out along the
+ * channel axis: planes[bits][B][Ho][Wo][PAD128(R*R*C)/32], element k = (i*R + j)*C + c, zero
+ * where the window leaves the image.  A first layer (3 channels, 7x7 or 11x11 filter:
+ * NN/alexnet.cu:43-45, NN/resnet18.cu:40-42) then runs as a 1x1 convolution over R*R*C channels
+ * with the filter rows in the same k order, instead of over C padded to 128. */
+apnn_status apnn_quantize_im2col(void *stream, const float *images, uint32_t *planes, int B, int H,
+                                 int W, int C, int R, int stride, int bits);
 
 /* ---- measurement aid ------------------------------------------------------------
  * Launches an operand-resident issue loop of one contraction instruction on every SM and

@@ -328,3 +328,16 @@ def bit_compress(lv, bits):
     out = np.zeros((bits,) + lv.shape[:-1] + (cw,), dtype=np.uint32)
     lib().apnn_oracle_bit_compress(pl, out.ctypes.data_as(_u32p), ctypes.c_long(rows), C, bits)
     return out
+
+
+def quantize_im2col(images, R, stride, bits):
+    """First-layer re-layout: quantised RxRxC windows along the channel axis,
+    planes[bits][B][Ho][Wo][PAD128(R*R*C)/32]."""
+    images = np.ascontiguousarray(images, dtype=np.float32)
+    B, H, Wd, C = images.shape
+    Ho, Wo = (H - 1) // stride + 1, (Wd - 1) // stride + 1
+    kw = (R * R * C + 127) // 128 * 4
+    out = np.zeros((bits, B, Ho, Wo, kw), dtype=np.uint32)
+    lib().apnn_oracle_quantize_im2col(images.ctypes.data_as(_f32p), out.ctypes.data_as(_u32p), B, H, Wd, C, R, stride,
+                                      bits)
+    return out

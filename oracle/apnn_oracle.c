@@ -459,3 +459,32 @@ void apnn_oracle_fold_bn(const float *scale, const float *bias, double mu, doubl
       T[(long)c * nl + (j - 1)] = (int32_t)ct;
     }
 }
+
+/* First-layer re-layout (project-defined, unpinned): Quantize_val on every element, then each
+ * output pixel's RxRxC window laid along the channel axis, k = (i*R + j)*C + c, zeros outside
+ * the image and up to PAD128(R*R*C).  planes[bits][B][Ho][Wo][Kp/32], element k in bit 31-k%32. */
+void apnn_oracle_quantize_im2col(const float *img, uint32_t *planes, int B, int H, int Wd, int C,
+                                 int R, int stride, int bits) {
+  int pad = (R - 1) / 2;
+  int Ho = (H - 1) / stride + 1, Wo = (Wd - 1) / stride + 1;
+  long kw = ((long)R * R * C + 127) / 128 * 4;
+  long pixels = (long)B * Ho * Wo;
+  memset(planes, 0, sizeof(uint32_t) * (size_t)bits * pixels * kw);
+  for (int b = 0; b < B; b++)
+    for (int ho = 0; ho < Ho; ho++)
+      for (int wo = 0; wo < Wo; wo++) {
+        long pix = ((long)b * Ho + ho) * Wo + wo;
+        for (int i = 0; i < R; i++)
+          for (int j = 0; j < R; j++) {
+            int hi = ho * stride + i - pad, wi = wo * stride + j - pad;
+            if (hi < 0 || hi >= H || wi < 0 || wi >= Wd) continue;
+            for (int c = 0; c < C; c++) {
+              uint32_t lv;
+              apnn_oracle_quantize(img + (((long)b * H + hi) * Wd + wi) * C + c, &lv, 1, bits);
+              long k = ((long)i * R + j) * C + c;
+              for (int p = 0; p < bits; p++)
+                if ((lv >> p) & 1u) planes[((long)p * pixels + pix) * kw + k / 32] |= 1u << (31 - (k % 32));
+            }
+          }
+      }
+}

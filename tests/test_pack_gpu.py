@@ -30,3 +30,20 @@ def test_images_quantization(cuda_device, shape, bits):
     flat[: min(64, flat.size)] = (-10 + step * (np.arange(min(64, flat.size)) % ((1 << bits) * 2 + 1)) / 2).astype(np.float32)
     got = to_host(ap.images_quantization(torch.from_numpy(x).cuda(), bits))
     assert np.array_equal(got, oracle.bit_compress(oracle.quantize(x, bits), bits))
+
+
+@pytest.mark.parametrize("B,H,Wd,C,R,stride,bits", [(2, 9, 7, 3, 3, 2, 2), (3, 32, 32, 3, 7, 4, 2), (2, 20, 24, 3, 11, 4, 2),
+                                                    (1, 8, 8, 5, 5, 1, 4), (2, 6, 6, 40, 3, 1, 2)])
+def test_quantize_im2col(cuda_device, B, H, Wd, C, R, stride, bits):
+    """First-layer re-layout: quantised RxRxC windows gathered along the channel axis."""
+    import ctypes
+    from apnn_tc_b200 import _cabi
+    rng = np.random.default_rng(B + H + R)
+    x = rng.uniform(-12, 12, size=(B, H, Wd, C)).astype(np.float32)
+    want = oracle.quantize_im2col(x, R, stride, bits)
+    out = torch.full(want.shape, -1, dtype=torch.int32, device="cuda")
+    xd = torch.from_numpy(x).cuda()
+    st = _cabi.lib().apnn_quantize_im2col(torch.cuda.current_stream().cuda_stream, xd.data_ptr(), out.data_ptr(), B, H, Wd,
+                                          C, R, stride, bits)
+    _cabi.check(st, "apnn_quantize_im2col")
+    assert np.array_equal(to_host(out), want)
