@@ -77,7 +77,7 @@ def lib() -> ctypes.CDLL:
     L.apnn_conv2d_workspace_bytes.restype = sz
     L.apnn_conv2d_workspace_bytes.argtypes = [i, i, i, i, i, i, i]
     L.apnn_conv2d_check.argtypes = [vp, vp, i, i, i, i, i, i]
-    L.apnn_conv2d_i8.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, ep, vp]
+    L.apnn_conv2d_i8.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, i, ep, vp]
     L.apnn_bit_compress.argtypes = [vp, vp, vp, lg, i, i]
     L.apnn_quantize_pack.argtypes = [vp, vp, vp, lg, i, i]
     L.apnn_probe_peak.argtypes = [vp, i, i, vp, ctypes.POINTER(ctypes.c_double)]

@@ -178,7 +178,7 @@ apnn_status apnn_conv2d_check(void* stream, const void* workspace, int B, int H,
 }
 
 apnn_status apnn_conv2d_i8(void* stream, const void* W8, const void* X8, void* Out, int B, int H, int W, int CIN,
-                           int COUT, int R, int w_signed, const apnn_epilogue* epi, int* status_flag) {
+                           int COUT, int R, int stride, int w_signed, const apnn_epilogue* epi, int* status_flag) {
   if (!W8 || !X8 || !Out || !status_flag) return APNN_ERR_INVALID_ARG;
   if (B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
   if (R < 1 || R > 11 || (R & 1) == 0) return APNN_ERR_UNSUPPORTED;
@@ -187,12 +187,14 @@ apnn_status apnn_conv2d_i8(void* stream, const void* W8, const void* X8, void* O
     if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;  // the sign is in the bytes
     apnn_status st = check_epilogue(epi, COUT, true, 1, 1);
     if (st != APNN_OK) return st;
-    if (epi->pool != APNN_POOL_NONE && ((H & 1) || (W & 1))) return APNN_ERR_UNSUPPORTED;
+    if (epi->pool != APNN_POOL_NONE && ((((H - 1) / (stride > 0 ? stride : 1) + 1) & 1) ||
+                                        (((W - 1) / (stride > 0 ? stride : 1) + 1) & 1)))
+      return APNN_ERR_UNSUPPORTED;
     if (epi->in_halo != 0 && epi->in_halo < (R - 1) / 2) return APNN_ERR_INVALID_ARG;
   }
-  if (!tc5_conv_supported(H, W, R, 1, epi ? epi->pool : APNN_POOL_NONE)) return APNN_ERR_UNSUPPORTED;
+  if (!tc5_conv_supported(H, W, R, stride, epi ? epi->pool : APNN_POOL_NONE)) return APNN_ERR_UNSUPPORTED;
   return tc5_conv_i8(reinterpret_cast<cudaStream_t>(stream), (const uint8_t*)X8, (const uint8_t*)W8, Out, B, H, W,
-                     CIN, COUT, R, w_signed != 0, epi, status_flag);
+                     CIN, COUT, R, stride, w_signed != 0, epi, status_flag);
 }
 
 apnn_status apnn_conv2d(void* stream, int wbits, int xbits, const void* Wt, const void* X, void* Out, int B, int H,
@@ -237,7 +239,7 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
     if (!workspace || workspace_bytes < tc5_conv_workspace_bytes(B, H, Wd, CIN, COUT, R)) return APNN_ERR_WORKSPACE;
     if (!aligned16(workspace)) return APNN_ERR_ALIGNMENT;
     return tc5_conv(reinterpret_cast<cudaStream_t>(stream), wbits, xbits, (const uint32_t*)Wt, (const uint32_t*)X, Out,
-                    B, H, Wd, CIN, COUT, R, epi, workspace);
+                    B, H, Wd, CIN, COUT, R, stride, epi, workspace);
   }
 
   CoreParams p;

@@ -119,16 +119,25 @@ __global__ void __launch_bounds__(256) quantize_im2col_kernel(const float* __res
     const int ho = (int)(t2 % Ho);
     const int b = (int)(t2 / Ho);
     uint32_t word[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-    for (int e = 0; e < 32; e++) {
-      const int k = w * 32 + e;
-      if (k >= kreal) break;
-      const int tap = k / C, c = k - tap * C;
-      const int i = tap / R, j = tap - i * R;
-      const int hi = ho * stride + i - pad, wi = wo * stride + j - pad;
-      if (hi < 0 || hi >= H || wi < 0 || wi >= W) continue;
-      const uint32_t lv = quantize_level(__ldg(img + (((long long)b * H + hi) * W + wi) * C + c), steps, maxlv);
+    int k = w * 32;
+    if (k < kreal) {
+      // walk (tap row i, tap column j, channel c) incrementally: two divisions per word, none per element
+      int tap = k / C, c = k - tap * C;
+      int i = tap / R, j = tap - i * R;
+      const int hbase = ho * stride - pad, wbase = wo * stride - pad;
+      const float* ib = img + (long long)b * H * W * C;
+      for (int e = 0; e < 32 && k < kreal; e++, k++) {
+        const int hi = hbase + i, wi = wbase + j;
+        if (hi >= 0 && hi < H && wi >= 0 && wi < W) {
+          const uint32_t lv = quantize_level(__ldg(ib + ((long long)hi * W + wi) * C + c), steps, maxlv);
 #pragma unroll
-      for (int p = 0; p < 8; p++) word[p] |= ((lv >> p) & 1u) << (31 - e);
+          for (int p = 0; p < 8; p++) word[p] |= ((lv >> p) & 1u) << (31 - e);
+        }
+        if (++c == C) {
+          c = 0;
+          if (++j == R) { j = 0; ++i; }
+        }
+      }
     }
 #pragma unroll
     for (int p = 0; p < 8; p++)

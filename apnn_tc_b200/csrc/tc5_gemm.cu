@@ -191,6 +191,7 @@ struct Tc5Params {
   int Bn, Ho, Wo;        // batch and conv output extent (before pooling)
   int cblocks, R;        // CIN / 128, filter size
   int in_off;            // stored ring width minus (R-1)/2
+  int stride;            // conv stride (1 or 2)
   int pool, out_h, out_w, out_halo;
   uint32_t a_box_bytes;  // bytes one A box deposits
   const int32_t* residual_in;  // optional dense int32 [rows][N], added before requantisation
@@ -319,7 +320,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           } else {
             mbar_expect_tx(full_bar(s), p.a_box_bytes + Cfg::B_STAGE_BYTES);
             const int ti = tap / p.R, tj = tap - ti * p.R;
-            tma_load_4d(sa, &map_a, cb * BK, w0 + tj + p.in_off, h0 + ti + p.in_off, b0, full_bar(s));
+            tma_load_4d(sa, &map_a, cb * BK, w0 * p.stride + tj + p.in_off, h0 * p.stride + ti + p.in_off, b0, full_bar(s));
             if (++cb == p.cblocks) { cb = 0; tap++; }
           }
           tma_load_2d(sa + A_STAGE_BYTES, &map_b, kb * BK, tn * BN, full_bar(s));
@@ -532,13 +533,15 @@ bool make_operand_map(CUtensorMap* map, const void* base, long long rows, long l
 }
 
 // int8 NHWC activations [B][Hp][Wp][CIN]; box = 128 channels x bw x bh x bb pixels
-bool make_activation_map(CUtensorMap* map, const void* base, int B, int Hp, int Wp, int CIN, int bw, int bh, int bb) {
+// With a traversal stride s the box spans bw*s x bh*s stored pixels and picks every s-th one.
+bool make_activation_map(CUtensorMap* map, const void* base, int B, int Hp, int Wp, int CIN, int bw, int bh, int bb,
+                         int stride) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t dims[4] = {(cuuint64_t)CIN, (cuuint64_t)Wp, (cuuint64_t)Hp, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)CIN, (cuuint64_t)Wp * CIN, (cuuint64_t)Hp * Wp * CIN};
-  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bb};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)(bw * stride), (cuuint32_t)(bh * stride), (cuuint32_t)bb};
+  cuuint32_t estr[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -683,17 +686,20 @@ size_t tc5_conv_workspace_bytes(int B, int H, int W, int CIN, int COUT, int R) {
          256;
 }
 
+// H, W: input extent (without ring).  Strides 1 and 2 (the TMA box extent bw*stride must stay <= 256).
 bool tc5_conv_supported(int H, int W, int R, int stride, int pool) {
-  if (stride != 1) return false;
+  if (stride != 1 && stride != 2) return false;
   int bw, bh, bb;
-  return tc5_conv_box(H, W, pool, &bw, &bh, &bb);
+  return tc5_conv_box((H - 1) / stride + 1, (W - 1) / stride + 1, pool, &bw, &bh, &bb);
 }
 
-apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int H, int W,
-                        int CIN, int COUT, int R, bool w_signed, const apnn_epilogue* epi, int* status_flag) {
+apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int Hin, int Win,
+                        int CIN, int COUT, int R, int stride, bool w_signed, const apnn_epilogue* epi,
+                        int* status_flag) {
   const int pad = (R - 1) / 2;
   const int in_halo = (epi && epi->in_halo) ? epi->in_halo : pad;
-  const int Hp = H + 2 * in_halo, Wp = W + 2 * in_halo;
+  const int Hp = Hin + 2 * in_halo, Wp = Win + 2 * in_halo;
+  const int H = (Hin - 1) / stride + 1, W = (Win - 1) / stride + 1;  // output extent
   const int pool = epi ? epi->pool : APNN_POOL_NONE;
   int bw = 0, bh = 0, bb = 0;
   if (!tc5_conv_box(H, W, pool, &bw, &bh, &bb)) return APNN_ERR_UNSUPPORTED;
@@ -714,6 +720,7 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.cblocks = CIN / BK;
   p.R = R;
   p.in_off = in_halo - pad;
+  p.stride = stride;
   p.pool = pool;
   p.out_h = pool ? H / 2 : H;
   p.out_w = pool ? W / 2 : W;
@@ -721,7 +728,7 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.a_box_bytes = (uint32_t)(bw * bh * bb * BK);
   const int bn = pick_bn(p.tiles_m, COUT, sms);
   CUtensorMap map_a, map_b;
-  if (!make_activation_map(&map_a, X8, B, Hp, Wp, CIN, bw, bh, bb) ||
+  if (!make_activation_map(&map_a, X8, B, Hp, Wp, CIN, bw, bh, bb, stride) ||
       !make_operand_map(&map_b, W8, COUT, (long long)R * R * CIN, bn)) {
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   }
@@ -747,7 +754,7 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
 }
 
 apnn_status tc5_conv(cudaStream_t s, int wbits, int xbits, const uint32_t* Wt, const uint32_t* X, void* Out, int B,
-                     int H, int W, int CIN, int COUT, int R, const apnn_epilogue* epi, void* workspace) {
+                     int H, int W, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi, void* workspace) {
   const int pad = (R - 1) / 2;
   const long long pixels = (long long)B * (H + 2 * pad) * (W + 2 * pad);
   uint8_t* x8 = reinterpret_cast<uint8_t*>(workspace);
@@ -758,7 +765,7 @@ apnn_status tc5_conv(cudaStream_t s, int wbits, int xbits, const uint32_t* Wt, c
   if (st != APNN_OK) return st;
   st = tc5_expand(s, Wt, w8, COUT, R * R * CIN, wbits, w_signed);
   if (st != APNN_OK) return st;
-  return tc5_conv_i8(s, x8, w8, Out, B, H, W, CIN, COUT, R, w_signed, epi, err);
+  return tc5_conv_i8(s, x8, w8, Out, B, H, W, CIN, COUT, R, stride, w_signed, epi, err);
 }
 
 int tc5_conv_read_error_flag(cudaStream_t s, const void* workspace, int B, int H, int W, int CIN, int COUT, int R) {

@@ -19,14 +19,14 @@ apnn_status tc5_expand(cudaStream_t s, const uint32_t* planes, uint8_t* out, lon
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag);
 // Convolution on the same kernel (implicit GEMM over 4-D TMA boxes of output pixels):
-// R in {1, 3}, stride 1, CIN % 128 == 0.  workspace holds the int8 activations (halo
+// R odd up to 11, stride 1 or 2, CIN % 128 == 0; H, W are the input extent.  workspace holds the int8 activations (halo
 // included), the int8 filter and the status flag.
 size_t tc5_conv_workspace_bytes(int B, int H, int W, int CIN, int COUT, int R);
 bool tc5_conv_supported(int H, int W, int R, int stride, int pool);
 apnn_status tc5_conv(cudaStream_t s, int wbits, int xbits, const uint32_t* Wt, const uint32_t* X, void* Out, int B,
-                     int H, int W, int CIN, int COUT, int R, const apnn_epilogue* epi, void* workspace);
+                     int H, int W, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi, void* workspace);
 apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int H, int W,
-                        int CIN, int COUT, int R, bool w_signed, const apnn_epilogue* epi, int* status_flag);
+                        int CIN, int COUT, int R, int stride, bool w_signed, const apnn_epilogue* epi, int* status_flag);
 int tc5_conv_read_error_flag(cudaStream_t s, const void* workspace, int B, int H, int W, int CIN, int COUT, int R);
 // Flag raised by a bounded wait (0 = ran to completion); synchronises the stream.
 int tc5_read_error_flag(cudaStream_t s, const void* workspace, int M, int N, int K);

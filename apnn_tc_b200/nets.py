@@ -272,7 +272,7 @@ class Network:
                                                     device=self.device)
                 Hc, Wc = (sh["H"] - 1) // ls.stride + 1, (sh["W"] - 1) // ls.stride + 1
                 pool_ok = not (ls.pool == 2 and (Hc % 2 or Wc % 2))
-                ok = use_tcgen05 and ls.stride == 1 and pool_ok
+                ok = use_tcgen05 and ls.stride in (1, 2) and pool_ok
                 if src is None and use_tcgen05 and pool_ok and p.im2col_planes is not None:
                     # first layer: windows gathered into channels, then a 1x1 convolution on tcgen05
                     kp = p.im2col_planes.shape[-1] * 32
@@ -342,15 +342,15 @@ class Network:
             _cabi.check(self.L.apnn_expand_planes(s, self.im2col_planes.data_ptr(), self.x8.data_ptr(), B * Hc * Wc, kp,
                                                   a, 0), "expand")
             _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), self.x8.data_ptr(), out.data_ptr(), B,
-                                              Hc, Wc, kp, sh["coutp"], 1, 1, ctypes.byref(epi), self.flag.data_ptr()),
+                                              Hc, Wc, kp, sh["coutp"], 1, 1, 1, ctypes.byref(epi), self.flag.data_ptr()),
                         "apnn_conv2d_i8 " + ls.name)
             return 2
         if self.tc5_ok[ls.name]:
             rows = X.shape[1] * X.shape[2] * X.shape[3]
             _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), rows, sh["cinp"], a, 0), "expand")
             _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), self.x8.data_ptr(), out.data_ptr(), B,
-                                              sh["H"], sh["W"], sh["cinp"], sh["coutp"], ls.R, 1, ctypes.byref(epi),
-                                              self.flag.data_ptr()), "apnn_conv2d_i8 " + ls.name)
+                                              sh["H"], sh["W"], sh["cinp"], sh["coutp"], ls.R, ls.stride, 1,
+                                              ctypes.byref(epi), self.flag.data_ptr()), "apnn_conv2d_i8 " + ls.name)
             return 2
         epi.signed_operand = _cabi.SIGN_W
         _cabi.check(self.L.apnn_conv2d_ex(s, _cabi.ALGO_IMMA, 1, a, self.w_planes[ls.name].data_ptr(), X.data_ptr(),

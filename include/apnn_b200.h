@@ -166,7 +166,7 @@ apnn_status apnn_conv2d(void *stream, int wbits, int xbits, const void *Wt, cons
                         void *Out, int B, int H, int W, int CIN, int COUT, int R, int stride,
                         const apnn_epilogue *epi);
 
-/* apnn_conv2d_ex adds the algorithm / workspace choice.  APNN_ALGO_TCGEN05 (stride 1 only, any supported R)
+/* apnn_conv2d_ex adds the algorithm / workspace choice.  APNN_ALGO_TCGEN05 (stride 1 or 2, any supported R)
  * expands activations and filter to int8 in the workspace and runs the implicit GEMM on
  * tcgen05 kind::i8, each A tile a 4-D TMA box of output pixels; APNN_ALGO_AUTO picks it when
  * the workspace is large enough and the contraction is at least ~2 GFLOP, else the
@@ -181,8 +181,8 @@ size_t apnn_conv2d_workspace_bytes(int algo, int B, int H, int W, int CIN, int C
 apnn_status apnn_conv2d_check(void *stream, const void *workspace, int B, int H, int W, int CIN, int COUT,
                               int R);
 apnn_status apnn_conv2d_i8(void *stream, const void *W8, const void *X8, void *Out, int B, int H, int W,
-                           int CIN, int COUT, int R, int w_signed, const apnn_epilogue *epi,
-                           int *status_flag);
+                           int CIN, int COUT, int R, int stride, int w_signed,
+                           const apnn_epilogue *epi, int *status_flag);
 
 /* ---- packers -------------------------------------------------------------------
  * apnn_bit_compress replaces Bit_compression (NN/kernel.cuh:46-77): one uint32 level per

@@ -120,14 +120,14 @@ def test_conv_host_front_end(cuda_device):
 
 
 # ------------------------------------------------------------------ tcgen05 implicit-GEMM path
-def run_tc5_conv(Wt, X, epilogue=None):
+def run_tc5_conv(Wt, X, epilogue=None, stride=1):
     import apnn_tc_b200 as ap
     xb, B, Hp, Wp, cw = X.shape
     wb, COUT, R = Wt.shape[0], Wt.shape[1], Wt.shape[2]
     p = (R - 1) // 2
     H, Wd, CIN = Hp - 2 * p, Wp - 2 * p, cw * 32
     ws = torch.empty(ap.conv_workspace_bytes(B, H, Wd, CIN, COUT, R), dtype=torch.uint8, device="cuda")
-    out = ap.apconv(to_dev(Wt), to_dev(X), epilogue=epilogue, algo="tcgen05", workspace=ws)
+    out = ap.apconv(to_dev(Wt), to_dev(X), stride=stride, epilogue=epilogue, algo="tcgen05", workspace=ws)
     ap.conv_check(ws, B, H, Wd, CIN, COUT, R)  # synchronises; raises if a bounded wait expired
     return out
 
@@ -205,8 +205,9 @@ def test_wide_filters_and_strides(cuda_device, R, stride):
     v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R, stride), 0)
     out = ap.apconv(to_dev(Wt), to_dev(X), stride=stride, epilogue=ap.make_epilogue("int32", signed="w"))
     assert np.array_equal(to_host(out, np.int32), v)
-    if stride == 1:
-        assert np.array_equal(to_host(run_tc5_conv(Wt, X, ap.make_epilogue("int32", signed="w")), np.int32), v)
+    if stride in (1, 2):
+        got = run_tc5_conv(Wt, X, ap.make_epilogue("int32", signed="w"), stride=stride)
+        assert np.array_equal(to_host(got, np.int32), v)
 
 
 @pytest.mark.parametrize("algo", ["imma", "tcgen05"])
@@ -233,3 +234,22 @@ def test_residual_in_and_out(cuda_device, algo, pool):
         out = ap.apconv(to_dev(Wt), to_dev(X), epilogue=epi)
     assert np.array_equal(to_host(res_out, np.int32), v)
     assert np.array_equal(to_host(out)[:, :, 1:-1, 1:-1], oracle.requant_pack(v, 2, 2, T))
+
+
+@pytest.mark.parametrize("B,H,Wd", [(2, 16, 16), (3, 14, 10), (1, 56, 56), (5, 7, 7)])
+@pytest.mark.parametrize("R", [3, 1])
+@pytest.mark.parametrize("pool", ["none", "max"])
+def test_tcgen05_stride2(cuda_device, B, H, Wd, R, pool):
+    """Stride-2 convolution on the tcgen05 path (TMA boxes that pick every second pixel)."""
+    import apnn_tc_b200 as ap
+    Ho, Wo = (H - 1) // 2 + 1, (Wd - 1) // 2 + 1
+    if pool != "none" and (Ho % 2 or Wo % 2):
+        pytest.skip("pooling needs even output")
+    rng = np.random.default_rng(B * 31 + H + R)
+    X, Wt = make_conv(rng, B, H, Wd, 256, 64, R, 1, 2)
+    acc = oracle.conv_popc(Wt, X, stride=2, threads=4)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R, 2), 0)
+    if pool != "none":
+        v = oracle.pool2x2(v, 2)
+    out = run_tc5_conv(Wt, X, ap.make_epilogue("int32", signed="w", pool=pool), stride=2)
+    assert np.array_equal(to_host(out, np.int32), v)
