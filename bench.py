@@ -248,6 +248,15 @@ def run_ours(args) -> None:
                 ev[1].record()
 
     launches_per_step = 3 if algo == "tcgen05" else 1
+    gathered = None
+    if args.allgather and dist is not None:
+        from apnn_tc_b200 import shard
+        gathered = torch.empty((world, M, N), dtype=torch.int32, device=dev)
+        base_step = step
+
+        def step(i: int, ev=None):  # noqa: F811 -- the GEMM followed by the output all-gather over NVLink
+            base_step(i, ev)
+            shard.allgather_columns(D, out=gathered)
 
     for i in range(args.warmup):
         step(i)
@@ -383,7 +392,9 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": world * flops_step / (ms_per_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8 operands, int32 accumulate (exact)", "data": "synthetic",
-        "config": workload_config(world, algo), "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+        "config": dict(workload_config(world, algo), collective=("all_gather of the int32 output slices, "
+                       f"{(world - 1) * M * N * 4} B inbound per rank per step" if gathered is not None else "none")),
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
         "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
@@ -483,6 +494,8 @@ def main() -> None:
     ap_.add_argument("--warmup", type=int, default=5)
     ap_.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap_.add_argument("--algo", default="tcgen05", choices=["tcgen05", "imma", "bmma"])
+    ap_.add_argument("--allgather", action="store_true",
+                     help="N > 1 only: all-gather the int32 output slices inside every timed step")
     ap_.add_argument("--profile", action="store_true",
                      help="timed steps only (no e2e, probe or CPU baseline): the command ncu captures")
     ap_.add_argument("--workload", default="gemm", choices=["gemm", "resnet18", "vgg_variant", "alexnet"],
