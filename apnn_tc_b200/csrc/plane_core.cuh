@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
 
     if constexpr (KIND == KIND_B1) {
       // two 128-bit chunks per m16n8k256 MMA
-#pragma unroll 1
+#pragma unroll
       for (int sub = 0; sub < 2; sub++) {
         uint32_t aw[ABITS][MT][4];
         uint32_t bw[BBITS][NT][2];
