@@ -15,13 +15,13 @@ LIB_PATH = os.path.join(_HERE, "libapnn_b200.so")
 OUT_INT32, OUT_LOWBITS, OUT_THRESHOLDS = 0, 1, 2
 SIGN_NONE, SIGN_W, SIGN_X = 0, 1, 2
 POOL_NONE, POOL_AVG2, POOL_MAX2 = 0, 1, 2
-ALGO_AUTO, ALGO_BMMA, ALGO_IMMA, ALGO_TCGEN05 = 0, 1, 2, 3
-ALGOS = {"auto": ALGO_AUTO, "bmma": ALGO_BMMA, "imma": ALGO_IMMA, "tcgen05": ALGO_TCGEN05}
+ALGO_AUTO, ALGO_BMMA, ALGO_IMMA, ALGO_TCGEN05, ALGO_TCGEN05_PAIR = 0, 1, 2, 3, 4
+ALGOS = {"auto": ALGO_AUTO, "bmma": ALGO_BMMA, "imma": ALGO_IMMA, "tcgen05": ALGO_TCGEN05, "tcgen05_pair": ALGO_TCGEN05_PAIR}
 
 # every symbol the header declares; the CPU test-suite checks the library exports them all
 EXPORTS = (
     "apnn_status_string", "apnn_last_cuda_error", "apnn_version", "apnn_gemm", "apnn_gemm_ex",
-    "apnn_gemm_workspace_bytes", "apnn_gemm_check", "apnn_expand_planes", "apnn_gemm_i8", "apnn_gemm_static_scratch", "apnn_conv2d", "apnn_conv2d_ex",
+    "apnn_gemm_workspace_bytes", "apnn_gemm_check", "apnn_expand_planes", "apnn_expand_planes_pair", "apnn_gemm_i8", "apnn_gemm_static_scratch", "apnn_conv2d", "apnn_conv2d_ex",
     "apnn_conv2d_workspace_bytes", "apnn_conv2d_check", "apnn_conv2d_i8", "apnn_bit_compress", "apnn_quantize_pack", "apnn_quantize_im2col", "apnn_create",
     "apnn_destroy", "apnn_gemm_host", "apnn_conv2d_host", "apnn_probe_peak",
 )
@@ -70,6 +70,7 @@ def lib() -> ctypes.CDLL:
     L.apnn_gemm_workspace_bytes.argtypes = [i, i, i, i, i, i]
     L.apnn_gemm_check.argtypes = [vp, vp, i, i, i]
     L.apnn_expand_planes.argtypes = [vp, vp, vp, lg, i, i, i]
+    L.apnn_expand_planes_pair.argtypes = [vp, vp, vp, lg, i, i, vp, vp, lg, i, i, i]
     L.apnn_gemm_i8.argtypes = [vp, vp, vp, vp, i, i, i, i, i, ep, vp]
     L.apnn_gemm_static_scratch.argtypes = [vp, i, i, vp, vp, vp, i, i, i, ep, vp]
     L.apnn_conv2d.argtypes = [vp, i, i, vp, vp, vp, i, i, i, i, i, i, i, ep]

@@ -76,7 +76,7 @@ int apnn_version(void) { return 100; }
 size_t apnn_gemm_workspace_bytes(int algo, int wbits, int xbits, int M, int N, int K) {
   (void)wbits;
   (void)xbits;
-  if (algo != APNN_ALGO_TCGEN05) return 0;
+  if (algo != APNN_ALGO_TCGEN05 && algo != APNN_ALGO_TCGEN05_PAIR) return 0;
   return tc5_workspace_bytes(M, N, K);
 }
 
@@ -90,10 +90,24 @@ apnn_status apnn_gemm_check(void* stream, const void* workspace, int M, int N, i
 apnn_status apnn_expand_planes(void* stream, const void* planes, void* out_i8, long rows, int K, int bits,
                                int is_signed) {
   if (!planes || !out_i8 || rows <= 0 || K <= 0 || bits < 1 || bits > 8) return APNN_ERR_INVALID_ARG;
+  if (bits > 4 && bits < 8) return APNN_ERR_UNSUPPORTED;
   if (is_signed && bits != 1) return APNN_ERR_UNSUPPORTED;
   if (K % 128 != 0 || !aligned16(planes) || !aligned16(out_i8)) return APNN_ERR_ALIGNMENT;
   return tc5_expand(reinterpret_cast<cudaStream_t>(stream), (const uint32_t*)planes, (uint8_t*)out_i8, rows, K, bits,
                     is_signed != 0);
+}
+
+apnn_status apnn_expand_planes_pair(void* stream, const void* planes_w, void* w_i8, long rows_w, int wbits,
+                                    int w_signed, const void* planes_x, void* x_i8, long rows_x, int xbits,
+                                    int x_signed, int K) {
+  if (!planes_w || !w_i8 || !planes_x || !x_i8 || rows_w <= 0 || rows_x <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
+  if (wbits < 1 || wbits > 8 || xbits < 1 || xbits > 8) return APNN_ERR_INVALID_ARG;
+  if ((wbits > 4 && wbits < 8) || (xbits > 4 && xbits < 8)) return APNN_ERR_UNSUPPORTED;
+  if ((w_signed && wbits != 1) || (x_signed && xbits != 1)) return APNN_ERR_UNSUPPORTED;
+  if (K % 128 != 0 || !aligned16(planes_w) || !aligned16(w_i8) || !aligned16(planes_x) || !aligned16(x_i8))
+    return APNN_ERR_ALIGNMENT;
+  return tc5_expand2(reinterpret_cast<cudaStream_t>(stream), (const uint32_t*)planes_w, (uint8_t*)w_i8, rows_w, wbits,
+                     w_signed != 0, (const uint32_t*)planes_x, (uint8_t*)x_i8, rows_x, xbits, x_signed != 0, K);
 }
 
 apnn_status apnn_gemm_i8(void* stream, const void* W8, const void* X8, void* D, int M, int N, int K, int w_signed,
@@ -114,7 +128,7 @@ apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const voi
                          int N, int K, const apnn_epilogue* epi, void* workspace, size_t workspace_bytes) {
   if (!W || !X || !D) return APNN_ERR_INVALID_ARG;
   if (M <= 0 || N <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
-  if (algo < APNN_ALGO_AUTO || algo > APNN_ALGO_TCGEN05) return APNN_ERR_INVALID_ARG;
+  if (algo < APNN_ALGO_AUTO || algo > APNN_ALGO_TCGEN05_PAIR) return APNN_ERR_INVALID_ARG;
   if (K % 128 != 0) return APNN_ERR_ALIGNMENT;
   if (!aligned16(W) || !aligned16(X) || !aligned16(D)) return APNN_ERR_ALIGNMENT;
   if (!core_supports(wbits, xbits)) return APNN_ERR_UNSUPPORTED;
@@ -126,10 +140,11 @@ apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const voi
     bool ws_ok = workspace && workspace_bytes >= tc5_workspace_bytes(M, N, K);
     algo = (ws_ok && tc5_worthwhile(M, N, K)) ? APNN_ALGO_TCGEN05 : APNN_ALGO_IMMA;
   }
-  if (algo == APNN_ALGO_TCGEN05) {
+  if (algo == APNN_ALGO_TCGEN05 || algo == APNN_ALGO_TCGEN05_PAIR) {
     if (!workspace || workspace_bytes < tc5_workspace_bytes(M, N, K)) return APNN_ERR_WORKSPACE;
     if (!aligned16(workspace)) return APNN_ERR_ALIGNMENT;
-    return tc5_gemm(s, wbits, xbits, (const uint32_t*)W, (const uint32_t*)X, D, M, N, K, epi, workspace);
+    return tc5_gemm(s, wbits, xbits, (const uint32_t*)W, (const uint32_t*)X, D, M, N, K, epi, workspace,
+                    algo == APNN_ALGO_TCGEN05_PAIR ? 1 : 0);
   }
 
   CoreParams p;

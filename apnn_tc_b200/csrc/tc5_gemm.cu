@@ -30,14 +30,16 @@
 
 #include "api_internal.h"
 #include "apnn_device.cuh"
+#include "tc5_common.cuh"
 #include "tc5_gemm.h"
 
 namespace apnn {
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BK = 128;  // bytes of K per stage = one 128-byte swizzle row
+using tc5::BM;
+using tc5::BK;
+
 constexpr int A_STAGE_BYTES = BM * BK;
 constexpr int THREADS = 192;
 constexpr int MAX_STAGES = 6;
@@ -56,124 +58,68 @@ struct TileCfg {
   static constexpr int TMEM_COLS = 2 * BN;
 };
 constexpr int GROUP_M = 16;  // tiles are walked in bands of 16 row-tiles for L2 reuse
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // a wait that lasts 2 s is a bug, not a delay
 
 // ------------------------------------------------------------------ expand kernel
-__global__ void __launch_bounds__(256) expand_planes_kernel(const uint32_t* __restrict__ planes,
-                                                            uint8_t* __restrict__ out, long long rows, int kwords,
-                                                            int bits, int is_signed) {
-  const long long total = rows * kwords;
-  const long long plane_words = total;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    uint32_t w[8];
+struct ExpandJob {
+  const uint32_t* planes;
+  uint8_t* out;
+  long long total;  // rows * K/32 words per plane
+  int bits;
+  int is_signed;
+};
+
+// One 32-k word of every plane -> 32 bytes.  Two words per thread per trip so their loads overlap.
+template <int BITS>
+__device__ __forceinline__ void expand_words(const ExpandJob& j, long long first, long long step) {
+  for (long long i = first; i < j.total; i += 2 * step) {
+    const long long i2 = i + step;
+    const bool two = i2 < j.total;
+    uint32_t w[2][BITS];
 #pragma unroll
-    for (int p = 0; p < 8; p++) w[p] = p < bits ? __ldg(planes + p * plane_words + i) : 0u;
-    uint32_t r[8];
+    for (int p = 0; p < BITS; p++) {
+      w[0][p] = __ldg(j.planes + p * j.total + i);
+      w[1][p] = two ? __ldg(j.planes + p * j.total + i2) : 0u;
+    }
 #pragma unroll
-    for (int q = 0; q < 8; q++) {
-      uint32_t v = 0;
+    for (int u = 0; u < 2; u++) {
+      if (u == 1 && !two) break;
+      uint32_t r[8];
 #pragma unroll
-      for (int p = 0; p < 8; p++) {
-        uint32_t s = (q >= p) ? (w[p] >> (q - p)) : (w[p] << (p - q));
-        v |= s & (0x01010101u << p);
+      for (int q = 0; q < 8; q++) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int p = 0; p < BITS; p++) {
+          uint32_t s = (q >= p) ? (w[u][p] >> (q - p)) : (w[u][p] << (p - q));
+          v |= s & (0x01010101u << p);
+        }
+        // signed 1-bit operand: bit 1 -> +1 (0x01), bit 0 -> -1 (0xFF)
+        r[q] = (BITS == 1 && j.is_signed) ? (0xFFFFFFFFu ^ (v * 0xFEu)) : v;
       }
-      // signed 1-bit operand: bit 1 -> +1 (0x01), bit 0 -> -1 (0xFF)
-      r[q] = is_signed ? (0xFFFFFFFFu ^ (v * 0xFEu)) : v;
-    }
-    uint4* dst = reinterpret_cast<uint4*>(out + i * 32);
-    dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
-    dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
-  }
-}
-
-// ------------------------------------------------------------------ PTX helpers
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: returns false when the time limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  unsigned long long t0 = 0;
-  for (uint32_t spin = 0;; spin++) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((spin & 255u) == 255u) {
-      unsigned long long now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) return false;
+      uint4* dst = reinterpret_cast<uint4*>(j.out + (u == 0 ? i : i2) * 32);
+      dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
+      dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
     }
   }
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], "
-      "[%6];" ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-      "%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
-// 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);  // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
-  return d;
+// Blocks [0, blocks_a) work on job a, the rest on job b (one launch for both GEMM operands).
+__global__ void __launch_bounds__(256) expand_planes_kernel(const ExpandJob a, const ExpandJob b, int blocks_a) {
+  const bool first = (int)blockIdx.x < blocks_a;
+  const ExpandJob& j = first ? a : b;
+  const long long nblk = first ? blocks_a : (long long)gridDim.x - blocks_a;
+  const long long blk = first ? blockIdx.x : blockIdx.x - blocks_a;
+  const long long i0 = blk * blockDim.x + threadIdx.x;
+  const long long step = nblk * blockDim.x;
+  switch (j.bits) {
+    case 1: expand_words<1>(j, i0, step); break;
+    case 2: expand_words<2>(j, i0, step); break;
+    case 3: expand_words<3>(j, i0, step); break;
+    case 4: expand_words<4>(j, i0, step); break;
+    default: expand_words<8>(j, i0, step); break;
+  }
 }
+
+using namespace tc5;
 
 struct Tc5Params {
   void* out;
@@ -594,13 +540,44 @@ bool tc5_worthwhile(int M, int N, int K) {
   return tiles >= 64 && K >= 1024;
 }
 
+namespace {
+int expand_blocks(long long total, int sms) {
+  long long want = (total + 511) / 512, cap = (long long)sms * 16;
+  long long b = want < cap ? want : cap;
+  return (int)(b < 1 ? 1 : b);
+}
+ExpandJob make_job(const uint32_t* planes, uint8_t* out, long long rows, int K, int bits, bool is_signed) {
+  ExpandJob j;
+  j.planes = planes;
+  j.out = out;
+  j.total = rows * (K / 32);
+  j.bits = (bits >= 5 && bits <= 8) ? 8 : bits;
+  j.is_signed = is_signed ? 1 : 0;
+  return j;
+}
+// planes of 5..7 bits run through the 8-plane code path and therefore need 8 readable planes;
+// the ABI only admits 1..4 and 8
+}  // namespace
+
 apnn_status tc5_expand(cudaStream_t s, const uint32_t* planes, uint8_t* out, long long rows, int K, int bits,
                        bool is_signed) {
   const int sms = device_sm_count();
-  long long total = rows * (K / 32);
-  long long want = (total + 255) / 256, cap = (long long)sms * 16;
-  int blocks = (int)(want < cap ? want : cap);
-  expand_planes_kernel<<<blocks, 256, 0, s>>>(planes, out, rows, K / 32, bits, is_signed ? 1 : 0);
+  ExpandJob a = make_job(planes, out, rows, K, bits, is_signed);
+  const int blocks = expand_blocks(a.total, sms);
+  expand_planes_kernel<<<blocks, 256, 0, s>>>(a, a, blocks);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "expand_planes launch");
+  return APNN_OK;
+}
+
+// Both operands of a GEMM in one launch.
+apnn_status tc5_expand2(cudaStream_t s, const uint32_t* pa, uint8_t* oa, long long rows_a, int bits_a, bool signed_a,
+                        const uint32_t* pb, uint8_t* ob, long long rows_b, int bits_b, bool signed_b, int K) {
+  const int sms = device_sm_count();
+  ExpandJob a = make_job(pa, oa, rows_a, K, bits_a, signed_a);
+  ExpandJob b = make_job(pb, ob, rows_b, K, bits_b, signed_b);
+  const int ba = expand_blocks(a.total, sms), bb = expand_blocks(b.total, sms);
+  expand_planes_kernel<<<ba + bb, 256, 0, s>>>(a, b, ba);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "expand_planes launch");
   return APNN_OK;
@@ -608,6 +585,7 @@ apnn_status tc5_expand(cudaStream_t s, const uint32_t* planes, uint8_t* out, lon
 
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
+  if (tc5_pair_worthwhile(M, N, K)) return tc5_gemm_i8_pair(s, A8, B8, D, M, N, K, a_signed, b_signed, epi, status_flag);
   cudaError_t e;
   const int sms = device_sm_count();
   Tc5Params p;
@@ -639,15 +617,14 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
 }
 
 apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, const uint32_t* X, void* D, int M,
-                     int N, int K, const apnn_epilogue* epi, void* workspace) {
+                     int N, int K, const apnn_epilogue* epi, void* workspace, int pair) {
   uint8_t* wa = reinterpret_cast<uint8_t*>(workspace);
   uint8_t* wb = wa + align_up((size_t)M * K, 256);
   int* err = reinterpret_cast<int*>(wb + align_up((size_t)N * K, 256));
   const int sign = epi ? epi->signed_operand : APNN_SIGN_NONE;
-  apnn_status st = tc5_expand(s, W, wa, M, K, wbits, sign == APNN_SIGN_W);
+  apnn_status st = tc5_expand2(s, W, wa, M, wbits, sign == APNN_SIGN_W, X, wb, N, xbits, sign == APNN_SIGN_X, K);
   if (st != APNN_OK) return st;
-  st = tc5_expand(s, X, wb, N, K, xbits, sign == APNN_SIGN_X);
-  if (st != APNN_OK) return st;
+  if (pair) return tc5_gemm_i8_pair(s, wa, wb, D, M, N, K, sign == APNN_SIGN_W, sign == APNN_SIGN_X, epi, err);
   return tc5_gemm_i8(s, wa, wb, D, M, N, K, sign == APNN_SIGN_W, sign == APNN_SIGN_X, epi, err);
 }
 

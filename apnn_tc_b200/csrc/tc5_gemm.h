@@ -11,11 +11,13 @@ size_t tc5_workspace_bytes(int M, int N, int K);
 // True when the problem is large enough for this path to beat the warp-level core.
 bool tc5_worthwhile(int M, int N, int K);
 apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, const uint32_t* X, void* D, int M,
-                     int N, int K, const apnn_epilogue* epi, void* workspace);
+                     int N, int K, const apnn_epilogue* epi, void* workspace, int pair = 0);
 // The two stages of tc5_gemm on their own: planes -> int8 rows (rows x K bytes), and the
 // int8 GEMM over already expanded operands (static weights are expanded once).
 apnn_status tc5_expand(cudaStream_t s, const uint32_t* planes, uint8_t* out, long long rows, int K, int bits,
                        bool is_signed);
+apnn_status tc5_expand2(cudaStream_t s, const uint32_t* pa, uint8_t* oa, long long rows_a, int bits_a, bool signed_a,
+                        const uint32_t* pb, uint8_t* ob, long long rows_b, int bits_b, bool signed_b, int K);
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag);
 // Convolution on the same kernel (implicit GEMM over 4-D TMA boxes of output pixels):
@@ -28,6 +30,11 @@ apnn_status tc5_conv(cudaStream_t s, int wbits, int xbits, const uint32_t* Wt, c
 apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int H, int W,
                         int CIN, int COUT, int R, int stride, bool w_signed, const apnn_epilogue* epi, int* status_flag);
 int tc5_conv_read_error_flag(cudaStream_t s, const void* workspace, int B, int H, int W, int CIN, int COUT, int R);
+// The same GEMM on CTA pairs (cta_group::2, 256 x 256 tiles); worthwhile once there are at
+// least as many pair tiles as SM pairs.
+bool tc5_pair_worthwhile(int M, int N, int K);
+apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
+                             bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag);
 // Flag raised by a bounded wait (0 = ran to completion); synchronises the stream.
 int tc5_read_error_flag(cudaStream_t s, const void* workspace, int M, int N, int K);
 }  // namespace apnn

@@ -1,0 +1,399 @@
+// tcgen05 GEMM on CTA pairs (cta_group::2): one 256 x 256 output tile per pair of SMs.
+//
+// Each CTA of a 2-CTA cluster stages only its own half of both operands -- 128 rows of A
+// (its half of M) and 128 rows of B (its half of N) per 128-byte K block, 32 KiB per stage
+// instead of 48 KiB for the same MMA time -- so a 6-stage ring fits and every SM pulls a
+// third fewer bytes from L2 per MMA than the single-CTA kernel.  The even CTA (the leader)
+// issues tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 32): the tensor cores of both SMs
+// read both shared memories, and each SM's TMEM receives its own 128 rows of the tile.
+//
+// Synchronisation (all waits time-bounded, as in the single-CTA kernel):
+//   full[s]      lives in the leader; both CTAs' TMA loads complete their bytes on it
+//                (cp.async.bulk.tensor ... cta_group::2 with the leader's barrier address)
+//   empty[s]     one per CTA; the leader's tcgen05.commit multicasts the arrival to both
+//   tmem_full[a] one per CTA, same multicast commit; each CTA's epilogue warps drain their
+//                own TMEM
+//   tmem_empty[a] lives in the leader, 8 arrivals (4 epilogue warps x 2 CTAs, the peer's
+//                through mapa + a cluster-scope arrive)
+// The loads carry no cluster multicast.  A cluster barrier closes the kernel so neither CTA
+// exits while the other may still touch its shared memory or barriers.
+#include <cstring>
+
+#include "api_internal.h"
+#include "tc5_common.cuh"
+#include "tc5_gemm.h"
+
+namespace apnn {
+
+namespace {
+
+using namespace tc5;
+
+constexpr int TILE_M = 256;   // over the pair
+constexpr int TILE_N = 256;
+constexpr int HALF = 128;     // rows of A and of B one CTA stages
+constexpr int STAGES = 6;
+constexpr int STAGE_BYTES = 2 * HALF * BK;  // 32 KiB per CTA
+constexpr int THR_BYTES_PER_WARP = TILE_N * 16;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * THR_BYTES_PER_WARP;
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 8;    // bands of 8 pair-tiles (2048 rows) for L2 reuse
+
+struct PairParams {
+  void* out;
+  const int32_t* thresholds;
+  const int32_t* residual_in;
+  int32_t* residual_out;
+  int M, N, kblocks;
+  int tiles_m, tiles_n;
+  int out_mode, out_bits;
+  uint32_t idesc;
+  long long out_plane_words;
+  int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of a CTA pair: data lands in this CTA, the bytes complete on `bar_cluster`
+// (a shared::cluster address, here always the leader's barrier)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], "
+      "[%4];" ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  // arrive on the barrier at this offset in both CTAs once the MMAs issued so far are done
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int band = GROUP_M * tiles_n;
+  const int g = tile / band;
+  const int first = g * GROUP_M;
+  const int rows = min(GROUP_M, tiles_m - first);
+  const int r = tile - g * band;
+  tm = first + r % rows;
+  tn = r / rows;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t bars = base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+  uint8_t* thr_stage = smem_raw + (bars + 256u - raw);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) *p.error_flag = 0;
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything remote touches them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one per CTA) ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int arow = tm * TILE_M + (int)rank * HALF;
+        const int brow = tn * TILE_N + (int)rank * HALF;
+        for (int kb = 0; kb < p.kblocks; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
+          const uint32_t leader_full = map_to_cta(full_bar(s), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);  // both CTAs' bytes
+          const uint32_t sa = base + s * STAGE_BYTES;
+          tma_load_2d_pair(sa, &map_a, kb * BK, arow, leader_full);
+          tma_load_2d_pair(sa + HALF * BK, &map_b, kb * BK, brow, leader_full);
+        }
+      }
+      if (!ok) atomicExch(p.error_flag, 1);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0;
+      uint32_t tl = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, tl++) {
+        const uint32_t acc = tl & 1u;
+        const uint32_t aph = (tl >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * TILE_N;
+        for (int kb = 0; kb < p.kblocks; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + s * STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + HALF * BK);
+#pragma unroll
+          for (int k = 0; k < BK / 32; k++)
+            tc_mma_i8_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit_pair(empty_bar(s));  // frees the stage in both CTAs
+        }
+        if (ok) tc_commit_pair(tfull_bar(acc));  // accumulators complete in both CTAs
+      }
+      if (!ok) atomicExch(p.error_flag, 2);
+    }
+  } else {
+    // ---------------- epilogue warps (2..5) of both CTAs ----------------
+    const int quarter = warp & 3;
+    uint32_t tl = 0;
+    bool ok = true;
+    const int nl = (1 << p.out_bits) - 1;
+    const bool thr_staged = p.out_mode == OUT_THRESHOLDS && nl <= 3;
+    int4* thr_s = reinterpret_cast<int4*>(thr_stage + (warp - 2) * THR_BYTES_PER_WARP);
+    int staged_tn = -1;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, tl++) {
+      int tm, tn;
+      pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      if (thr_staged && tn != staged_tn) {
+        __syncwarp();
+        for (int cidx = lane; cidx < TILE_N; cidx += 32) {
+          const int col = tn * TILE_N + cidx;
+          int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
+          if (col < p.N) {
+            const int32_t* T = p.thresholds + (long long)col * nl;
+            t4.x = __ldg(T);
+            if (nl > 1) { t4.y = __ldg(T + 1); t4.z = __ldg(T + 2); }
+          }
+          thr_s[cidx] = t4;
+        }
+        __syncwarp();
+        staged_tn = tn;
+      }
+      const uint32_t acc = tl & 1u;
+      const uint32_t aph = (tl >> 1) & 1u;
+      if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
+      tc_fence_after();
+      const long long row = (long long)tm * TILE_M + (int)rank * HALF + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TILE_N;
+#pragma unroll 1
+      for (int c = 0; c < TILE_N / 32; c++) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col0 = tn * TILE_N + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        const bool whole = (p.N & 3) == 0 && col0 + 32 <= p.N;
+        if (p.residual_in != nullptr || p.residual_out != nullptr) {
+          const long long at = row * (long long)p.N + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (col0 + j < p.N) {
+              if (p.residual_in != nullptr) v[j] = (uint32_t)((int)v[j] + __ldg(p.residual_in + at + j));
+              if (p.residual_out != nullptr) p.residual_out[at + j] = (int32_t)v[j];
+            }
+        }
+        if (p.out_mode == OUT_INT32) {
+          int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
+          if (whole) {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+              reinterpret_cast<uint4*>(D)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < p.N) D[j] = (int32_t)v[j];
+          }
+        } else {
+          uint32_t lv[32];
+          if (p.out_mode == OUT_LOWBITS) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) lv[j] = v[j] & (uint32_t)nl;
+          } else if (thr_staged) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              const int4 t4 = thr_s[c * 32 + j];
+              const int x = (int)v[j];
+              lv[j] = (x >= t4.x ? 1u : 0u) + (x >= t4.y ? 1u : 0u) + (x >= t4.z ? 1u : 0u);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              const int32_t* T = p.thresholds + (long long)(col0 + j) * nl;
+              uint32_t l = 0;
+              for (int t = 0; t < nl; t++) l += ((int32_t)v[j] >= __ldg(T + t)) ? 1u : 0u;
+              lv[j] = l;
+            }
+          }
+          uint32_t* O = reinterpret_cast<uint32_t*>(p.out);
+          for (int b = 0; b < p.out_bits; b++) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < 32; j++) word |= ((lv[j] >> b) & 1u) << (31 - j);
+            O[b * p.out_plane_words + row * (p.N >> 5) + (col0 >> 5)] = word;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));  // the leader's barrier
+    }
+    if (!ok && lane == 0) atomicExch(p.error_flag, 3);
+  }
+
+  // ---------------- tear-down ----------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may not leave while the leader's MMAs or arrivals can still reach it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool make_half_map(CUtensorMap* map, const void* base, long long rows, long long K) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return false;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)HALF};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool tc5_pair_worthwhile(int M, int N, int K) {
+  long long tiles = (long long)((M + TILE_M - 1) / TILE_M) * ((N + TILE_N - 1) / TILE_N);
+  return tiles >= device_sm_count() / 2 && K >= 1024;
+}
+
+apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
+                             bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
+  CUtensorMap map_a, map_b;
+  if (!make_half_map(&map_a, A8, M, K) || !make_half_map(&map_b, B8, N, K))
+    return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaError_t e;
+  if (dev >= 16 || !attr_set[dev]) {
+    e = cudaFuncSetAttribute(tc5_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return cuda_fail(e, "tc5 pair smem attribute");
+    if (dev < 16) attr_set[dev] = true;
+  }
+  PairParams p;
+  memset(&p, 0, sizeof(p));
+  p.out = D;
+  p.thresholds = epi ? epi->thresholds : nullptr;
+  p.residual_in = epi ? epi->residual_in : nullptr;
+  p.residual_out = epi ? epi->residual_out : nullptr;
+  p.M = M;
+  p.N = N;
+  p.kblocks = K / BK;
+  p.tiles_m = (M + TILE_M - 1) / TILE_M;
+  p.tiles_n = (N + TILE_N - 1) / TILE_N;
+  p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
+  p.out_bits = epi ? epi->out_bits : 0;
+  p.out_plane_words = (long long)M * (N / 32);
+  p.error_flag = status_flag;
+  // D = s32, A/B = u8 or s8, K-major, N = 256, M = 256 over the pair
+  p.idesc = (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(TILE_N >> 3) << 17) |
+            ((uint32_t)(TILE_M >> 4) << 24);
+  const int sms = device_sm_count();
+  long long tiles = (long long)p.tiles_m * p.tiles_n;
+  int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
+
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel, map_a, map_b, p);
+  if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm_pair launch");
+  return APNN_OK;
+}
+
+}  // namespace apnn

@@ -10,7 +10,7 @@ rank owns the same weights and its own 8192 activation rows, i.e. a slice D[:, n
 GEMM that is g times wider -- no data-path collective, weak scaling.
 
 Prints ONE JSON line (rank 0).  Keys beyond the usual ones:
-  roofline      tensor-pipe roofline of the dominant kernel (tc5_gemm_kernel), timed with its
+  roofline      tensor-pipe roofline of the dominant kernel (tc5_gemm_pair_kernel), timed with its
                 own CUDA events inside the timed steps; peak = the tcgen05 kind::i8 issue-loop
                 peak measured in this run (MEASURED_PEAKS.json's bf16 figure is quoted beside it)
   cpu_baseline  the reference's own bit-serial compute_ref (compiled unmodified into
@@ -231,10 +231,11 @@ def run_ours(args) -> None:
     def step(i: int, ev=None):
         W, X = Ws[i % N_OPERAND_SETS], Xs[i % N_OPERAND_SETS]
         if algo == "tcgen05":
-            # the same three launches apnn_gemm_ex(APNN_ALGO_TCGEN05) makes, issued one by one
+            # the same two launches apnn_gemm_ex(APNN_ALGO_TCGEN05) makes, issued one by one
             # so the GEMM kernel can be bracketed by its own events
-            ap.expand_planes(W, out=W8)
-            ap.expand_planes(X, out=X8)
+            _cabi.check(_cabi.lib().apnn_expand_planes_pair(torch.cuda.current_stream().cuda_stream, W.data_ptr(),
+                                                             W8.data_ptr(), M, WBITS, 0, X.data_ptr(), X8.data_ptr(), N,
+                                                             XBITS, 0, K), "apnn_expand_planes_pair")
             if ev is not None:
                 ev[0].record()
             ap.gemm_i8(W8, X8, D, status_flag=flag)
@@ -247,7 +248,7 @@ def run_ours(args) -> None:
             if ev is not None:
                 ev[1].record()
 
-    launches_per_step = 3 if algo == "tcgen05" else 1
+    launches_per_step = 2 if algo == "tcgen05" else 1
     gathered = None
     if args.allgather and dist is not None:
         from apnn_tc_b200 import shard
@@ -353,7 +354,7 @@ def run_ours(args) -> None:
     ops_launch = flops_step * (WBITS * XBITS if algo == "bmma" else 1)  # bit-ops for the b1 path
     achieved = ops_launch / (kernel_ms * 1e-3) / 1e12
     roofline = {
-        "bound": "tensor", "kernel": {"tcgen05": "tc5_gemm_kernel", "imma": "plane_core_kernel<u8>",
+        "bound": "tensor", "kernel": {"tcgen05": "tc5_gemm_pair_kernel (cta_group::2)", "imma": "plane_core_kernel<u8>",
                                       "bmma": "plane_core_kernel<b1>"}[algo],
         "achieved": achieved, "peak": peak_ops / 1e12, "unit": "TOP/s" if algo != "bmma" else "Tbitop/s",
         "frac": achieved / (peak_ops / 1e12),

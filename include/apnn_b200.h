@@ -57,8 +57,10 @@ enum {
   APNN_ALGO_BMMA = 1,    /* 1-bit and-popcount mma.sync per plane pair (emulated on sm_100a;
                             kept as the measured comparison), no workspace */
   APNN_ALGO_IMMA = 2,    /* planes spread to u8 in registers, mma.sync m16n8k32, no workspace */
-  APNN_ALGO_TCGEN05 = 3  /* planes expanded to int8 in the workspace, TMA-fed tcgen05 kind::i8
+  APNN_ALGO_TCGEN05 = 3, /* planes expanded to int8 in the workspace, TMA-fed tcgen05 kind::i8
                             with TMEM accumulators */
+  APNN_ALGO_TCGEN05_PAIR = 4 /* GEMM only: the same on CTA pairs (cta_group::2, 256x256 tiles,
+                                each SM stages half of both operands); same workspace */
 };
 
 typedef struct apnn_epilogue {
@@ -121,12 +123,17 @@ apnn_status apnn_gemm_check(void *stream, const void *workspace, int M, int N, i
  * apnn_expand_planes: planes[bits][rows][K/32] -> out_i8[rows][K], one byte per element,
  *   value = sum_p bit_p << p, or -1/+1 for a 1-bit operand with is_signed != 0.  The byte
  *   order inside each group of 32 k is a fixed permutation shared by both operands.
- * apnn_gemm_i8: D = W8 * X8^T over operands produced by apnn_expand_planes, same epilogue
+ * apnn_gemm_i8: D = W8 * X8^T over operands produced by apnn_expand_planes, same epilogue;
+ *   problems with at least as many 256x256 tiles as SM pairs run on CTA pairs (cta_group::2)
  *   (signed_operand must be APNN_SIGN_NONE: the sign is in the bytes; pass w_signed /
  *   x_signed to say which operand holds -1/+1).  status_flag: 4 bytes of device memory,
  *   written 0 at launch and non-zero if a bounded wait expires. */
 apnn_status apnn_expand_planes(void *stream, const void *planes, void *out_i8, long rows, int K,
                                int bits, int is_signed);
+/* Both operands of a GEMM in one launch (what apnn_gemm_ex does internally). */
+apnn_status apnn_expand_planes_pair(void *stream, const void *planes_w, void *w_i8, long rows_w,
+                                    int wbits, int w_signed, const void *planes_x, void *x_i8,
+                                    long rows_x, int xbits, int x_signed, int K);
 apnn_status apnn_gemm_i8(void *stream, const void *W8, const void *X8, void *D, int M, int N, int K,
                          int w_signed, int x_signed, const apnn_epilogue *epi, int *status_flag);
 
