@@ -19,6 +19,8 @@ apnn_status cuda_fail(cudaError_t e, const char* where) {
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// the expand kernel writes the int8 images with 32-byte stores
+static bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 int device_sm_count() {
   static int sms[16] = {};
@@ -92,7 +94,7 @@ apnn_status apnn_expand_planes(void* stream, const void* planes, void* out_i8, l
   if (!planes || !out_i8 || rows <= 0 || K <= 0 || bits < 1 || bits > 8) return APNN_ERR_INVALID_ARG;
   if (bits > 4 && bits < 8) return APNN_ERR_UNSUPPORTED;
   if (is_signed && bits != 1) return APNN_ERR_UNSUPPORTED;
-  if (K % 128 != 0 || !aligned16(planes) || !aligned16(out_i8)) return APNN_ERR_ALIGNMENT;
+  if (K % 128 != 0 || !aligned16(planes) || !aligned32(out_i8)) return APNN_ERR_ALIGNMENT;
   return tc5_expand(reinterpret_cast<cudaStream_t>(stream), (const uint32_t*)planes, (uint8_t*)out_i8, rows, K, bits,
                     is_signed != 0);
 }
@@ -104,7 +106,7 @@ apnn_status apnn_expand_planes_pair(void* stream, const void* planes_w, void* w_
   if (wbits < 1 || wbits > 8 || xbits < 1 || xbits > 8) return APNN_ERR_INVALID_ARG;
   if ((wbits > 4 && wbits < 8) || (xbits > 4 && xbits < 8)) return APNN_ERR_UNSUPPORTED;
   if ((w_signed && wbits != 1) || (x_signed && xbits != 1)) return APNN_ERR_UNSUPPORTED;
-  if (K % 128 != 0 || !aligned16(planes_w) || !aligned16(w_i8) || !aligned16(planes_x) || !aligned16(x_i8))
+  if (K % 128 != 0 || !aligned16(planes_w) || !aligned32(w_i8) || !aligned16(planes_x) || !aligned32(x_i8))
     return APNN_ERR_ALIGNMENT;
   return tc5_expand2(reinterpret_cast<cudaStream_t>(stream), (const uint32_t*)planes_w, (uint8_t*)w_i8, rows_w, wbits,
                      w_signed != 0, (const uint32_t*)planes_x, (uint8_t*)x_i8, rows_x, xbits, x_signed != 0, K);
@@ -142,7 +144,7 @@ apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const voi
   }
   if (algo == APNN_ALGO_TCGEN05 || algo == APNN_ALGO_TCGEN05_PAIR) {
     if (!workspace || workspace_bytes < tc5_workspace_bytes(M, N, K)) return APNN_ERR_WORKSPACE;
-    if (!aligned16(workspace)) return APNN_ERR_ALIGNMENT;
+    if (!aligned32(workspace)) return APNN_ERR_ALIGNMENT;
     return tc5_gemm(s, wbits, xbits, (const uint32_t*)W, (const uint32_t*)X, D, M, N, K, epi, workspace,
                     algo == APNN_ALGO_TCGEN05_PAIR ? 1 : 0);
   }
@@ -252,7 +254,7 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
     if (epi && epi->in_halo != 0 && epi->in_halo != pad) return APNN_ERR_UNSUPPORTED;  // use apnn_conv2d_i8
     if (epi && epi->signed_operand == APNN_SIGN_X) return APNN_ERR_UNSUPPORTED;
     if (!workspace || workspace_bytes < tc5_conv_workspace_bytes(B, H, Wd, CIN, COUT, R)) return APNN_ERR_WORKSPACE;
-    if (!aligned16(workspace)) return APNN_ERR_ALIGNMENT;
+    if (!aligned32(workspace)) return APNN_ERR_ALIGNMENT;
     return tc5_conv(reinterpret_cast<cudaStream_t>(stream), wbits, xbits, (const uint32_t*)Wt, (const uint32_t*)X, Out,
                     B, H, Wd, CIN, COUT, R, stride, epi, workspace);
   }

@@ -95,9 +95,11 @@ __device__ __forceinline__ void expand_words(const ExpandJob& j, long long first
         // signed 1-bit operand: bit 1 -> +1 (0x01), bit 0 -> -1 (0xFF)
         r[q] = (BITS == 1 && j.is_signed) ? (0xFFFFFFFFu ^ (v * 0xFEu)) : v;
       }
-      uint4* dst = reinterpret_cast<uint4*>(j.out + (u == 0 ? i : i2) * 32);
-      dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
-      dst[1] = make_uint4(r[4], r[5], r[6], r[7]);
+      // one 32-byte store per word: a warp writes 1 KiB of whole sectors per instruction
+      uint8_t* dst = j.out + (u == 0 ? i : i2) * 32;
+      asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                   "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                   : "memory");
     }
   }
 }

@@ -120,7 +120,8 @@ apnn_status apnn_gemm_check(void *stream, const void *workspace, int M, int N, i
 /* The two stages of APNN_ALGO_TCGEN05 as entry points of their own, so that a static
  * operand (the weights of a layer) is expanded once and reused.  No counterpart in the
  * reference, whose kernels read the planes directly.
- * apnn_expand_planes: planes[bits][rows][K/32] -> out_i8[rows][K], one byte per element,
+ * apnn_expand_planes: planes[bits][rows][K/32] -> out_i8[rows][K] (32-byte aligned, as is any
+ *   workspace), one byte per element,
  *   value = sum_p bit_p << p, or -1/+1 for a 1-bit operand with is_signed != 0.  The byte
  *   order inside each group of 32 k is a fixed permutation shared by both operands.
  * apnn_gemm_i8: D = W8 * X8^T over operands produced by apnn_expand_planes, same epilogue;
