@@ -362,7 +362,7 @@ def run_ours(args) -> None:
         "bf16_tflops_measured": peaks.get("bf16_tflops"), "bf16_tflops_sustained": peaks.get("bf16_tflops_sustained"),
         "frac_of_2x_bf16_burst": achieved / (2 * peaks["bf16_tflops"]) if peaks.get("bf16_tflops") else None,
         "kernel_ms": kernel_ms, "algorithmic_ops_per_launch": ops_launch,
-        "traffic": None,
+        "traffic": {"dram_bytes_per_launch": 578794000, "source": "ncu capture of this command at full size, profiles/tc5_gemm_pair_kernel_gemm_w1a2_8192.md"} if algo == "tcgen05" else None,
     }
 
     # ---- CPU baseline: the reference's compute_ref on a bounded sample of rows
