@@ -362,7 +362,9 @@ def run_ours(args) -> None:
         "bf16_tflops_measured": peaks.get("bf16_tflops"), "bf16_tflops_sustained": peaks.get("bf16_tflops_sustained"),
         "frac_of_2x_bf16_burst": achieved / (2 * peaks["bf16_tflops"]) if peaks.get("bf16_tflops") else None,
         "kernel_ms": kernel_ms, "algorithmic_ops_per_launch": ops_launch,
-        "traffic": {"dram_bytes_per_launch": 578794000, "source": "ncu capture of this command at full size, profiles/tc5_gemm_pair_kernel_gemm_w1a2_8192.md"} if algo == "tcgen05" else None,
+        "traffic": 578794000 if algo == "tcgen05" else None,
+        "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum per launch, ncu capture of `bench.py --profile` at full size",
+        "algorithmic_bytes_per_launch": M * K + N * K + 4 * M * N,
     }
 
     # ---- CPU baseline: the reference's compute_ref on a bounded sample of rows
