@@ -38,6 +38,9 @@ class Epilogue(ctypes.Structure):
         ("thresholds", ctypes.c_void_p),
         ("residual_in", ctypes.c_void_p),
         ("residual_out", ctypes.c_void_p),
+        ("n_peer_out", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("peer_out", ctypes.c_void_p * 7),
     ]
 
 

@@ -48,6 +48,9 @@ apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, i
   if (!is_conv && (e->pool != APNN_POOL_NONE || e->out_halo != 0)) return APNN_ERR_INVALID_ARG;
   if (e->out_halo < 0 || e->out_halo > 8) return APNN_ERR_INVALID_ARG;
   if (e->in_halo < 0 || e->in_halo > 8 || (!is_conv && e->in_halo != 0)) return APNN_ERR_INVALID_ARG;
+  if (e->n_peer_out < 0 || e->n_peer_out > 7 || (is_conv && e->n_peer_out != 0)) return APNN_ERR_INVALID_ARG;
+  for (int i = 0; i < e->n_peer_out; i++)
+    if (!e->peer_out[i] || (reinterpret_cast<uintptr_t>(e->peer_out[i]) & 15u)) return APNN_ERR_INVALID_ARG;
   return APNN_OK;
 }
 
@@ -149,6 +152,7 @@ apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const voi
                     algo == APNN_ALGO_TCGEN05_PAIR ? 1 : 0);
   }
 
+  if (epi && epi->n_peer_out != 0) return APNN_ERR_UNSUPPORTED;  // peer stores exist in the pair kernel only
   CoreParams p;
   memset(&p, 0, sizeof(p));
   p.A = (const uint32_t*)W;

@@ -587,7 +587,8 @@ apnn_status tc5_expand2(cudaStream_t s, const uint32_t* pa, uint8_t* oa, long lo
 
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
-  if (tc5_pair_worthwhile(M, N, K)) return tc5_gemm_i8_pair(s, A8, B8, D, M, N, K, a_signed, b_signed, epi, status_flag);
+  if (tc5_pair_worthwhile(M, N, K) || (epi && epi->n_peer_out > 0))
+    return tc5_gemm_i8_pair(s, A8, B8, D, M, N, K, a_signed, b_signed, epi, status_flag);
   cudaError_t e;
   const int sms = device_sm_count();
   Tc5Params p;

@@ -34,7 +34,7 @@ constexpr int TILE_N = 256;
 constexpr int HALF = 128;     // rows of A and of B one CTA stages
 constexpr int STAGES = 6;
 constexpr int STAGE_BYTES = 2 * HALF * BK;  // 32 KiB per CTA
-constexpr int THR_BYTES_PER_WARP = TILE_N * 16;
+constexpr int THR_BYTES_PER_WARP = 32 * 36 * 4;  // thresholds (256 x 16 B) or a padded 32 x 32 int32 block
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * THR_BYTES_PER_WARP;
 constexpr int THREADS = 192;
 constexpr int GROUP_M = 8;    // bands of 8 pair-tiles (2048 rows) for L2 reuse
@@ -50,6 +50,8 @@ struct PairParams {
   uint32_t idesc;
   long long out_plane_words;
   int* error_flag;
+  int n_out;       // destinations of every output tile: out itself, then peer-mapped copies
+  void* outs[8];
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -243,9 +245,9 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         tmem_ld32(taddr + c * 32, v);
         tmem_ld_wait();
         const int col0 = tn * TILE_N + c * 32;
-        if (!row_ok || col0 >= p.N) continue;
-        const bool whole = (p.N & 3) == 0 && col0 + 32 <= p.N;
-        if (p.residual_in != nullptr || p.residual_out != nullptr) {
+        if (col0 >= p.N) continue;                        // uniform over the warp
+        if (p.out_mode != OUT_INT32 && !row_ok) continue;  // packed modes: a thread writes only its own row
+        if (row_ok && (p.residual_in != nullptr || p.residual_out != nullptr)) {
           const long long at = row * (long long)p.N + col0;
 #pragma unroll
           for (int j = 0; j < 32; j++)
@@ -255,15 +257,38 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
         }
         if (p.out_mode == OUT_INT32) {
-          int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
-          if (whole) {
+          // Transpose the warp's 32 x 32 block through shared memory (rows padded to 36 words,
+          // 16-byte accesses, conflict-free) so that every store instruction writes four whole
+          // 128-byte row segments: full lines for HBM and, for the fused all-gather, for NVLink.
+          // The block goes to the local output and to every peer's buffer.
+          uint32_t* tile_s = reinterpret_cast<uint32_t*>(thr_s);  // this warp's slice
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 8; j++)
-              reinterpret_cast<uint4*>(D)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {
+          for (int j = 0; j < 8; j++)
+            *reinterpret_cast<uint4*>(tile_s + lane * 36 + 4 * j) =
+                make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          __syncwarp();
+          const long long row0 = (long long)tm * TILE_M + (int)rank * HALF + quarter * 32;
+          const int sub_r = lane >> 3, c4 = (lane & 7) * 4;
+          const bool vec_ok = (p.N & 3) == 0 && col0 + 32 <= p.N;
 #pragma unroll
-            for (int j = 0; j < 32; j++)
-              if (col0 + j < p.N) D[j] = (int32_t)v[j];
+          for (int i = 0; i < 8; i++) {
+            const int r = 4 * i + sub_r;
+            const uint4 x = *reinterpret_cast<const uint4*>(tile_s + r * 36 + c4);
+            if (row0 + r < p.M) {
+              const long long at = (row0 + r) * (long long)p.N + col0 + c4;
+              for (int q = 0; q < p.n_out; q++) {
+                uint32_t* dst = reinterpret_cast<uint32_t*>(p.outs[q]) + at;
+                if (vec_ok) {
+                  *reinterpret_cast<uint4*>(dst) = x;
+                } else {
+                  if (col0 + c4 < p.N) dst[0] = x.x;
+                  if (col0 + c4 + 1 < p.N) dst[1] = x.y;
+                  if (col0 + c4 + 2 < p.N) dst[2] = x.z;
+                  if (col0 + c4 + 3 < p.N) dst[3] = x.w;
+                }
+              }
+            }
           }
         } else {
           uint32_t lv[32];
@@ -286,12 +311,12 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               lv[j] = l;
             }
           }
-          uint32_t* O = reinterpret_cast<uint32_t*>(p.out);
           for (int b = 0; b < p.out_bits; b++) {
             uint32_t word = 0;
 #pragma unroll
             for (int j = 0; j < 32; j++) word |= ((lv[j] >> b) & 1u) << (31 - j);
-            O[b * p.out_plane_words + row * (p.N >> 5) + (col0 >> 5)] = word;
+            for (int q = 0; q < p.n_out; q++)
+              reinterpret_cast<uint32_t*>(p.outs[q])[b * p.out_plane_words + row * (p.N >> 5) + (col0 >> 5)] = word;
           }
         }
       }
@@ -371,6 +396,10 @@ apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B
   p.out_bits = epi ? epi->out_bits : 0;
   p.out_plane_words = (long long)M * (N / 32);
   p.error_flag = status_flag;
+  p.n_out = 1;
+  p.outs[0] = D;
+  if (epi)
+    for (int i = 0; i < epi->n_peer_out && p.n_out < 8; i++) p.outs[p.n_out++] = epi->peer_out[i];
   // D = s32, A/B = u8 or s8, K-major, N = 256, M = 256 over the pair
   p.idesc = (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(TILE_N >> 3) << 17) |
             ((uint32_t)(TILE_M >> 4) << 24);

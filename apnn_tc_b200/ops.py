@@ -40,13 +40,15 @@ def _dev_words(t: torch.Tensor, name: str) -> torch.Tensor:
 
 def make_epilogue(out_mode: str = "int32", out_bits: int = 0, signed: str = "none", pool: str = "none",
                   out_halo: int = 0, in_halo: int = 0, thresholds: Optional[torch.Tensor] = None,
-                  residual_in: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None) -> Epilogue:
+                  residual_in: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None,
+                  peer_out: Optional[list] = None) -> Epilogue:
     """Build the fused-epilogue descriptor.
 
     out_mode: "int32" | "lowbits" (the reference's ``val & (2^bits-1)``) | "thresholds"
     signed:   "none" | "w" | "x" -- which argument's bits mean -1/+1
     pool:     "none" | "avg" (reference: truncating (a+b+c+d)/4 before requantisation) | "max"
     residual_in / residual_out: dense int32 [rows, channels] added before / saved after the add
+    peer_out: raw device addresses that also receive every output tile (tcgen05 pair GEMM only)
     """
     e = Epilogue()
     e.out_mode = {"int32": 0, "lowbits": 1, "thresholds": 2}[out_mode]
@@ -58,6 +60,12 @@ def make_epilogue(out_mode: str = "int32", out_bits: int = 0, signed: str = "non
     e.thresholds = thresholds.data_ptr() if thresholds is not None else None
     e.residual_in = residual_in.data_ptr() if residual_in is not None else None
     e.residual_out = residual_out.data_ptr() if residual_out is not None else None
+    if peer_out:
+        if len(peer_out) > 7:
+            raise ValueError("at most 7 peer destinations")
+        e.n_peer_out = len(peer_out)
+        for i, ptr in enumerate(peer_out):   # raw device addresses (peer-mapped memory)
+            e.peer_out[i] = int(ptr)
     e._keepalive = (thresholds, residual_in, residual_out)
     return e
 

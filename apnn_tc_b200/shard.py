@@ -49,3 +49,32 @@ def max_over_ranks(value: float, device, group=None) -> float:
     t = torch.tensor([value], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t[0])
+
+
+class SymmetricGather:
+    """A [world][M][n] int32 buffer allocated as symmetric memory (the same buffer, peer-mapped, on
+    every rank) for the fused all-gather: a rank's GEMM writes its column block into slot ``rank``
+    of its own buffer and -- through ``peer_destinations()`` handed to the epilogue as
+    ``peer_out`` -- into slot ``rank`` of every other rank's buffer, with plain stores over NVLink
+    from the kernel that computes the tile.  ``barrier()`` orders the ranks before anyone reads.
+    """
+
+    def __init__(self, M: int, n: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.buffer = symm_mem.empty((self.world, M, n), dtype=torch.int32, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.slot_bytes = M * n * 4
+
+    def local_slot(self) -> torch.Tensor:
+        return self.buffer[self.rank]
+
+    def peer_destinations(self) -> list:
+        """Device addresses of slot ``rank`` in every other rank's buffer."""
+        ptrs = list(self.handle.buffer_ptrs)
+        return [int(ptrs[r]) + self.rank * self.slot_bytes for r in range(self.world) if r != self.rank]
+
+    def barrier(self) -> None:
+        self.handle.barrier()

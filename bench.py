@@ -250,14 +250,33 @@ def run_ours(args) -> None:
 
     launches_per_step = 2 if algo == "tcgen05" else 1
     gathered = None
-    if args.allgather and dist is not None:
+    if args.allgather != "none" and dist is not None:
         from apnn_tc_b200 import shard
-        gathered = torch.empty((world, M, N), dtype=torch.int32, device=dev)
-        base_step = step
+        if args.allgather == "nccl":
+            gathered = torch.empty((world, M, N), dtype=torch.int32, device=dev)
+            base_step = step
 
-        def step(i: int, ev=None):  # noqa: F811 -- the GEMM followed by the output all-gather over NVLink
-            base_step(i, ev)
-            shard.allgather_columns(D, out=gathered)
+            def step(i: int, ev=None):  # noqa: F811 -- the GEMM followed by an NCCL all-gather of the slices
+                base_step(i, ev)
+                shard.allgather_columns(D, out=gathered)
+        else:
+            # fused: the GEMM epilogue stores every tile into all ranks' buffers (peer stores over NVLink)
+            sg = shard.SymmetricGather(M, N, dev)
+            gathered = sg.buffer
+            D = sg.local_slot()
+            fused_epi = ap.make_epilogue("int32", peer_out=sg.peer_destinations())
+
+            def step(i: int, ev=None):  # noqa: F811
+                W, X = Ws[i % N_OPERAND_SETS], Xs[i % N_OPERAND_SETS]
+                _cabi.check(_cabi.lib().apnn_expand_planes_pair(torch.cuda.current_stream().cuda_stream, W.data_ptr(),
+                                                                 W8.data_ptr(), M, WBITS, 0, X.data_ptr(), X8.data_ptr(),
+                                                                 N, XBITS, 0, K), "apnn_expand_planes_pair")
+                if ev is not None:
+                    ev[0].record()
+                ap.gemm_i8(W8, X8, D, status_flag=flag, epilogue=fused_epi)
+                if ev is not None:
+                    ev[1].record()
+                sg.barrier()   # every rank's tiles have landed before the next step overwrites them
 
     for i in range(args.warmup):
         step(i)
@@ -303,6 +322,15 @@ def run_ours(args) -> None:
         got = D[torch.from_numpy(rows).to(dev)].cpu().numpy()
         if not np.array_equal(got, want):
             raise SystemExit("bench output does not match the oracle")
+
+    if gathered is not None:
+        # every rank: the gathered buffer must equal an NCCL all-gather of the ranks' own slices
+        ref = torch.empty((world, M, N), dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(ref.view(world * M, N), D.contiguous())
+        torch.cuda.synchronize()
+        if not torch.equal(ref, gathered):
+            raise SystemExit(f"rank {rank}: gathered output differs from the all-gather of the slices")
+        del ref
 
     if args.profile:
         if rank == 0:
@@ -396,7 +424,8 @@ def run_ours(args) -> None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8 operands, int32 accumulate (exact)", "data": "synthetic",
         "config": dict(workload_config(world, algo), collective=("all_gather of the int32 output slices, "
-                       f"{(world - 1) * M * N * 4} B inbound per rank per step" if gathered is not None else "none")),
+                       f"{(world - 1) * M * N * 4} B inbound per rank per step, mode " + args.allgather if gathered is not None
+                       else "none")),
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
         "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
     }
@@ -497,8 +526,9 @@ def main() -> None:
     ap_.add_argument("--warmup", type=int, default=5)
     ap_.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap_.add_argument("--algo", default="tcgen05", choices=["tcgen05", "imma", "bmma"])
-    ap_.add_argument("--allgather", action="store_true",
-                     help="N > 1 only: all-gather the int32 output slices inside every timed step")
+    ap_.add_argument("--allgather", default="none", choices=["none", "nccl", "fused"],
+                     help="N > 1 only: gather the int32 output slices on every rank inside every timed step, by an "
+                          "NCCL all-gather after the GEMM or fused into the GEMM epilogue as peer stores")
     ap_.add_argument("--profile", action="store_true",
                      help="timed steps only (no e2e, probe or CPU baseline): the command ncu captures")
     ap_.add_argument("--workload", default="gemm", choices=["gemm", "resnet18", "vgg_variant", "alexnet"],

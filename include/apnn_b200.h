@@ -82,6 +82,16 @@ typedef struct apnn_epilogue {
   int32_t *residual_out;      /* optional, same shape: receives the int32 value (after the
                                  residual add) next to the requantised output, i.e. the
                                  "save_residual" output of NN/param.h:943-945 */
+  int32_t n_peer_out;         /* GEMM on the tcgen05 CTA-pair kernel only: number of extra
+                                 destinations in peer_out (0..7) */
+  int32_t reserved;
+  void *peer_out[7];          /* every output tile is also stored, in D's layout, to these
+                                 addresses -- peer-mapped memory of other GPUs (NVLink): with D and
+                                 peer_out[] pointing at this rank's slot of a [ranks][M][N/ranks]
+                                 buffer on every GPU, the N-sharded GEMM leaves the gathered
+                                 result everywhere without a separate all-gather.  The caller
+                                 synchronises the ranks before reading.  No reference counterpart
+                                 (the reference is single-GPU). */
 } apnn_epilogue;
 
 const char *apnn_status_string(apnn_status s);

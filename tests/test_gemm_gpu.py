@@ -278,3 +278,39 @@ def test_gemm_residual(cuda_device, algo):
         out = ap.apmm(to_dev(W), to_dev(X), epilogue=epi, algo=algo)
     assert np.array_equal(to_host(res_out, np.int32), v)
     assert np.array_equal(to_host(out), oracle.requant_pack(v, 2, 1))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (300, 260, 384), (130, 257, 640)])
+@pytest.mark.parametrize("mode", ["int32", "lowbits"])
+def test_tcgen05_peer_destinations(cuda_device, M, N, K, mode):
+    """Every output tile also lands in the extra destinations (the fused all-gather's store path);
+    here the extra destinations are two more local buffers."""
+    import apnn_tc_b200 as ap
+    if mode == "lowbits" and N % 32:
+        pytest.skip("packed outputs need N % 32 == 0")
+    rng = np.random.default_rng(M + 3 * N + K)
+    W, _ = oracle.value_planes(rng, M, K, 1)
+    X, _ = oracle.value_planes(rng, N, K, 2)
+    acc = oracle.gemm_popc(W, X, threads=4)
+    if mode == "int32":
+        want = acc
+        extra = [torch.full((M, N), -7, dtype=torch.int32, device="cuda") for _ in range(2)]
+        epi = ap.make_epilogue("int32", peer_out=[t.data_ptr() for t in extra])
+    else:
+        want = oracle.requant_pack(acc, 2, 1)
+        extra = [torch.full(want.shape, -7, dtype=torch.int32, device="cuda") for _ in range(2)]
+        epi = ap.make_epilogue("lowbits", 2, peer_out=[t.data_ptr() for t in extra])
+    out = run_tc5(W, X, epi)
+    host = np.int32 if mode == "int32" else np.uint32
+    assert np.array_equal(to_host(out, host), want)
+    for t in extra:
+        assert np.array_equal(to_host(t, host), want)
+
+
+def test_peer_destinations_refused_off_the_pair_kernel(cuda_device):
+    import apnn_tc_b200 as ap
+    W = torch.zeros((1, 64, 4), dtype=torch.int32, device="cuda")
+    X = torch.zeros((2, 64, 4), dtype=torch.int32, device="cuda")
+    extra = torch.zeros((64, 64), dtype=torch.int32, device="cuda")
+    with pytest.raises(ap.ApnnError):
+        ap.apmm(W, X, algo="imma", epilogue=ap.make_epilogue("int32", peer_out=[extra.data_ptr()]))
