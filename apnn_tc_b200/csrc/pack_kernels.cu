@@ -171,6 +171,79 @@ apnn_status launch_pack(void* stream, const void* in, uint32_t* planes, long row
 }
 
 }  // namespace
+// The same re-layout with each image element quantised once per output row instead of once per
+// window it falls in: a CTA owns the output rows (b, ho) it walks; it loads the R input rows
+// that row needs with coalesced 16-byte loads, quantises them into shared memory as one byte
+// per element (zero bytes for the padding ring), and then every thread assembles 32-k words
+// from contiguous runs of R*C bytes.  Output words of one row are contiguous in every plane.
+template <int BITS>   // plane count, or 0 to take it from the argument
+__global__ void __launch_bounds__(256) quantize_im2col_rows_kernel(const float* __restrict__ img,
+                                                                   uint32_t* __restrict__ planes, int B, int H,
+                                                                   int W, int C, int R, int stride, int bits,
+                                                                   int Ho, int Wo, int kwords, int rowlen) {
+  extern __shared__ __align__(16) unsigned char lv_s[];   // [R][rowlen]
+  if (BITS) bits = BITS;
+  const float steps = (float)(1 << bits);
+  const uint32_t maxlv = (1u << bits) - 1u;
+  const int pad = (R - 1) / 2;
+  const int kreal = R * R * C, tapw = R * C, wc = W * C;
+  const long long plane_words = (long long)B * Ho * Wo * kwords;
+  const bool vec = (wc & 3) == 0;
+  for (int orow = blockIdx.x; orow < B * Ho; orow += gridDim.x) {
+    const int b = orow / Ho, ho = orow - b * Ho;
+    const int hbase = ho * stride - pad;
+    __syncthreads();   // the previous row's readers are done
+    // zero the left / right padding bytes of every staged row
+    for (int t = threadIdx.x; t < R * 2 * pad * C; t += blockDim.x) {
+      const int i = t / (2 * pad * C), o = t - i * (2 * pad * C);
+      lv_s[i * rowlen + (o < pad * C ? o : wc + o)] = 0;
+    }
+    for (int i = 0; i < R; i++) {
+      const int hi = hbase + i;
+      unsigned char* dst = lv_s + i * rowlen + pad * C;
+      if (hi < 0 || hi >= H) {
+        for (int t = threadIdx.x; t < wc; t += blockDim.x) dst[t] = 0;
+      } else {
+        const float* src = img + ((long long)b * H + hi) * wc;
+        if (vec) {
+          for (int t = threadIdx.x; t < wc / 4; t += blockDim.x) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(src) + t);
+            dst[4 * t] = (unsigned char)quantize_level(f.x, steps, maxlv);
+            dst[4 * t + 1] = (unsigned char)quantize_level(f.y, steps, maxlv);
+            dst[4 * t + 2] = (unsigned char)quantize_level(f.z, steps, maxlv);
+            dst[4 * t + 3] = (unsigned char)quantize_level(f.w, steps, maxlv);
+          }
+        } else {
+          for (int t = threadIdx.x; t < wc; t += blockDim.x)
+            dst[t] = (unsigned char)quantize_level(__ldg(src + t), steps, maxlv);
+        }
+      }
+    }
+    __syncthreads();
+    const long long out0 = (long long)orow * Wo * kwords;
+    for (int t = threadIdx.x; t < Wo * kwords; t += blockDim.x) {
+      const int wo = t / kwords, w = t - wo * kwords;
+      uint32_t word[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+      int k = w * 32;
+      if (k < kreal) {
+        int i = k / tapw, off = k - i * tapw;
+        const unsigned char* rowp = lv_s + i * rowlen + wo * stride * C;
+        for (int e = 0; e < 32 && k < kreal; e++, k++) {
+          const uint32_t lv = rowp[off];
+#pragma unroll
+          for (int pl = 0; pl < 8; pl++)
+            if (pl < bits) word[pl] |= ((lv >> pl) & 1u) << (31 - e);
+          if (++off == tapw) { off = 0; rowp += rowlen; }
+        }
+      }
+#pragma unroll
+      for (int pl = 0; pl < 8; pl++)
+        if (pl < bits) planes[(long long)pl * plane_words + out0 + t] = word[pl];
+    }
+  }
+}
+
+
 }  // namespace apnn
 
 extern "C" {
@@ -193,10 +266,23 @@ apnn_status apnn_quantize_im2col(void* stream, const float* images, uint32_t* pl
   const int Ho = (H - 1) / stride + 1, Wo = (W - 1) / stride + 1;
   const int kwords = (R * R * C + 127) / 128 * 4;
   const long long total = (long long)B * Ho * Wo * kwords;
-  long long nb = (total + 255) / 256, cap = (long long)device_sm_count() * 16;
-  if (nb > cap) nb = cap;
-  quantize_im2col_kernel<<<(unsigned)nb, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(images, planes, B, H, W, C, R,
-                                                                                          stride, bits, Ho, Wo, kwords);
+  const int pad = (R - 1) / 2;
+  const int rowlen = ((W + 2 * pad) * C + 15) / 16 * 16;
+  const size_t smem = (size_t)R * rowlen;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (smem <= 48 * 1024) {
+    // one CTA per output row, as many resident rows as the device holds at once
+    long long nb = (long long)B * Ho, cap = (long long)device_sm_count() * 8;
+    if (nb > cap) nb = cap;
+    auto kern = bits == 1 ? quantize_im2col_rows_kernel<1> : bits == 2 ? quantize_im2col_rows_kernel<2>
+              : bits == 3 ? quantize_im2col_rows_kernel<3> : bits == 4 ? quantize_im2col_rows_kernel<4>
+                                                           : quantize_im2col_rows_kernel<0>;
+    kern<<<(unsigned)nb, 256, smem, s>>>(images, planes, B, H, W, C, R, stride, bits, Ho, Wo, kwords, rowlen);
+  } else {
+    long long nb = (total + 255) / 256, cap = (long long)device_sm_count() * 16;
+    if (nb > cap) nb = cap;
+    quantize_im2col_kernel<<<(unsigned)nb, 256, 0, s>>>(images, planes, B, H, W, C, R, stride, bits, Ho, Wo, kwords);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "quantize_im2col launch");
   return APNN_OK;

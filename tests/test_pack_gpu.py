@@ -33,7 +33,9 @@ def test_images_quantization(cuda_device, shape, bits):
 
 
 @pytest.mark.parametrize("B,H,Wd,C,R,stride,bits", [(2, 9, 7, 3, 3, 2, 2), (3, 32, 32, 3, 7, 4, 2), (2, 20, 24, 3, 11, 4, 2),
-                                                    (1, 8, 8, 5, 5, 1, 4), (2, 6, 6, 40, 3, 1, 2)])
+                                                    (1, 8, 8, 5, 5, 1, 4), (2, 6, 6, 40, 3, 1, 2),
+                                                    (1, 224, 224, 3, 7, 4, 2), (1, 16, 12, 3, 3, 1, 8),
+                                                    (1, 12, 1500, 3, 11, 4, 2)])
 def test_quantize_im2col(cuda_device, B, H, Wd, C, R, stride, bits):
     """First-layer re-layout: quantised RxRxC windows gathered along the channel axis."""
     import ctypes
