@@ -97,7 +97,7 @@ apnn_status apnn_expand_planes(void* stream, const void* planes, void* out_i8, l
   if (!planes || !out_i8 || rows <= 0 || K <= 0 || bits < 1 || bits > 8) return APNN_ERR_INVALID_ARG;
   if (bits > 4 && bits < 8) return APNN_ERR_UNSUPPORTED;
   if (is_signed && bits != 1) return APNN_ERR_UNSUPPORTED;
-  if (K % 128 != 0 || !aligned16(planes) || !aligned32(out_i8)) return APNN_ERR_ALIGNMENT;
+  if (K % 64 != 0 || !aligned16(planes) || !aligned32(out_i8)) return APNN_ERR_ALIGNMENT;
   return tc5_expand(reinterpret_cast<cudaStream_t>(stream), (const uint32_t*)planes, (uint8_t*)out_i8, rows, K, bits,
                     is_signed != 0);
 }
@@ -203,7 +203,7 @@ apnn_status apnn_conv2d_i8(void* stream, const void* W8, const void* X8, void* O
   if (!W8 || !X8 || !Out || !status_flag) return APNN_ERR_INVALID_ARG;
   if (B <= 0 || H <= 0 || W <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
   if (R < 1 || R > 11 || (R & 1) == 0) return APNN_ERR_UNSUPPORTED;
-  if (CIN % 128 != 0 || !aligned16(W8) || !aligned16(X8) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
+  if (CIN % 64 != 0 || !aligned16(W8) || !aligned16(X8) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
   if (epi) {
     if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;  // the sign is in the bytes
     apnn_status st = check_epilogue(epi, COUT, true, 1, 1);
@@ -232,7 +232,8 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
   if (B <= 0 || H <= 0 || Wd <= 0 || CIN <= 0 || COUT <= 0) return APNN_ERR_INVALID_ARG;
   if (R < 1 || R > 11 || (R & 1) == 0) return APNN_ERR_UNSUPPORTED;
   if (stride < 1 || stride > 4) return APNN_ERR_UNSUPPORTED;
-  if (CIN % 128 != 0) return APNN_ERR_ALIGNMENT;
+  // 64-channel feature maps run on the tcgen05 path only (64-byte swizzle rows)
+  if (CIN % 128 != 0 && !(CIN % 64 == 0 && algo == APNN_ALGO_TCGEN05)) return APNN_ERR_ALIGNMENT;
   if (!aligned16(Wt) || !aligned16(X) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
   // core operand A = activations (xbits), B = filter (wbits)
   if (!core_supports(xbits, wbits)) return APNN_ERR_UNSUPPORTED;

@@ -2,6 +2,7 @@
 // the three contraction paths on the device at hand (no global-memory traffic in the loop).
 //   kind 0: tcgen05.mma kind::i8, M=128 N=256 K=32, operands fixed in shared memory,
 //           two TMEM accumulators, one CTA per SM
+//   kind 3, 4: the same with N=128 and N=64 (narrow tiles of the convolution path)
 //   kind 1: mma.sync m16n8k32 u8, register operands
 //   kind 2: mma.sync m16n8k256 b1 and.popc, register operands
 #include <cuda.h>
@@ -15,6 +16,7 @@ namespace {
 
 constexpr unsigned long long PROBE_WAIT_NS = 2000000000ull;
 
+template <int PN>   // MMA width N: 256, 128 or 64
 __global__ void __launch_bounds__(128, 1) probe_tcgen05_i8(int iters, int* flag) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -43,9 +45,9 @@ __global__ void __launch_bounds__(128, 1) probe_tcgen05_i8(int iters, int* flag)
              ((uint64_t)2 << 61);
     };
     const uint64_t ad = desc(base), bd = desc(base + 128 * 128);
-    const uint32_t idesc = (2u << 4) | (32u << 17) | (8u << 24);
+    const uint32_t idesc = (2u << 4) | ((uint32_t)(PN >> 3) << 17) | (8u << 24);
     for (int it = 0; it < iters; it++) {
-      const uint32_t d = tmem + (it & 1) * 256;
+      const uint32_t d = tmem + (it & 1) * PN;
 #pragma unroll
       for (int k = 0; k < 4; k++) {
         asm volatile(
@@ -112,17 +114,19 @@ __global__ void __launch_bounds__(512) probe_mma_sync(int iters, int* sink) {
 
 extern "C" apnn_status apnn_probe_peak(void* stream, int kind, int iters, int* scratch_flag, double* ops_per_launch) {
   using namespace apnn;
-  if (!scratch_flag || !ops_per_launch || iters <= 0 || kind < 0 || kind > 2) return APNN_ERR_INVALID_ARG;
+  if (!scratch_flag || !ops_per_launch || iters <= 0 || kind < 0 || kind > 4) return APNN_ERR_INVALID_ARG;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int sms = device_sm_count();
   cudaError_t e = cudaMemsetAsync(scratch_flag, 0, sizeof(int), s);
   if (e != cudaSuccess) return cuda_fail(e, "probe flag reset");
-  if (kind == 0) {
+  if (kind == 0 || kind == 3 || kind == 4) {
     const int smem = 128 * 128 + 256 * 128 + 1024 + 64;
-    e = cudaFuncSetAttribute(probe_tcgen05_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const int pn = kind == 0 ? 256 : kind == 3 ? 128 : 64;
+    auto kern = kind == 0 ? probe_tcgen05_i8<256> : kind == 3 ? probe_tcgen05_i8<128> : probe_tcgen05_i8<64>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_fail(e, "probe smem attribute");
-    probe_tcgen05_i8<<<sms, 128, smem, s>>>(iters, scratch_flag);
-    *ops_per_launch = (double)sms * iters * 4.0 * 2.0 * 128 * 256 * 32;
+    kern<<<sms, 128, smem, s>>>(iters, scratch_flag);
+    *ops_per_launch = (double)sms * iters * 4.0 * 2.0 * 128 * pn * 32;
   } else if (kind == 1) {
     probe_mma_sync<1><<<sms * 2, 512, 0, s>>>(iters, scratch_flag);
     *ops_per_launch = (double)sms * 2 * 16 * iters * 8.0 * 2.0 * 16 * 8 * 32;

@@ -102,5 +102,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
+// The same for rows of BKB bytes (128: SWIZZLE_128B, groups 1024 bytes apart; 64: SWIZZLE_64B,
+// groups 512 bytes apart).
+template <int BKB>
+__device__ __forceinline__ uint64_t make_smem_desc_k(uint32_t saddr) {
+  static_assert(BKB == 128 || BKB == 64, "swizzle span");
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)((8 * BKB) >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)(BKB == 128 ? 2 : 4) << 61;
+  return d;
+}
+
 }  // namespace tc5
 }  // namespace apnn

@@ -40,22 +40,24 @@ namespace {
 using tc5::BM;
 using tc5::BK;
 
-constexpr int A_STAGE_BYTES = BM * BK;
-constexpr int THREADS = 192;
-constexpr int MAX_STAGES = 6;
+constexpr int THREADS = 320;     // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int EPI_WARPS = 8;     // two per TMEM lane quarter, splitting a tile's 32-column chunks
+constexpr int MAX_STAGES = 12;
+constexpr int SMEM_LIMIT = 232448;   // 227 KiB of dynamic shared memory per CTA
 
-// Tile width N is 256 (4 stages of 48 KiB) when that still fills the device, else 128
-// (6 stages of 32 KiB): twice as many tiles for mid-sized problems.
-template <int BN>
+// Tile shape: 128 rows x BN columns; BKB bytes of K per stage row (= the swizzle span: 128,
+// or 64 for operands whose K is a multiple of 64 only, e.g. 64-channel feature maps).
+template <int BN, int BKB>
 struct TileCfg {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
-  static constexpr int B_STAGE_BYTES = BN * BK;
-  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  // each epilogue warp keeps the tile's thresholds as one 16-byte entry per column
-  static constexpr int THR_BYTES_PER_WARP = BN * 16;
-  static constexpr int SMEM_BYTES =
-      STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * THR_BYTES_PER_WARP;
+  static constexpr int A_STAGE_BYTES = BM * BKB;
+  static constexpr int B_STAGE_BYTES = BN * BKB;
   static constexpr int TMEM_COLS = 2 * BN;
+  // after the operand tiles: barriers, then per epilogue warp 32 threshold entries of 16 bytes
+  // and a 32 x 16-word transposition block
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int THR_BYTES_PER_WARP = 32 * 16;
+  static constexpr int XPOSE_BYTES_PER_WARP = 32 * 16 * 4;
+  static constexpr int FIXED_BYTES = 1024 /*alignment slack*/ + BAR_BYTES + EPI_WARPS * (THR_BYTES_PER_WARP + XPOSE_BYTES_PER_WARP);
 };
 constexpr int GROUP_M = 16;  // tiles are walked in bands of 16 row-tiles for L2 reuse
 
@@ -144,6 +146,11 @@ struct Tc5Params {
   uint32_t a_box_bytes;  // bytes one A box deposits
   const int32_t* residual_in;  // optional dense int32 [rows][N], added before requantisation
   int32_t* residual_out;       // optional dense int32 [rows][N], the value after the add
+  // shared-memory plan (chosen on the host)
+  int stages;            // ring depth
+  int kgroup;            // K blocks per stage (one barrier round trip and one commit per group)
+  int b_resident;        // 1: the whole B operand (one tile column, all K blocks) stays in shared
+                         // memory for the life of the CTA and the ring carries A tiles only
 };
 
 // Output row (units of N channels) and validity of tile row r; for pooled outputs only the
@@ -153,7 +160,21 @@ struct RowDst {
   long long dense;  // output row without the ring (index of the residual tensors)
   bool valid;
 };
-__device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, int r) {
+// Position of tile row r inside its pixel box: fixed for a thread over the whole kernel.
+struct RowInBox {
+  int wi, hi, bi;
+};
+__device__ __forceinline__ RowInBox row_in_box(const Tc5Params& p, int r) {
+  RowInBox q = {0, 0, 0};
+  if (p.is_conv) {
+    q.wi = r % p.bw;
+    const int r2 = r / p.bw;
+    q.hi = r2 % p.bh;
+    q.bi = r2 / p.bh;
+  }
+  return q;
+}
+__device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, int r, const RowInBox& q) {
   RowDst d;
   if (!p.is_conv) {
     d.row = (long long)tm * BM + r;
@@ -165,15 +186,11 @@ __device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, in
   const int t2 = tm / p.tiles_w;
   const int th = t2 % p.tiles_h;
   const int bg = t2 / p.tiles_h;
-  const int wi = r % p.bw;
-  const int r2 = r / p.bw;
-  const int hi = r2 % p.bh;
-  const int bi = r2 / p.bh;
-  const int b = bg * p.bb + bi, ho = th * p.bh + hi, wo = tw * p.bw + wi;
-  d.valid = bi < p.bb && b < p.Bn && ho < p.Ho && wo < p.Wo;
+  const int b = bg * p.bb + q.bi, ho = th * p.bh + q.hi, wo = tw * p.bw + q.wi;
+  d.valid = q.bi < p.bb && b < p.Bn && ho < p.Ho && wo < p.Wo;
   int oh = ho, ow = wo;
   if (p.pool != POOL_NONE) {
-    d.valid = d.valid && ((hi | wi) & 1) == 0;
+    d.valid = d.valid && ((q.hi | q.wi) & 1) == 0;
     oh = ho >> 1;
     ow = wo >> 1;
   }
@@ -193,40 +210,63 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / rows;
 }
 
-template <int BN>
+// The MMAs of G consecutive K blocks: A tiles G x 128 rows at sa, B tiles G x BN rows at sb.
+template <int BN, int BKB, int G>
+__device__ __forceinline__ void issue_group(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc, bool accumulate) {
+  constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB;
+#pragma unroll
+  for (int g = 0; g < G; g++) {
+    const uint64_t adesc = make_smem_desc_k<BKB>(sa + g * A_BYTES);
+    const uint64_t bdesc = make_smem_desc_k<BKB>(sb + g * B_BYTES);
+#pragma unroll
+    for (int k = 0; k < BKB / 32; k++) {
+      // advancing 32 bytes along K inside the swizzle row = +2 in 16-byte units
+      tc_mma_i8(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (accumulate || (g | k) != 0) ? 1u : 0u);
+    }
+  }
+}
+
+template <int BN, int BKB>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Tc5Params p) {
-  using Cfg = TileCfg<BN>;
-  constexpr int STAGES = Cfg::STAGES;
-  constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
+  using Cfg = TileCfg<BN, BKB>;
+  constexpr int A_STAGE_BYTES = Cfg::A_STAGE_BYTES;
+  constexpr int B_STAGE_BYTES = Cfg::B_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t bars = base + STAGES * STAGE_BYTES;
-  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then the TMEM pointer
+  // layout: [resident B: kblocks x B tile] [stages x (A tile [+ B tile])] [barriers] [thresholds] [transposition]
+  const int stages = p.stages;
+  const uint32_t bres_bytes = p.b_resident ? (uint32_t)p.kblocks * B_STAGE_BYTES : 0u;
+  const int kgroup = p.kgroup;
+  const uint32_t stage_bytes = (uint32_t)kgroup * (A_STAGE_BYTES + (p.b_resident ? 0 : B_STAGE_BYTES));
+  const uint32_t ring = base + bres_bytes;
+  const uint32_t bars = ring + (uint32_t)stages * stage_bytes;
+  // barriers (8 bytes each): full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], b_resident, then the TMEM pointer
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
-  volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
-  uint8_t* thr_stage = smem_raw + (bars + 256u - raw);  // 4 x THR_BYTES_PER_WARP
+  auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + 2 + a); };
+  const uint32_t bres_bar = bars + 8u * (2 * MAX_STAGES + 4);
+  const uint32_t tmem_slot = bars + 8u * (2 * MAX_STAGES + 5);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+  uint8_t* epi_smem = smem_raw + (bars + Cfg::BAR_BYTES - raw);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     if (blockIdx.x == 0) *p.error_flag = 0;  // only ever raised after a 2 s wait, long after this store
-    for (int s = 0; s < STAGES; s++) {
+    for (int s = 0; s < stages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), EPI_WARPS);
     }
+    mbar_init(bres_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -244,8 +284,17 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
+      if (p.b_resident && (int)blockIdx.x < num_tiles) {
+        // tiles_n == 1: every tile of this CTA uses the same B rows; fetch all K blocks once
+        mbar_expect_tx(bres_bar, bres_bytes);
+        for (int kb = 0; kb < p.kblocks; kb++)
+          tma_load_2d(base + (uint32_t)kb * B_STAGE_BYTES, &map_b, kb * BKB, 0, bres_bar);
+      }
+      const uint32_t stage_tx = (uint32_t)kgroup * ((p.is_conv ? p.a_box_bytes : (uint32_t)A_STAGE_BYTES) +
+                                                    (p.b_resident ? 0u : (uint32_t)B_STAGE_BYTES));
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
@@ -256,22 +305,26 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           h0 = (t2 % p.tiles_h) * p.bh;
           b0 = (t2 / p.tiles_h) * p.bb;
         }
-        int tap = 0, cb = 0;  // conv: K block = (filter tap, 128-channel block)
-        for (int kb = 0; kb < p.kblocks; kb++, it++) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+        int ti = 0, tj = 0, cb = 0;  // conv: K block = (filter tap row, tap column, BKB-channel block)
+        const int wbase = w0 * p.stride + p.in_off, hbase = h0 * p.stride + p.in_off;
+        for (int kb = 0; kb < p.kblocks; kb += kgroup) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
-          const uint32_t sa = base + s * STAGE_BYTES;
-          if (!p.is_conv) {
-            mbar_expect_tx(full_bar(s), STAGE_BYTES);
-            tma_load_2d(sa, &map_a, kb * BK, tm * BM, full_bar(s));
-          } else {
-            mbar_expect_tx(full_bar(s), p.a_box_bytes + Cfg::B_STAGE_BYTES);
-            const int ti = tap / p.R, tj = tap - ti * p.R;
-            tma_load_4d(sa, &map_a, cb * BK, w0 * p.stride + tj + p.in_off, h0 * p.stride + ti + p.in_off, b0, full_bar(s));
-            if (++cb == p.cblocks) { cb = 0; tap++; }
+          const uint32_t sa = ring + (uint32_t)s * stage_bytes;
+          const uint32_t sb = sa + (uint32_t)kgroup * A_STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), stage_tx);
+          for (int g = 0; g < kgroup; g++) {
+            if (!p.is_conv) {
+              tma_load_2d(sa + g * A_STAGE_BYTES, &map_a, (kb + g) * BKB, tm * BM, full_bar(s));
+            } else {
+              tma_load_4d(sa + g * A_STAGE_BYTES, &map_a, cb * BKB, wbase + tj, hbase + ti, b0, full_bar(s));
+              if (++cb == p.cblocks) {
+                cb = 0;
+                if (++tj == p.R) { tj = 0; ti++; }
+              }
+            }
+            if (!p.b_resident) tma_load_2d(sb + g * B_STAGE_BYTES, &map_b, (kb + g) * BKB, tn * BN, full_bar(s));
           }
-          tma_load_2d(sa + A_STAGE_BYTES, &map_b, kb * BK, tn * BN, full_bar(s));
+          if (++s == stages) { s = 0; ph ^= 1u; }
         }
       }
       if (!ok) atomicExch(p.error_flag, 1);
@@ -279,79 +332,115 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       uint32_t tl = 0;
       bool ok = true;
+      if (p.b_resident && (int)blockIdx.x < num_tiles) {
+        ok = mbar_wait(bres_bar, 0u);
+        tc_fence_after();
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
         const uint32_t acc = tl & 1u;
         const uint32_t aph = (tl >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.kblocks; kb++, it++) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+        for (int kb = 0; kb < p.kblocks; kb += kgroup) {
           if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = base + s * STAGE_BYTES;
-          const uint64_t adesc = make_smem_desc(sa);
-          const uint64_t bdesc = make_smem_desc(sa + A_STAGE_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK / 32; k++) {
-            // advancing 32 bytes along K inside the swizzle row = +2 in 16-byte units
-            tc_mma_i8(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          const uint32_t sa = ring + (uint32_t)s * stage_bytes;
+          const uint32_t sb = sa + (uint32_t)kgroup * A_STAGE_BYTES;
+          const uint32_t b0addr = p.b_resident ? base + (uint32_t)kb * B_STAGE_BYTES : sb;
+          // unrolled per group size: this thread's instruction stream is on the critical path
+          switch (kgroup) {
+            case 1: issue_group<BN, BKB, 1>(d_tmem, sa, b0addr, p.idesc, kb != 0); break;
+            case 2: issue_group<BN, BKB, 2>(d_tmem, sa, b0addr, p.idesc, kb != 0); break;
+            default: issue_group<BN, BKB, 3>(d_tmem, sa, b0addr, p.idesc, kb != 0); break;
           }
           tc_commit(empty_bar(s));  // frees the stage when these MMAs have read it
+          if (++s == stages) { s = 0; ph ^= 1u; }
         }
         if (ok) tc_commit(tfull_bar(acc));  // accumulator complete
       }
       if (!ok) atomicExch(p.error_flag, 2);
     }
   } else {
-    // ---------------- epilogue warps (2..5) ----------------
-    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
+    // ---------------- epilogue warps (2..9) ----------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+    const int half = ew >> 2;      // this warp drains the tile's 32-column chunks half, half+2, ...
     uint32_t tl = 0;
     bool ok = true;
     const int nl = (1 << p.out_bits) - 1;
-    // thresholds of up to 2-bit outputs are staged per tile in this warp's shared-memory
+    // thresholds of up to 2-bit outputs are staged per chunk in this warp's shared-memory
     // slice, one int4 per column (unused slots = INT_MAX), so a value costs one broadcast
     // 16-byte load instead of nl global loads
     const bool thr_staged = p.out_mode == OUT_THRESHOLDS && nl <= 3;
-    int4* thr_s = reinterpret_cast<int4*>(thr_stage + (warp - 2) * Cfg::THR_BYTES_PER_WARP);
-    int staged_tn = -1;
+    int4* thr_s = reinterpret_cast<int4*>(epi_smem + ew * Cfg::THR_BYTES_PER_WARP);
+    // 32 rows x 16 words, 16-byte groups XOR-swizzled by (row >> 1): both the row-per-lane
+    // accesses and the 4-lanes-per-row accesses below are free of bank conflicts
+    uint32_t* xp = reinterpret_cast<uint32_t*>(epi_smem + EPI_WARPS * Cfg::THR_BYTES_PER_WARP +
+                                               ew * Cfg::XPOSE_BYTES_PER_WARP);
+    auto swz = [](int r, int g) { return r * 16 + (((g ^ (r >> 1)) & 3) << 2); };
+    const bool vec_rows = (p.N & 3) == 0;
+    const int sub_r = lane >> 2, grp = lane & 3;
+    const RowInBox in_box = row_in_box(p, quarter * 32 + lane);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-      if (thr_staged && tn != staged_tn) {
-        __syncwarp();
-        for (int cidx = lane; cidx < BN; cidx += 32) {
-          const int col = tn * BN + cidx;
-          int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
-          if (col < p.N) {
-            const int32_t* T = p.thresholds + (long long)col * nl;
-            t4.x = __ldg(T);
-            if (nl > 1) { t4.y = __ldg(T + 1); t4.z = __ldg(T + 2); }
-          }
-          thr_s[cidx] = t4;
-        }
-        __syncwarp();
-        staged_tn = tn;
-      }
       const uint32_t acc = tl & 1u;
       const uint32_t aph = (tl >> 1) & 1u;
-      if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
-      tc_fence_after();
-      const RowDst dst = row_destination(p, tm, quarter * 32 + lane);
+      const RowDst dst = row_destination(p, tm, quarter * 32 + lane, in_box);
       const long long row = dst.row;
       const bool row_ok = dst.valid;
+      // destinations of the rows this lane serves in the coalesced (4 lanes per row) accesses
+      long long row_of[4], dense_of[4];
+      bool ok_of[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        row_of[i] = __shfl_sync(0xffffffffu, dst.row, 8 * i + sub_r);
+        dense_of[i] = __shfl_sync(0xffffffffu, dst.dense, 8 * i + sub_r);
+        ok_of[i] = __shfl_sync(0xffffffffu, (int)dst.valid, 8 * i + sub_r) != 0;
+      }
+      // residual rows of the chunk about to be processed, fetched ahead of their use (for the
+      // first chunk of a tile: before the wait for the accumulator) as 64-byte row segments
+      uint4 rin[8];
+      auto fetch_residual = [&](int c) {
+        const int col0 = tn * BN + c * 32;
+        if (p.residual_in == nullptr || !vec_rows || col0 + 32 > p.N) return;
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            rin[4 * hf + i] = make_uint4(0u, 0u, 0u, 0u);
+            if (ok_of[i])
+              rin[4 * hf + i] =
+                  __ldg(reinterpret_cast<const uint4*>(p.residual_in + dense_of[i] * p.N + col0 + 16 * hf + 4 * grp));
+          }
+      };
+      fetch_residual(half);
+      if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
+      tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
+      for (int c = half; c < BN / 32; c += 2) {
+        const int col0 = tn * BN + c * 32;
+        if (col0 >= p.N) continue;  // uniform over the warp
+        int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
+        if (thr_staged && col0 + lane < p.N) {
+          const int32_t* T = p.thresholds + (long long)(col0 + lane) * nl;
+          t4.x = __ldg(T);
+          if (nl > 1) { t4.y = __ldg(T + 1); t4.z = __ldg(T + 2); }
+        }
         uint32_t v[32];
         tmem_ld32(taddr + c * 32, v);
         tmem_ld_wait();
-        const int col0 = tn * BN + c * 32;
-        if (col0 >= p.N) continue;  // uniform over the warp
+        if (thr_staged) {
+          __syncwarp();   // the previous chunk's readers are done
+          thr_s[lane] = t4;
+          __syncwarp();
+        }
         if (p.pool != POOL_NONE) {
           // the four pixels of a window are lanes l, l^1 (next column) and l^bw, l^bw^1 (next row)
 #pragma unroll
@@ -363,26 +452,46 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             v[j] = (uint32_t)(p.pool == POOL_AVG2 ? (a0 + a1 + a2 + a3) / 4 : max(max(a0, a1), max(a2, a3)));
           }
         }
-        if (!row_ok) continue;
+        const bool whole = vec_rows && col0 + 32 <= p.N;   // uniform: 16-byte accesses cover the chunk
         if (p.residual_in != nullptr || p.residual_out != nullptr) {
-          const long long at = dst.dense * (long long)p.N + col0;
-          if ((p.N & 3) == 0 && col0 + 32 <= p.N) {
-            // this thread's 32 columns are 128 contiguous bytes: 16-byte accesses
+          if (whole) {
+            // int32 rows move through the transposition block so that global accesses are
+            // 64 contiguous bytes per row, 8 rows per instruction
             if (p.residual_in != nullptr) {
-              const int4* R4 = reinterpret_cast<const int4*>(p.residual_in + at);
 #pragma unroll
-              for (int j = 0; j < 8; j++) {
-                const int4 r = __ldg(R4 + j);
-                v[4 * j] += (uint32_t)r.x; v[4 * j + 1] += (uint32_t)r.y;
-                v[4 * j + 2] += (uint32_t)r.z; v[4 * j + 3] += (uint32_t)r.w;
+              for (int hf = 0; hf < 2; hf++) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(xp + swz(8 * i + sub_r, grp)) = rin[4 * hf + i];
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  const uint4 x = *reinterpret_cast<const uint4*>(xp + swz(lane, j));
+                  v[16 * hf + 4 * j] += x.x; v[16 * hf + 4 * j + 1] += x.y;
+                  v[16 * hf + 4 * j + 2] += x.z; v[16 * hf + 4 * j + 3] += x.w;
+                }
+                __syncwarp();
               }
+              if (c + 2 < BN / 32) fetch_residual(c + 2);   // the next chunk's rows, in flight during this one's tail
             }
             if (p.residual_out != nullptr) {
-              uint4* O4 = reinterpret_cast<uint4*>(p.residual_out + at);
 #pragma unroll
-              for (int j = 0; j < 8; j++) O4[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              for (int hf = 0; hf < 2; hf++) {
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                  *reinterpret_cast<uint4*>(xp + swz(lane, j)) =
+                      make_uint4(v[16 * hf + 4 * j], v[16 * hf + 4 * j + 1], v[16 * hf + 4 * j + 2], v[16 * hf + 4 * j + 3]);
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                  const uint4 x = *reinterpret_cast<const uint4*>(xp + swz(8 * i + sub_r, grp));
+                  if (ok_of[i])
+                    *reinterpret_cast<uint4*>(p.residual_out + dense_of[i] * p.N + col0 + 16 * hf + 4 * grp) = x;
+                }
+                __syncwarp();
+              }
             }
-          } else {
+          } else if (row_ok) {
+            const long long at = dst.dense * (long long)p.N + col0;
 #pragma unroll
             for (int j = 0; j < 32; j++)
               if (col0 + j < p.N) {
@@ -392,17 +501,29 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
         if (p.out_mode == OUT_INT32) {
-          int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
-          if ((p.N & 3) == 0 && col0 + 32 <= p.N) {
+          if (whole) {
 #pragma unroll
-            for (int j = 0; j < 8; j++)
-              reinterpret_cast<uint4*>(D)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {
+            for (int hf = 0; hf < 2; hf++) {
+#pragma unroll
+              for (int j = 0; j < 4; j++)
+                *reinterpret_cast<uint4*>(xp + swz(lane, j)) =
+                    make_uint4(v[16 * hf + 4 * j], v[16 * hf + 4 * j + 1], v[16 * hf + 4 * j + 2], v[16 * hf + 4 * j + 3]);
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                const uint4 x = *reinterpret_cast<const uint4*>(xp + swz(8 * i + sub_r, grp));
+                if (ok_of[i])
+                  *reinterpret_cast<uint4*>(reinterpret_cast<int32_t*>(p.out) + row_of[i] * p.N + col0 + 16 * hf + 4 * grp) = x;
+              }
+              __syncwarp();
+            }
+          } else if (row_ok) {
+            int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
 #pragma unroll
             for (int j = 0; j < 32; j++)
               if (col0 + j < p.N) D[j] = (int32_t)v[j];
           }
-        } else {
+        } else if (row_ok) {
           // packed modes need N % 32 == 0, so this word is whole
           uint32_t lv[32];
           if (p.out_mode == OUT_LOWBITS) {
@@ -411,9 +532,9 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           } else if (thr_staged) {
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-              const int4 t4 = thr_s[c * 32 + j];
+              const int4 q4 = thr_s[j];
               const int x = (int)v[j];
-              lv[j] = (x >= t4.x ? 1u : 0u) + (x >= t4.y ? 1u : 0u) + (x >= t4.z ? 1u : 0u);
+              lv[j] = (x >= q4.x ? 1u : 0u) + (x >= q4.y ? 1u : 0u) + (x >= q4.z ? 1u : 0u);
             }
           } else {
 #pragma unroll
@@ -426,10 +547,10 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
           uint32_t* O = reinterpret_cast<uint32_t*>(p.out);
           for (int b = 0; b < p.out_bits; b++) {
-            uint32_t word = 0;
+            uint32_t part[4] = {0u, 0u, 0u, 0u};   // four independent chains instead of one of 32 ORs
 #pragma unroll
-            for (int j = 0; j < 32; j++) word |= ((lv[j] >> b) & 1u) << (31 - j);
-            O[b * p.out_plane_words + row * (p.N >> 5) + (col0 >> 5)] = word;
+            for (int j = 0; j < 32; j++) part[j & 3] |= ((lv[j] >> b) & 1u) << (31 - j);
+            O[b * p.out_plane_words + row * (p.N >> 5) + (col0 >> 5)] = (part[0] | part[1]) | (part[2] | part[3]);
           }
         }
       }
@@ -466,56 +587,103 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// rows x K bytes, row-major; box = box_rows x 128 bytes, 128-byte swizzle, zero fill outside
-bool make_operand_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+// rows x K bytes, row-major; box = box_rows x span bytes (span = 128 or 64 = the swizzle span), zero fill outside
+bool make_operand_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows, int span = 128) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)span, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, span == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
-// int8 NHWC activations [B][Hp][Wp][CIN]; box = 128 channels x bw x bh x bb pixels
+// int8 NHWC activations [B][Hp][Wp][CIN]; box = span channels x bw x bh x bb pixels
 // With a traversal stride s the box spans bw*s x bh*s stored pixels and picks every s-th one.
 bool make_activation_map(CUtensorMap* map, const void* base, int B, int Hp, int Wp, int CIN, int bw, int bh, int bb,
-                         int stride) {
+                         int stride, int span) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t dims[4] = {(cuuint64_t)CIN, (cuuint64_t)Wp, (cuuint64_t)Hp, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)CIN, (cuuint64_t)Wp * CIN, (cuuint64_t)Hp * Wp * CIN};
-  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)(bw * stride), (cuuint32_t)(bh * stride), (cuuint32_t)bb};
+  cuuint32_t box[4] = {(cuuint32_t)span, (cuuint32_t)(bw * stride), (cuuint32_t)(bh * stride), (cuuint32_t)bb};
   cuuint32_t estr[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, span == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-template <int BN>
-cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const Tc5Params& p,
-                       int grid) {
+// Shared-memory plan: keep the whole B operand resident when the problem has one tile column
+// and its K blocks leave room for at least three A stages; otherwise a ring of A+B stages.
+template <int BN, int BKB>
+void plan_smem(Tc5Params& p, int* smem_bytes) {
+  using Cfg = TileCfg<BN, BKB>;
+  const int room = SMEM_LIMIT - Cfg::FIXED_BYTES;
+  const long long bres = (long long)p.kblocks * Cfg::B_STAGE_BYTES;
+  p.b_resident = 0;
+  int stage = Cfg::A_STAGE_BYTES + Cfg::B_STAGE_BYTES;
+  long long fixed = 0;
+  if (p.is_conv && p.tiles_n == 1 && p.tiles_m >= 4 * device_sm_count() &&
+      bres + 3LL * Cfg::A_STAGE_BYTES <= room) {
+    p.b_resident = 1;
+    stage = Cfg::A_STAGE_BYTES;
+    fixed = bres;
+  }
+  // narrow stages are grouped (up to three K blocks per barrier round trip) while at least
+  // four groups still fit: the per-stage wait / commit latency of the single issuing thread,
+  // not the MMA time, bounds tiles whose K block is only a few KiB
+  int kgroup = 1;
+  for (int g = 3; g >= 2; g--)
+    if (p.kblocks % g == 0 && stage <= 16384 && (room - fixed) / ((long long)g * stage) >= 4) { kgroup = g; break; }
+  p.kgroup = kgroup;
+  stage *= kgroup;
+  int stages = (int)((room - fixed) / stage);
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  p.stages = stages;
+  *smem_bytes = (int)(Cfg::FIXED_BYTES + fixed + (long long)stages * stage);
+}
+
+template <int BN, int BKB>
+cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid) {
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 16 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tc5_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         TileCfg<BN>::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(tc5_gemm_kernel<BN, BKB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_LIMIT);
     if (e != cudaSuccess) return e;
     if (dev < 16) attr_set[dev] = true;
   }
-  tc5_gemm_kernel<BN><<<grid, THREADS, TileCfg<BN>::SMEM_BYTES, s>>>(map_a, map_b, p);
+  int smem = 0;
+  plan_smem<BN, BKB>(p, &smem);
+  tc5_gemm_kernel<BN, BKB><<<grid, THREADS, smem, s>>>(map_a, map_b, p);
   return cudaGetLastError();
 }
 
-// Tile width: 256 unless that leaves the device under-filled and 128 does better.
+cudaError_t launch_tc5_any(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid,
+                           int bn, int span) {
+  if (span == 64) {
+    if (bn == 64) return launch_tc5<64, 64>(s, map_a, map_b, p, grid);
+    if (bn == 128) return launch_tc5<128, 64>(s, map_a, map_b, p, grid);
+    return launch_tc5<256, 64>(s, map_a, map_b, p, grid);
+  }
+  if (bn == 64) return launch_tc5<64, 128>(s, map_a, map_b, p, grid);
+  if (bn == 128) return launch_tc5<128, 128>(s, map_a, map_b, p, grid);
+  return launch_tc5<256, 128>(s, map_a, map_b, p, grid);
+}
+
+// Tile width: 64 for operands of at most 64 columns; else 256 unless that leaves the device
+// under-filled and 128 does better.
 int pick_bn(long long tiles_m, int N, int sms) {
+  if (N <= 64) return 64;
   long long t256 = tiles_m * ((N + 255) / 256), t128 = tiles_m * ((N + 127) / 128);
   if (t256 >= sms) return 256;
   // waves needed with each width, in units of a 256-wide tile's work
@@ -614,7 +782,7 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.idesc = make_idesc(a_signed, b_signed, bn);
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < sms ? tiles : sms);
-  e = bn == 256 ? launch_tc5<256>(s, map_a, map_b, p, grid) : launch_tc5<128>(s, map_a, map_b, p, grid);
+  e = launch_tc5_any(s, map_a, map_b, p, grid, bn, 128);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm launch");
   return APNN_OK;
 }
@@ -633,7 +801,7 @@ apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, co
 
 // ------------------------------------------------------------------ convolution
 // Pixel box of an A tile: bw x bh (x bb whole images when an image is smaller than a tile),
-// at most 128 pixels, chosen for the fewest wasted MMA rows.  With pooling the box is a
+// at most 128 pixels, chosen for the fewest wasted MMA rows and, among equals, the widest.  With pooling the box is a
 // power of two wide (<= 16) and even high, so a 2x2 window never straddles warps.
 bool tc5_conv_box(int Ho, int Wo, int pool, int* bw_out, int* bh_out, int* bb_out) {
   double best = -1.0;
@@ -650,8 +818,9 @@ bool tc5_conv_box(int Ho, int Wo, int pool, int* bw_out, int* bh_out, int* bb_ou
     double covered = (double)Wo * Ho;
     double spent = (double)((Wo + bw - 1) / bw) * ((Ho + bh - 1) / bh) * 128.0 / bb;
     double util = covered / spent;
-    if (util > best + 1e-9) {
-      best = util;
+    // ties go to the widest box: longer contiguous runs per TMA request
+    if (util > best - 1e-9) {
+      best = util > best ? util : best;
       *bw_out = bw;
       *bh_out = bh;
       *bb_out = bb;
@@ -697,7 +866,8 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.Bn = B;
   p.Ho = H;
   p.Wo = W;
-  p.cblocks = CIN / BK;
+  const int span = (CIN % 128 == 0) ? 128 : 64;   // bytes of K per stage row; CIN % 64 == 0
+  p.cblocks = CIN / span;
   p.R = R;
   p.in_off = in_halo - pad;
   p.stride = stride;
@@ -705,11 +875,11 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.out_h = pool ? H / 2 : H;
   p.out_w = pool ? W / 2 : W;
   p.out_halo = epi ? epi->out_halo : 0;
-  p.a_box_bytes = (uint32_t)(bw * bh * bb * BK);
+  p.a_box_bytes = (uint32_t)(bw * bh * bb * span);
   const int bn = pick_bn(p.tiles_m, COUT, sms);
   CUtensorMap map_a, map_b;
-  if (!make_activation_map(&map_a, X8, B, Hp, Wp, CIN, bw, bh, bb, stride) ||
-      !make_operand_map(&map_b, W8, COUT, (long long)R * R * CIN, bn)) {
+  if (!make_activation_map(&map_a, X8, B, Hp, Wp, CIN, bw, bh, bb, stride, span) ||
+      !make_operand_map(&map_b, W8, COUT, (long long)R * R * CIN, bn, span)) {
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   }
   p.out = Out;
@@ -728,7 +898,7 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.idesc = make_idesc(false, w_signed, bn);  // A = activations (unsigned), B = filter
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < sms ? tiles : sms);
-  e = bn == 256 ? launch_tc5<256>(s, map_a, map_b, p, grid) : launch_tc5<128>(s, map_a, map_b, p, grid);
+  e = launch_tc5_any(s, map_a, map_b, p, grid, bn, span);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_conv launch");
   return APNN_OK;
 }

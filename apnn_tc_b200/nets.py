@@ -37,6 +37,12 @@ def pad128(c: int) -> int:
     return (c + 127) // 128 * 128
 
 
+def padc(c: int, narrow: bool) -> int:
+    """Stored channel count of a feature map: a multiple of 128, or 64 for maps of at most 64
+    channels when the layers run on the tcgen05 path (64-byte swizzle rows)."""
+    return 64 if (narrow and c <= 64) else pad128(c)
+
+
 @dataclass
 class LayerSpec:
     """One layer of a model list.  kind: 'conv' | 'fc' | 'out'."""
@@ -148,9 +154,12 @@ def fold_thresholds(scale: np.ndarray, bias: np.ndarray, mu: float, sigma: float
     return np.clip(np.ceil(t), -2**31, INT_MAX).astype(np.int64).astype(np.int32)
 
 
-def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[int] = None) -> Dict[str, LayerParams]:
+def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[int] = None,
+                narrow: bool = True) -> Dict[str, LayerParams]:
     """Random +-1 weights (uniform bits), BN scale U[0.5,1.5] and bias U[-1,1] folded to thresholds with
-    mu = 0 and sigma = sqrt(3.5 * fan_in)/4 (variance of a +-1 x uniform-level dot product)."""
+    mu = 0 and sigma = sqrt(3.5 * fan_in)/4 (variance of a +-1 x uniform-level dot product).
+    narrow: store feature maps of at most 64 channels with 64 channels instead of 128 (the random
+    draws cover real channels only, so both paddings hold the same network)."""
     rng = np.random.default_rng(seed)
     hw = image_hw or spec.image_hw
     out: Dict[str, LayerParams] = {}
@@ -160,7 +169,7 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
         src = ls.src or prev
         if ls.kind == "conv":
             H, W, _ = dims[src] if src else (hw, hw, spec.image_channels)
-            cinp, coutp = pad128(ls.cin), pad128(ls.cout)
+            cinp, coutp = padc(ls.cin, narrow), padc(ls.cout, narrow)
             bits = np.zeros((coutp, ls.R, ls.R, cinp), dtype=np.uint8)
             bits[: ls.cout, :, :, : ls.cin] = rng.integers(0, 2, size=(ls.cout, ls.R, ls.R, ls.cin), dtype=np.uint8)
             planes = _pack_bits_msb(bits)[None]
@@ -179,9 +188,9 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
         else:
             if ls.kind == "fc" and ls.cin == 0:
                 H, W, C = dims[src]
-                K = H * W * pad128(C)
+                K = H * W * padc(C, narrow)
                 fan_in = H * W * C
-                kbits = np.zeros((pad128(ls.cout), H, W, pad128(C)), dtype=np.uint8)
+                kbits = np.zeros((pad128(ls.cout), H, W, padc(C, narrow)), dtype=np.uint8)
                 kbits[: ls.cout, :, :, :C] = rng.integers(0, 2, size=(ls.cout, H, W, C), dtype=np.uint8)
                 kbits = kbits.reshape(pad128(ls.cout), K)
             else:
@@ -228,7 +237,7 @@ class Network:
         self.spec, self.batch = spec, batch
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.hw = image_hw or spec.image_hw
-        self.params = params if params is not None else make_params(spec, image_hw=self.hw)
+        self.params = params if params is not None else make_params(spec, image_hw=self.hw, narrow=use_tcgen05)
         self.use_tcgen05 = use_tcgen05
         self.L = _cabi.lib()
         self.by_name = {ls.name: ls for ls in spec.layers}
@@ -246,7 +255,7 @@ class Network:
             prev = ls.name
         self.halo = halo
         B = batch
-        cp = pad128(spec.image_channels)
+        cp = self.params[spec.layers[0].name].shape["cinp"]
         h0 = halo[None]
         self.out: Dict[str, torch.Tensor] = {}
         self.res: Dict[str, torch.Tensor] = {}
@@ -282,6 +291,8 @@ class Network:
                     x8_bytes = max(x8_bytes, B * Hc * Wc * kp)
                     ok = True
                 self.tc5_ok[ls.name] = ok
+                if not ok and sh["cinp"] % 128:
+                    raise ValueError(f"{ls.name}: a {sh['cinp']}-channel input needs the tcgen05 path")
                 if ok and not (self.first_im2col and self.first_im2col[0] == ls.name):
                     ih = halo[src]
                     x8_bytes = max(x8_bytes, B * (sh["H"] + 2 * ih) * (sh["W"] + 2 * ih) * sh["cinp"])

@@ -227,7 +227,8 @@ apnn_status apnn_quantize_im2col(void *stream, const float *images, uint32_t *pl
  * returns the operations one launch performs; the caller times the launch with events to
  * get the device's peak for that path (the roofline denominator).  kind 0: tcgen05.mma
  * kind::i8 (128x256x32, operands fixed in shared memory), 1: mma.sync m16n8k32 u8,
- * 2: mma.sync m16n8k256 b1 and.popc (bit operations).  scratch_flag: 4 bytes of device
+ * 2: mma.sync m16n8k256 b1 and.popc (bit operations), 3 / 4: kind 0 with N = 128 / 64.
+ * scratch_flag: 4 bytes of device
  * memory.  No counterpart in the reference. */
 apnn_status apnn_probe_peak(void *stream, int kind, int iters, int *scratch_flag,
                             double *ops_per_launch);

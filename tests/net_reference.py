@@ -7,7 +7,6 @@ the oracle's +-1 correction, 2x2 maximum, residual add and threshold requantisat
 import numpy as np
 
 import oracle
-from apnn_tc_b200.nets import pad128
 
 
 def forward_reference(spec, params, images, threads=8):
@@ -15,7 +14,7 @@ def forward_reference(spec, params, images, threads=8):
     a = spec.a_bit
     B = images.shape[0]
     lv0 = oracle.quantize(images, a)
-    cp = pad128(spec.image_channels)
+    cp = params[spec.layers[0].name].shape["cinp"]   # stored channels of the image (zero-padded)
     x0 = np.zeros(images.shape[:3] + (cp,), dtype=np.uint32)
     x0[..., : spec.image_channels] = lv0
     levels = {None: x0}

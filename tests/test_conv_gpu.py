@@ -253,3 +253,45 @@ def test_tcgen05_stride2(cuda_device, B, H, Wd, R, pool):
         v = oracle.pool2x2(v, 2)
     out = run_tc5_conv(Wt, X, ap.make_epilogue("int32", signed="w", pool=pool), stride=2)
     assert np.array_equal(to_host(out, np.int32), v)
+
+
+# ------------------------------------------------------------------ 64-channel maps, resident filter
+@pytest.mark.parametrize("CIN,COUT", [(64, 64), (64, 128), (192, 64), (128, 64)])
+@pytest.mark.parametrize("R,stride,pool", [(3, 1, "none"), (3, 1, "max"), (1, 1, "none"), (3, 2, "none")])
+def test_tcgen05_64_channel_maps(cuda_device, CIN, COUT, R, stride, pool):
+    """Feature maps whose channel count is a multiple of 64 only (64-byte swizzle rows) and
+    64-column tiles, with thresholds, residual in / out and an output ring."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(CIN + COUT + R + stride)
+    B, H, Wd = 3, 12, 16
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, R, 1, 2)
+    acc = oracle.conv_popc(Wt, X, stride=stride, threads=4)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R, stride), 0)
+    if pool != "none":
+        v = oracle.pool2x2(v, 2)
+    out = run_tc5_conv(Wt, X, ap.make_epilogue("int32", signed="w", pool=pool), stride=stride)
+    assert np.array_equal(to_host(out, np.int32), v)
+    res = rng.integers(-300, 300, size=v.shape).astype(np.int32)
+    v2 = v + res
+    T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v2.mean()), float(v2.std()) / 4, 2)
+    res_out = torch.zeros(v2.shape, dtype=torch.int32, device="cuda")
+    epi = ap.make_epilogue("thresholds", 2, signed="w", pool=pool, out_halo=1, thresholds=to_dev(T),
+                           residual_in=to_dev(res), residual_out=res_out)
+    got = to_host(run_tc5_conv(Wt, X, epi, stride=stride))
+    assert np.array_equal(to_host(res_out, np.int32), v2)
+    assert np.array_equal(got[:, :, 1:-1, 1:-1], oracle.requant_pack(v2, 2, 2, T))
+
+
+@pytest.mark.parametrize("CIN,COUT,R", [(64, 64, 3), (128, 128, 3), (128, 128, 1), (256, 64, 1)])
+def test_tcgen05_resident_filter(cuda_device, CIN, COUT, R):
+    """Enough row tiles per SM that the kernel keeps the whole filter in shared memory and
+    streams activation tiles only (one tile column, >= 4 tiles per SM)."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(CIN * 3 + COUT + R)
+    B, H, Wd = 25, 56, 56       # 28 pixel boxes per image: 700 row tiles, more than 4 per SM
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, R, 1, 2)
+    acc = oracle.conv_popc(Wt, X, threads=8)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R, 1), 0)
+    T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
+    out = run_tc5_conv(Wt, X, ap.make_epilogue("thresholds", 2, signed="w", thresholds=to_dev(T)))
+    assert np.array_equal(to_host(out), oracle.requant_pack(v, 2, 2, T))

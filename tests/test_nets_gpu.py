@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 def test_model_logits_match_reference(cuda_device, model, hw, batch, use_tcgen05):
     from apnn_tc_b200 import nets
     spec = nets.MODELS[model](n_classes=200)
-    params = nets.make_params(spec, image_hw=hw)
+    params = nets.make_params(spec, image_hw=hw, narrow=use_tcgen05)
     rng = np.random.default_rng(123)
     images = rng.uniform(-10, 10, size=(batch, hw, hw, 3)).astype(np.float32)
     want, levels, values = forward_reference(spec, params, images)
