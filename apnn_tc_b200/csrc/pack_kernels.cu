@@ -244,6 +244,76 @@ __global__ void __launch_bounds__(256) quantize_im2col_rows_kernel(const float* 
 }
 
 
+// First layer straight to the int8 operand of the tcgen05 path: the same window gather as
+// quantize_im2col_rows_kernel, but every output pixel becomes a row of kp bytes, one level per
+// byte in the byte order apnn_expand_planes produces (within each group of 32 k, element e sits
+// at byte 4*((31-e)&7) + ((31-e)>>3)), zero beyond R*R*C.  No packed planes, no expand pass.
+__global__ void __launch_bounds__(256) quantize_im2col_i8_kernel(const float* __restrict__ img,
+                                                                 uint8_t* __restrict__ out, int B, int H, int W,
+                                                                 int C, int R, int stride, int bits, int Ho, int Wo,
+                                                                 int kp, int rowlen, int lpad) {
+  extern __shared__ __align__(16) unsigned char lv_s[];   // [R][rowlen], image columns start at byte lpad
+  const float steps = (float)(1 << bits);
+  const uint32_t maxlv = (1u << bits) - 1u;
+  const int pad = (R - 1) / 2;
+  const int kreal = R * R * C, tapw = R * C, wc = W * C;
+  const int groups = kp / 32;
+  const bool vec = (wc & 3) == 0;
+  const int quads = wc >> 2;
+  for (int orow = blockIdx.x; orow < B * Ho; orow += gridDim.x) {
+    const int b = orow / Ho, ho = orow - b * Ho;
+    const int hbase = ho * stride - pad;
+    __syncthreads();   // the previous row's readers are done
+    // padding bytes left and right of the image columns
+    for (int t = threadIdx.x; t < R * (rowlen - wc); t += blockDim.x) {
+      const int i = t / (rowlen - wc), o = t - i * (rowlen - wc);
+      lv_s[i * rowlen + (o < lpad ? o : wc + o)] = 0;
+    }
+    if (vec) {
+      // all R rows in one flat loop: every thread's loads are independent and in flight together
+      for (int t = threadIdx.x; t < R * quads; t += blockDim.x) {
+        const int i = t / quads, q = t - i * quads;
+        const int hi = hbase + i;
+        uint32_t packed = 0u;
+        if (hi >= 0 && hi < H) {
+          const float4 f = __ldg(reinterpret_cast<const float4*>(img + ((long long)b * H + hi) * wc) + q);
+          packed = quantize_level(f.x, steps, maxlv) | (quantize_level(f.y, steps, maxlv) << 8) |
+                   (quantize_level(f.z, steps, maxlv) << 16) | (quantize_level(f.w, steps, maxlv) << 24);
+        }
+        *reinterpret_cast<uint32_t*>(lv_s + i * rowlen + lpad + 4 * q) = packed;
+      }
+    } else {
+      for (int t = threadIdx.x; t < R * wc; t += blockDim.x) {
+        const int i = t / wc, q = t - i * wc;
+        const int hi = hbase + i;
+        lv_s[i * rowlen + lpad + q] =
+            (hi >= 0 && hi < H) ? (unsigned char)quantize_level(__ldg(img + ((long long)b * H + hi) * wc + q), steps, maxlv) : 0;
+      }
+    }
+    __syncthreads();
+    uint8_t* orow_out = out + (long long)orow * Wo * kp;
+    for (int t = threadIdx.x; t < Wo * groups; t += blockDim.x) {
+      const int wo = t / groups, w = t - wo * groups;
+      uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+      int k = w * 32;
+      if (k < kreal) {
+        int i = k / tapw, off = k - i * tapw;
+        const unsigned char* rowp = lv_s + i * rowlen + (lpad - pad * C) + wo * stride * C;
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          if (k + e < kreal) {
+            r[(31 - e) & 7] |= (uint32_t)rowp[off] << (8 * ((31 - e) >> 3));
+            if (++off == tapw) { off = 0; rowp += rowlen; }
+          }
+        }
+      }
+      asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(orow_out + (long long)t * 32), "r"(r[0]),
+                   "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                   : "memory");
+    }
+  }
+}
+
 }  // namespace apnn
 
 extern "C" {
@@ -285,6 +355,29 @@ apnn_status apnn_quantize_im2col(void* stream, const float* images, uint32_t* pl
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "quantize_im2col launch");
+  return APNN_OK;
+}
+
+apnn_status apnn_quantize_im2col_i8(void* stream, const float* images, void* out_i8, int B, int H, int W, int C,
+                                    int R, int stride, int bits, int kp) {
+  using namespace apnn;
+  if (!images || !out_i8) return APNN_ERR_INVALID_ARG;
+  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || bits < 1 || bits > 8) return APNN_ERR_INVALID_ARG;
+  if (R < 1 || R > 11 || (R & 1) == 0 || stride < 1 || stride > 4) return APNN_ERR_UNSUPPORTED;
+  if (kp < R * R * C || kp % 64 != 0) return APNN_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(images) & 15u) || (reinterpret_cast<uintptr_t>(out_i8) & 31u)) return APNN_ERR_ALIGNMENT;
+  const int Ho = (H - 1) / stride + 1, Wo = (W - 1) / stride + 1;
+  const int pad = (R - 1) / 2;
+  const int lpad = (pad * C + 3) / 4 * 4;   // image columns start on a 4-byte boundary
+  const int rowlen = (lpad + W * C + pad * C + 15) / 16 * 16;
+  const size_t smem = (size_t)R * rowlen;
+  if (smem > 48 * 1024) return APNN_ERR_UNSUPPORTED;   // rows of this width: use apnn_quantize_im2col + apnn_expand_planes
+  long long nb = (long long)B * Ho, cap = (long long)device_sm_count() * 8;
+  if (nb > cap) nb = cap;
+  quantize_im2col_i8_kernel<<<(unsigned)nb, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      images, reinterpret_cast<uint8_t*>(out_i8), B, H, W, C, R, stride, bits, Ho, Wo, kp, rowlen, lpad);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "quantize_im2col_i8 launch");
   return APNN_OK;
 }
 

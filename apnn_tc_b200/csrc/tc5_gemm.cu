@@ -684,6 +684,7 @@ cudaError_t launch_tc5_any(cudaStream_t s, const CUtensorMap& map_a, const CUten
 // under-filled and 128 does better.
 int pick_bn(long long tiles_m, int N, int sms) {
   if (N <= 64) return 64;
+  if (N <= 128) return 128;   // a 256-wide tile would spend half its MMA columns on zero fill
   long long t256 = tiles_m * ((N + 255) / 256), t128 = tiles_m * ((N + 127) / 128);
   if (t256 >= sms) return 256;
   // waves needed with each width, in units of a 256-wide tile's work

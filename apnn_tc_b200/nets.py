@@ -175,7 +175,7 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
             planes = _pack_bits_msb(bits)[None]
             im2col = None
             if src is None:   # the same filter with the real channels only, laid out for the im2col first layer
-                kp = pad128(ls.R * ls.R * ls.cin)
+                kp = (ls.R * ls.R * ls.cin + 63) // 64 * 64 if narrow else pad128(ls.R * ls.R * ls.cin)
                 flat = np.zeros((coutp, kp), dtype=np.uint8)
                 flat[:, : ls.R * ls.R * ls.cin] = bits[:, :, :, : ls.cin].reshape(coutp, -1)
                 im2col = np.ascontiguousarray(_pack_bits_msb(flat)[None])
@@ -286,7 +286,6 @@ class Network:
                     # first layer: windows gathered into channels, then a 1x1 convolution on tcgen05
                     kp = p.im2col_planes.shape[-1] * 32
                     self.first_im2col = (ls.name, Hc, Wc, kp)
-                    self.im2col_planes = torch.zeros((a, B, Hc, Wc, kp // 32), dtype=torch.int32, device=self.device)
                     self.w_planes[ls.name] = _dev_words(p.im2col_planes, self.device)
                     x8_bytes = max(x8_bytes, B * Hc * Wc * kp)
                     ok = True
@@ -328,7 +327,7 @@ class Network:
     def _input_of(self, name: str) -> torch.Tensor:
         src = self.src_of[name]
         if src is None:
-            return self.im2col_planes if self.first_im2col else self.image_planes
+            return None if self.first_im2col else self.image_planes   # the im2col first layer reads self.x8
         return self.out[src]
 
     def _epilogue(self, ls: LayerSpec, conv: bool):
@@ -350,12 +349,10 @@ class Network:
         if self.first_im2col and self.first_im2col[0] == ls.name:
             _, Hc, Wc, kp = self.first_im2col
             epi.in_halo = 0
-            _cabi.check(self.L.apnn_expand_planes(s, self.im2col_planes.data_ptr(), self.x8.data_ptr(), B * Hc * Wc, kp,
-                                                  a, 0), "expand")
             _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), self.x8.data_ptr(), out.data_ptr(), B,
                                               Hc, Wc, kp, sh["coutp"], 1, 1, 1, ctypes.byref(epi), self.flag.data_ptr()),
                         "apnn_conv2d_i8 " + ls.name)
-            return 2
+            return 1
         if self.tc5_ok[ls.name]:
             rows = X.shape[1] * X.shape[2] * X.shape[3]
             _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), rows, sh["cinp"], a, 0), "expand")
@@ -395,10 +392,11 @@ class Network:
         n = 1
         h0 = self.halo[None]
         if self.first_im2col:
+            # quantise + gather the first layer's windows straight into the int8 operand buffer
             first = self.by_name[self.first_im2col[0]]
-            _cabi.check(self.L.apnn_quantize_im2col(s, images.data_ptr(), self.im2col_planes.data_ptr(), self.batch,
-                                                    self.hw, self.hw, self.spec.image_channels, first.R, first.stride, a),
-                        "apnn_quantize_im2col")
+            _cabi.check(self.L.apnn_quantize_im2col_i8(s, images.data_ptr(), self.x8.data_ptr(), self.batch, self.hw,
+                                                       self.hw, self.spec.image_channels, first.R, first.stride, a,
+                                                       self.first_im2col[3]), "apnn_quantize_im2col_i8")
         else:
             target = self.image_levels if h0 else self.image_planes
             _cabi.check(self.L.apnn_quantize_pack(s, images.data_ptr(), target.data_ptr(), rows,

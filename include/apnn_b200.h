@@ -222,6 +222,14 @@ apnn_status apnn_quantize_pack(void *stream, const float *values, uint32_t *plan
 apnn_status apnn_quantize_im2col(void *stream, const float *images, uint32_t *planes, int B, int H,
                                  int W, int C, int R, int stride, int bits);
 
+/* The same first-layer gather written straight as the int8 operand of apnn_conv2d_i8 (a 1x1
+ * convolution over kp "channels"): out_i8[B*Ho*Wo][kp], one quantised level per byte in the
+ * byte order of apnn_expand_planes, zero beyond R*R*C.  kp: a multiple of 64, >= R*R*C.
+ * Replaces images_quantization + Bit_compression + the expand pass for the first layer
+ * (NN/kernel.cuh:129-161); no counterpart of the window gather in the reference. */
+apnn_status apnn_quantize_im2col_i8(void *stream, const float *images, void *out_i8, int B, int H,
+                                    int W, int C, int R, int stride, int bits, int kp);
+
 /* ---- measurement aid ------------------------------------------------------------
  * Launches an operand-resident issue loop of one contraction instruction on every SM and
  * returns the operations one launch performs; the caller times the launch with events to

@@ -49,3 +49,47 @@ def test_quantize_im2col(cuda_device, B, H, Wd, C, R, stride, bits):
                                           C, R, stride, bits)
     _cabi.check(st, "apnn_quantize_im2col")
     assert np.array_equal(to_host(out), want)
+
+
+def spread_bytes(levels: np.ndarray) -> np.ndarray:
+    """Byte order of the int8 operands: inside each group of 32 k, element e sits at byte
+    4*((31-e)&7) + ((31-e)>>3) (the order apnn_expand_planes writes and both GEMM operands share)."""
+    K = levels.shape[-1]
+    e = np.arange(32)
+    pos = 4 * ((31 - e) & 7) + ((31 - e) >> 3)
+    out = np.zeros(levels.shape, dtype=np.uint8)
+    grouped = levels.reshape(levels.shape[:-1] + (K // 32, 32))
+    og = out.reshape(grouped.shape)
+    og[..., pos] = grouped
+    return out
+
+
+@pytest.mark.parametrize("bits,rows,K", [(1, 5, 64), (2, 37, 128), (4, 9, 320), (3, 3, 192)])
+def test_expand_planes_byte_layout(cuda_device, bits, rows, K):
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(bits + rows + K)
+    planes, lv = oracle.value_planes(rng, rows, K, bits)
+    got = ap.expand_planes(torch.from_numpy(planes.view(np.int32)).cuda()).cpu().numpy()
+    assert np.array_equal(got, spread_bytes(lv.astype(np.uint8)))
+
+
+@pytest.mark.parametrize("B,H,Wd,C,R,stride,bits,kp", [(2, 9, 7, 3, 3, 2, 2, 64), (3, 32, 32, 3, 7, 4, 2, 192),
+                                                       (2, 20, 24, 3, 11, 4, 2, 384), (1, 8, 8, 5, 5, 1, 4, 128),
+                                                       (1, 224, 224, 3, 7, 4, 2, 192), (2, 6, 6, 40, 3, 1, 2, 384)])
+def test_quantize_im2col_i8(cuda_device, B, H, Wd, C, R, stride, bits, kp):
+    """First layer straight to int8 rows: the oracle's gathered levels in the operand byte order."""
+    from apnn_tc_b200 import _cabi
+    rng = np.random.default_rng(B + H + R + kp)
+    x = rng.uniform(-12, 12, size=(B, H, Wd, C)).astype(np.float32)
+    lv = oracle.unpack_levels(oracle.quantize_im2col(x, R, stride, bits))     # [B, Ho, Wo, PAD128(R*R*C)]
+    want = np.zeros(lv.shape[:3] + (kp,), dtype=np.uint8)
+    n = min(kp, lv.shape[-1])
+    want[..., :n] = lv[..., :n]
+    assert not lv[..., n:].any()
+    want = spread_bytes(want)
+    out = torch.full(want.shape, 0x55, dtype=torch.uint8, device="cuda")
+    xd = torch.from_numpy(x).cuda()
+    st = _cabi.lib().apnn_quantize_im2col_i8(torch.cuda.current_stream().cuda_stream, xd.data_ptr(), out.data_ptr(), B, H,
+                                             Wd, C, R, stride, bits, kp)
+    _cabi.check(st, "apnn_quantize_im2col_i8")
+    assert np.array_equal(out.cpu().numpy(), want)
