@@ -39,7 +39,7 @@ class Epilogue(ctypes.Structure):
         ("residual_in", ctypes.c_void_p),
         ("residual_out", ctypes.c_void_p),
         ("n_peer_out", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("out_i8", ctypes.c_int32),
         ("peer_out", ctypes.c_void_p * 7),
     ]
 

@@ -33,8 +33,11 @@ int device_sm_count() {
   return n;
 }
 
-apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, int abits_signed_w, int abits_signed_x) {
+apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, int abits_signed_w, int abits_signed_x,
+                           bool i8_rows_ok) {
   if (!e) return APNN_OK;
+  if (e->out_i8 != 0 && (e->out_i8 != 1 || !i8_rows_ok || e->out_mode == APNN_OUT_INT32 || e->n_peer_out != 0))
+    return e->out_i8 == 1 && !i8_rows_ok ? APNN_ERR_UNSUPPORTED : APNN_ERR_INVALID_ARG;
   if (e->out_mode < APNN_OUT_INT32 || e->out_mode > APNN_OUT_THRESHOLDS) return APNN_ERR_INVALID_ARG;
   if (e->out_mode != APNN_OUT_INT32) {
     if (e->out_bits < 1 || e->out_bits > 8) return APNN_ERR_INVALID_ARG;
@@ -122,7 +125,8 @@ apnn_status apnn_gemm_i8(void* stream, const void* W8, const void* X8, void* D, 
   if (epi) {
     // the sign lives in the expanded bytes; the epilogue must not correct again
     if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;
-    apnn_status st = check_epilogue(epi, N, false, 1, 1);
+    apnn_status st = check_epilogue(epi, N, false, 1, 1, true);
+    if (st == APNN_OK && epi->out_i8 && !aligned32(D)) st = APNN_ERR_ALIGNMENT;
     if (st != APNN_OK) return st;
   }
   return tc5_gemm_i8(reinterpret_cast<cudaStream_t>(stream), (const uint8_t*)W8, (const uint8_t*)X8, D, M, N, K,
@@ -206,7 +210,8 @@ apnn_status apnn_conv2d_i8(void* stream, const void* W8, const void* X8, void* O
   if (CIN % 64 != 0 || !aligned16(W8) || !aligned16(X8) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
   if (epi) {
     if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;  // the sign is in the bytes
-    apnn_status st = check_epilogue(epi, COUT, true, 1, 1);
+    apnn_status st = check_epilogue(epi, COUT, true, 1, 1, true);
+    if (st == APNN_OK && epi->out_i8 && !aligned32(Out)) st = APNN_ERR_ALIGNMENT;
     if (st != APNN_OK) return st;
     if (epi->pool != APNN_POOL_NONE && ((((H - 1) / (stride > 0 ? stride : 1) + 1) & 1) ||
                                         (((W - 1) / (stride > 0 ? stride : 1) + 1) & 1)))

@@ -8,5 +8,6 @@ namespace apnn {
 apnn_status cuda_fail(cudaError_t e, const char* where);
 int device_sm_count();
 // Validates an epilogue descriptor; wbits/xbits are the widths of the W and X arguments.
-apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, int wbits, int xbits);
+apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, int wbits, int xbits,
+                           bool i8_rows_ok = false);
 }  // namespace apnn

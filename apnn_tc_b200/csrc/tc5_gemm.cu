@@ -131,6 +131,7 @@ struct Tc5Params {
   int M, N, kblocks;
   int tiles_m, tiles_n;
   int out_mode, out_bits;
+  int out_i8;            // quantised outputs as one byte per element (rows of N bytes) instead of packed planes
   uint32_t idesc;
   long long out_plane_words;
   int* error_flag;
@@ -545,6 +546,18 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               lv[j] = l;
             }
           }
+          if (p.out_i8) {
+            // the next layer's int8 operand: element j of this 32-column group at byte
+            // 4*((31-j)&7) + ((31-j)>>3), the order apnn_expand_planes writes
+            uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 32; j++) r[(31 - j) & 7] |= lv[j] << (8 * ((31 - j) >> 3));
+            uint8_t* O8 = reinterpret_cast<uint8_t*>(p.out) + row * p.N + col0;
+            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(O8), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                         "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                         : "memory");
+            continue;
+          }
           uint32_t* O = reinterpret_cast<uint32_t*>(p.out);
           for (int b = 0; b < p.out_bits; b++) {
             uint32_t part[4] = {0u, 0u, 0u, 0u};   // four independent chains instead of one of 32 ORs
@@ -756,7 +769,7 @@ apnn_status tc5_expand2(cudaStream_t s, const uint32_t* pa, uint8_t* oa, long lo
 
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
-  if (tc5_pair_worthwhile(M, N, K) || (epi && epi->n_peer_out > 0))
+  if ((tc5_pair_worthwhile(M, N, K) && !(epi && epi->out_i8)) || (epi && epi->n_peer_out > 0))
     return tc5_gemm_i8_pair(s, A8, B8, D, M, N, K, a_signed, b_signed, epi, status_flag);
   cudaError_t e;
   const int sms = device_sm_count();
@@ -776,6 +789,7 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.tiles_n = (N + bn - 1) / bn;
   p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
   p.out_bits = epi ? epi->out_bits : 0;
+  p.out_i8 = epi ? epi->out_i8 : 0;
   p.out_plane_words = (long long)M * (N / 32);
   p.error_flag = status_flag;
   p.residual_in = epi ? epi->residual_in : nullptr;
@@ -891,6 +905,7 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.tiles_n = (COUT + bn - 1) / bn;
   p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
   p.out_bits = epi ? epi->out_bits : 0;
+  p.out_i8 = epi ? epi->out_i8 : 0;
   p.out_plane_words =
       (long long)B * (p.out_h + 2 * p.out_halo) * (p.out_w + 2 * p.out_halo) * (COUT / 32);
   p.error_flag = status_flag;

@@ -311,6 +311,21 @@ class Network:
                 _cabi.check(self.L.apnn_expand_planes(_stream_ptr(), wp.data_ptr(), w8.data_ptr(), rows, k, 1, 1),
                             "expand weights")
                 self.w8[ls.name] = w8
+        # a quantised output feeds the next layers as int8 rows, written by the producing kernel's
+        # epilogue, when producer and every consumer run on the tcgen05 path: no packed planes in
+        # between and no expand pass
+        self.i8_out: Dict[str, bool] = {}
+        for ls in spec.layers:
+            users = [c.name for c in spec.layers if self.src_of[c.name] == ls.name]
+            if use_tcgen05 and ls.quantise and users and self.tc5_ok[ls.name] and all(self.tc5_ok[u] for u in users):
+                sh = self.params[ls.name].shape
+                if ls.kind == "conv":
+                    hh = halo[ls.name]
+                    shape = (B, sh["Ho"] + 2 * hh, sh["Wo"] + 2 * hh, sh["coutp"])
+                else:
+                    shape = (B, sh["coutp"])
+                self.out[ls.name] = torch.zeros(shape, dtype=torch.uint8, device=self.device)
+                self.i8_out[ls.name] = True
         if self.first_im2col is None:
             self.image_planes = torch.zeros((a, B, self.hw + 2 * h0, self.hw + 2 * h0, cp // 32), dtype=torch.int32,
                                             device=self.device)
@@ -324,6 +339,19 @@ class Network:
         torch.cuda.synchronize(self.device)
 
     # -- one layer -------------------------------------------------------------------
+    def levels_of(self, name: str) -> torch.Tensor:
+        """Quantised output of a layer as levels [B, (H, W,) C] without its ring, whichever form it is stored in."""
+        t, h = self.out[name], self.halo.get(name, 0)
+        if self.i8_out.get(name, False):
+            e = torch.arange(32, device=t.device)
+            pos = 4 * ((31 - e) & 7) + ((31 - e) >> 3)      # byte of element e inside a group of 32 channels
+            g = t.reshape(t.shape[:-1] + (t.shape[-1] // 32, 32))[..., pos].reshape(t.shape)
+        else:
+            shifts = torch.arange(31, -1, -1, device=t.device, dtype=torch.int32)
+            bitsel = (t.unsqueeze(-1) >> shifts) & 1                     # [a, ..., C/32, 32]
+            g = sum((bitsel[b].to(torch.uint8) << b) for b in range(t.shape[0])).reshape(t.shape[1:-1] + (t.shape[-1] * 32,))
+        return g[:, h:g.shape[1] - h, h:g.shape[2] - h] if (h and g.dim() == 4) else g
+
     def _input_of(self, name: str) -> torch.Tensor:
         src = self.src_of[name]
         if src is None:
@@ -337,7 +365,7 @@ class Network:
         return make_epilogue(mode, self.spec.a_bit if ls.quantise else 0, signed="none",
                              pool="max" if ls.pool == 2 else "none", out_halo=self.halo[ls.name] if conv else 0,
                              in_halo=self.halo[self.src_of[ls.name]] if conv else 0, thresholds=self.thr[ls.name],
-                             residual_in=res_in, residual_out=res_out)
+                             residual_in=res_in, residual_out=res_out, out_i8=self.i8_out.get(ls.name, False))
 
     def _run_conv(self, ls: LayerSpec) -> int:
         sh = self.params[ls.name].shape
@@ -354,12 +382,15 @@ class Network:
                         "apnn_conv2d_i8 " + ls.name)
             return 1
         if self.tc5_ok[ls.name]:
-            rows = X.shape[1] * X.shape[2] * X.shape[3]
-            _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), rows, sh["cinp"], a, 0), "expand")
-            _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), self.x8.data_ptr(), out.data_ptr(), B,
+            n, x8 = 1, X
+            if not self.i8_out.get(self.src_of[ls.name], False):
+                rows = X.shape[1] * X.shape[2] * X.shape[3]
+                _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), rows, sh["cinp"], a, 0), "expand")
+                n, x8 = 2, self.x8
+            _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), x8.data_ptr(), out.data_ptr(), B,
                                               sh["H"], sh["W"], sh["cinp"], sh["coutp"], ls.R, ls.stride, 1,
                                               ctypes.byref(epi), self.flag.data_ptr()), "apnn_conv2d_i8 " + ls.name)
-            return 2
+            return n
         epi.signed_operand = _cabi.SIGN_W
         _cabi.check(self.L.apnn_conv2d_ex(s, _cabi.ALGO_IMMA, 1, a, self.w_planes[ls.name].data_ptr(), X.data_ptr(),
                                           out.data_ptr(), B, sh["H"], sh["W"], sh["cinp"], sh["coutp"], ls.R, ls.stride,
@@ -374,10 +405,13 @@ class Network:
         out = self.out[ls.name]
         s = _stream_ptr()
         if self.tc5_ok[ls.name]:
-            _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), B, K, a, 0), "expand")
-            _cabi.check(self.L.apnn_gemm_i8(s, self.x8.data_ptr(), self.w8[ls.name].data_ptr(), out.data_ptr(), B, N, K,
+            n, x8 = 1, X
+            if not self.i8_out.get(self.src_of[ls.name], False):
+                _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), B, K, a, 0), "expand")
+                n, x8 = 2, self.x8
+            _cabi.check(self.L.apnn_gemm_i8(s, x8.data_ptr(), self.w8[ls.name].data_ptr(), out.data_ptr(), B, N, K,
                                             0, 1, ctypes.byref(epi), self.flag.data_ptr()), "apnn_gemm_i8 " + ls.name)
-            return 2
+            return n
         epi.signed_operand = _cabi.SIGN_X
         _cabi.check(self.L.apnn_gemm_ex(s, _cabi.ALGO_IMMA, a, 1, X.data_ptr(), self.w_planes[ls.name].data_ptr(),
                                         out.data_ptr(), B, N, K, ctypes.byref(epi), None, 0), "apnn_gemm_ex " + ls.name)

@@ -84,7 +84,12 @@ typedef struct apnn_epilogue {
                                  "save_residual" output of NN/param.h:943-945 */
   int32_t n_peer_out;         /* GEMM on the tcgen05 CTA-pair kernel only: number of extra
                                  destinations in peer_out (0..7) */
-  int32_t reserved;
+  int32_t out_i8;             /* apnn_conv2d_i8 / apnn_gemm_i8 only, with a quantising out_mode: 1 =
+                                 write one byte per output element (the level), rows of `channels`
+                                 bytes in the byte order of apnn_expand_planes and the same ring
+                                 as the packed output, instead of packed planes -- the next
+                                 layer's int8 operand without an expand pass.  No reference
+                                 counterpart. */
   void *peer_out[7];          /* every output tile is also stored, in D's layout, to these
                                  addresses -- peer-mapped memory of other GPUs (NVLink): with D and
                                  peer_out[] pointing at this rank's slot of a [ranks][M][N/ranks]

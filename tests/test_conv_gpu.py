@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import oracle
-from gpu_util import to_dev, to_host
+from gpu_util import spread_bytes, to_dev, to_host
 
 pytestmark = pytest.mark.gpu
 
@@ -295,3 +295,48 @@ def test_tcgen05_resident_filter(cuda_device, CIN, COUT, R):
     T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
     out = run_tc5_conv(Wt, X, ap.make_epilogue("thresholds", 2, signed="w", thresholds=to_dev(T)))
     assert np.array_equal(to_host(out), oracle.requant_pack(v, 2, 2, T))
+
+
+@pytest.mark.parametrize("CIN,COUT,pool", [(64, 64, "none"), (128, 192, "max"), (256, 128, "none")])
+def test_tcgen05_int8_row_output_chains(cuda_device, CIN, COUT, pool):
+    """out_i8: the quantised output leaves the epilogue as one byte per element inside its ring,
+    and is the next convolution's operand as it stands (no packed planes, no expand pass)."""
+    import ctypes
+    import apnn_tc_b200 as ap
+    from apnn_tc_b200 import _cabi
+    rng = np.random.default_rng(CIN + COUT)
+    B, H, Wd = 3, 12, 16
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, 3, 1, 2)
+    acc = oracle.conv_popc(Wt, X, threads=4)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, 3), 0)
+    if pool != "none":
+        v = oracle.pool2x2(v, 2)
+    T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
+    lv = oracle.levels(v, 2, 2, T)                                  # [B, Ho, Wo, COUT]
+    Ho, Wo = lv.shape[1], lv.shape[2]
+    x8 = ap.expand_planes(to_dev(X).reshape(2, -1, CIN // 32))
+    w8 = ap.expand_planes(to_dev(Wt).reshape(1, COUT, -1), signed=True)
+    out = torch.zeros((B, Ho + 2, Wo + 2, COUT), dtype=torch.uint8, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    epi = ap.make_epilogue("thresholds", 2, pool=pool, out_halo=1, thresholds=to_dev(T), out_i8=True)
+    s = torch.cuda.current_stream().cuda_stream
+    _cabi.check(_cabi.lib().apnn_conv2d_i8(s, w8.data_ptr(), x8.data_ptr(), out.data_ptr(), B, H, Wd, CIN, COUT, 3, 1, 1,
+                                           ctypes.byref(epi), flag.data_ptr()), "conv")
+    got = out.cpu().numpy()
+    assert int(flag.item()) == 0
+    assert np.array_equal(got[:, 1:-1, 1:-1], spread_bytes(lv.astype(np.uint8)))
+    assert not got[:, 0].any() and not got[:, -1].any() and not got[:, :, 0].any() and not got[:, :, -1].any()
+    # second convolution straight from those bytes
+    rng2 = np.random.default_rng(5)
+    wl2 = rng2.integers(0, 2, size=(64, 3, 3, COUT), dtype=np.uint32)
+    W2 = oracle.pack_levels(wl2, 1)
+    w8b = ap.expand_planes(to_dev(W2).reshape(1, 64, -1), signed=True)
+    out2 = torch.zeros((B, Ho, Wo, 64), dtype=torch.int32, device="cuda")
+    epi2 = ap.make_epilogue("int32")
+    _cabi.check(_cabi.lib().apnn_conv2d_i8(s, w8b.data_ptr(), out.data_ptr(), out2.data_ptr(), B, Ho, Wo, COUT, 64, 3, 1, 1,
+                                           ctypes.byref(epi2), flag.data_ptr()), "conv2")
+    xp = np.zeros((B, Ho + 2, Wo + 2, COUT), dtype=np.uint32)
+    xp[:, 1:-1, 1:-1] = lv
+    X2 = oracle.pack_levels(xp, 2)
+    want2 = oracle.signed_correct(oracle.conv_popc(W2, X2, threads=4), oracle.conv_window_sums(X2, 3), 0)
+    assert np.array_equal(out2.cpu().numpy(), want2)

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import oracle
-from gpu_util import to_dev, to_host
+from gpu_util import spread_bytes, to_dev, to_host
 
 pytestmark = pytest.mark.gpu
 
@@ -49,19 +49,6 @@ def test_quantize_im2col(cuda_device, B, H, Wd, C, R, stride, bits):
                                           C, R, stride, bits)
     _cabi.check(st, "apnn_quantize_im2col")
     assert np.array_equal(to_host(out), want)
-
-
-def spread_bytes(levels: np.ndarray) -> np.ndarray:
-    """Byte order of the int8 operands: inside each group of 32 k, element e sits at byte
-    4*((31-e)&7) + ((31-e)>>3) (the order apnn_expand_planes writes and both GEMM operands share)."""
-    K = levels.shape[-1]
-    e = np.arange(32)
-    pos = 4 * ((31 - e) & 7) + ((31 - e) >> 3)
-    out = np.zeros(levels.shape, dtype=np.uint8)
-    grouped = levels.reshape(levels.shape[:-1] + (K // 32, 32))
-    og = out.reshape(grouped.shape)
-    og[..., pos] = grouped
-    return out
 
 
 @pytest.mark.parametrize("bits,rows,K", [(1, 5, 64), (2, 37, 128), (4, 9, 320), (3, 3, 192)])
