@@ -152,6 +152,16 @@ struct Tc5Params {
   int kgroup;            // K blocks per stage (one barrier round trip and one commit per group)
   int b_resident;        // 1: the whole B operand (one tile column, all K blocks) stays in shared
                          // memory for the life of the CTA and the ring carries A tiles only
+  // flat convolution (is_conv == 2): stride 1, no pooling.  Output positions are the flattened
+  // padded pixels q = (b*Hp + h)*Wp + w (top-left anchored); a tile is 128 consecutive q, and
+  // filter tap (ti, tj) reads input rows q + (ti+in_off)*Wp + tj+in_off of the flattened image
+  // -- all taps of a channel block read ONE buffer of consecutive rows through row-shifted
+  // descriptors, so the activations enter shared memory once per tile instead of once per tap.
+  int flat_wp;           // Wp
+  int flat_hpwp;         // Hp * Wp
+  int flat_nblk;         // row blocks per channel block: 1 (all taps in one box) or R (one per filter row)
+  int flat_blk_rows;     // rows per block (multiple of 8, at most 256)
+  int flat_na, flat_nb;  // A-buffer ring depth; B-tile ring depth (0 when the filter is resident)
 };
 
 // Output row (units of N channels) and validity of tile row r; for pooled outputs only the
@@ -167,7 +177,7 @@ struct RowInBox {
 };
 __device__ __forceinline__ RowInBox row_in_box(const Tc5Params& p, int r) {
   RowInBox q = {0, 0, 0};
-  if (p.is_conv) {
+  if (p.is_conv == 1) {
     q.wi = r % p.bw;
     const int r2 = r / p.bw;
     q.hi = r2 % p.bh;
@@ -183,12 +193,22 @@ __device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, in
     d.valid = d.row < p.M;
     return d;
   }
-  const int tw = tm % p.tiles_w;
-  const int t2 = tm / p.tiles_w;
-  const int th = t2 % p.tiles_h;
-  const int bg = t2 / p.tiles_h;
-  const int b = bg * p.bb + q.bi, ho = th * p.bh + q.hi, wo = tw * p.bw + q.wi;
-  d.valid = q.bi < p.bb && b < p.Bn && ho < p.Ho && wo < p.Wo;
+  int b, ho, wo;
+  if (p.is_conv == 2) {
+    const int pos = tm * BM + r;   // below 2^31: the host checks the flattened row count
+    b = pos / p.flat_hpwp;
+    const int rem = pos - b * p.flat_hpwp;
+    ho = rem / p.flat_wp;
+    wo = rem - ho * p.flat_wp;
+    d.valid = b < p.Bn && ho < p.Ho && wo < p.Wo;
+  } else {
+    const int tw = tm % p.tiles_w;
+    const int t2 = tm / p.tiles_w;
+    const int th = t2 % p.tiles_h;
+    const int bg = t2 / p.tiles_h;
+    b = bg * p.bb + q.bi, ho = th * p.bh + q.hi, wo = tw * p.bw + q.wi;
+    d.valid = q.bi < p.bb && b < p.Bn && ho < p.Ho && wo < p.Wo;
+  }
   int oh = ho, ow = wo;
   if (p.pool != POOL_NONE) {
     d.valid = d.valid && ((q.hi | q.wi) & 1) == 0;
@@ -227,6 +247,59 @@ __device__ __forceinline__ void issue_group(uint32_t d_tmem, uint32_t sa, uint32
   }
 }
 
+// Flat convolution, resident filter: the MMAs of all RR x RR taps of one channel block as
+// straight-line code.  Descriptors differ only in their 14-bit address field, so they are
+// advanced as 32-bit adds on the low word.  a_lo / b_lo: low descriptor words of the buffer and
+// of tap 0's filter tile; row_step: 16-byte units between filter rows in the buffer;
+// b_step: 16-byte units between consecutive taps' filter tiles.
+template <int BKB, int RR>
+__device__ __forceinline__ void flat_issue_taps(uint32_t d_tmem, uint32_t a_lo, uint32_t row_step, uint32_t b_lo,
+                                                uint32_t b_step, uint32_t desc_hi, uint32_t idesc, uint32_t& enable) {
+#pragma unroll
+  for (int ti = 0; ti < RR; ti++) {
+#pragma unroll
+    for (int tj = 0; tj < RR; tj++) {
+      const uint32_t a_tap = a_lo + ti * row_step + tj * (BKB / 16);
+      const uint32_t b_tap = b_lo + (ti * RR + tj) * b_step;
+#pragma unroll
+      for (int k = 0; k < BKB / 32; k++) {
+        const uint64_t adesc = ((uint64_t)desc_hi << 32) | (a_tap + 2u * k);
+        const uint64_t bdesc = ((uint64_t)desc_hi << 32) | (b_tap + 2u * k);
+        tc_mma_i8(d_tmem, adesc, bdesc, idesc, enable);
+        enable = 1u;
+      }
+    }
+  }
+}
+
+// The same with the filter tiles arriving through their ring: wait, issue, release per tap.
+// Returns false when a wait ran out of time.
+template <int BKB, int RR>
+__device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a_lo, uint32_t row_step, uint32_t lo0,
+                                                     uint32_t bring, uint32_t b_bytes, uint32_t bfull0, uint32_t bempty0,
+                                                     int nb, int& sb, uint32_t& phb, uint32_t desc_hi, uint32_t idesc,
+                                                     uint32_t& enable) {
+#pragma unroll
+  for (int ti = 0; ti < RR; ti++) {
+#pragma unroll
+    for (int tj = 0; tj < RR; tj++) {
+      const uint32_t a_tap = a_lo + ti * row_step + tj * (BKB / 16);
+      if (!mbar_wait(bfull0 + 8u * sb, phb)) return false;
+      tc_fence_after();
+      const uint32_t b_tap = lo0 | (((bring + (uint32_t)sb * b_bytes) & 0x3FFFFu) >> 4);
+#pragma unroll
+      for (int k = 0; k < BKB / 32; k++) {
+        tc_mma_i8(d_tmem, ((uint64_t)desc_hi << 32) | (a_tap + 2u * k), ((uint64_t)desc_hi << 32) | (b_tap + 2u * k), idesc,
+                  enable);
+        enable = 1u;
+      }
+      tc_commit(bempty0 + 8u * sb);
+      if (++sb == nb) { sb = 0; phb ^= 1u; }
+    }
+  }
+  return true;
+}
+
 template <int BN, int BKB>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -241,9 +314,13 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int stages = p.stages;
   const uint32_t bres_bytes = p.b_resident ? (uint32_t)p.kblocks * B_STAGE_BYTES : 0u;
   const int kgroup = p.kgroup;
-  const uint32_t stage_bytes = (uint32_t)kgroup * (A_STAGE_BYTES + (p.b_resident ? 0 : B_STAGE_BYTES));
+  const bool flat = p.is_conv == 2;
+  const uint32_t flat_a_bytes = (uint32_t)(p.flat_nblk * p.flat_blk_rows) * BKB;
+  const uint32_t stage_bytes =
+      flat ? flat_a_bytes : (uint32_t)kgroup * (A_STAGE_BYTES + (p.b_resident ? 0 : B_STAGE_BYTES));
   const uint32_t ring = base + bres_bytes;
-  const uint32_t bars = ring + (uint32_t)stages * stage_bytes;
+  const uint32_t bring = ring + (uint32_t)stages * stage_bytes;   // flat: B-tile ring
+  const uint32_t bars = bring + (flat ? (uint32_t)p.flat_nb * B_STAGE_BYTES : 0u);
   // barriers (8 bytes each): full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], b_resident, then the TMEM pointer
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
@@ -251,6 +328,9 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + 2 + a); };
   const uint32_t bres_bar = bars + 8u * (2 * MAX_STAGES + 4);
   const uint32_t tmem_slot = bars + 8u * (2 * MAX_STAGES + 5);
+  // flat convolution: the ring above holds A buffers (full_bar / empty_bar), a second ring of B tiles follows
+  auto bfull_bar = [&](int s) { return bars + 8u * (2 * MAX_STAGES + 6 + s); };
+  auto bempty_bar = [&](int s) { return bars + 8u * (3 * MAX_STAGES + 6 + s); };
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
   uint8_t* epi_smem = smem_raw + (bars + Cfg::BAR_BYTES - raw);
 
@@ -268,6 +348,11 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       mbar_init(tempty_bar(a), EPI_WARPS);
     }
     mbar_init(bres_bar, 1);
+    if (flat)
+      for (int s = 0; s < p.flat_nb; s++) {
+        mbar_init(bfull_bar(s), 1);
+        mbar_init(bempty_bar(s), 1);
+      }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -296,6 +381,36 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       const uint32_t stage_tx = (uint32_t)kgroup * ((p.is_conv ? p.a_box_bytes : (uint32_t)A_STAGE_BYTES) +
                                                     (p.b_resident ? 0u : (uint32_t)B_STAGE_BYTES));
+      if (flat) {
+        // one buffer of consecutive input rows per (tile, channel block); then, unless the filter
+        // is resident, the B tile of each tap through its own ring
+        int sb = 0;
+        uint32_t phb = 0;
+        const int taps = p.R * p.R;
+        const uint32_t blk_bytes = (uint32_t)p.flat_blk_rows * BKB;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+          int tm, tn;
+          tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+          const int q0 = tm * BM + p.in_off * p.flat_wp + p.in_off;
+          for (int cb = 0; cb < p.cblocks && ok; cb++) {
+            if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
+            const uint32_t sa = ring + (uint32_t)s * stage_bytes;
+            mbar_expect_tx(full_bar(s), flat_a_bytes);
+            for (int blk = 0; blk < p.flat_nblk; blk++)
+              tma_load_2d(sa + blk * blk_bytes, &map_a, cb * BKB, q0 + blk * p.flat_wp, full_bar(s));
+            if (++s == stages) { s = 0; ph ^= 1u; }
+            if (!p.b_resident) {
+              for (int tap = 0; tap < taps; tap++) {
+                if (!mbar_wait(bempty_bar(sb), phb ^ 1u)) { ok = false; break; }
+                mbar_expect_tx(bfull_bar(sb), B_STAGE_BYTES);
+                tma_load_2d(bring + (uint32_t)sb * B_STAGE_BYTES, &map_b, (tap * p.cblocks + cb) * BKB, tn * BN,
+                            bfull_bar(sb));
+                if (++sb == p.flat_nb) { sb = 0; phb ^= 1u; }
+              }
+            }
+          }
+        }
+      } else
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
@@ -341,6 +456,71 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         ok = mbar_wait(bres_bar, 0u);
         tc_fence_after();
       }
+      if (flat) {
+        int sb = 0;
+        uint32_t phb = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
+          const uint32_t acc = tl & 1u;
+          const uint32_t aph = (tl >> 1) & 1u;
+          if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          for (int cb = 0; cb < p.cblocks && ok; cb++) {
+            if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = ring + (uint32_t)s * stage_bytes;
+            if (p.R == 3 || p.R == 1) {
+              const uint64_t d0 = make_smem_desc_k<BKB>(0);
+              const uint32_t desc_hi = (uint32_t)(d0 >> 32), lo0 = (uint32_t)d0;
+              const uint32_t a_lo = lo0 | ((sa & 0x3FFFFu) >> 4);
+              const uint32_t row_step = (uint32_t)(p.flat_nblk == 1 ? p.flat_wp : p.flat_blk_rows) * (BKB / 16);
+              uint32_t enable = cb != 0 ? 1u : 0u;
+              if (p.b_resident) {
+                const uint32_t b_lo = lo0 | (((base + (uint32_t)cb * B_STAGE_BYTES) & 0x3FFFFu) >> 4);
+                const uint32_t b_step = (uint32_t)p.cblocks * (B_STAGE_BYTES / 16);
+                if (p.R == 3) flat_issue_taps<BKB, 3>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
+                else flat_issue_taps<BKB, 1>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
+              } else {
+                ok = p.R == 3 ? flat_issue_taps_ring<BKB, 3>(d_tmem, a_lo, row_step, lo0, bring, B_STAGE_BYTES, bfull_bar(0),
+                                                             bempty_bar(0), p.flat_nb, sb, phb, desc_hi, p.idesc, enable)
+                              : flat_issue_taps_ring<BKB, 1>(d_tmem, a_lo, row_step, lo0, bring, B_STAGE_BYTES, bfull_bar(0),
+                                                             bempty_bar(0), p.flat_nb, sb, phb, desc_hi, p.idesc, enable);
+                if (!ok) break;
+              }
+              tc_commit(empty_bar(s));
+              if (++s == stages) { s = 0; ph ^= 1u; }
+              continue;
+            }
+            int tap = 0;
+            for (int ti = 0; ti < p.R && ok; ti++) {
+              // rows of the buffer this filter row starts at: ti image rows down (one box), or block ti
+              const uint32_t row_a = p.flat_nblk == 1 ? (uint32_t)(ti * p.flat_wp) : (uint32_t)(ti * p.flat_blk_rows);
+              for (int tj = 0; tj < p.R; tj++, tap++) {
+                // a descriptor may start at any row: the swizzle is a function of the shared-memory address
+                const uint64_t adesc = make_smem_desc_k<BKB>(sa + (row_a + tj) * BKB);
+                uint64_t bdesc;
+                if (p.b_resident) {
+                  bdesc = make_smem_desc_k<BKB>(base + (uint32_t)(tap * p.cblocks + cb) * B_STAGE_BYTES);
+                } else {
+                  if (!mbar_wait(bfull_bar(sb), phb)) { ok = false; break; }
+                  tc_fence_after();
+                  bdesc = make_smem_desc_k<BKB>(bring + (uint32_t)sb * B_STAGE_BYTES);
+                }
+#pragma unroll
+                for (int k = 0; k < BKB / 32; k++)
+                  tc_mma_i8(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (cb | tap | k) != 0 ? 1u : 0u);
+                if (!p.b_resident) {
+                  tc_commit(bempty_bar(sb));
+                  if (++sb == p.flat_nb) { sb = 0; phb ^= 1u; }
+                }
+              }
+            }
+            tc_commit(empty_bar(s));  // the buffer is free once every tap has read it
+            if (++s == stages) { s = 0; ph ^= 1u; }
+          }
+          if (ok) tc_commit(tfull_bar(acc));
+        }
+      } else
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
         const uint32_t acc = tl & 1u;
         const uint32_t aph = (tl >> 1) & 1u;
@@ -387,11 +567,29 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const bool vec_rows = (p.N & 3) == 0;
     const int sub_r = lane >> 2, grp = lane & 3;
     const RowInBox in_box = row_in_box(p, quarter * 32 + lane);
+    constexpr int THR_CHUNKS = BN >= 64 ? BN / 64 : 1;   // chunks per epilogue warp
+    int4 thr_of[THR_CHUNKS];
+    int thr_tn = -1;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       const uint32_t acc = tl & 1u;
       const uint32_t aph = (tl >> 1) & 1u;
+      if (thr_staged && tn != thr_tn) {
+        // this lane's column of each chunk the warp drains; reloaded only when the tile column changes
+#pragma unroll
+        for (int i = 0; i < THR_CHUNKS; i++) {
+          const int col = tn * BN + (half + 2 * i) * 32 + lane;
+          int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
+          if (col < p.N) {
+            const int32_t* T = p.thresholds + (long long)col * nl;
+            t4.x = __ldg(T);
+            if (nl > 1) { t4.y = __ldg(T + 1); t4.z = __ldg(T + 2); }
+          }
+          thr_of[i] = t4;
+        }
+        thr_tn = tn;
+      }
       const RowDst dst = row_destination(p, tm, quarter * 32 + lane, in_box);
       const long long row = dst.row;
       const bool row_ok = dst.valid;
@@ -428,20 +626,14 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       for (int c = half; c < BN / 32; c += 2) {
         const int col0 = tn * BN + c * 32;
         if (col0 >= p.N) continue;  // uniform over the warp
-        int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
-        if (thr_staged && col0 + lane < p.N) {
-          const int32_t* T = p.thresholds + (long long)(col0 + lane) * nl;
-          t4.x = __ldg(T);
-          if (nl > 1) { t4.y = __ldg(T + 1); t4.z = __ldg(T + 2); }
-        }
         uint32_t v[32];
         tmem_ld32(taddr + c * 32, v);
-        tmem_ld_wait();
         if (thr_staged) {
           __syncwarp();   // the previous chunk's readers are done
-          thr_s[lane] = t4;
+          thr_s[lane] = thr_of[c >> 1];
           __syncwarp();
         }
+        tmem_ld_wait();
         if (p.pool != POOL_NONE) {
           // the four pixels of a window are lanes l, l^1 (next column) and l^bw, l^bw^1 (next row)
 #pragma unroll
@@ -664,6 +856,34 @@ void plan_smem(Tc5Params& p, int* smem_bytes) {
   *smem_bytes = (int)(Cfg::FIXED_BYTES + fixed + (long long)stages * stage);
 }
 
+// Flat convolution: A-buffer ring plus (unless the filter is resident) a ring of B tiles.
+template <int BN, int BKB>
+void plan_flat(Tc5Params& p, int* smem_bytes) {
+  using Cfg = TileCfg<BN, BKB>;
+  const long long room = SMEM_LIMIT - Cfg::FIXED_BYTES;
+  const long long a_bytes = (long long)p.flat_nblk * p.flat_blk_rows * BKB;
+  const long long bres = (long long)p.kblocks * Cfg::B_STAGE_BYTES;
+  p.kgroup = 1;
+  p.b_resident = 0;
+  long long fixed = 0;
+  if (p.tiles_n == 1 && p.tiles_m >= 4 * device_sm_count() && bres + 2 * a_bytes <= room) {
+    p.b_resident = 1;
+    p.flat_nb = 0;
+    fixed = bres;
+  } else {
+    int nb = 4;
+    while (nb > 2 && nb * (long long)Cfg::B_STAGE_BYTES + 2 * a_bytes > room) nb--;
+    p.flat_nb = nb;
+    fixed = nb * (long long)Cfg::B_STAGE_BYTES;
+  }
+  long long na = (room - fixed) / a_bytes;
+  if (na > 6) na = 6;
+  if (na < 1) na = 1;
+  p.flat_na = (int)na;
+  p.stages = (int)na;
+  *smem_bytes = (int)(Cfg::FIXED_BYTES + fixed + na * a_bytes);
+}
+
 template <int BN, int BKB>
 cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid) {
   static bool attr_set[16] = {};
@@ -676,7 +896,8 @@ cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorM
     if (dev < 16) attr_set[dev] = true;
   }
   int smem = 0;
-  plan_smem<BN, BKB>(p, &smem);
+  if (p.is_conv == 2) plan_flat<BN, BKB>(p, &smem);
+  else plan_smem<BN, BKB>(p, &smem);
   tc5_gemm_kernel<BN, BKB><<<grid, THREADS, smem, s>>>(map_a, map_b, p);
   return cudaGetLastError();
 }
@@ -891,12 +1112,34 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.out_w = pool ? W / 2 : W;
   p.out_halo = epi ? epi->out_halo : 0;
   p.a_box_bytes = (uint32_t)(bw * bh * bb * span);
+  // stride-1 convolutions without pooling run "flat": tiles of 128 consecutive padded pixels,
+  // every tap a row-shifted view of one buffer of consecutive input rows (2-D TMA loads)
+  const long long flat_rows = (long long)B * Hp * Wp;
+  // ... unless the padding ring wastes more MMA rows than the pixel boxes would (tiny images)
+  const double flat_util = (double)H * W / ((double)Hp * Wp);
+  const double box_util = (double)H * W * bb / ((double)p.tiles_h * p.tiles_w * BM);
+  const bool flat = stride == 1 && pool == APNN_POOL_NONE && flat_rows < 0x7fffff00LL && flat_util >= 0.95 * box_util;
+  if (flat) {
+    p.is_conv = 2;
+    p.flat_wp = Wp;
+    p.flat_hpwp = Hp * Wp;
+    p.tiles_m = (int)((flat_rows + BM - 1) / BM);
+    const int all_rows = (BM + (R - 1) * (Wp + 1) + 7) / 8 * 8;
+    if (all_rows <= 256) {
+      p.flat_nblk = 1;
+      p.flat_blk_rows = all_rows;
+    } else {
+      p.flat_nblk = R;
+      p.flat_blk_rows = (BM + R - 1 + 7) / 8 * 8;
+    }
+  }
   const int bn = pick_bn(p.tiles_m, COUT, sms);
   CUtensorMap map_a, map_b;
-  if (!make_activation_map(&map_a, X8, B, Hp, Wp, CIN, bw, bh, bb, stride, span) ||
-      !make_operand_map(&map_b, W8, COUT, (long long)R * R * CIN, bn, span)) {
-    return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
-  }
+  const bool maps_ok =
+      (flat ? make_operand_map(&map_a, X8, flat_rows, CIN, p.flat_blk_rows, span)
+            : make_activation_map(&map_a, X8, B, Hp, Wp, CIN, bw, bh, bb, stride, span)) &&
+      make_operand_map(&map_b, W8, COUT, (long long)R * R * CIN, bn, span);
+  if (!maps_ok) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   p.out = Out;
   p.thresholds = epi ? epi->thresholds : nullptr;
   p.M = B * H * W;
