@@ -41,6 +41,7 @@ class Epilogue(ctypes.Structure):
         ("n_peer_out", ctypes.c_int32),
         ("out_i8", ctypes.c_int32),
         ("peer_out", ctypes.c_void_p * 7),
+        ("residual_i16", ctypes.c_int32),
     ]
 
 

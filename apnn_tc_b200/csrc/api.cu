@@ -36,6 +36,8 @@ int device_sm_count() {
 apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, int abits_signed_w, int abits_signed_x,
                            bool i8_rows_ok) {
   if (!e) return APNN_OK;
+  if (e->residual_i16 != 0 && (e->residual_i16 < 0 || e->residual_i16 > 3 || !i8_rows_ok || e->n_peer_out != 0))
+    return (e->residual_i16 > 0 && e->residual_i16 <= 3 && !i8_rows_ok) ? APNN_ERR_UNSUPPORTED : APNN_ERR_INVALID_ARG;
   if (e->out_i8 != 0 && (e->out_i8 != 1 || !i8_rows_ok || e->out_mode == APNN_OUT_INT32 || e->n_peer_out != 0))
     return e->out_i8 == 1 && !i8_rows_ok ? APNN_ERR_UNSUPPORTED : APNN_ERR_INVALID_ARG;
   if (e->out_mode < APNN_OUT_INT32 || e->out_mode > APNN_OUT_THRESHOLDS) return APNN_ERR_INVALID_ARG;

@@ -147,6 +147,7 @@ struct Tc5Params {
   uint32_t a_box_bytes;  // bytes one A box deposits
   const int32_t* residual_in;  // optional dense int32 [rows][N], added before requantisation
   int32_t* residual_out;       // optional dense int32 [rows][N], the value after the add
+  int res16_in, res16_out;     // residual_in / residual_out hold int16 (values saturate on the way out)
   // shared-memory plan (chosen on the host)
   int stages;            // ring depth
   int kgroup;            // K blocks per stage (one barrier round trip and one commit per group)
@@ -608,6 +609,16 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       auto fetch_residual = [&](int c) {
         const int col0 = tn * BN + c * 32;
         if (p.residual_in == nullptr || !vec_rows || col0 + 32 > p.N) return;
+        if (p.res16_in) {
+          // int16 rows: 64 bytes per row and chunk, 8 values per lane and load
+          const int16_t* R16 = reinterpret_cast<const int16_t*>(p.residual_in);
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            rin[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (ok_of[i]) rin[i] = __ldg(reinterpret_cast<const uint4*>(R16 + dense_of[i] * p.N + col0 + 8 * grp));
+          }
+          return;
+        }
 #pragma unroll
         for (int hf = 0; hf < 2; hf++)
 #pragma unroll
@@ -650,7 +661,22 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (whole) {
             // int32 rows move through the transposition block so that global accesses are
             // 64 contiguous bytes per row, 8 rows per instruction
-            if (p.residual_in != nullptr) {
+            auto lo16 = [](uint32_t w) { return (uint32_t)(int)(short)(w & 0xffffu); };
+            auto hi16 = [](uint32_t w) { return (uint32_t)((int)w >> 16); };
+            auto sat16 = [](uint32_t x) { return (uint32_t)min(max((int)x, -32768), 32767) & 0xffffu; };
+            if (p.residual_in != nullptr && p.res16_in) {
+#pragma unroll
+              for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(xp + swz(8 * i + sub_r, grp)) = rin[i];
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                const uint4 x = *reinterpret_cast<const uint4*>(xp + swz(lane, j));
+                v[8 * j] += lo16(x.x); v[8 * j + 1] += hi16(x.x); v[8 * j + 2] += lo16(x.y); v[8 * j + 3] += hi16(x.y);
+                v[8 * j + 4] += lo16(x.z); v[8 * j + 5] += hi16(x.z); v[8 * j + 6] += lo16(x.w); v[8 * j + 7] += hi16(x.w);
+              }
+              __syncwarp();
+              if (c + 2 < BN / 32) fetch_residual(c + 2);
+            } else if (p.residual_in != nullptr) {
 #pragma unroll
               for (int hf = 0; hf < 2; hf++) {
 #pragma unroll
@@ -666,7 +692,21 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               }
               if (c + 2 < BN / 32) fetch_residual(c + 2);   // the next chunk's rows, in flight during this one's tail
             }
-            if (p.residual_out != nullptr) {
+            if (p.residual_out != nullptr && p.res16_out) {
+              int16_t* O16 = reinterpret_cast<int16_t*>(p.residual_out);
+#pragma unroll
+              for (int j = 0; j < 4; j++)
+                *reinterpret_cast<uint4*>(xp + swz(lane, j)) =
+                    make_uint4(sat16(v[8 * j]) | (sat16(v[8 * j + 1]) << 16), sat16(v[8 * j + 2]) | (sat16(v[8 * j + 3]) << 16),
+                               sat16(v[8 * j + 4]) | (sat16(v[8 * j + 5]) << 16), sat16(v[8 * j + 6]) | (sat16(v[8 * j + 7]) << 16));
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                const uint4 x = *reinterpret_cast<const uint4*>(xp + swz(8 * i + sub_r, grp));
+                if (ok_of[i]) *reinterpret_cast<uint4*>(O16 + dense_of[i] * p.N + col0 + 8 * grp) = x;
+              }
+              __syncwarp();
+            } else if (p.residual_out != nullptr) {
 #pragma unroll
               for (int hf = 0; hf < 2; hf++) {
 #pragma unroll
@@ -688,8 +728,13 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 32; j++)
               if (col0 + j < p.N) {
-                if (p.residual_in != nullptr) v[j] = (uint32_t)((int)v[j] + __ldg(p.residual_in + at + j));
-                if (p.residual_out != nullptr) p.residual_out[at + j] = (int32_t)v[j];
+                if (p.residual_in != nullptr)
+                  v[j] = (uint32_t)((int)v[j] + (p.res16_in ? (int)__ldg(reinterpret_cast<const int16_t*>(p.residual_in) + at + j)
+                                                             : __ldg(p.residual_in + at + j)));
+                if (p.residual_out != nullptr) {
+                  if (p.res16_out) reinterpret_cast<int16_t*>(p.residual_out)[at + j] = (int16_t)min(max((int)v[j], -32768), 32767);
+                  else p.residual_out[at + j] = (int32_t)v[j];
+                }
               }
           }
         }
@@ -990,7 +1035,7 @@ apnn_status tc5_expand2(cudaStream_t s, const uint32_t* pa, uint8_t* oa, long lo
 
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
-  if ((tc5_pair_worthwhile(M, N, K) && !(epi && epi->out_i8)) || (epi && epi->n_peer_out > 0))
+  if ((tc5_pair_worthwhile(M, N, K) && !(epi && (epi->out_i8 || epi->residual_i16))) || (epi && epi->n_peer_out > 0))
     return tc5_gemm_i8_pair(s, A8, B8, D, M, N, K, a_signed, b_signed, epi, status_flag);
   cudaError_t e;
   const int sms = device_sm_count();
@@ -1015,6 +1060,8 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.error_flag = status_flag;
   p.residual_in = epi ? epi->residual_in : nullptr;
   p.residual_out = epi ? epi->residual_out : nullptr;
+  p.res16_in = epi ? (epi->residual_i16 & 1) : 0;
+  p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
   p.idesc = make_idesc(a_signed, b_signed, bn);
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < sms ? tiles : sms);
@@ -1154,6 +1201,8 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.error_flag = status_flag;
   p.residual_in = epi ? epi->residual_in : nullptr;
   p.residual_out = epi ? epi->residual_out : nullptr;
+  p.res16_in = epi ? (epi->residual_i16 & 1) : 0;
+  p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
   p.idesc = make_idesc(false, w_signed, bn);  // A = activations (unsigned), B = filter
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < sms ? tiles : sms);

@@ -314,6 +314,21 @@ class Network:
         # a quantised output feeds the next layers as int8 rows, written by the producing kernel's
         # epilogue, when producer and every consumer run on the tcgen05 path: no packed planes in
         # between and no expand pass
+        # residual tensors are int16 where every value provably fits: |value| <= (2^a - 1) * fan_in
+        # plus the bound of the residual it adds, and producer and readers run on the tcgen05 path
+        self.res16: Dict[str, bool] = {}
+        bound: Dict[str, int] = {}
+        for ls in spec.layers:
+            sh = self.params[ls.name].shape
+            fan = sh["K"] if ls.kind != "conv" else ls.R * ls.R * ls.cin
+            bound[ls.name] = ((1 << a) - 1) * fan + (bound[ls.residual_from] if ls.residual_from else 0)
+        for ls in spec.layers:
+            if ls.name in self.res:
+                readers = [c.name for c in spec.layers if c.residual_from == ls.name]
+                if (use_tcgen05 and self.tc5_ok[ls.name] and all(self.tc5_ok[r] for r in readers)
+                        and bound[ls.name] <= 32767 and ls.quantise):
+                    self.res[ls.name] = torch.zeros(self.res[ls.name].shape, dtype=torch.int16, device=self.device)
+                    self.res16[ls.name] = True
         self.i8_out: Dict[str, bool] = {}
         for ls in spec.layers:
             users = [c.name for c in spec.layers if self.src_of[c.name] == ls.name]
@@ -362,10 +377,13 @@ class Network:
         mode = "thresholds" if ls.quantise else "int32"
         res_in = self.res[ls.residual_from] if ls.residual_from else None
         res_out = self.res.get(ls.name) if (ls.save_residual and ls.quantise) else None
+        r16 = (1 if (ls.residual_from and self.res16.get(ls.residual_from, False)) else 0) | \
+              (2 if (res_out is not None and self.res16.get(ls.name, False)) else 0)
         return make_epilogue(mode, self.spec.a_bit if ls.quantise else 0, signed="none",
                              pool="max" if ls.pool == 2 else "none", out_halo=self.halo[ls.name] if conv else 0,
                              in_halo=self.halo[self.src_of[ls.name]] if conv else 0, thresholds=self.thr[ls.name],
-                             residual_in=res_in, residual_out=res_out, out_i8=self.i8_out.get(ls.name, False))
+                             residual_in=res_in, residual_out=res_out, out_i8=self.i8_out.get(ls.name, False),
+                             residual_i16=r16)
 
     def _run_conv(self, ls: LayerSpec) -> int:
         sh = self.params[ls.name].shape

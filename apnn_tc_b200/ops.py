@@ -41,7 +41,7 @@ def _dev_words(t: torch.Tensor, name: str) -> torch.Tensor:
 def make_epilogue(out_mode: str = "int32", out_bits: int = 0, signed: str = "none", pool: str = "none",
                   out_halo: int = 0, in_halo: int = 0, thresholds: Optional[torch.Tensor] = None,
                   residual_in: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None,
-                  peer_out: Optional[list] = None, out_i8: bool = False) -> Epilogue:
+                  peer_out: Optional[list] = None, out_i8: bool = False, residual_i16: int = 0) -> Epilogue:
     """Build the fused-epilogue descriptor.
 
     out_mode: "int32" | "lowbits" (the reference's ``val & (2^bits-1)``) | "thresholds"
@@ -60,6 +60,7 @@ def make_epilogue(out_mode: str = "int32", out_bits: int = 0, signed: str = "non
     e.thresholds = thresholds.data_ptr() if thresholds is not None else None
     e.residual_in = residual_in.data_ptr() if residual_in is not None else None
     e.residual_out = residual_out.data_ptr() if residual_out is not None else None
+    e.residual_i16 = int(residual_i16)   # bit 0: residual_in is int16, bit 1: residual_out is int16 (gemm_i8 / conv2d_i8)
     e.out_i8 = 1 if out_i8 else 0   # one byte per output element instead of packed planes (gemm_i8 / conv2d_i8)
     if peer_out:
         if len(peer_out) > 7:

@@ -97,6 +97,12 @@ typedef struct apnn_epilogue {
                                  result everywhere without a separate all-gather.  The caller
                                  synchronises the ranks before reading.  No reference counterpart
                                  (the reference is single-GPU). */
+  int32_t residual_i16;       /* apnn_conv2d_i8 / apnn_gemm_i8 only: bit 0 = residual_in holds int16,
+                                 bit 1 = residual_out holds int16, instead of int32 (half the traffic
+                                 of the residual tensors, which bound the second convolution of a
+                                 ResNet block).  The caller guarantees the values fit (|value| <=
+                                 (2^xbits - 1) * K plus the bound of the added residual); stores
+                                 saturate.  No reference counterpart. */
 } apnn_epilogue;
 
 const char *apnn_status_string(apnn_status s);

@@ -340,3 +340,33 @@ def test_tcgen05_int8_row_output_chains(cuda_device, CIN, COUT, pool):
     X2 = oracle.pack_levels(xp, 2)
     want2 = oracle.signed_correct(oracle.conv_popc(W2, X2, threads=4), oracle.conv_window_sums(X2, 3), 0)
     assert np.array_equal(out2.cpu().numpy(), want2)
+
+
+@pytest.mark.parametrize("widths", [1, 2, 3])
+@pytest.mark.parametrize("CIN,COUT", [(64, 64), (128, 160)])
+def test_tcgen05_int16_residuals(cuda_device, widths, CIN, COUT):
+    """residual_i16: bit 0 = residual_in is int16, bit 1 = residual_out is int16; same values as int32."""
+    import ctypes
+    import apnn_tc_b200 as ap
+    from apnn_tc_b200 import _cabi
+    rng = np.random.default_rng(widths + CIN)
+    B, H, Wd = 3, 12, 16
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, 3, 1, 2)
+    v = oracle.signed_correct(oracle.conv_popc(Wt, X, threads=4), oracle.conv_window_sums(X, 3), 0)
+    res = rng.integers(-3000, 3000, size=v.shape).astype(np.int32)
+    v = v + res
+    T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
+    x8 = ap.expand_planes(to_dev(X).reshape(2, -1, CIN // 32))
+    w8 = ap.expand_planes(to_dev(Wt).reshape(1, COUT, -1), signed=True)
+    rin = torch.from_numpy(res.astype(np.int16) if widths & 1 else res).cuda()
+    rout = torch.zeros(v.shape, dtype=torch.int16 if widths & 2 else torch.int32, device="cuda")
+    out = torch.zeros((2, B, H + 2, Wd + 2, COUT // 32), dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    epi = ap.make_epilogue("thresholds", 2, out_halo=1, thresholds=to_dev(T), residual_in=rin, residual_out=rout,
+                           residual_i16=widths)
+    _cabi.check(_cabi.lib().apnn_conv2d_i8(torch.cuda.current_stream().cuda_stream, w8.data_ptr(), x8.data_ptr(),
+                                           out.data_ptr(), B, H, Wd, CIN, COUT, 3, 1, 1, ctypes.byref(epi), flag.data_ptr()),
+                "conv")
+    assert int(flag.item()) == 0
+    assert np.array_equal(rout.cpu().numpy().astype(np.int32), v)
+    assert np.array_equal(to_host(out)[:, :, 1:-1, 1:-1], oracle.requant_pack(v, 2, 2, T))

@@ -30,7 +30,8 @@ def test_model_logits_match_reference(cuda_device, model, hw, batch, use_tcgen05
             # packed planes or int8 rows, ring removed
             assert np.array_equal(net.levels_of(ls.name).cpu().numpy(), levels[ls.name]), ls.name
         if ls.name in net.res:
-            assert np.array_equal(to_host(net.res[ls.name], np.int32).reshape(values[ls.name].shape), values[ls.name]), ls.name
+            got = net.res[ls.name].cpu().numpy().astype(np.int32)        # int32, or int16 where the values provably fit
+            assert np.array_equal(got.reshape(values[ls.name].shape), values[ls.name]), ls.name
     # the quantiser is exercised: more than one level occurs in the last hidden layer
     assert len(np.unique(levels[spec.layers[-2].name])) > 1
 
