@@ -4,6 +4,8 @@
     python -m apnn_tc_b200.sweep conv     # 16x16, C=O=128..1024, 3x3, batch 1 and 8 (README.md:160-167)
     python -m apnn_tc_b200.sweep big      # M=N=K=8192 for the four bit pairs and the three algorithms
     python -m apnn_tc_b200.sweep conv w=1 a=2 B=8 C=128      # one shape only (for ncu captures)
+    python -m apnn_tc_b200.sweep layers [B=512] [mode=thresholds] [H=56] ...   # ResNet-18 layer shapes on
+                                        # apnn_conv2d_i8 (pre-expanded operands) with each epilogue
 
 Launch-bound shapes are timed by replaying a CUDA graph of many back-to-back launches (device time
 per launch without host launch overhead) and, beside it, by plain back-to-back launches with one
@@ -138,6 +140,55 @@ def sweep_big():
                               "ms": round(ms, 4), "tops": round(2.0 * M * N * K / ms / 1e9, 1)}), flush=True)
 
 
+def sweep_layers():
+    """The 3x3 / 1x1 layer shapes of ResNet-18 at a large batch through ``apnn_conv2d_i8`` (int8 operands
+    as the networks chain them), with int32, low-bit, threshold and threshold + int32 residual in/out
+    epilogues.  Plain back-to-back launches between one event pair (each call runs 50 us or more)."""
+    import ctypes
+    from . import _cabi
+    from .ops import _stream_ptr
+    L = _cabi.lib()
+    B = int(FILTER.pop("B", 512))
+    gen = torch.Generator(device="cuda").manual_seed(0xA9117C + 6)
+    for (H, C, O, R) in ((56, 64, 64, 3), (56, 192, 64, 1), (56, 128, 128, 3), (28, 128, 128, 3), (14, 256, 256, 3),
+                         (7, 512, 512, 3)):
+        for mode, res in (("int32", False), ("lowbits", False), ("thresholds", False), ("thresholds", True)):
+            if not _keep(H=H, C=C, mode=mode, res=int(res)):
+                continue
+            pad = (R - 1) // 2
+            x8 = torch.randint(0, 4, (B, H + 2 * pad, H + 2 * pad, C), dtype=torch.uint8, device="cuda", generator=gen)
+            w8 = (torch.randint(0, 2, (O, R, R, C), dtype=torch.int8, device="cuda", generator=gen) * 2 - 1)
+            flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+            thr = torch.sort(torch.randint(-300, 300, (O, 3), dtype=torch.int32, device="cuda", generator=gen),
+                             dim=1).values.contiguous()
+            rin = torch.randint(-100, 100, (B * H * H, O), dtype=torch.int32, device="cuda", generator=gen) if res else None
+            rout = torch.empty((B * H * H, O), dtype=torch.int32, device="cuda") if res else None
+            if mode == "int32":
+                out = torch.empty((B, H, H, O), dtype=torch.int32, device="cuda")
+                epi = ap.make_epilogue("int32")
+            else:
+                out = torch.zeros((2, B, H + 2, H + 2, O // 32), dtype=torch.int32, device="cuda")
+                epi = ap.make_epilogue(mode, 2, out_halo=1, thresholds=thr if mode == "thresholds" else None,
+                                       residual_in=rin, residual_out=rout)
+
+            def call():
+                _cabi.check(L.apnn_conv2d_i8(_stream_ptr(), w8.data_ptr(), x8.data_ptr(), out.data_ptr(), B, H, H, C, O, R, 1,
+                                             1, ctypes.byref(epi), flag.data_ptr()), "conv")
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                call()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 100.0
+            print(json.dumps({"op": "conv2d_i8", "B": B, "HW": H, "C": C, "O": O, "R": R, "epilogue": mode,
+                              "residual": res, "us": round(us, 1),
+                              "tops": round(2.0 * B * H * H * O * R * R * C / us / 1e6, 1)}), flush=True)
+
+
 FILTER = {}
 
 
@@ -151,7 +202,7 @@ def main():
     for tok in sys.argv[2:]:
         k, v = tok.split("=")
         FILTER[k] = v
-    {"gemm": sweep_gemm, "conv": sweep_conv, "big": sweep_big}[what]()
+    {"gemm": sweep_gemm, "conv": sweep_conv, "big": sweep_big, "layers": sweep_layers}[what]()
 
 
 if __name__ == "__main__":
