@@ -20,6 +20,22 @@ __device__ __forceinline__ uint32_t quantize_level(float x, float steps, uint32_
   return u > maxlv ? maxlv : u;
 }
 
+// The quantiser is a non-decreasing function of x (every float operation in it is), so
+// level(x) = #{ j : x >= first_x[j] } with first_x[j] the smallest float that reaches level j+1.
+// For up to 3 bits the kernels compare against those 2^bits - 1 floats (found once on the host
+// by bisection over the float ordering, with the same float arithmetic) instead of dividing.
+struct QuantSteps {
+  float first_x[7];
+  int n;   // 2^bits - 1, or 0: use the arithmetic form
+};
+__device__ __forceinline__ uint32_t quantize_by_steps(float x, const QuantSteps& qs) {
+  uint32_t lv = 0;
+#pragma unroll
+  for (int j = 0; j < 7; j++)
+    if (j < qs.n) lv += x >= qs.first_x[j] ? 1u : 0u;
+  return lv;
+}
+
 template <bool FROM_FLOAT>
 __global__ void __launch_bounds__(256) pack_planes_kernel(const void* __restrict__ in, uint32_t* __restrict__ planes,
                                                           long long rows, int C, int bits) {
@@ -314,6 +330,136 @@ __global__ void __launch_bounds__(256) quantize_im2col_i8_kernel(const float* __
   }
 }
 
+// The same gather when one pass of the block covers an output row (Wo * kp/32 <= blockDim.x):
+// a thread keeps its (pixel, 32-byte group) for the whole kernel, so the 32 shared-memory
+// offsets of its elements are computed once and the per-row work is 32 byte loads, 32
+// shift-ORs and one 32-byte store, with no index arithmetic or branches.
+__global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const float* __restrict__ img,
+                                                                       uint8_t* __restrict__ out, int B, int H, int W,
+                                                                       int C, int R, int stride, int bits, int Ho,
+                                                                       int Wo, int kp, int rowlen, int lpad,
+                                                                       const QuantSteps qs) {
+  extern __shared__ __align__(16) unsigned char lv_s[];   // [R][rowlen], image columns start at byte lpad
+  const float steps = (float)(1 << bits);
+  const uint32_t maxlv = (1u << bits) - 1u;
+  const int pad = (R - 1) / 2;
+  const int kreal = R * R * C, tapw = R * C, wc = W * C;
+  const int groups = kp / 32;
+  const int quads = wc >> 2;
+  const int T = blockDim.x;
+  // this thread's task and the offsets of its 32 elements, two 16-bit offsets per register
+  // (byte 0 of the buffer, always padding, for k >= R*R*C)
+  const bool worker = (int)threadIdx.x < Wo * groups;
+  const int wo = threadIdx.x / groups, w = threadIdx.x - wo * groups;
+  uint32_t src[16];
+  {
+    int k = w * 32;
+    int i = k / tapw, off = k - i * tapw;
+#pragma unroll
+    for (int e = 0; e < 32; e++) {
+      const uint32_t o = (worker && k + e < kreal) ? (uint32_t)(i * rowlen + (lpad - pad * C) + wo * stride * C + off) : 0u;
+      if (e & 1) src[e >> 1] |= o << 16;
+      else src[e >> 1] = o;
+      if (++off == tapw) { off = 0; i++; }
+    }
+  }
+  for (int t = threadIdx.x; t < R * (rowlen - wc); t += T) {
+    const int i = t / (rowlen - wc), o = t - i * (rowlen - wc);
+    lv_s[i * rowlen + (o < lpad ? o : wc + o)] = 0;
+  }
+  // the R input rows of an output row pass through registers: fetched while the previous row
+  // is assembled, quantised into shared memory afterwards (R * W*C/4 <= 4 * blockDim.x)
+  float4 nxt[4];
+  // which input element quad each of this thread's four slots carries: fixed for the kernel
+  int tap_row[4], img_off[4], smem_off[4];
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    const int t = threadIdx.x + u * T;
+    const int i = t / quads, q = t - i * quads;
+    tap_row[u] = t < R * quads ? i : -1000000;      // never inside the image
+    img_off[u] = i * wc + 4 * q;
+    smem_off[u] = i * rowlen + lpad + 4 * q;
+  }
+  auto fetch = [&](int orow) {
+    const int b = orow / Ho, ho = orow - b * Ho;
+    const int hbase = ho * stride - pad;
+    const float* first = img + ((long long)b * H + hbase) * wc;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int hi = hbase + tap_row[u];
+      nxt[u] = make_float4(-100.f, -100.f, -100.f, -100.f);   // clips to level 0: rows outside the image
+      if (hi >= 0 && hi < H) nxt[u] = __ldg(reinterpret_cast<const float4*>(first + img_off[u]));
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      if (tap_row[u] >= 0) {
+        const float4 f = nxt[u];
+        uint32_t packed;
+        if (qs.n)
+          packed = quantize_by_steps(f.x, qs) | (quantize_by_steps(f.y, qs) << 8) | (quantize_by_steps(f.z, qs) << 16) |
+                   (quantize_by_steps(f.w, qs) << 24);
+        else
+          packed = quantize_level(f.x, steps, maxlv) | (quantize_level(f.y, steps, maxlv) << 8) |
+                   (quantize_level(f.z, steps, maxlv) << 16) | (quantize_level(f.w, steps, maxlv) << 24);
+        *reinterpret_cast<uint32_t*>(lv_s + smem_off[u]) = packed;
+      }
+    }
+  };
+  int orow = blockIdx.x;
+  if (orow < B * Ho) fetch(orow);
+  for (; orow < B * Ho; orow += gridDim.x) {
+    __syncthreads();   // the previous row's readers are done
+    stash();
+    __syncthreads();
+    if (orow + (int)gridDim.x < B * Ho) fetch(orow + gridDim.x);
+    if (worker) {
+      uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int e = 0; e < 32; e++) {
+        const uint32_t o = (e & 1) ? (src[e >> 1] >> 16) : (src[e >> 1] & 0xffffu);
+        r[(31 - e) & 7] |= (uint32_t)lv_s[o] << (8 * ((31 - e) >> 3));
+      }
+      asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(out + ((long long)orow * Wo * groups + threadIdx.x) * 32),
+                   "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                   : "memory");
+    }
+  }
+}
+
+// Host restatement of quantize_level with the same IEEE single-precision operations.
+static uint32_t quantize_level_host(float x, int bits) {
+  volatile float a = x < -10.0f ? -10.0f : (x > 10.0f ? 10.0f : x);   // NaN never reaches here
+  volatile float s1 = a + 10.0f;
+  volatile float s2 = s1 * (float)(1 << bits);
+  volatile float q = s2 / 20.0f;
+  const uint32_t u = (uint32_t)nearbyintf(q);   // round to nearest even, as __float2uint_rn
+  const uint32_t maxlv = (1u << bits) - 1u;
+  return u > maxlv ? maxlv : u;
+}
+static QuantSteps make_quant_steps(int bits) {
+  static QuantSteps cache[4];   // per bit width; a race would only recompute the same values
+  if (bits <= 3 && cache[bits].n) return cache[bits];
+  QuantSteps qs;
+  memset(&qs, 0, sizeof(qs));
+  if (bits > 3) return qs;
+  qs.n = (1 << bits) - 1;
+  for (int j = 0; j < qs.n; j++) {
+    // bisection over the ordered floats of [-10, 10]: smallest x with level >= j + 1
+    float lo = -10.0f, hi = 10.0f;   // level(lo) = 0 < j + 1 <= level(hi) = 2^bits - 1
+    while (nextafterf(lo, hi) < hi) {
+      const float mid = lo + (hi - lo) * 0.5f;
+      const float m = (mid <= lo) ? nextafterf(lo, hi) : (mid >= hi ? nextafterf(hi, lo) : mid);
+      if (quantize_level_host(m, bits) >= (uint32_t)(j + 1)) hi = m;
+      else lo = m;
+    }
+    qs.first_x[j] = hi;
+  }
+  cache[bits] = qs;
+  return qs;
+}
+
 }  // namespace apnn
 
 extern "C" {
@@ -368,14 +514,24 @@ apnn_status apnn_quantize_im2col_i8(void* stream, const float* images, void* out
   if ((reinterpret_cast<uintptr_t>(images) & 15u) || (reinterpret_cast<uintptr_t>(out_i8) & 31u)) return APNN_ERR_ALIGNMENT;
   const int Ho = (H - 1) / stride + 1, Wo = (W - 1) / stride + 1;
   const int pad = (R - 1) / 2;
-  const int lpad = (pad * C + 3) / 4 * 4;   // image columns start on a 4-byte boundary
+  const int lpad = pad * C < 4 ? 4 : (pad * C + 3) / 4 * 4;   // image columns start on a 4-byte boundary; byte 0 is always padding
   const int rowlen = (lpad + W * C + pad * C + 15) / 16 * 16;
   const size_t smem = (size_t)R * rowlen;
   if (smem > 48 * 1024) return APNN_ERR_UNSUPPORTED;   // rows of this width: use apnn_quantize_im2col + apnn_expand_planes
-  long long nb = (long long)B * Ho, cap = (long long)device_sm_count() * 8;
-  if (nb > cap) nb = cap;
-  quantize_im2col_i8_kernel<<<(unsigned)nb, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      images, reinterpret_cast<uint8_t*>(out_i8), B, H, W, C, R, stride, bits, Ho, Wo, kp, rowlen, lpad);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int tasks = Wo * (kp / 32), wc = W * C;
+  const int threads = tasks < 128 ? 128 : (tasks + 31) / 32 * 32;
+  if ((wc & 3) == 0 && tasks <= 512 && R * (wc >> 2) <= 4 * threads && (size_t)R * rowlen < 65536) {
+    long long nb = (long long)B * Ho, cap = (long long)device_sm_count() * (2048 / threads);
+    if (nb > cap) nb = cap;
+    quantize_im2col_i8_fixed_kernel<<<(unsigned)nb, threads, smem, st>>>(
+        images, reinterpret_cast<uint8_t*>(out_i8), B, H, W, C, R, stride, bits, Ho, Wo, kp, rowlen, lpad, make_quant_steps(bits));
+  } else {
+    long long nb = (long long)B * Ho, cap = (long long)device_sm_count() * 8;
+    if (nb > cap) nb = cap;
+    quantize_im2col_i8_kernel<<<(unsigned)nb, 256, smem, st>>>(images, reinterpret_cast<uint8_t*>(out_i8), B, H, W, C, R,
+                                                              stride, bits, Ho, Wo, kp, rowlen, lpad);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "quantize_im2col_i8 launch");
   return APNN_OK;

@@ -68,6 +68,13 @@ def test_quantize_im2col_i8(cuda_device, B, H, Wd, C, R, stride, bits, kp):
     from apnn_tc_b200 import _cabi
     rng = np.random.default_rng(B + H + R + kp)
     x = rng.uniform(-12, 12, size=(B, H, Wd, C)).astype(np.float32)
+    # the points where the level changes (ties round to even) and their float neighbours
+    step = 20.0 / (1 << bits)
+    edges = (-10 + step * (np.arange(1 << bits) + 0.5)).astype(np.float32)
+    probe = np.concatenate([edges, np.nextafter(edges, np.float32(-20)), np.nextafter(edges, np.float32(20)),
+                            np.array([-10, 10, -10.5, 10.5, 0], np.float32)])
+    flat = x.reshape(-1)
+    flat[: min(probe.size, flat.size)] = probe[: flat.size]
     lv = oracle.unpack_levels(oracle.quantize_im2col(x, R, stride, bits))     # [B, Ho, Wo, PAD128(R*R*C)]
     want = np.zeros(lv.shape[:3] + (kp,), dtype=np.uint8)
     n = min(kp, lv.shape[-1])
