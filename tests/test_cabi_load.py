@@ -73,3 +73,35 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_cabi, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError):
         _cabi.lib()
+
+
+def test_reference_named_shims_compile(tmp_path):
+    """include/apnn_b200_shims.h (the reference's kernel, packer and layer-launch names over the
+    C ABI) compiles as C++/CUDA host code against structs with the reference's field names."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc")
+    if nvcc is None:
+        import pytest
+        pytest.skip("nvcc not on PATH")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "shim_user.cu"
+    src.write_text(r'''
+#include "apnn_b200_shims.h"
+struct ConvP { uin32 *filter_gpu, *input_gpu, *output_gpu; int batch, input_height, input_width, input_channels, output_channels; };
+struct FcP { uin32 *input_gpu, *weight_gpu, *output_gpu; int input_height, input_width, weight_width; };
+void use(ConvP* c, FcP* f, float* h, float* d, uin32* planes, int4* w, int4* x, int* out) {
+  Conv_new_global(c); FC_new_global(f); Output_new_global(f);
+  uin32* img = images_quantization(h, 8, 224, 224, 3, 2); uin32* flt = nullptr;
+  filter_quantization(flt, d, 64, 3, 3, 128, 1); weight_quantization(planes, d, 512, 1000, 1);
+  weight_quantization_fc_hidden(planes, d, 512, 512, 1);
+  apmm_w1a2(w, x, out, 64, 1024, 1024); apmm_w1a3(w, x, out, 64, 1024, 1024); apmm_w1a4(w, x, out, 64, 1024, 1024);
+  apmm_w2a2(w, x, out, 64, 1024, 1024); apmm_w1a2_decompose(w, x, out, 64, 1024, 1024);
+  APConv_w1a2_pack(w, x, out, 16, 16, 128, 128); APConv_w1a2_pack_pool(w, x, out, 16, 16, 128, 128);
+  APConv_w2a2_pack(w, x, out, 16, 16, 128, 128); compute_conv_imma(w, x, out, 16, 16, 128, 128, 1, 2);
+  (void)img;
+}
+''')
+    r = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(root, "include"), "-c",
+                        str(src), "-o", str(tmp_path / "shim_user.o")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
