@@ -59,6 +59,9 @@ apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, i
   return APNN_OK;
 }
 
+// Plane counts the int8 (tcgen05) path takes: every level of up to 8 bits fits one byte.
+bool tc5_bits_ok(int bits) { return (bits >= 1 && bits <= 4) || bits == 8; }
+
 }  // namespace apnn
 
 using namespace apnn;
@@ -142,15 +145,20 @@ apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const voi
   if (algo < APNN_ALGO_AUTO || algo > APNN_ALGO_TCGEN05_PAIR) return APNN_ERR_INVALID_ARG;
   if (K % 128 != 0) return APNN_ERR_ALIGNMENT;
   if (!aligned16(W) || !aligned16(X) || !aligned16(D)) return APNN_ERR_ALIGNMENT;
-  if (!core_supports(wbits, xbits)) return APNN_ERR_UNSUPPORTED;
+  // the warp-level kernels are instantiated for the reference's pairs (w1a1..w1a4, w2a2 and
+  // their mirrors); wider pairs (w4a4, w1a8, w2a8 ...) exist on the int8 tcgen05 path only
+  const bool warp_ok = core_supports(wbits, xbits);
+  if (!warp_ok && !(tc5_bits_ok(wbits) && tc5_bits_ok(xbits))) return APNN_ERR_UNSUPPORTED;
   apnn_status st = check_epilogue(epi, N, false, wbits, xbits);
   if (st != APNN_OK) return st;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 
   if (algo == APNN_ALGO_AUTO) {
     bool ws_ok = workspace && workspace_bytes >= tc5_workspace_bytes(M, N, K);
-    algo = (ws_ok && tc5_worthwhile(M, N, K)) ? APNN_ALGO_TCGEN05 : APNN_ALGO_IMMA;
+    algo = (ws_ok && (tc5_worthwhile(M, N, K) || !warp_ok)) ? APNN_ALGO_TCGEN05 : APNN_ALGO_IMMA;
   }
+  if (!warp_ok && algo != APNN_ALGO_TCGEN05 && algo != APNN_ALGO_TCGEN05_PAIR)
+    return workspace ? APNN_ERR_UNSUPPORTED : APNN_ERR_WORKSPACE;
   if (algo == APNN_ALGO_TCGEN05 || algo == APNN_ALGO_TCGEN05_PAIR) {
     if (!workspace || workspace_bytes < tc5_workspace_bytes(M, N, K)) return APNN_ERR_WORKSPACE;
     if (!aligned32(workspace)) return APNN_ERR_ALIGNMENT;
@@ -243,7 +251,8 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
   if (CIN % 128 != 0 && !(CIN % 64 == 0 && algo == APNN_ALGO_TCGEN05)) return APNN_ERR_ALIGNMENT;
   if (!aligned16(Wt) || !aligned16(X) || !aligned16(Out)) return APNN_ERR_ALIGNMENT;
   // core operand A = activations (xbits), B = filter (wbits)
-  if (!core_supports(xbits, wbits)) return APNN_ERR_UNSUPPORTED;
+  const bool warp_ok = core_supports(xbits, wbits);
+  if (!warp_ok && !(tc5_bits_ok(wbits) && tc5_bits_ok(xbits))) return APNN_ERR_UNSUPPORTED;
   apnn_status st = check_epilogue(epi, COUT, true, wbits, xbits);
   if (st != APNN_OK) return st;
   const int pad = (R - 1) / 2;
@@ -258,9 +267,11 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
     const bool ws_ok = workspace && workspace_bytes >= tc5_conv_workspace_bytes(B, H, Wd, CIN, COUT, R);
     const double flops = 2.0 * (double)pixels * COUT * R * R * CIN;
     const bool exact_ring = !epi || epi->in_halo == 0 || epi->in_halo == pad;
-    algo = (ws_ok && exact_ring && tc5_conv_supported(H, Wd, R, stride, pool) && flops >= 2e9) ? APNN_ALGO_TCGEN05
-                                                                                               : APNN_ALGO_IMMA;
+    algo = (ws_ok && exact_ring && tc5_conv_supported(H, Wd, R, stride, pool) && (flops >= 2e9 || !warp_ok))
+               ? APNN_ALGO_TCGEN05
+               : APNN_ALGO_IMMA;
   }
+  if (!warp_ok && algo != APNN_ALGO_TCGEN05) return workspace ? APNN_ERR_UNSUPPORTED : APNN_ERR_WORKSPACE;
   if (algo == APNN_ALGO_TCGEN05) {
     if (!tc5_conv_supported(H, Wd, R, stride, pool)) return APNN_ERR_UNSUPPORTED;
     if (epi && epi->in_halo != 0 && epi->in_halo != pad) return APNN_ERR_UNSUPPORTED;  // use apnn_conv2d_i8

@@ -124,7 +124,11 @@ apnn_status apnn_gemm(void *stream, int wbits, int xbits, const void *W, const v
  * APNN_OUT_LOWBITS it replaces apmm_w1a2_decompose (LIB/66_bmmaTensorCoreGemm.cuh:81-280)
  * and apmm_w2a2_decompose (LIB/73_bmmaTensorCoreGemm.cuh:81-297), which FC_new_global /
  * Output_new_global call (NN/kernel.cuh:299-318).  Packed modes need N % 32 == 0.
- * epi == NULL means int32 output.  workspace may be NULL for every algorithm but APNN_ALGO_TCGEN05. */
+ * epi == NULL means int32 output.  workspace may be NULL for every algorithm but APNN_ALGO_TCGEN05.
+ * With a workspace (APNN_ALGO_TCGEN05, or AUTO) every pair of widths from {1, 2, 3, 4, 8} runs --
+ * the reference's w4a4 / w1a8 / w2a8 programs (LIB/83, 77, 76_bmmaTensorCoreGemm.cu) included:
+ * on the int8 path a level of up to 8 bits is one byte whatever its width.  apnn_conv2d_ex
+ * follows the same rule. */
 apnn_status apnn_gemm_ex(void *stream, int algo, int wbits, int xbits, const void *W,
                          const void *X, void *D, int M, int N, int K,
                          const apnn_epilogue *epi, void *workspace, size_t workspace_bytes);

@@ -370,3 +370,10 @@ def test_tcgen05_int16_residuals(cuda_device, widths, CIN, COUT):
     assert int(flag.item()) == 0
     assert np.array_equal(rout.cpu().numpy().astype(np.int32), v)
     assert np.array_equal(to_host(out)[:, :, 1:-1, 1:-1], oracle.requant_pack(v, 2, 2, T))
+
+
+@pytest.mark.parametrize("wb,xb", [(4, 4), (2, 8)])
+def test_tcgen05_wider_pairs_conv(cuda_device, wb, xb):
+    rng = np.random.default_rng(wb + xb)
+    X, Wt = make_conv(rng, 2, 10, 12, 128, 64, 3, wb, xb)
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X), np.int32), oracle.conv_popc(Wt, X, threads=4))

@@ -314,3 +314,21 @@ def test_peer_destinations_refused_off_the_pair_kernel(cuda_device):
     extra = torch.zeros((64, 64), dtype=torch.int32, device="cuda")
     with pytest.raises(ap.ApnnError):
         ap.apmm(W, X, algo="imma", epilogue=ap.make_epilogue("int32", peer_out=[extra.data_ptr()]))
+
+
+@pytest.mark.parametrize("wb,xb", [(4, 4), (1, 8), (2, 8), (3, 3), (8, 8)])
+def test_tcgen05_wider_pairs(cuda_device, wb, xb):
+    """Bit pairs beyond the warp-level instantiations (the reference's w4a4 / w1a8 / w2a8 programs,
+    LIB/83, 77, 76) run on the int8 path: any level of up to 8 bits is one byte."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(wb * 16 + xb)
+    W, wl = oracle.value_planes(rng, 200, 1024, wb)
+    X, xl = oracle.value_planes(rng, 328, 1024, xb)
+    want = wl.astype(np.int64) @ xl.astype(np.int64).T
+    assert np.array_equal(to_host(run_tc5(W, X), np.int32), want)
+    assert np.array_equal(oracle.gemm_popc(W, X, threads=4), want)
+    # AUTO picks the int8 path when given a workspace; without one the pair is refused
+    ws = torch.empty(ap.gemm_workspace_bytes(200, 328, 1024), dtype=torch.uint8, device="cuda")
+    assert np.array_equal(to_host(ap.apmm(to_dev(W), to_dev(X), algo="auto", workspace=ws), np.int32), want)
+    with pytest.raises(ap.ApnnError):
+        ap.apmm(to_dev(W), to_dev(X), algo="imma")
