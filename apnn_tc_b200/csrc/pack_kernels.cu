@@ -460,6 +460,31 @@ static QuantSteps make_quant_steps(int bits) {
   return qs;
 }
 
+// 2x2 maximum over int8 NHWC rows: a thread owns 16 channels of one output pixel.
+__global__ void __launch_bounds__(256) maxpool2x2_i8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
+                                                            int B, int Ho, int Wo, int C, int ih, int oh) {
+  const int cv = C >> 4;   // 16-byte vectors per pixel
+  const long long total = (long long)B * Ho * Wo * cv;
+  const int Wi = 2 * Wo + 2 * ih, Hi = 2 * Ho + 2 * ih, Wq = Wo + 2 * oh, Hq = Ho + 2 * oh;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(t % cv);
+    long long pix = t / cv;
+    const int wo = (int)(pix % Wo);
+    pix /= Wo;
+    const int ho = (int)(pix % Ho);
+    const int b = (int)(pix / Ho);
+    const uint4* src = reinterpret_cast<const uint4*>(in + (((long long)b * Hi + 2 * ho + ih) * Wi + 2 * wo + ih) * C) + v;
+    const uint4 a = __ldg(src), c = __ldg(src + cv);
+    const uint4 d = __ldg(src + (long long)Wi * cv), e = __ldg(src + (long long)Wi * cv + cv);
+    uint4 m;
+    m.x = __vmaxu4(__vmaxu4(a.x, c.x), __vmaxu4(d.x, e.x));
+    m.y = __vmaxu4(__vmaxu4(a.y, c.y), __vmaxu4(d.y, e.y));
+    m.z = __vmaxu4(__vmaxu4(a.z, c.z), __vmaxu4(d.z, e.z));
+    m.w = __vmaxu4(__vmaxu4(a.w, c.w), __vmaxu4(d.w, e.w));
+    reinterpret_cast<uint4*>(out + (((long long)b * Hq + ho + oh) * Wq + wo + oh) * C)[v] = m;
+  }
+}
+
 }  // namespace apnn
 
 extern "C" {
@@ -534,6 +559,24 @@ apnn_status apnn_quantize_im2col_i8(void* stream, const float* images, void* out
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "quantize_im2col_i8 launch");
+  return APNN_OK;
+}
+
+apnn_status apnn_maxpool2x2_i8(void* stream, const void* in_i8, void* out_i8, int B, int H, int W, int C, int in_halo,
+                               int out_halo) {
+  using namespace apnn;
+  if (!in_i8 || !out_i8 || B <= 0 || H <= 0 || W <= 0 || C <= 0) return APNN_ERR_INVALID_ARG;
+  if (in_halo < 0 || in_halo > 8 || out_halo < 0 || out_halo > 8) return APNN_ERR_INVALID_ARG;
+  if ((H & 1) || (W & 1)) return APNN_ERR_UNSUPPORTED;
+  if (C % 16 != 0 || (reinterpret_cast<uintptr_t>(in_i8) & 15u) || (reinterpret_cast<uintptr_t>(out_i8) & 15u))
+    return APNN_ERR_ALIGNMENT;
+  const long long total = (long long)B * (H / 2) * (W / 2) * (C / 16);
+  long long nb = (total + 255) / 256, cap = (long long)device_sm_count() * 32;
+  if (nb > cap) nb = cap;
+  maxpool2x2_i8_kernel<<<(unsigned)nb, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint8_t*>(in_i8), reinterpret_cast<uint8_t*>(out_i8), B, H / 2, W / 2, C, in_halo, out_halo);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "maxpool2x2_i8 launch");
   return APNN_OK;
 }
 

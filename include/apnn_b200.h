@@ -217,6 +217,16 @@ apnn_status apnn_conv2d_i8(void *stream, const void *W8, const void *X8, void *O
                            int CIN, int COUT, int R, int stride, int w_signed,
                            const apnn_epilogue *epi, int *status_flag);
 
+/* 2x2 maximum over int8 rows (levels as apnn_conv2d_i8 writes them with out_i8): in
+ * [B][H+2*in_halo][W+2*in_halo][C] -> out [B][H/2+2*out_halo][W/2+2*out_halo][C], ring untouched.
+ * For threshold outputs with ascending thresholds the maximum of the levels is the level of the
+ * maximum, so an unpooled convolution followed by this pass equals APNN_POOL_MAX2 in the
+ * epilogue; it lets pooled stride-1 layers run on the flat convolution.  C % 16 == 0, H and W
+ * even, both pointers 16-byte aligned.  Pooling semantics: NN/kernel.cuh:856-859 (OR of
+ * binarised outputs = maximum of 1-bit levels). */
+apnn_status apnn_maxpool2x2_i8(void *stream, const void *in_i8, void *out_i8, int B, int H, int W, int C,
+                               int in_halo, int out_halo);
+
 /* ---- packers -------------------------------------------------------------------
  * apnn_bit_compress replaces Bit_compression (NN/kernel.cuh:46-77): one uint32 level per
  * element, levels[rows][C] -> planes[bits][rows][PAD128(C)/32], channel c in bit 31-(c%32);

@@ -45,7 +45,8 @@ def test_argument_validation_returns_status_codes():
     assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 96, None, None, 0) == 3
     assert L.apnn_gemm_ex(None, 0, 1, 2, p + 4, p, p, 64, 64, 128, None, None, 0) == 3
     # unsupported widths, packed output with N % 32 != 0, signed operand wider than 1 bit
-    assert L.apnn_gemm_ex(None, 0, 3, 3, p, p, p, 64, 64, 128, None, None, 0) == 2
+    assert L.apnn_gemm_ex(None, 0, 3, 3, p, p, p, 64, 64, 128, None, None, 0) == 4   # int8 path only: needs a workspace
+    assert L.apnn_gemm_ex(None, 0, 5, 5, p, p, p, 64, 64, 128, None, None, 0) == 2
     e = _cabi.Epilogue(out_mode=1, out_bits=2)
     assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 48, 128, ctypes.byref(e), None, 0) == 2
     e = _cabi.Epilogue(out_mode=0, signed_operand=2)
