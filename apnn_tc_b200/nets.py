@@ -341,6 +341,18 @@ class Network:
                     shape = (B, sh["coutp"])
                 self.out[ls.name] = torch.zeros(shape, dtype=torch.uint8, device=self.device)
                 self.i8_out[ls.name] = True
+        # pooled stride-1 layers whose output leaves as int8 rows run the (faster) flat convolution
+        # unpooled into a scratch map and pool the level bytes afterwards: with ascending thresholds
+        # the maximum of the levels is the level of the maximum
+        self.split_pool: Dict[str, bool] = {}
+        pool_bytes = 0
+        for ls in spec.layers:
+            if (ls.kind == "conv" and ls.pool == 2 and self.i8_out.get(ls.name, False) and not ls.save_residual
+                    and ls.residual_from is None and (ls.stride == 1 or (self.first_im2col and self.first_im2col[0] == ls.name))):
+                sh = self.params[ls.name].shape
+                self.split_pool[ls.name] = True
+                pool_bytes = max(pool_bytes, B * 2 * sh["Ho"] * 2 * sh["Wo"] * sh["coutp"])
+        self.unpooled = torch.empty(max(pool_bytes, 16), dtype=torch.uint8, device=self.device)
         if self.first_im2col is None:
             self.image_planes = torch.zeros((a, B, self.hw + 2 * h0, self.hw + 2 * h0, cp // 32), dtype=torch.int32,
                                             device=self.device)
@@ -379,8 +391,10 @@ class Network:
         res_out = self.res.get(ls.name) if (ls.save_residual and ls.quantise) else None
         r16 = (1 if (ls.residual_from and self.res16.get(ls.residual_from, False)) else 0) | \
               (2 if (res_out is not None and self.res16.get(ls.name, False)) else 0)
+        split = self.split_pool.get(ls.name, False)
         return make_epilogue(mode, self.spec.a_bit if ls.quantise else 0, signed="none",
-                             pool="max" if ls.pool == 2 else "none", out_halo=self.halo[ls.name] if conv else 0,
+                             pool="max" if (ls.pool == 2 and not split) else "none",
+                             out_halo=self.halo[ls.name] if (conv and not split) else 0,
                              in_halo=self.halo[self.src_of[ls.name]] if conv else 0, thresholds=self.thr[ls.name],
                              residual_in=res_in, residual_out=res_out, out_i8=self.i8_out.get(ls.name, False),
                              residual_i16=r16)
@@ -392,6 +406,15 @@ class Network:
         epi = self._epilogue(ls, True)
         out = self.out[ls.name] if ls.quantise else self.res[ls.name]
         s = _stream_ptr()
+        if self.split_pool.get(ls.name, False):
+            final, out = out, self.unpooled
+            n = self._launch_conv(ls, sh, X, a, B, epi, out, s)
+            _cabi.check(self.L.apnn_maxpool2x2_i8(s, out.data_ptr(), final.data_ptr(), B, 2 * sh["Ho"], 2 * sh["Wo"],
+                                                  sh["coutp"], 0, self.halo[ls.name]), "apnn_maxpool2x2_i8 " + ls.name)
+            return n + 1
+        return self._launch_conv(ls, sh, X, a, B, epi, out, s)
+
+    def _launch_conv(self, ls, sh, X, a, B, epi, out, s) -> int:
         if self.first_im2col and self.first_im2col[0] == ls.name:
             _, Hc, Wc, kp = self.first_im2col
             epi.in_halo = 0

@@ -87,3 +87,20 @@ def test_quantize_im2col_i8(cuda_device, B, H, Wd, C, R, stride, bits, kp):
                                              Wd, C, R, stride, bits, kp)
     _cabi.check(st, "apnn_quantize_im2col_i8")
     assert np.array_equal(out.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("B,H,Wd,C,ih,oh", [(2, 8, 12, 64, 0, 1), (3, 6, 6, 128, 1, 0), (1, 56, 56, 16, 0, 0)])
+def test_maxpool2x2_i8(cuda_device, B, H, Wd, C, ih, oh):
+    from apnn_tc_b200 import _cabi
+    rng = np.random.default_rng(B + H + C)
+    x = rng.integers(0, 256, size=(B, H + 2 * ih, Wd + 2 * ih, C), dtype=np.uint8)
+    core = x[:, ih:ih + H, ih:ih + Wd]
+    want = core.reshape(B, H // 2, 2, Wd // 2, 2, C).max(axis=(2, 4))
+    out = torch.full((B, H // 2 + 2 * oh, Wd // 2 + 2 * oh, C), 7, dtype=torch.uint8, device="cuda")
+    xd = torch.from_numpy(x).cuda()
+    _cabi.check(_cabi.lib().apnn_maxpool2x2_i8(torch.cuda.current_stream().cuda_stream, xd.data_ptr(), out.data_ptr(), B, H, Wd,
+                                               C, ih, oh), "apnn_maxpool2x2_i8")
+    got = out.cpu().numpy()
+    assert np.array_equal(got[:, oh:oh + H // 2, oh:oh + Wd // 2], want)
+    if oh:
+        assert (got[:, 0] == 7).all() and (got[:, :, 0] == 7).all()   # the ring is not written
