@@ -418,6 +418,22 @@ def run_ours(args) -> None:
                     "kind": kind_cpu,
                     "sample": f"{threads * rpt} of {M} output rows ({rpt} per thread), full N and K, bit-serial compute_ref"}
 
+    # beside the CPU loops: the reference's own GPU kernel for this pair, compiled unmodified for
+    # sm_100a into oracle/_ref (part of the same baseline leg; absent -> omitted)
+    bar = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "bar_gemm_w1a2")
+    if world == 1 and os.path.exists(bar) and (WBITS, XBITS) == (1, 2):
+        try:
+            import subprocess
+            torch.cuda.synchronize()
+            r = subprocess.run([bar, "gemm", str(M), str(N), str(K), "3"], capture_output=True, text=True, timeout=120)
+            rec = json.loads(r.stdout.strip().splitlines()[-1])
+            cpu_baseline["reference_gpu_kernel"] = {
+                "kernel": rec["kernel"], "value": rec["tops"], "unit": UNIT, "ms_per_launch": rec["us_per_launch"] / 1e3,
+                "note": "APNN-TC-lib/bmmaTensorCoreGemm/src/71_bmmaTensorCoreGemm.cu built for sm_100a, its own launch "
+                        "configuration, same shape, on this GPU"}
+        except Exception as exc:   # the bar is optional
+            cpu_baseline["reference_gpu_kernel"] = {"unavailable": str(exc)[:120]}
+
     ms_per_step = elapsed_ms / args.steps
     line = {
         "metric": METRIC, "value": world * flops_step / (ms_per_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
