@@ -334,6 +334,7 @@ __global__ void __launch_bounds__(256) quantize_im2col_i8_kernel(const float* __
 // a thread keeps its (pixel, 32-byte group) for the whole kernel, so the 32 shared-memory
 // offsets of its elements are computed once and the per-row work is 32 byte loads, 32
 // shift-ORs and one 32-byte store, with no index arithmetic or branches.
+template <int TPT, int NQ>   // 32-byte groups per thread; 16-byte input quads per thread and row
 __global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const float* __restrict__ img,
                                                                        uint8_t* __restrict__ out, int B, int H, int W,
                                                                        int C, int R, int stride, int bits, int Ho,
@@ -347,19 +348,21 @@ __global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const flo
   const int groups = kp / 32;
   const int quads = wc >> 2;
   const int T = blockDim.x;
-  // this thread's task and the offsets of its 32 elements, two 16-bit offsets per register
-  // (byte 0 of the buffer, always padding, for k >= R*R*C)
-  const bool worker = (int)threadIdx.x < Wo * groups;
-  const int wo = threadIdx.x / groups, w = threadIdx.x - wo * groups;
-  uint32_t src[16];
-  {
+  // this thread's tasks (task = threadIdx.x + j * blockDim.x) and the offsets of their 32 elements,
+  // two 16-bit offsets per register (byte 0 of the buffer, always padding, for k >= R*R*C)
+  uint32_t src[TPT][16];
+#pragma unroll
+  for (int j = 0; j < TPT; j++) {
+    const int task = threadIdx.x + j * T;
+    const bool worker = task < Wo * groups;
+    const int wo = task / groups, w = task - wo * groups;
     int k = w * 32;
     int i = k / tapw, off = k - i * tapw;
 #pragma unroll
     for (int e = 0; e < 32; e++) {
       const uint32_t o = (worker && k + e < kreal) ? (uint32_t)(i * rowlen + (lpad - pad * C) + wo * stride * C + off) : 0u;
-      if (e & 1) src[e >> 1] |= o << 16;
-      else src[e >> 1] = o;
+      if (e & 1) src[j][e >> 1] |= o << 16;
+      else src[j][e >> 1] = o;
       if (++off == tapw) { off = 0; i++; }
     }
   }
@@ -368,12 +371,12 @@ __global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const flo
     lv_s[i * rowlen + (o < lpad ? o : wc + o)] = 0;
   }
   // the R input rows of an output row pass through registers: fetched while the previous row
-  // is assembled, quantised into shared memory afterwards (R * W*C/4 <= 4 * blockDim.x)
-  float4 nxt[4];
-  // which input element quad each of this thread's four slots carries: fixed for the kernel
-  int tap_row[4], img_off[4], smem_off[4];
+  // is assembled, quantised into shared memory afterwards (R * W*C/4 <= NQ * blockDim.x)
+  float4 nxt[NQ];
+  // which input element quad each of this thread's slots carries: fixed for the kernel
+  int tap_row[NQ], img_off[NQ], smem_off[NQ];
 #pragma unroll
-  for (int u = 0; u < 4; u++) {
+  for (int u = 0; u < NQ; u++) {
     const int t = threadIdx.x + u * T;
     const int i = t / quads, q = t - i * quads;
     tap_row[u] = t < R * quads ? i : -1000000;      // never inside the image
@@ -385,7 +388,7 @@ __global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const flo
     const int hbase = ho * stride - pad;
     const float* first = img + ((long long)b * H + hbase) * wc;
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < NQ; u++) {
       const int hi = hbase + tap_row[u];
       nxt[u] = make_float4(-100.f, -100.f, -100.f, -100.f);   // clips to level 0: rows outside the image
       if (hi >= 0 && hi < H) nxt[u] = __ldg(reinterpret_cast<const float4*>(first + img_off[u]));
@@ -393,7 +396,7 @@ __global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const flo
   };
   auto stash = [&]() {
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < NQ; u++) {
       if (tap_row[u] >= 0) {
         const float4 f = nxt[u];
         uint32_t packed;
@@ -414,16 +417,20 @@ __global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const flo
     stash();
     __syncthreads();
     if (orow + (int)gridDim.x < B * Ho) fetch(orow + gridDim.x);
-    if (worker) {
-      uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 #pragma unroll
-      for (int e = 0; e < 32; e++) {
-        const uint32_t o = (e & 1) ? (src[e >> 1] >> 16) : (src[e >> 1] & 0xffffu);
-        r[(31 - e) & 7] |= (uint32_t)lv_s[o] << (8 * ((31 - e) >> 3));
+    for (int j = 0; j < TPT; j++) {
+      const int task = threadIdx.x + j * T;
+      if (task < Wo * groups) {
+        uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          const uint32_t o = (e & 1) ? (src[j][e >> 1] >> 16) : (src[j][e >> 1] & 0xffffu);
+          r[(31 - e) & 7] |= (uint32_t)lv_s[o] << (8 * ((31 - e) >> 3));
+        }
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(out + ((long long)orow * Wo * groups + task) * 32),
+                     "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                     : "memory");
       }
-      asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(out + ((long long)orow * Wo * groups + threadIdx.x) * 32),
-                   "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                   : "memory");
     }
   }
 }
@@ -545,12 +552,20 @@ apnn_status apnn_quantize_im2col_i8(void* stream, const float* images, void* out
   if (smem > 48 * 1024) return APNN_ERR_UNSUPPORTED;   // rows of this width: use apnn_quantize_im2col + apnn_expand_planes
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int tasks = Wo * (kp / 32), wc = W * C;
-  const int threads = tasks < 128 ? 128 : (tasks + 31) / 32 * 32;
-  if ((wc & 3) == 0 && tasks <= 512 && R * (wc >> 2) <= 4 * threads && (size_t)R * rowlen < 65536) {
+  const int tpt = tasks <= 512 ? 1 : 2;
+  const int per_thread = (tasks + tpt - 1) / tpt;
+  const int threads = per_thread < 128 ? 128 : (per_thread + 31) / 32 * 32;
+  const int quads_per_row = R * (wc >> 2);
+  const int nq = quads_per_row <= 4 * threads ? 4 : 8;
+  // two tasks per thread or eight quads per thread measured slower than the generic kernel (register
+  // pressure halves the resident blocks): the fixed-task kernel takes rows of at most 512 groups
+  if ((wc & 3) == 0 && tasks <= 512 && nq == 4 && (size_t)R * rowlen < 65536) {
     long long nb = (long long)B * Ho, cap = (long long)device_sm_count() * (2048 / threads);
     if (nb > cap) nb = cap;
-    quantize_im2col_i8_fixed_kernel<<<(unsigned)nb, threads, smem, st>>>(
-        images, reinterpret_cast<uint8_t*>(out_i8), B, H, W, C, R, stride, bits, Ho, Wo, kp, rowlen, lpad, make_quant_steps(bits));
+    auto kern = tpt == 1 ? (nq == 4 ? quantize_im2col_i8_fixed_kernel<1, 4> : quantize_im2col_i8_fixed_kernel<1, 8>)
+                         : (nq == 4 ? quantize_im2col_i8_fixed_kernel<2, 4> : quantize_im2col_i8_fixed_kernel<2, 8>);
+    kern<<<(unsigned)nb, threads, smem, st>>>(images, reinterpret_cast<uint8_t*>(out_i8), B, H, W, C, R, stride, bits, Ho, Wo,
+                                              kp, rowlen, lpad, make_quant_steps(bits));
   } else {
     long long nb = (long long)B * Ho, cap = (long long)device_sm_count() * 8;
     if (nb > cap) nb = cap;
