@@ -377,3 +377,32 @@ def test_tcgen05_wider_pairs_conv(cuda_device, wb, xb):
     rng = np.random.default_rng(wb + xb)
     X, Wt = make_conv(rng, 2, 10, 12, 128, 64, 3, wb, xb)
     assert np.array_equal(to_host(run_tc5_conv(Wt, X), np.int32), oracle.conv_popc(Wt, X, threads=4))
+
+
+@pytest.mark.parametrize("R,ring", [(1, 1), (3, 2), (1, 3)])
+def test_tcgen05_flat_conv_with_wider_input_ring(cuda_device, R, ring):
+    """The stored ring of the input may be wider than the filter needs (a 1x1 convolution reading a map
+    whose other consumer is a 3x3 one): in_halo tells the kernel, which offsets its reads."""
+    import ctypes
+    import apnn_tc_b200 as ap
+    from apnn_tc_b200 import _cabi
+    rng = np.random.default_rng(R * 10 + ring)
+    B, H, Wd, CIN, COUT = 3, 10, 14, 128, 96
+    pad = (R - 1) // 2
+    xl = np.zeros((B, H + 2 * ring, Wd + 2 * ring, CIN), dtype=np.uint32)
+    xl[:, ring:ring + H, ring:ring + Wd] = rng.integers(0, 4, size=(B, H, Wd, CIN), dtype=np.uint32)
+    wl = rng.integers(0, 2, size=(COUT, R, R, CIN), dtype=np.uint32)
+    # oracle on the exactly-padded image
+    xe = xl[:, ring - pad:ring + H + pad, ring - pad:ring + Wd + pad]
+    X, Wt = oracle.pack_levels(np.ascontiguousarray(xe), 2), oracle.pack_levels(wl, 1)
+    want = oracle.signed_correct(oracle.conv_popc(Wt, X, threads=4), oracle.conv_window_sums(X, R), 0)
+    x8 = ap.expand_planes(to_dev(oracle.pack_levels(xl, 2)).reshape(2, -1, CIN // 32))
+    w8 = ap.expand_planes(to_dev(Wt).reshape(1, COUT, -1), signed=True)
+    out = torch.zeros((B, H, Wd, COUT), dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    epi = ap.make_epilogue("int32", in_halo=ring)
+    _cabi.check(_cabi.lib().apnn_conv2d_i8(torch.cuda.current_stream().cuda_stream, w8.data_ptr(), x8.data_ptr(),
+                                           out.data_ptr(), B, H, Wd, CIN, COUT, R, 1, 1, ctypes.byref(epi), flag.data_ptr()),
+                "conv")
+    assert int(flag.item()) == 0
+    assert np.array_equal(out.cpu().numpy(), want)
