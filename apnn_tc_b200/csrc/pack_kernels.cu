@@ -492,6 +492,54 @@ __global__ void __launch_bounds__(256) maxpool2x2_i8_kernel(const uint8_t* __res
   }
 }
 
+// int32 values [rows][N] -> levels (low bits, or count of per-channel thresholds reached) ->
+// packed planes [bits][rows][N/32] or int8 rows [rows][N] in the operand byte order.
+// A warp owns one 32-column group and walks rows: a lane keeps its column's thresholds in
+// registers, loads are 128 contiguous bytes per row, planes are packed by ballot.
+__global__ void __launch_bounds__(256) requantize_i32_kernel(const int32_t* __restrict__ acc, void* __restrict__ out,
+                                                             long long rows, int N, int out_mode, int out_bits,
+                                                             const int32_t* __restrict__ thresholds, int out_i8) {
+  const int groups = N >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t nl = (1u << out_bits) - 1u;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int row_lanes = warps / groups > 0 ? warps / groups : 1;   // warps that share a column group, striding rows
+  const int pos = 4 * ((31 - lane) & 7) + ((31 - lane) >> 3);      // byte of element `lane` in the operand order
+  const int g = warp % groups, r0 = warp / groups;
+  if (r0 >= row_lanes) return;   // surplus warps of the last block (the whole warp leaves together)
+  {
+    int32_t thr[7];
+#pragma unroll
+    for (int k = 0; k < 7; k++)
+      thr[k] = (out_mode == APNN_OUT_THRESHOLDS && (uint32_t)k < nl && nl <= 7) ? __ldg(thresholds + (long long)(g * 32 + lane) * nl + k)
+                                                                               : 0x7fffffff;
+    for (long long row = r0; row < rows; row += row_lanes) {
+      const int x = __ldg(acc + row * N + g * 32 + lane);
+      uint32_t lv;
+      if (out_mode != APNN_OUT_THRESHOLDS) {
+        lv = (uint32_t)x & nl;
+      } else if (nl <= 7) {
+        lv = 0;
+#pragma unroll
+        for (int k = 0; k < 7; k++) lv += x >= thr[k] ? 1u : 0u;
+      } else {
+        lv = 0;
+        const int32_t* T = thresholds + (long long)(g * 32 + lane) * nl;
+        for (uint32_t k = 0; k < nl; k++) lv += x >= __ldg(T + k) ? 1u : 0u;
+      }
+      if (out_i8) {
+        reinterpret_cast<uint8_t*>(out)[row * N + g * 32 + pos] = (uint8_t)lv;
+      } else {
+        for (int b = 0; b < out_bits; b++) {
+          const uint32_t word = __brev(__ballot_sync(0xffffffffu, (lv >> b) & 1u));
+          if (lane == 0) reinterpret_cast<uint32_t*>(out)[(long long)b * rows * groups + row * groups + g] = word;
+        }
+      }
+    }
+  }
+}
+
 }  // namespace apnn
 
 extern "C" {
@@ -592,6 +640,32 @@ apnn_status apnn_maxpool2x2_i8(void* stream, const void* in_i8, void* out_i8, in
       reinterpret_cast<const uint8_t*>(in_i8), reinterpret_cast<uint8_t*>(out_i8), B, H / 2, W / 2, C, in_halo, out_halo);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "maxpool2x2_i8 launch");
+  return APNN_OK;
+}
+
+apnn_status apnn_requantize_i32(void* stream, const int32_t* values, void* out, long rows, int N, const apnn_epilogue* epi) {
+  using namespace apnn;
+  if (!values || !out || !epi || rows <= 0 || N <= 0) return APNN_ERR_INVALID_ARG;
+  if (epi->out_mode != APNN_OUT_LOWBITS && epi->out_mode != APNN_OUT_THRESHOLDS) return APNN_ERR_INVALID_ARG;
+  if (epi->out_bits < 1 || epi->out_bits > 8 || (epi->out_mode == APNN_OUT_THRESHOLDS && !epi->thresholds))
+    return APNN_ERR_INVALID_ARG;
+  if (epi->pool != APNN_POOL_NONE || epi->residual_in || epi->residual_out || epi->signed_operand != APNN_SIGN_NONE ||
+      epi->n_peer_out != 0)
+    return APNN_ERR_UNSUPPORTED;
+  if (N % 32 != 0) return APNN_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(values) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) return APNN_ERR_ALIGNMENT;
+  // every column group gets the same number of warps; more of them when there are many rows
+  const int groups = N / 32;
+  long long per_group = (rows + 63) / 64;
+  const long long cap = (long long)device_sm_count() * 64 / groups;
+  if (per_group > cap) per_group = cap;
+  if (per_group < 1) per_group = 1;
+  const long long warps = per_group * groups;
+  const unsigned nb = (unsigned)((warps + 7) / 8);
+  requantize_i32_kernel<<<nb, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      values, out, rows, N, epi->out_mode, epi->out_bits, epi->thresholds, epi->out_i8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "requantize_i32 launch");
   return APNN_OK;
 }
 

@@ -151,6 +151,8 @@ struct Tc5Params {
   // shared-memory plan (chosen on the host)
   int stages;            // ring depth
   int kgroup;            // K blocks per stage (one barrier round trip and one commit per group)
+  int splits, kper;      // split-K instantiation only (GEMM, int32 output): `splits` CTAs share a tile, each sums
+                         // kper K blocks and adds its part to the zeroed output with atomic adds
   int b_resident;        // 1: the whole B operand (one tile column, all K blocks) stays in shared
                          // memory for the life of the CTA and the ring carries A tiles only
   // flat convolution (is_conv == 2): stride 1, no pooling.  Output positions are the flattened
@@ -301,7 +303,7 @@ __device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a
   return true;
 }
 
-template <int BN, int BKB>
+template <int BN, int BKB, bool SPLITK = false>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Tc5Params p) {
@@ -366,7 +368,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int mn_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = SPLITK ? mn_tiles * p.splits : mn_tiles;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -414,7 +417,15 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       } else
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        int kb0 = 0, kb1 = p.kblocks;
+        if constexpr (SPLITK) {
+          const int split = tile / mn_tiles;
+          tile_coords(tile - split * mn_tiles, p.tiles_m, p.tiles_n, tm, tn);
+          kb0 = split * p.kper;
+          kb1 = min(p.kblocks, kb0 + p.kper);
+        } else {
+          tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        }
         int w0 = 0, h0 = 0, b0 = 0;
         if (p.is_conv) {
           w0 = (tm % p.tiles_w) * p.bw;
@@ -424,7 +435,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         int ti = 0, tj = 0, cb = 0;  // conv: K block = (filter tap row, tap column, BKB-channel block)
         const int wbase = w0 * p.stride + p.in_off, hbase = h0 * p.stride + p.in_off;
-        for (int kb = 0; kb < p.kblocks; kb += kgroup) {
+        for (int kb = kb0; kb < kb1; kb += kgroup) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
           const uint32_t sa = ring + (uint32_t)s * stage_bytes;
           const uint32_t sb = sa + (uint32_t)kgroup * A_STAGE_BYTES;
@@ -528,7 +539,12 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.kblocks; kb += kgroup) {
+        int kb0 = 0, kb1 = p.kblocks;
+        if constexpr (SPLITK) {
+          kb0 = (tile / mn_tiles) * p.kper;
+          kb1 = min(p.kblocks, kb0 + p.kper);
+        }
+        for (int kb = kb0; kb < kb1; kb += kgroup) {
           if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = ring + (uint32_t)s * stage_bytes;
@@ -536,9 +552,9 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t b0addr = p.b_resident ? base + (uint32_t)kb * B_STAGE_BYTES : sb;
           // unrolled per group size: this thread's instruction stream is on the critical path
           switch (kgroup) {
-            case 1: issue_group<BN, BKB, 1>(d_tmem, sa, b0addr, p.idesc, kb != 0); break;
-            case 2: issue_group<BN, BKB, 2>(d_tmem, sa, b0addr, p.idesc, kb != 0); break;
-            default: issue_group<BN, BKB, 3>(d_tmem, sa, b0addr, p.idesc, kb != 0); break;
+            case 1: issue_group<BN, BKB, 1>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
+            case 2: issue_group<BN, BKB, 2>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
+            default: issue_group<BN, BKB, 3>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
           }
           tc_commit(empty_bar(s));  // frees the stage when these MMAs have read it
           if (++s == stages) { s = 0; ph ^= 1u; }
@@ -573,7 +589,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int thr_tn = -1;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(SPLITK ? tile % mn_tiles : tile, p.tiles_m, p.tiles_n, tm, tn);
       const uint32_t acc = tl & 1u;
       const uint32_t aph = (tl >> 1) & 1u;
       if (thr_staged && tn != thr_tn) {
@@ -738,7 +754,15 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               }
           }
         }
-        if (p.out_mode == OUT_INT32) {
+        if (SPLITK) {
+          // split-K (int32 output only): this CTA's part of the sum goes into the zeroed output
+          if (row_ok) {
+            int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < p.N) atomicAdd(D + j, (int32_t)v[j]);
+          }
+        } else if (p.out_mode == OUT_INT32) {
           if (whole) {
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
@@ -1064,6 +1088,34 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
   p.idesc = make_idesc(a_signed, b_signed, bn);
   long long tiles = (long long)p.tiles_m * p.tiles_n;
+  if (bn == 128 && p.out_mode == APNN_OUT_INT32 && !p.residual_in && !p.residual_out && tiles * 8 <= sms &&
+      p.kblocks >= 32) {
+    // a handful of tiles with a long K (the first fully connected layer of a network at a small
+    // batch): split K over the idle SMs; the parts meet in the zeroed output through atomic adds.
+    // With 32 tiles or more the atomics cost more than the idle SMs gain (measured on AlexNet's
+    // 9216 -> 4096 layer at batch 128).
+    int splits = (int)(sms / tiles);
+    if (splits > p.kblocks / 8) splits = p.kblocks / 8;
+    p.kper = (p.kblocks + splits - 1) / splits;
+    p.splits = (p.kblocks + p.kper - 1) / p.kper;
+    e = cudaMemsetAsync(D, 0, (size_t)M * N * sizeof(int32_t), s);
+    if (e != cudaSuccess) return cuda_fail(e, "split-K output reset");
+    tiles *= p.splits;
+    static bool attr_set[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 16 || !attr_set[dev]) {
+      e = cudaFuncSetAttribute(tc5_gemm_kernel<128, 128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+      if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm attribute");
+      if (dev < 16) attr_set[dev] = true;
+    }
+    int smem = 0;
+    plan_smem<128, 128>(p, &smem);
+    tc5_gemm_kernel<128, 128, true><<<(int)(tiles < sms ? tiles : sms), THREADS, smem, s>>>(map_a, map_b, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm split-K launch");
+    return APNN_OK;
+  }
   int grid = (int)(tiles < sms ? tiles : sms);
   e = launch_tc5_any(s, map_a, map_b, p, grid, bn, 128);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm launch");

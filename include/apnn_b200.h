@@ -217,6 +217,16 @@ apnn_status apnn_conv2d_i8(void *stream, const void *W8, const void *X8, void *O
                            int CIN, int COUT, int R, int stride, int w_signed,
                            const apnn_epilogue *epi, int *status_flag);
 
+/* The quantising part of the epilogue on its own: int32 values[rows][N] -> levels (out_mode
+ * APNN_OUT_LOWBITS or APNN_OUT_THRESHOLDS with epi->thresholds [N][2^out_bits - 1]) -> packed
+ * planes [out_bits][rows][N/32], or int8 rows [rows][N] when epi->out_i8 is set.  It follows a
+ * GEMM whose int32 result was produced by split-K (apnn_gemm_i8 splits K over idle SMs when a
+ * problem has few tiles and a long K, which needs the int32 output).  N % 32 == 0; pooling,
+ * residuals and sign correction are not taken here.  Semantics of `val & 3` / thresholds as in
+ * the fused epilogue (LIB/66_bmmaTensorCoreGemm.cuh:263-268). */
+apnn_status apnn_requantize_i32(void *stream, const int32_t *values, void *out, long rows, int N,
+                                const apnn_epilogue *epi);
+
 /* 2x2 maximum over int8 rows (levels as apnn_conv2d_i8 writes them with out_i8): in
  * [B][H+2*in_halo][W+2*in_halo][C] -> out [B][H/2+2*out_halo][W/2+2*out_halo][C], ring untouched.
  * For threshold outputs with ascending thresholds the maximum of the levels is the level of the

@@ -332,3 +332,40 @@ def test_tcgen05_wider_pairs(cuda_device, wb, xb):
     assert np.array_equal(to_host(ap.apmm(to_dev(W), to_dev(X), algo="auto", workspace=ws), np.int32), want)
     with pytest.raises(ap.ApnnError):
         ap.apmm(to_dev(W), to_dev(X), algo="imma")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 512, 25088), (200, 256, 4096), (64, 128, 8192)])
+def test_tcgen05_split_k_and_requantize(cuda_device, M, N, K):
+    """Few tiles, long K: apnn_gemm_i8 splits K over the SMs (atomic adds into the zeroed int32
+    output); apnn_requantize_i32 then applies the thresholds."""
+    import ctypes
+    import apnn_tc_b200 as ap
+    from apnn_tc_b200 import _cabi
+    from gpu_util import spread_bytes
+    rng = np.random.default_rng(M + N + K)
+    W, wl = oracle.value_planes(rng, M, K, 2)
+    X, xl = oracle.value_planes(rng, N, K, 1)
+    want = (wl.astype(np.int64) @ (2 * xl.astype(np.int64) - 1).T).astype(np.int32)     # +-1 second operand
+    a8 = ap.expand_planes(to_dev(W))
+    b8 = ap.expand_planes(to_dev(X), signed=True)
+    D = torch.full((M, N), 12345, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    epi = ap.make_epilogue("int32")
+    _cabi.check(_cabi.lib().apnn_gemm_i8(s, a8.data_ptr(), b8.data_ptr(), D.data_ptr(), M, N, K, 0, 1, ctypes.byref(epi),
+                                         flag.data_ptr()), "gemm_i8")
+    assert int(flag.item()) == 0
+    assert np.array_equal(D.cpu().numpy(), want)
+    T = oracle.fold_bn(np.ones(N, np.float32), np.zeros(N, np.float32), float(want.mean()), float(want.std()) / 4, 2)
+    q = ap.make_epilogue("thresholds", 2, thresholds=to_dev(T), out_i8=True)
+    out8 = torch.zeros((M, N), dtype=torch.uint8, device="cuda")
+    _cabi.check(_cabi.lib().apnn_requantize_i32(s, D.data_ptr(), out8.data_ptr(), M, N, ctypes.byref(q)), "requantize")
+    assert np.array_equal(out8.cpu().numpy(), spread_bytes(oracle.levels(want, 2, 2, T).astype(np.uint8)))
+    q2 = ap.make_epilogue("thresholds", 2, thresholds=to_dev(T))
+    outp = torch.zeros((2, M, N // 32), dtype=torch.int32, device="cuda")
+    _cabi.check(_cabi.lib().apnn_requantize_i32(s, D.data_ptr(), outp.data_ptr(), M, N, ctypes.byref(q2)), "requantize")
+    assert np.array_equal(to_host(outp), oracle.requant_pack(want, 2, 2, T))
+    q3 = ap.make_epilogue("lowbits", 3)
+    outl = torch.zeros((3, M, N // 32), dtype=torch.int32, device="cuda")
+    _cabi.check(_cabi.lib().apnn_requantize_i32(s, D.data_ptr(), outl.data_ptr(), M, N, ctypes.byref(q3)), "requantize")
+    assert np.array_equal(to_host(outl), oracle.requant_pack(want, 3, 1))
