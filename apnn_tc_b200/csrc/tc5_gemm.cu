@@ -303,7 +303,14 @@ __device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a
   return true;
 }
 
-template <int BN, int BKB, bool SPLITK = false>
+// EPI selects an epilogue compiled for one family of uses (the code of the other paths is
+// compiled out; these warps are bound by instruction fetch and issue, so the smaller bodies
+// are measurably faster):
+//   0  everything decided at run time
+//   1  quantise only (thresholds or low bits; packed planes or int8 rows): no pooling, residuals or int32 output
+//   2  thresholds of at most 2 bits -> int8 rows, nothing else (hidden layers of the networks)
+//   3  as 2 plus residual in / out of either width (second convolution of a ResNet block)
+template <int BN, int BKB, bool SPLITK = false, int EPI = 0>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Tc5Params p) {
@@ -565,6 +572,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else {
     // ---------------- epilogue warps (2..9) ----------------
+    constexpr bool C_NOPOOL = EPI >= 1, C_NORES = EPI == 1 || EPI == 2, C_NOINT32 = EPI >= 1, C_I8THR = EPI >= 2;
     const int ew = warp - 2;
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
     const int half = ew >> 2;      // this warp drains the tile's 32-column chunks half, half+2, ...
@@ -574,7 +582,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // thresholds of up to 2-bit outputs are staged per chunk in this warp's shared-memory
     // slice, one int4 per column (unused slots = INT_MAX), so a value costs one broadcast
     // 16-byte load instead of nl global loads
-    const bool thr_staged = p.out_mode == OUT_THRESHOLDS && nl <= 3;
+    const bool thr_staged = C_I8THR || (p.out_mode == OUT_THRESHOLDS && nl <= 3);
     int4* thr_s = reinterpret_cast<int4*>(epi_smem + ew * Cfg::THR_BYTES_PER_WARP);
     // 32 rows x 16 words, 16-byte groups XOR-swizzled by (row >> 1): both the row-per-lane
     // accesses and the 4-lanes-per-row accesses below are free of bank conflicts
@@ -611,13 +619,15 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const long long row = dst.row;
       const bool row_ok = dst.valid;
       // destinations of the rows this lane serves in the coalesced (4 lanes per row) accesses
-      long long row_of[4], dense_of[4];
-      bool ok_of[4];
+      long long row_of[4] = {0, 0, 0, 0}, dense_of[4] = {0, 0, 0, 0};
+      bool ok_of[4] = {false, false, false, false};
+      if constexpr (!(C_NORES && C_NOINT32)) {
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        row_of[i] = __shfl_sync(0xffffffffu, dst.row, 8 * i + sub_r);
-        dense_of[i] = __shfl_sync(0xffffffffu, dst.dense, 8 * i + sub_r);
-        ok_of[i] = __shfl_sync(0xffffffffu, (int)dst.valid, 8 * i + sub_r) != 0;
+        for (int i = 0; i < 4; i++) {
+          row_of[i] = __shfl_sync(0xffffffffu, dst.row, 8 * i + sub_r);
+          dense_of[i] = __shfl_sync(0xffffffffu, dst.dense, 8 * i + sub_r);
+          ok_of[i] = __shfl_sync(0xffffffffu, (int)dst.valid, 8 * i + sub_r) != 0;
+        }
       }
       // residual rows of the chunk about to be processed, fetched ahead of their use (for the
       // first chunk of a tile: before the wait for the accumulator) as 64-byte row segments
@@ -645,7 +655,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                   __ldg(reinterpret_cast<const uint4*>(p.residual_in + dense_of[i] * p.N + col0 + 16 * hf + 4 * grp));
           }
       };
-      fetch_residual(half);
+      if constexpr (!C_NORES) fetch_residual(half);
       if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -661,7 +671,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           __syncwarp();
         }
         tmem_ld_wait();
-        if (p.pool != POOL_NONE) {
+        if (!C_NOPOOL && p.pool != POOL_NONE) {
           // the four pixels of a window are lanes l, l^1 (next column) and l^bw, l^bw^1 (next row)
 #pragma unroll
           for (int j = 0; j < 32; j++) {
@@ -673,7 +683,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
         const bool whole = vec_rows && col0 + 32 <= p.N;   // uniform: 16-byte accesses cover the chunk
-        if (p.residual_in != nullptr || p.residual_out != nullptr) {
+        if (!C_NORES && (p.residual_in != nullptr || p.residual_out != nullptr)) {
           if (whole) {
             // int32 rows move through the transposition block so that global accesses are
             // 64 contiguous bytes per row, 8 rows per instruction
@@ -762,7 +772,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int j = 0; j < 32; j++)
               if (col0 + j < p.N) atomicAdd(D + j, (int32_t)v[j]);
           }
-        } else if (p.out_mode == OUT_INT32) {
+        } else if (!C_NOINT32 && p.out_mode == OUT_INT32) {
           if (whole) {
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
@@ -788,10 +798,10 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         } else if (row_ok) {
           // packed modes need N % 32 == 0, so this word is whole
           uint32_t lv[32];
-          if (p.out_mode == OUT_LOWBITS) {
+          if (!C_I8THR && p.out_mode == OUT_LOWBITS) {
 #pragma unroll
             for (int j = 0; j < 32; j++) lv[j] = v[j] & (uint32_t)nl;
-          } else if (thr_staged) {
+          } else if (C_I8THR || thr_staged) {
 #pragma unroll
             for (int j = 0; j < 32; j++) {
               const int4 q4 = thr_s[j];
@@ -807,7 +817,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               lv[j] = l;
             }
           }
-          if (p.out_i8) {
+          if (C_I8THR || p.out_i8) {
             // the next layer's int8 operand: element j of this 32-column group at byte
             // 4*((31-j)&7) + ((31-j)>>3), the order apnn_expand_planes writes
             uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
@@ -819,6 +829,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                          : "memory");
             continue;
           }
+          if constexpr (C_I8THR) continue;   // (not reached: int8 rows left above)
           uint32_t* O = reinterpret_cast<uint32_t*>(p.out);
           for (int b = 0; b < p.out_bits; b++) {
             uint32_t part[4] = {0u, 0u, 0u, 0u};   // four independent chains instead of one of 32 ORs
@@ -967,6 +978,23 @@ cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorM
   int smem = 0;
   if (p.is_conv == 2) plan_flat<BN, BKB>(p, &smem);
   else plan_smem<BN, BKB>(p, &smem);
+  const bool quantising = p.out_mode != APNN_OUT_INT32 && p.pool == APNN_POOL_NONE;
+  const bool residuals = p.residual_in || p.residual_out;
+  const bool thr_i8 = p.out_mode == APNN_OUT_THRESHOLDS && p.out_bits <= 2 && p.out_i8;
+  const int epi = !quantising ? 0 : (thr_i8 ? (residuals ? 3 : 2) : (residuals ? 0 : 1));
+  auto launch = [&](auto kernel, bool* attr_done) -> cudaError_t {
+    if (dev >= 16 || !attr_done[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+      if (e != cudaSuccess) return e;
+      if (dev < 16) attr_done[dev] = true;
+    }
+    kernel<<<grid, THREADS, smem, s>>>(map_a, map_b, p);
+    return cudaGetLastError();
+  };
+  static bool done1[16] = {}, done2[16] = {}, done3[16] = {};
+  if (epi == 1) return launch(tc5_gemm_kernel<BN, BKB, false, 1>, done1);
+  if (epi == 2) return launch(tc5_gemm_kernel<BN, BKB, false, 2>, done2);
+  if (epi == 3) return launch(tc5_gemm_kernel<BN, BKB, false, 3>, done3);
   tc5_gemm_kernel<BN, BKB><<<grid, THREADS, smem, s>>>(map_a, map_b, p);
   return cudaGetLastError();
 }
@@ -1105,13 +1133,13 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 16 || !attr_set[dev]) {
-      e = cudaFuncSetAttribute(tc5_gemm_kernel<128, 128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+      e = cudaFuncSetAttribute(tc5_gemm_kernel<128, 128, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
       if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm attribute");
       if (dev < 16) attr_set[dev] = true;
     }
     int smem = 0;
     plan_smem<128, 128>(p, &smem);
-    tc5_gemm_kernel<128, 128, true><<<(int)(tiles < sms ? tiles : sms), THREADS, smem, s>>>(map_a, map_b, p);
+    tc5_gemm_kernel<128, 128, true, 0><<<(int)(tiles < sms ? tiles : sms), THREADS, smem, s>>>(map_a, map_b, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm split-K launch");
     return APNN_OK;
