@@ -310,6 +310,8 @@ __device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a
 //   1  quantise only (thresholds or low bits; packed planes or int8 rows): no pooling, residuals or int32 output
 //   2  thresholds of at most 2 bits -> int8 rows, nothing else (hidden layers of the networks)
 //   3  as 2 plus residual in / out of either width (second convolution of a ResNet block)
+//   4  as 3 with every residual tensor present being int16 (no int32 residual code)
+//   5  int32 output only (shortcut convolutions, logits)
 template <int BN, int BKB, bool SPLITK = false, int EPI = 0>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -572,7 +574,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else {
     // ---------------- epilogue warps (2..9) ----------------
-    constexpr bool C_NOPOOL = EPI >= 1, C_NORES = EPI == 1 || EPI == 2, C_NOINT32 = EPI >= 1, C_I8THR = EPI >= 2;
+    constexpr bool C_NOPOOL = EPI >= 1, C_NORES = EPI == 1 || EPI == 2 || EPI == 5, C_NOINT32 = EPI >= 1 && EPI <= 4;
+    constexpr bool C_I8THR = EPI >= 2 && EPI <= 4, C_RES16 = EPI == 4, C_INT32 = EPI == 5;
     const int ew = warp - 2;
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
     const int half = ew >> 2;      // this warp drains the tile's 32-column chunks half, half+2, ...
@@ -582,7 +585,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // thresholds of up to 2-bit outputs are staged per chunk in this warp's shared-memory
     // slice, one int4 per column (unused slots = INT_MAX), so a value costs one broadcast
     // 16-byte load instead of nl global loads
-    const bool thr_staged = C_I8THR || (p.out_mode == OUT_THRESHOLDS && nl <= 3);
+    const bool thr_staged = C_I8THR || (!C_INT32 && p.out_mode == OUT_THRESHOLDS && nl <= 3);
     int4* thr_s = reinterpret_cast<int4*>(epi_smem + ew * Cfg::THR_BYTES_PER_WARP);
     // 32 rows x 16 words, 16-byte groups XOR-swizzled by (row >> 1): both the row-per-lane
     // accesses and the 4-lanes-per-row accesses below are free of bank conflicts
@@ -635,7 +638,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       auto fetch_residual = [&](int c) {
         const int col0 = tn * BN + c * 32;
         if (p.residual_in == nullptr || !vec_rows || col0 + 32 > p.N) return;
-        if (p.res16_in) {
+        if (C_RES16 || p.res16_in) {
           // int16 rows: 64 bytes per row and chunk, 8 values per lane and load
           const int16_t* R16 = reinterpret_cast<const int16_t*>(p.residual_in);
 #pragma unroll
@@ -645,15 +648,17 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
           return;
         }
+        if constexpr (!C_RES16) {
 #pragma unroll
-        for (int hf = 0; hf < 2; hf++)
+          for (int hf = 0; hf < 2; hf++)
 #pragma unroll
-          for (int i = 0; i < 4; i++) {
-            rin[4 * hf + i] = make_uint4(0u, 0u, 0u, 0u);
-            if (ok_of[i])
-              rin[4 * hf + i] =
-                  __ldg(reinterpret_cast<const uint4*>(p.residual_in + dense_of[i] * p.N + col0 + 16 * hf + 4 * grp));
-          }
+            for (int i = 0; i < 4; i++) {
+              rin[4 * hf + i] = make_uint4(0u, 0u, 0u, 0u);
+              if (ok_of[i])
+                rin[4 * hf + i] =
+                    __ldg(reinterpret_cast<const uint4*>(p.residual_in + dense_of[i] * p.N + col0 + 16 * hf + 4 * grp));
+            }
+        }
       };
       if constexpr (!C_NORES) fetch_residual(half);
       if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
@@ -690,7 +695,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             auto lo16 = [](uint32_t w) { return (uint32_t)(int)(short)(w & 0xffffu); };
             auto hi16 = [](uint32_t w) { return (uint32_t)((int)w >> 16); };
             auto sat16 = [](uint32_t x) { return (uint32_t)min(max((int)x, -32768), 32767) & 0xffffu; };
-            if (p.residual_in != nullptr && p.res16_in) {
+            if (p.residual_in != nullptr && (C_RES16 || p.res16_in)) {
 #pragma unroll
               for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(xp + swz(8 * i + sub_r, grp)) = rin[i];
               __syncwarp();
@@ -702,7 +707,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               }
               __syncwarp();
               if (c + 2 < BN / 32) fetch_residual(c + 2);
-            } else if (p.residual_in != nullptr) {
+            } else if (!C_RES16 && p.residual_in != nullptr) {
 #pragma unroll
               for (int hf = 0; hf < 2; hf++) {
 #pragma unroll
@@ -718,7 +723,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               }
               if (c + 2 < BN / 32) fetch_residual(c + 2);   // the next chunk's rows, in flight during this one's tail
             }
-            if (p.residual_out != nullptr && p.res16_out) {
+            if (p.residual_out != nullptr && (C_RES16 || p.res16_out)) {
               int16_t* O16 = reinterpret_cast<int16_t*>(p.residual_out);
 #pragma unroll
               for (int j = 0; j < 4; j++)
@@ -732,7 +737,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (ok_of[i]) *reinterpret_cast<uint4*>(O16 + dense_of[i] * p.N + col0 + 8 * grp) = x;
               }
               __syncwarp();
-            } else if (p.residual_out != nullptr) {
+            } else if (!C_RES16 && p.residual_out != nullptr) {
 #pragma unroll
               for (int hf = 0; hf < 2; hf++) {
 #pragma unroll
@@ -772,7 +777,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int j = 0; j < 32; j++)
               if (col0 + j < p.N) atomicAdd(D + j, (int32_t)v[j]);
           }
-        } else if (!C_NOINT32 && p.out_mode == OUT_INT32) {
+        } else if (C_INT32 || (!C_NOINT32 && p.out_mode == OUT_INT32)) {
           if (whole) {
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
@@ -795,7 +800,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int j = 0; j < 32; j++)
               if (col0 + j < p.N) D[j] = (int32_t)v[j];
           }
-        } else if (row_ok) {
+        } else if (!C_INT32 && row_ok) {
           // packed modes need N % 32 == 0, so this word is whole
           uint32_t lv[32];
           if (!C_I8THR && p.out_mode == OUT_LOWBITS) {
@@ -981,7 +986,9 @@ cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorM
   const bool quantising = p.out_mode != APNN_OUT_INT32 && p.pool == APNN_POOL_NONE;
   const bool residuals = p.residual_in || p.residual_out;
   const bool thr_i8 = p.out_mode == APNN_OUT_THRESHOLDS && p.out_bits <= 2 && p.out_i8;
-  const int epi = !quantising ? 0 : (thr_i8 ? (residuals ? 3 : 2) : (residuals ? 0 : 1));
+  const bool all16 = (!p.residual_in || p.res16_in) && (!p.residual_out || p.res16_out);
+  const bool int32_only = p.out_mode == APNN_OUT_INT32 && p.pool == APNN_POOL_NONE && !residuals;
+  const int epi = int32_only ? 5 : !quantising ? 0 : (thr_i8 ? (residuals ? (all16 ? 4 : 3) : 2) : (residuals ? 0 : 1));
   auto launch = [&](auto kernel, bool* attr_done) -> cudaError_t {
     if (dev >= 16 || !attr_done[dev]) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
@@ -991,10 +998,12 @@ cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorM
     kernel<<<grid, THREADS, smem, s>>>(map_a, map_b, p);
     return cudaGetLastError();
   };
-  static bool done1[16] = {}, done2[16] = {}, done3[16] = {};
+  static bool done1[16] = {}, done2[16] = {}, done3[16] = {}, done4[16] = {}, done5[16] = {};
   if (epi == 1) return launch(tc5_gemm_kernel<BN, BKB, false, 1>, done1);
   if (epi == 2) return launch(tc5_gemm_kernel<BN, BKB, false, 2>, done2);
   if (epi == 3) return launch(tc5_gemm_kernel<BN, BKB, false, 3>, done3);
+  if (epi == 4) return launch(tc5_gemm_kernel<BN, BKB, false, 4>, done4);
+  if (epi == 5) return launch(tc5_gemm_kernel<BN, BKB, false, 5>, done5);
   tc5_gemm_kernel<BN, BKB><<<grid, THREADS, smem, s>>>(map_a, map_b, p);
   return cudaGetLastError();
 }
