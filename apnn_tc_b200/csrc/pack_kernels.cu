@@ -28,12 +28,23 @@ struct QuantSteps {
   float first_x[7];
   int n;   // 2^bits - 1, or 0: use the arithmetic form
 };
+template <int NSTEPS>
 __device__ __forceinline__ uint32_t quantize_by_steps(float x, const QuantSteps& qs) {
   uint32_t lv = 0;
 #pragma unroll
-  for (int j = 0; j < 7; j++)
-    if (j < qs.n) lv += x >= qs.first_x[j] ? 1u : 0u;
+  for (int j = 0; j < NSTEPS; j++) lv += x >= qs.first_x[j] ? 1u : 0u;
   return lv;
+}
+// Four elements at once -> their levels in the four bytes of a word.
+__device__ __forceinline__ uint32_t quantize4_by_steps(const float4& f, const QuantSteps& qs) {
+  if (qs.n == 3)
+    return quantize_by_steps<3>(f.x, qs) | (quantize_by_steps<3>(f.y, qs) << 8) | (quantize_by_steps<3>(f.z, qs) << 16) |
+           (quantize_by_steps<3>(f.w, qs) << 24);
+  if (qs.n == 1)
+    return quantize_by_steps<1>(f.x, qs) | (quantize_by_steps<1>(f.y, qs) << 8) | (quantize_by_steps<1>(f.z, qs) << 16) |
+           (quantize_by_steps<1>(f.w, qs) << 24);
+  return quantize_by_steps<7>(f.x, qs) | (quantize_by_steps<7>(f.y, qs) << 8) | (quantize_by_steps<7>(f.z, qs) << 16) |
+         (quantize_by_steps<7>(f.w, qs) << 24);
 }
 
 template <bool FROM_FLOAT>
@@ -401,8 +412,7 @@ __global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const flo
         const float4 f = nxt[u];
         uint32_t packed;
         if (qs.n)
-          packed = quantize_by_steps(f.x, qs) | (quantize_by_steps(f.y, qs) << 8) | (quantize_by_steps(f.z, qs) << 16) |
-                   (quantize_by_steps(f.w, qs) << 24);
+          packed = quantize4_by_steps(f, qs);
         else
           packed = quantize_level(f.x, steps, maxlv) | (quantize_level(f.y, steps, maxlv) << 8) |
                    (quantize_level(f.z, steps, maxlv) << 16) | (quantize_level(f.w, steps, maxlv) << 24);
