@@ -598,9 +598,65 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     constexpr int THR_CHUNKS = BN >= 64 ? BN / 64 : 1;   // chunks per epilogue warp
     int4 thr_of[THR_CHUNKS];
     int thr_tn = -1;
+    // Row destinations of a tile: this lane's own row, and (for int32 rows and residuals) the
+    // rows it serves in the coalesced 4-lanes-per-row accesses.
+    struct TileRows {
+      int tn;
+      RowDst dst;
+      long long row_of[4], dense_of[4];
+      bool ok_of[4];
+    };
+    auto rows_of_tile = [&](int tile, TileRows& t) {
+      int tm;
+      tile_coords(SPLITK ? tile % mn_tiles : tile, p.tiles_m, p.tiles_n, tm, t.tn);
+      t.dst = row_destination(p, tm, quarter * 32 + lane, in_box);
+      if constexpr (!(C_NORES && C_NOINT32)) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          t.row_of[i] = __shfl_sync(0xffffffffu, t.dst.row, 8 * i + sub_r);
+          t.dense_of[i] = __shfl_sync(0xffffffffu, t.dst.dense, 8 * i + sub_r);
+          t.ok_of[i] = __shfl_sync(0xffffffffu, (int)t.dst.valid, 8 * i + sub_r) != 0;
+        }
+      }
+    };
+    // residual rows of a chunk, fetched ahead of their use as 64-byte row segments: the next
+    // chunk's while this one finishes, the next TILE's first chunk while this tile finishes
+    // (the wait for the accumulator is short when the epilogue is the bound, so a fetch
+    // issued at the top of a tile would expose the whole memory latency every tile)
+    uint4 rin[8];
+    auto fetch_residual = [&](const TileRows& t, int c) {
+      const int col0 = t.tn * BN + c * 32;
+      if (p.residual_in == nullptr || !vec_rows || col0 + 32 > p.N) return;
+      if (C_RES16 || p.res16_in) {
+        // int16 rows: 64 bytes per row and chunk, 8 values per lane and load
+        const int16_t* R16 = reinterpret_cast<const int16_t*>(p.residual_in);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          rin[i] = make_uint4(0u, 0u, 0u, 0u);
+          if (t.ok_of[i]) rin[i] = __ldg(reinterpret_cast<const uint4*>(R16 + t.dense_of[i] * p.N + col0 + 8 * grp));
+        }
+        return;
+      }
+      if constexpr (!C_RES16) {
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            rin[4 * hf + i] = make_uint4(0u, 0u, 0u, 0u);
+            if (t.ok_of[i])
+              rin[4 * hf + i] =
+                  __ldg(reinterpret_cast<const uint4*>(p.residual_in + t.dense_of[i] * p.N + col0 + 16 * hf + 4 * grp));
+          }
+      }
+    };
+    TileRows cur, nxt;
+    if ((int)blockIdx.x < num_tiles) {
+      rows_of_tile(blockIdx.x, cur);
+      if constexpr (!C_NORES) fetch_residual(cur, half);
+    }
+    nxt = cur;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
-      int tm, tn;
-      tile_coords(SPLITK ? tile % mn_tiles : tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int tn = cur.tn;
       const uint32_t acc = tl & 1u;
       const uint32_t aph = (tl >> 1) & 1u;
       if (thr_staged && tn != thr_tn) {
@@ -618,49 +674,18 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         thr_tn = tn;
       }
-      const RowDst dst = row_destination(p, tm, quarter * 32 + lane, in_box);
+      const RowDst dst = cur.dst;
       const long long row = dst.row;
       const bool row_ok = dst.valid;
-      // destinations of the rows this lane serves in the coalesced (4 lanes per row) accesses
-      long long row_of[4] = {0, 0, 0, 0}, dense_of[4] = {0, 0, 0, 0};
-      bool ok_of[4] = {false, false, false, false};
-      if constexpr (!(C_NORES && C_NOINT32)) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          row_of[i] = __shfl_sync(0xffffffffu, dst.row, 8 * i + sub_r);
-          dense_of[i] = __shfl_sync(0xffffffffu, dst.dense, 8 * i + sub_r);
-          ok_of[i] = __shfl_sync(0xffffffffu, (int)dst.valid, 8 * i + sub_r) != 0;
-        }
+      const long long(&row_of)[4] = cur.row_of;
+      const long long(&dense_of)[4] = cur.dense_of;
+      const bool(&ok_of)[4] = cur.ok_of;
+      const bool has_next = tile + (int)gridDim.x < num_tiles;
+      bool nxt_ready = false, nxt_fetched = false;
+      if (C_NORES && has_next) {   // no residuals: nothing to overlap, do it before the wait
+        rows_of_tile(tile + gridDim.x, nxt);
+        nxt_ready = true;
       }
-      // residual rows of the chunk about to be processed, fetched ahead of their use (for the
-      // first chunk of a tile: before the wait for the accumulator) as 64-byte row segments
-      uint4 rin[8];
-      auto fetch_residual = [&](int c) {
-        const int col0 = tn * BN + c * 32;
-        if (p.residual_in == nullptr || !vec_rows || col0 + 32 > p.N) return;
-        if (C_RES16 || p.res16_in) {
-          // int16 rows: 64 bytes per row and chunk, 8 values per lane and load
-          const int16_t* R16 = reinterpret_cast<const int16_t*>(p.residual_in);
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            rin[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (ok_of[i]) rin[i] = __ldg(reinterpret_cast<const uint4*>(R16 + dense_of[i] * p.N + col0 + 8 * grp));
-          }
-          return;
-        }
-        if constexpr (!C_RES16) {
-#pragma unroll
-          for (int hf = 0; hf < 2; hf++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-              rin[4 * hf + i] = make_uint4(0u, 0u, 0u, 0u);
-              if (ok_of[i])
-                rin[4 * hf + i] =
-                    __ldg(reinterpret_cast<const uint4*>(p.residual_in + dense_of[i] * p.N + col0 + 16 * hf + 4 * grp));
-            }
-        }
-      };
-      if constexpr (!C_NORES) fetch_residual(half);
       if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -706,7 +731,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 v[8 * j + 4] += lo16(x.z); v[8 * j + 5] += hi16(x.z); v[8 * j + 6] += lo16(x.w); v[8 * j + 7] += hi16(x.w);
               }
               __syncwarp();
-              if (c + 2 < BN / 32) fetch_residual(c + 2);
+              if (c + 2 < BN / 32) fetch_residual(cur, c + 2);
+              else if (has_next) { rows_of_tile(tile + gridDim.x, nxt); fetch_residual(nxt, half); nxt_ready = nxt_fetched = true; }
             } else if (!C_RES16 && p.residual_in != nullptr) {
 #pragma unroll
               for (int hf = 0; hf < 2; hf++) {
@@ -721,7 +747,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
                 __syncwarp();
               }
-              if (c + 2 < BN / 32) fetch_residual(c + 2);   // the next chunk's rows, in flight during this one's tail
+              if (c + 2 < BN / 32) fetch_residual(cur, c + 2);   // the next chunk's rows, in flight during this one's tail
+              else if (has_next) { rows_of_tile(tile + gridDim.x, nxt); fetch_residual(nxt, half); nxt_ready = nxt_fetched = true; }
             }
             if (p.residual_out != nullptr && (C_RES16 || p.res16_out)) {
               int16_t* O16 = reinterpret_cast<int16_t*>(p.residual_out);
@@ -847,6 +874,13 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (has_next) {
+        if (!nxt_ready) rows_of_tile(tile + gridDim.x, nxt);
+        if constexpr (!C_NORES) {
+          if (!nxt_fetched) fetch_residual(nxt, half);
+        }
+        cur = nxt;
+      }
     }
     if (!ok && lane == 0) atomicExch(p.error_flag, 3);
   }
