@@ -26,6 +26,7 @@
 // stops issuing work, and falls through to the common tear-down (TMEM is released).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "api_internal.h"
@@ -990,7 +991,7 @@ void plan_flat(Tc5Params& p, int* smem_bytes) {
     p.flat_nb = 0;
     fixed = bres;
   } else {
-    int nb = 4;
+    int nb = 10;   // filter tiles in flight: the taps of a latency-bound small problem wait on these loads
     while (nb > 2 && nb * (long long)Cfg::B_STAGE_BYTES + 2 * a_bytes > room) nb--;
     p.flat_nb = nb;
     fixed = nb * (long long)Cfg::B_STAGE_BYTES;
@@ -1285,10 +1286,18 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   // stride-1 convolutions without pooling run "flat": tiles of 128 consecutive padded pixels,
   // every tap a row-shifted view of one buffer of consecutive input rows (2-D TMA loads)
   const long long flat_rows = (long long)B * Hp * Wp;
-  // ... unless the padding ring wastes more MMA rows than the pixel boxes would (tiny images)
-  const double flat_util = (double)H * W / ((double)Hp * Wp);
-  const double box_util = (double)H * W * bb / ((double)p.tiles_h * p.tiles_w * BM);
-  const bool flat = stride == 1 && pool == APNN_POOL_NONE && flat_rows < 0x7fffff00LL && flat_util >= 0.95 * box_util;
+  // ... unless that needs more waves of tiles over the SMs than the pixel boxes would (the ring
+  // positions are computed and dropped: tiny images, or a tile count just past a multiple of the
+  // SM count).  Cost of a formulation = waves x tile width.
+  auto cost = [&](long long tiles_m) {
+    const int bn_ = pick_bn(tiles_m, COUT, sms);
+    const long long tiles = tiles_m * ((COUT + bn_ - 1) / bn_);
+    return ((tiles + sms - 1) / sms) * bn_;
+  };
+  // (with many waves a few per cent more tiles still win: a flat tile loads 5-8x fewer rows)
+  const long long cost_box = cost(p.tiles_m), cost_flat = cost((flat_rows + BM - 1) / BM);
+  const bool flat = stride == 1 && pool == APNN_POOL_NONE && flat_rows < 0x7fffff00LL &&
+                    (cost_flat <= cost_box || (cost_box >= 8 * 64 && cost_flat * 100 <= cost_box * 105));
   if (flat) {
     p.is_conv = 2;
     p.flat_wp = Wp;

@@ -105,6 +105,24 @@ def sweep_conv():
                 ws = torch.empty(ap.conv_workspace_bytes(B, H, Wd, C, C, 3), dtype=torch.uint8, device="cuda")
                 flops = 2.0 * B * H * Wd * C * 9 * C
                 byts = xb * B * 18 * 18 * C / 8 + wb * 9 * C * C / 8 + 2 * B * 256 * C / 8 + 12 * C
+                if wb == 1 and _keep(algo="tcgen05_i8"):
+                    # the layer as a network chains it: filter expanded once, activations already int8
+                    # rows (the previous layer's out_i8), so one launch per layer
+                    import ctypes
+                    from . import _cabi
+                    from .ops import _stream_ptr
+                    x8 = ap.expand_planes(X.reshape(xb, -1, C // 32))
+                    w8 = ap.expand_planes(Wt.reshape(wb, C, -1), signed=True)
+                    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+                    epi8 = ap.make_epilogue("thresholds", 2, thresholds=T)
+                    L = _cabi.lib()
+                    gus, pus = time_call(lambda: _cabi.check(L.apnn_conv2d_i8(
+                        _stream_ptr(), w8.data_ptr(), x8.data_ptr(), out.data_ptr(), B, H, Wd, C, C, 3, 1, 1,
+                        ctypes.byref(epi8), flag.data_ptr()), "conv2d_i8"))
+                    print(json.dumps({"op": "conv3x3_bn_requant2", "w": wb, "a": xb, "B": B, "HW": 16, "C": C,
+                                      "algo": "tcgen05_i8", "graph_us": round(gus, 3), "plain_us": round(pus, 3),
+                                      "tops": round(flops / gus / 1e6, 2), "algorithmic_bytes": int(byts),
+                                      "gbps": round(byts / gus / 1e3, 1)}), flush=True)
                 for algo in ("imma", "tcgen05"):
                     if not _keep(algo=algo):
                         continue
