@@ -217,6 +217,18 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
     return out
 
 
+def value_bounds(spec: ModelSpec, params: Dict[str, LayerParams]) -> Dict[str, int]:
+    """Largest magnitude the int32 value of each layer can take: (2^a - 1) * fan_in for +-1 weights and
+    a-bit activations, plus the bound of the residual it adds.  A residual tensor whose bound is at most
+    32767 can be stored as int16 without changing any result."""
+    bound: Dict[str, int] = {}
+    for ls in spec.layers:
+        sh = params[ls.name].shape
+        fan = sh["K"] if ls.kind != "conv" else ls.R * ls.R * ls.cin
+        bound[ls.name] = ((1 << spec.a_bit) - 1) * fan + (bound[ls.residual_from] if ls.residual_from else 0)
+    return bound
+
+
 # ----------------------------------------------------------------------------- device runtime
 def _dev_words(a: np.ndarray, device) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(a).view(np.int32)).to(device)
@@ -317,11 +329,7 @@ class Network:
         # residual tensors are int16 where every value provably fits: |value| <= (2^a - 1) * fan_in
         # plus the bound of the residual it adds, and producer and readers run on the tcgen05 path
         self.res16: Dict[str, bool] = {}
-        bound: Dict[str, int] = {}
-        for ls in spec.layers:
-            sh = self.params[ls.name].shape
-            fan = sh["K"] if ls.kind != "conv" else ls.R * ls.R * ls.cin
-            bound[ls.name] = ((1 << a) - 1) * fan + (bound[ls.residual_from] if ls.residual_from else 0)
+        bound = value_bounds(spec, self.params)
         for ls in spec.layers:
             if ls.name in self.res:
                 readers = [c.name for c in spec.layers if c.residual_from == ls.name]

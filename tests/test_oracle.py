@@ -167,3 +167,19 @@ def test_packers():
     lv2 = rng.integers(0, 16, size=(5, 160), dtype=np.uint32)
     assert np.array_equal(oracle.unpack_levels(oracle.bit_compress(lv2, 4))[:, :160], lv2)
     assert np.array_equal(oracle.bit_compress(lv2[:, :128], 4), oracle.pack_levels(lv2[:, :128], 4))
+
+
+def test_network_value_bounds_decide_int16_residuals():
+    """nets.value_bounds: ResNet-18 w1a2 residual values stay below 2^15 (so they may be stored as
+    int16); with 4-bit activations the deep blocks do not, and stay int32."""
+    from apnn_tc_b200 import nets
+    spec = nets.resnet18_spec(n_classes=10)
+    params = nets.make_params(spec, image_hw=32)
+    b = nets.value_bounds(spec, params)
+    assert b["Conv1"] == 3 * 7 * 7 * 3
+    assert b["L1B1C2"] == 3 * 9 * 64 + b["Conv1"]
+    assert max(v for k, v in b.items() if k.endswith("C2")) == b["L4B2C2"] == 28416
+    spec4 = nets.resnet18_spec(n_classes=10)
+    spec4.a_bit = 4
+    b4 = nets.value_bounds(spec4, nets.make_params(spec4, image_hw=32))
+    assert b4["L4B2C2"] > 32767 and b4["L1B1C2"] <= 32767
