@@ -1,29 +1,36 @@
-// tcgen05 path for large GEMMs and 3x3 / 1x1 stride-1 convolutions.
+// tcgen05 path: GEMMs and convolutions on int8 operands, one CTA per SM.
 //
-// Step 1 (expand_planes_kernel): every operand is rewritten once from bit planes to one
-// int8 per element, value = sum_p bit_p << p (or -1/+1 for a signed 1-bit operand), rows of
-// K bytes in the caller's workspace.  Within each group of 32 k the byte order is the
-// "spread" order (bit q+8j of the word -> byte 4q+j); both operands use it, so the dot
-// product is unchanged.
+// Step 1 (expand_planes_kernel): an operand is rewritten once from bit planes to one int8 per
+// element, value = sum_p bit_p << p (or -1/+1 for a signed 1-bit operand), rows of K bytes in
+// the caller's workspace.  Within each group of 32 k the byte order is the "spread" order (bit
+// q+8j of the word -> byte 4q+j); both operands use it, so the dot product is unchanged.
+// Networks skip this step: a layer's epilogue writes the next layer's int8 rows directly.
 //
-// Step 2 (tc5_gemm_kernel): persistent, warp-specialised int8 GEMM.  One CTA per SM walks
-// over 128 x 256 output tiles.  Warp 0 streams K blocks of 128 bytes per row with TMA
-// (128-byte swizzle) through a 4-stage shared-memory ring; warp 1 issues tcgen05.mma
-// kind::i8 (M=128, N=256, K=32) from shared-memory descriptors into one of two 256-column
-// TMEM accumulators; warps 2-5 drain the other accumulator with tcgen05.ld and run the
-// epilogue (int32 stores, or requantise + bit-plane pack: a thread owns one row and 32
-// consecutive columns, i.e. exactly one output word per plane).  No cluster, no multicast.
+// Step 2 (tc5_gemm_kernel<BN, BKB, SPLITK, EPI>): persistent, warp-specialised.  Warp 0 streams
+// operand tiles with TMA (swizzle span BKB = 128 or 64 bytes of K per row) through mbarrier
+// rings; warp 1 issues tcgen05.mma kind::i8 (M=128, N=BN, K=32) from shared-memory descriptors
+// into one of two BN-column TMEM accumulators; warps 2-9 drain the other with tcgen05.ld (two
+// warps per TMEM lane quarter, alternating 32-column chunks) and run the epilogue: a thread
+// owns one row and 32 consecutive columns, i.e. one output word per plane or 32 output bytes.
+// No cluster, no multicast.  What bounds it is shared-memory bandwidth (128 B/clk feed both the
+// MMA's operand reads and TMA's writes) and the instruction streams of the single producer / MMA
+// threads and of the few epilogue warps, so:
+//   * the filter stays resident in shared memory when the problem has one tile column;
+//   * narrow K blocks are grouped per barrier round trip, and all index arithmetic in the
+//     producer / MMA loops is incremental (no divisions);
+//   * the epilogue is compiled per family of uses (EPI) instead of branching at run time.
 //
-// Convolution reuses the same kernel as an implicit GEMM: the activations are expanded to
-// int8 NHWC (halo included), and the A tile of a K block is one 4-D TMA box -- 128 bytes of
-// channels x (bw x bh x bb) output pixels -- fetched at the halo offset of the filter tap,
-// which lands in shared memory as the same 128-byte-swizzled row block a GEMM tile would.
-// K runs over (tap_i, tap_j, 128-channel block), matching the filter rows' K order.  A
-// 2x2 pooling window lies inside one warp (the box is at most 16 pixels wide), so the
-// epilogue pools with three lane shuffles before requantising.
+// Convolution, stride 1 without pooling ("flat"): output positions are the flattened padded
+// pixels q = (b*Hp + h)*Wp + w, a tile is 128 consecutive q, and tap (i, j) reads input rows
+// q + i*Wp + j of the flattened int8 image -- so ONE 2-D TMA box of 128 + (R-1)*(Wp+1) rows
+// per (tile, channel block) serves every tap through descriptors whose start address is
+// shifted by whole rows (the swizzle is a function of the shared-memory address).  Positions in
+// the padding ring are computed and dropped.  Other convolutions (stride 2, fused pooling,
+// tiny images) fetch one 4-D TMA box of bw x bh x bb output pixels per tap; a 2x2 pooling
+// window then lies inside one warp and is reduced with three lane shuffles.
 //
-// Every mbarrier wait is bounded: on expiry the kernel raises a flag in global memory,
-// stops issuing work, and falls through to the common tear-down (TMEM is released).
+// Every mbarrier wait is bounded: on expiry the kernel raises a flag in global memory, stops
+// issuing work, and falls through to the common tear-down (TMEM is released).
 #include <cuda.h>
 
 #include <cstdlib>
