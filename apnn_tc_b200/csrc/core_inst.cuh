@@ -9,14 +9,14 @@ namespace apnn {
 
 // tile classes
 //   big   : 128 x 128 outputs, 8 warps (2 x 4), each warp 64 x 32
-//   small :  64 x  32 outputs, 2 warps (2 x 1), each warp 32 x 32 -- spreads tiny problems
-//            over many SMs
+//   small :  64 x  32 outputs, 2 x 1 warps of 32 x 32 times two K groups (4 warps): spreads tiny
+//            problems over many SMs and halves a warp's serial chain of K steps
 //   b1    : 128 x 64 outputs, 8 warps (4 x 2); one accumulator set per weight class, so the
 //            warp tile shrinks to 32 x 32
 template <int KIND, int AB, int BB>
 using BigCfg = CoreCfg<KIND, AB, BB, 4, 4, 2, 4, ((AB * 128 + BB * 128) * 64 * 4 <= 160 * 1024 ? 4 : 3)>;
 template <int KIND, int AB, int BB>
-using SmallCfg = CoreCfg<KIND, AB, BB, 2, 4, 2, 1, 4>;
+using SmallCfg = CoreCfg<KIND, AB, BB, 2, 4, 2, 1, 4, 2>;   // four groups measured no faster than two
 template <int AB, int BB>
 using B1Cfg = CoreCfg<KIND_B1, AB, BB, 2, 4, 4, 2, 4>;
 

@@ -22,13 +22,16 @@ namespace apnn {
 
 enum { KIND_U8 = 0, KIND_B1 = 1 };
 
-template <int KIND_, int ABITS_, int BBITS_, int MT_, int NT_, int WARPS_M_, int WARPS_N_, int STAGES_>
+// KSPLIT_ warp groups share a tile and split the K chunks of every stage between them (u8 path);
+// their partial sums meet in shared memory before the epilogue.  For latency-bound tiny
+// problems it shortens the serial chain of one warp by KSPLIT_.
+template <int KIND_, int ABITS_, int BBITS_, int MT_, int NT_, int WARPS_M_, int WARPS_N_, int STAGES_, int KSPLIT_ = 1>
 struct CoreCfg {
   static constexpr int KIND = KIND_, ABITS = ABITS_, BBITS = BBITS_, MT = MT_, NT = NT_;
-  static constexpr int WARPS_M = WARPS_M_, WARPS_N = WARPS_N_, STAGES = STAGES_;
+  static constexpr int WARPS_M = WARPS_M_, WARPS_N = WARPS_N_, STAGES = STAGES_, KSPLIT = KSPLIT_;
   static constexpr int BM = WARPS_M * MT * 16;
   static constexpr int BN = WARPS_N * NT * 8;
-  static constexpr int THREADS = WARPS_M * WARPS_N * 32;
+  static constexpr int THREADS = WARPS_M * WARPS_N * KSPLIT * 32;
   static constexpr int A_ROWS = ABITS * BM;
   static constexpr int B_ROWS = BBITS * BN;
   static constexpr int ROW_BYTES = 64;  // one stage holds 512 bits of K per row
@@ -40,6 +43,9 @@ struct CoreCfg {
   static constexpr int B_SLOTS = B_ROWS / RPP;
   static_assert(A_ROWS % RPP == 0 && B_ROWS % RPP == 0, "tile rows must divide over the copy passes");
   static_assert(NT % 4 == 0 && MT % 2 == 0, "fragments are fetched four 8-row matrices at a time");
+  static_assert(KSPLIT == 1 || (KIND == KIND_U8 && (KSPLIT == 2 || KSPLIT == 4)), "K split: u8 path, 2 or 4 groups");
+  static_assert(KSPLIT == 1 || (KSPLIT - 1) * WARPS_M * WARPS_N * 32 * (MT * NT * 4 + MT * 2 + NT) * 4 <= SMEM_BYTES,
+                "partial sums must fit the pipeline buffers");
 };
 
 // Spread bit (q + 8j) of every plane word into byte j: value = sum_p bit_p << p.
@@ -123,8 +129,11 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int warp_m = warp / Cfg::WARPS_N;
-  const int warp_n = warp % Cfg::WARPS_N;
+  constexpr int KSPLIT = Cfg::KSPLIT;
+  const int kgroup = warp / (Cfg::WARPS_M * Cfg::WARPS_N);   // which share of every stage's K chunks
+  const int wlocal = warp % (Cfg::WARPS_M * Cfg::WARPS_N);
+  const int warp_m = wlocal / Cfg::WARPS_N;
+  const int warp_n = wlocal % Cfg::WARPS_N;
   const int g = lane >> 2, t4 = lane & 3;
 
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -275,7 +284,7 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
       // one 128-bit chunk per iteration: a compact body (four k32 steps) that stays in the
       // instruction cache, executed four times per stage
 #pragma unroll 1
-      for (int c = 0; c < 4; c++) {
+      for (int c = kgroup; c < 4; c += KSPLIT) {
         uint32_t aw[ABITS][MT][2];  // [plane][m-tile][rows g / g+8]: word t4 of the chunk
         uint32_t bw[BBITS][NT];     // [plane][n-tile]: word t4 of row g
         const uint32_t a_ch = (uint32_t)((c ^ sw) << 4);
@@ -352,6 +361,50 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
   }
   cp_async_wait<0>();
 
+  if constexpr (KSPLIT > 1) {
+    // the groups' partial accumulators and popcount sums meet in the (now idle) pipeline buffers
+    constexpr int PER_THREAD = MT * NT * 4 + MT * 2 + NT;
+    int* red = reinterpret_cast<int*>(smem);
+    __syncthreads();   // every warp is done with the last stage
+    if (kgroup > 0) {
+      int* mine = red + ((kgroup - 1) * Cfg::WARPS_M * Cfg::WARPS_N * 32 + wlocal * 32 + lane);
+      constexpr int STRIDE = (KSPLIT - 1) * Cfg::WARPS_M * Cfg::WARPS_N * 32;   // element-major: conflict-free
+      int n = 0;
+#pragma unroll
+      for (int i = 0; i < MT; i++)
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+          for (int e = 0; e < 4; e++) mine[(n++) * STRIDE] = acc[0][i][j][e];
+#pragma unroll
+      for (int i = 0; i < MT; i++) { mine[(n++) * STRIDE] = sum_a[i][0]; mine[(n++) * STRIDE] = sum_a[i][1]; }
+#pragma unroll
+      for (int j = 0; j < NT; j++) mine[(n++) * STRIDE] = sum_b[j];
+      static_assert(PER_THREAD == MT * NT * 4 + MT * 2 + NT, "layout");
+    }
+    __syncthreads();
+    if (kgroup == 0) {
+      constexpr int STRIDE = (KSPLIT - 1) * Cfg::WARPS_M * Cfg::WARPS_N * 32;
+#pragma unroll
+      for (int gk = 1; gk < KSPLIT; gk++) {
+        const int* theirs = red + ((gk - 1) * Cfg::WARPS_M * Cfg::WARPS_N * 32 + wlocal * 32 + lane);
+        int n = 0;
+#pragma unroll
+        for (int i = 0; i < MT; i++)
+#pragma unroll
+          for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[0][i][j][e] += theirs[(n++) * STRIDE];
+#pragma unroll
+        for (int i = 0; i < MT; i++) { sum_a[i][0] += theirs[(n++) * STRIDE]; sum_a[i][1] += theirs[(n++) * STRIDE]; }
+#pragma unroll
+        for (int j = 0; j < NT; j++) sum_b[j] += theirs[(n++) * STRIDE];
+      }
+    }
+    __syncthreads();   // the buffers may be reused (threshold staging) once everyone has read
+  }
+  const bool writer = KSPLIT == 1 || kgroup == 0;   // the other groups only keep the barriers company
+
   // ---- epilogue -------------------------------------------------------------------
   // fold the weight classes (b1 path) into acc[0]
   if constexpr (NACC > 1) {
@@ -421,6 +474,7 @@ __global__ void __launch_bounds__(Cfg::THREADS) plane_core_kernel(const CorePara
     }
     __syncthreads();
   }
+  if (!writer) return;   // no block-wide barrier follows
 
   auto level_of = [&](int v, int col) -> uint32_t {
     if (p.out_mode == OUT_LOWBITS) return (uint32_t)v & (uint32_t)nl;
