@@ -133,6 +133,7 @@ class LayerParams:
     thresholds: Optional[np.ndarray]   # [COUTp][2^a_bit - 1] int32, or None when not quantised
     shape: Dict[str, int] = field(default_factory=dict)
     im2col_planes: Optional[np.ndarray] = None   # first layer only: [1][COUTp][PAD128(R*R*C)/32], k = (i*R+j)*C+c
+    window_planes: Optional[np.ndarray] = None   # first layer only: the same filter for apnn_quantize_window_rows_i8
 
 
 def _pack_bits_msb(bits: np.ndarray) -> np.ndarray:
@@ -141,6 +142,32 @@ def _pack_bits_msb(bits: np.ndarray) -> np.ndarray:
     by = np.packbits(bits.astype(np.uint8).reshape(*bits.shape[:-1], K // 32, 32), axis=-1, bitorder="big")
     return (by[..., 0].astype(np.uint32) << 24) | (by[..., 1].astype(np.uint32) << 16) | \
         (by[..., 2].astype(np.uint32) << 8) | by[..., 3].astype(np.uint32)
+
+
+def _window_row_planes(bits: np.ndarray, narrow: bool) -> np.ndarray:
+    """Filter bits [COUT][R][R][C] -> planes [1][COUT][kp/32] whose expansion (apnn_expand_planes) puts the
+    weight of (i, j, c) at byte i*seg + j*C + c of a row, seg = R*C rounded up to 4: the layout of the rows
+    apnn_quantize_window_rows_i8 writes.  Expansion puts packed element e of a 32-group at byte
+    4*((31-e)&7) + ((31-e)>>3), so element e takes the weight meant for that byte."""
+    cout, R, _, C = bits.shape
+    seg = (R * C + 3) // 4 * 4
+    kp = (R * seg + 63) // 64 * 64 if narrow else pad128(R * seg)
+    rows = np.zeros((cout, kp), dtype=np.uint8)
+    for i in range(R):
+        rows[:, i * seg:i * seg + R * C] = bits[:, i].reshape(cout, R * C)
+    f = 31 - np.arange(32)
+    byte_of = 4 * (f & 7) + (f >> 3)
+    packed_order = rows.reshape(cout, kp // 32, 32)[:, :, byte_of].reshape(cout, kp)
+    return np.ascontiguousarray(_pack_bits_msb(packed_order)[None])
+
+
+def window_rows_supported(W: int, C: int, R: int, stride: int, kp: int) -> bool:
+    """The shapes apnn_quantize_window_rows_i8 takes (it returns APNN_ERR_UNSUPPORTED otherwise)."""
+    pad, wc = (R - 1) // 2, W * C
+    lpad = max(8, (pad * C + 3) // 4 * 4)
+    rowlen = (lpad + wc + pad * C + 8 + 15) // 16 * 16
+    Wo = (W - 1) // stride + 1
+    return wc % 4 == 0 and R * rowlen <= 48 * 1024 and Wo * (kp // 16) <= 2048 and R * (wc // 4) <= 4096
 
 
 def fold_thresholds(scale: np.ndarray, bias: np.ndarray, mu: float, sigma: float, out_bits: int) -> np.ndarray:
@@ -173,12 +200,13 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
             bits = np.zeros((coutp, ls.R, ls.R, cinp), dtype=np.uint8)
             bits[: ls.cout, :, :, : ls.cin] = rng.integers(0, 2, size=(ls.cout, ls.R, ls.R, ls.cin), dtype=np.uint8)
             planes = _pack_bits_msb(bits)[None]
-            im2col = None
+            im2col = window = None
             if src is None:   # the same filter with the real channels only, laid out for the im2col first layer
                 kp = (ls.R * ls.R * ls.cin + 63) // 64 * 64 if narrow else pad128(ls.R * ls.R * ls.cin)
                 flat = np.zeros((coutp, kp), dtype=np.uint8)
                 flat[:, : ls.R * ls.R * ls.cin] = bits[:, :, :, : ls.cin].reshape(coutp, -1)
                 im2col = np.ascontiguousarray(_pack_bits_msb(flat)[None])
+                window = _window_row_planes(bits[:, :, :, : ls.cin], narrow)
             Ho, Wo = (H - 1) // ls.stride + 1, (W - 1) // ls.stride + 1
             if ls.pool == 2:
                 Ho, Wo = Ho // 2, Wo // 2
@@ -213,6 +241,7 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
         out[ls.name] = LayerParams(np.ascontiguousarray(planes), thr, shape)
         if ls.kind == "conv" and src is None:
             out[ls.name].im2col_planes = im2col
+            out[ls.name].window_planes = window
         prev = ls.name
     return out
 
@@ -276,6 +305,7 @@ class Network:
         self.thr: Dict[str, Optional[torch.Tensor]] = {}
         self.tc5_ok: Dict[str, bool] = {}
         self.first_im2col = None
+        self.first_window_rows = False
         x8_bytes = 0
         for ls in spec.layers:
             p = self.params[ls.name]
@@ -297,8 +327,15 @@ class Network:
                 if src is None and use_tcgen05 and pool_ok and p.im2col_planes is not None:
                     # first layer: windows gathered into channels, then a 1x1 convolution on tcgen05
                     kp = p.im2col_planes.shape[-1] * 32
+                    wkp = p.window_planes.shape[-1] * 32
+                    # whole-word gather where it covers the shape and does not widen the rows by more than a quarter
+                    self.first_window_rows = (window_rows_supported(sh["W"], self.spec.image_channels, ls.R, ls.stride, wkp)
+                                              and 4 * wkp <= 5 * kp)
+                    if self.first_window_rows:
+                        kp = wkp
                     self.first_im2col = (ls.name, Hc, Wc, kp)
-                    self.w_planes[ls.name] = _dev_words(p.im2col_planes, self.device)
+                    self.w_planes[ls.name] = _dev_words(p.window_planes if self.first_window_rows else p.im2col_planes,
+                                                        self.device)
                     x8_bytes = max(x8_bytes, B * Hc * Wc * kp)
                     ok = True
                 self.tc5_ok[ls.name] = ok
@@ -498,9 +535,10 @@ class Network:
         if self.first_im2col:
             # quantise + gather the first layer's windows straight into the int8 operand buffer
             first = self.by_name[self.first_im2col[0]]
-            _cabi.check(self.L.apnn_quantize_im2col_i8(s, images.data_ptr(), self.x8.data_ptr(), self.batch, self.hw,
-                                                       self.hw, self.spec.image_channels, first.R, first.stride, a,
-                                                       self.first_im2col[3]), "apnn_quantize_im2col_i8")
+            gather = self.L.apnn_quantize_window_rows_i8 if self.first_window_rows else self.L.apnn_quantize_im2col_i8
+            _cabi.check(gather(s, images.data_ptr(), self.x8.data_ptr(), self.batch, self.hw, self.hw,
+                               self.spec.image_channels, first.R, first.stride, a, self.first_im2col[3]),
+                        "first-layer gather")
         else:
             target = self.image_levels if h0 else self.image_planes
             _cabi.check(self.L.apnn_quantize_pack(s, images.data_ptr(), target.data_ptr(), rows,

@@ -265,6 +265,16 @@ apnn_status apnn_quantize_im2col(void *stream, const float *images, uint32_t *pl
 apnn_status apnn_quantize_im2col_i8(void *stream, const float *images, void *out_i8, int B, int H,
                                     int W, int C, int R, int stride, int bits, int kp);
 
+/* The first-layer gather as whole words: out_i8[B*Ho*Wo][kp] with an output pixel's row made of
+ * R segments of seg = 4*ceil(R*C/4) bytes in plain byte order (byte p of the row is k = p):
+ * segment i, byte t < R*C = the level of input element (row ho*stride - pad + i, column
+ * wo*stride - pad + t/C, channel t%C), zero outside the image; every other byte is zero.  The
+ * filter row for apnn_conv2d_i8 is laid out the same way, k = i*seg + j*C + c.  kp: a multiple
+ * of 64, >= R*seg.  Returns APNN_ERR_UNSUPPORTED for rows it does not cover (W*C not a multiple
+ * of 4, Wo*kp/16 > 2048): use apnn_quantize_im2col_i8 there.  No counterpart in the reference. */
+apnn_status apnn_quantize_window_rows_i8(void *stream, const float *images, void *out_i8, int B,
+                                         int H, int W, int C, int R, int stride, int bits, int kp);
+
 /* ---- measurement aid ------------------------------------------------------------
  * Launches an operand-resident issue loop of one contraction instruction on every SM and
  * returns the operations one launch performs; the caller times the launch with events to

@@ -89,6 +89,50 @@ def test_quantize_im2col_i8(cuda_device, B, H, Wd, C, R, stride, bits, kp):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("B,H,Wd,C,R,stride,bits,kp", [(2, 10, 8, 3, 3, 2, 2, 64), (3, 32, 32, 3, 7, 4, 2, 192),
+                                                       (2, 20, 24, 3, 11, 4, 2, 448), (1, 8, 8, 4, 5, 1, 4, 128),
+                                                       (1, 224, 224, 3, 7, 4, 2, 192), (2, 224, 224, 3, 11, 4, 2, 448),
+                                                       (1, 224, 224, 3, 3, 2, 2, 64), (2, 6, 6, 40, 3, 1, 3, 384)])
+def test_quantize_window_rows_i8(cuda_device, B, H, Wd, C, R, stride, bits, kp):
+    """First layer as R segments per pixel: segment i of pixel (ho, wo) = the oracle's levels of the R*C
+    elements of image row ho*stride - pad + i from column wo*stride - pad on, zero outside the image."""
+    from apnn_tc_b200 import _cabi
+    rng = np.random.default_rng(B + H + R + kp)
+    x = rng.uniform(-12, 12, size=(B, H, Wd, C)).astype(np.float32)
+    step = 20.0 / (1 << bits)
+    edges = (-10 + step * (np.arange(1 << bits) + 0.5)).astype(np.float32)
+    probe = np.concatenate([edges, np.nextafter(edges, np.float32(-20)), np.nextafter(edges, np.float32(20)),
+                            np.array([-10, 10, -10.5, 10.5, 0], np.float32)])
+    flat = x.reshape(-1)
+    flat[: min(probe.size, flat.size)] = probe[: flat.size]
+    pad, seg = (R - 1) // 2, (R * C + 3) // 4 * 4
+    Ho, Wo = (H - 1) // stride + 1, (Wd - 1) // stride + 1
+    lv = oracle.quantize(x, bits).astype(np.uint8).reshape(B, H, Wd * C)
+    # every image row with pad*C zero bytes on the left and enough on the right, pad zero rows above and below
+    padded = np.zeros((B, H + 2 * pad, pad * C + Wd * C + pad * C + 4), dtype=np.uint8)
+    padded[:, pad:pad + H, pad * C:pad * C + Wd * C] = lv
+    want = np.zeros((B, Ho, Wo, kp), dtype=np.uint8)
+    for i in range(R):
+        for wo in range(Wo):
+            a = wo * stride * C
+            want[:, :, wo, i * seg:i * seg + R * C] = padded[:, i:i + (Ho - 1) * stride + 1:stride, a:a + R * C]
+    out = torch.full(want.shape, 0x55, dtype=torch.uint8, device="cuda")
+    xd = torch.from_numpy(x).cuda()
+    st = _cabi.lib().apnn_quantize_window_rows_i8(torch.cuda.current_stream().cuda_stream, xd.data_ptr(), out.data_ptr(),
+                                                  B, H, Wd, C, R, stride, bits, kp)
+    _cabi.check(st, "apnn_quantize_window_rows_i8")
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_quantize_window_rows_i8_refuses_what_it_does_not_cover(cuda_device):
+    from apnn_tc_b200 import _cabi
+    x = torch.zeros((1, 8, 7, 3), dtype=torch.float32, device="cuda")     # W*C = 21: not whole quads
+    out = torch.zeros((1, 8, 7, 64), dtype=torch.uint8, device="cuda")
+    st = _cabi.lib().apnn_quantize_window_rows_i8(torch.cuda.current_stream().cuda_stream, x.data_ptr(), out.data_ptr(),
+                                                  1, 8, 7, 3, 3, 1, 2, 64)
+    assert st == 2   # APNN_ERR_UNSUPPORTED
+
+
 @pytest.mark.parametrize("B,H,Wd,C,ih,oh", [(2, 8, 12, 64, 0, 1), (3, 6, 6, 128, 1, 0), (1, 56, 56, 16, 0, 0)])
 def test_maxpool2x2_i8(cuda_device, B, H, Wd, C, ih, oh):
     from apnn_tc_b200 import _cabi
