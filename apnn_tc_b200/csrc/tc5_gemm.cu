@@ -1259,6 +1259,8 @@ bool tc5_conv_supported(int H, int W, int R, int stride, int pool) {
 apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int Hin, int Win,
                         int CIN, int COUT, int R, int stride, bool w_signed, const apnn_epilogue* epi,
                         int* status_flag) {
+  if (tc5_conv_pair_applies(B, Hin, Win, CIN, COUT, R, stride, epi))
+    return tc5_conv_i8_pair(s, X8, W8, Out, B, Hin, Win, CIN, COUT, R, w_signed, epi, status_flag);
   const int pad = (R - 1) / 2;
   const int in_halo = (epi && epi->in_halo) ? epi->in_halo : pad;
   const int Hp = Hin + 2 * in_halo, Wp = Win + 2 * in_halo;

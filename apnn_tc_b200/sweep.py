@@ -160,8 +160,8 @@ def sweep_big():
 
 def sweep_layers():
     """The 3x3 / 1x1 layer shapes of ResNet-18 at a large batch through ``apnn_conv2d_i8`` (int8 operands
-    as the networks chain them), with int32, low-bit, threshold and threshold + int32 residual in/out
-    epilogues.  Plain back-to-back launches between one event pair (each call runs 50 us or more)."""
+    as the networks chain them), with int32, low-bit, threshold, threshold + int32 residual in/out and
+    threshold -> int8 row ("i8rows") epilogues.  Plain back-to-back launches between one event pair (each call runs 50 us or more)."""
     import ctypes
     from . import _cabi
     from .ops import _stream_ptr
@@ -169,8 +169,9 @@ def sweep_layers():
     B = int(FILTER.pop("B", 512))
     gen = torch.Generator(device="cuda").manual_seed(0xA9117C + 6)
     for (H, C, O, R) in ((56, 64, 64, 3), (56, 192, 64, 1), (56, 128, 128, 3), (28, 128, 128, 3), (14, 256, 256, 3),
-                         (7, 512, 512, 3)):
-        for mode, res in (("int32", False), ("lowbits", False), ("thresholds", False), ("thresholds", True)):
+                         (7, 512, 512, 3), (56, 256, 256, 3), (28, 512, 512, 3), (14, 512, 512, 3)):
+        for mode, res in (("int32", False), ("lowbits", False), ("thresholds", False), ("thresholds", True),
+                          ("i8rows", False)):
             if not _keep(H=H, C=C, mode=mode, res=int(res)):
                 continue
             pad = (R - 1) // 2
@@ -184,6 +185,9 @@ def sweep_layers():
             if mode == "int32":
                 out = torch.empty((B, H, H, O), dtype=torch.int32, device="cuda")
                 epi = ap.make_epilogue("int32")
+            elif mode == "i8rows":   # thresholds -> one byte per element, the form the networks chain
+                out = torch.zeros((B, H + 2, H + 2, O), dtype=torch.uint8, device="cuda")
+                epi = ap.make_epilogue("thresholds", 2, out_halo=1, thresholds=thr, out_i8=True)
             else:
                 out = torch.zeros((2, B, H + 2, H + 2, O // 32), dtype=torch.int32, device="cuda")
                 epi = ap.make_epilogue(mode, 2, out_halo=1, thresholds=thr if mode == "thresholds" else None,

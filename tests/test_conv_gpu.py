@@ -342,6 +342,46 @@ def test_tcgen05_int8_row_output_chains(cuda_device, CIN, COUT, pool):
     assert np.array_equal(out2.cpu().numpy(), want2)
 
 
+@pytest.mark.parametrize("B,H,Wd,CIN,COUT,R,ring,bits", [(300, 14, 14, 128, 256, 3, 1, 2), (90, 28, 28, 128, 256, 3, 1, 2),
+                                                         (400, 14, 14, 256, 256, 1, 0, 2), (40, 28, 28, 128, 512, 3, 2, 1),
+                                                         (301, 13, 15, 256, 256, 3, 1, 2)])
+def test_tcgen05_pair_flat_conv(cuda_device, B, H, Wd, CIN, COUT, R, ring, bits):
+    """Wide layers (CIN % 128 == 0, COUT % 256 == 0, thresholds -> int8 rows, enough tiles) on the CTA-pair
+    flat convolution (selected by APNN_CONV_PAIR=1, which tests/conftest.py sets before the library
+    loads): same bytes as the oracle's levels, ring left untouched."""
+    import ctypes
+    import apnn_tc_b200 as ap
+    from apnn_tc_b200 import _cabi
+    assert os.environ.get("APNN_CONV_PAIR") == "1"
+    rng = np.random.default_rng(B + H + CIN + COUT + R)
+    pad = (R - 1) // 2
+    X, Wt = make_conv(rng, B, H, Wd, CIN, COUT, R, 1, 2)           # X carries a ring of pad pixels
+    acc = oracle.conv_popc(Wt, X, threads=8)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R), 0)
+    scale = rng.uniform(0.5, 1.5, COUT).astype(np.float32)
+    bias = rng.uniform(-1, 1, COUT).astype(np.float32)
+    T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, bits)
+    lv = oracle.levels(v, bits, 2, T)                               # [B, H, Wd, COUT]
+    x8 = ap.expand_planes(to_dev(X).reshape(2, -1, CIN // 32)).reshape(B, H + 2 * pad, Wd + 2 * pad, CIN)
+    if ring > pad:   # a wider stored ring than the filter needs
+        wide = torch.zeros((B, H + 2 * ring, Wd + 2 * ring, CIN), dtype=torch.uint8, device="cuda")
+        wide[:, ring - pad:ring - pad + H + 2 * pad, ring - pad:ring - pad + Wd + 2 * pad] = x8
+        x8 = wide
+    in_halo = max(ring, pad)
+    w8 = ap.expand_planes(to_dev(Wt).reshape(1, COUT, -1), signed=True)
+    out = torch.full((B, H + 2, Wd + 2, COUT), 0x77, dtype=torch.uint8, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    epi = ap.make_epilogue("thresholds", bits, out_halo=1, thresholds=to_dev(T), out_i8=True)
+    epi.in_halo = in_halo
+    s = torch.cuda.current_stream().cuda_stream
+    _cabi.check(_cabi.lib().apnn_conv2d_i8(s, w8.data_ptr(), x8.data_ptr(), out.data_ptr(), B, H, Wd, CIN, COUT, R, 1, 1,
+                                           ctypes.byref(epi), flag.data_ptr()), "conv")
+    got = out.cpu().numpy()
+    assert int(flag.item()) == 0
+    assert np.array_equal(got[:, 1:-1, 1:-1], spread_bytes(lv.astype(np.uint8)))
+    assert (got[:, 0] == 0x77).all() and (got[:, -1] == 0x77).all() and (got[:, :, 0] == 0x77).all() and (got[:, :, -1] == 0x77).all()
+
+
 @pytest.mark.parametrize("widths", [1, 2, 3])
 @pytest.mark.parametrize("CIN,COUT", [(64, 64), (128, 160)])
 def test_tcgen05_int16_residuals(cuda_device, widths, CIN, COUT):
