@@ -452,13 +452,16 @@ __global__ void __launch_bounds__(512) quantize_im2col_i8_fixed_kernel(const flo
 // window's byte offset (the last word of a segment masked to its real bytes), then one 16-byte
 // store.  Against the byte-wise gather above this is about 16 instead of 50 instructions per
 // 16 output bytes; the quantise phase is the same.
-template <int TPT, int NQ>
+// G consecutive output rows of an image share one pass: they need R + (G-1)*stride input rows
+// instead of G*R, so every image element is quantised fewer times (7x7 stride 4, G = 3: 5 rows
+// per output row instead of 7; 11x11 stride 4: 6.3 instead of 11).
+template <int TPT, int NQ, int G>
 __global__ void __launch_bounds__(512) quantize_window_rows_i8_kernel(const float* __restrict__ img,
                                                                       uint8_t* __restrict__ out, int B, int H, int W,
                                                                       int C, int R, int stride, int bits, int Ho,
                                                                       int Wo, int kp, int seg, int rowlen, int lpad,
                                                                       const QuantSteps qs) {
-  extern __shared__ __align__(16) unsigned char lv_s[];   // [R][rowlen], image columns start at byte lpad >= 8
+  extern __shared__ __align__(16) unsigned char lv_s[];   // [R + (G-1)*stride][rowlen], image columns start at byte lpad >= 8
   const uint32_t* lv32 = reinterpret_cast<const uint32_t*>(lv_s);
   const float steps = (float)(1 << bits);
   const uint32_t maxlv = (1u << bits) - 1u;
@@ -467,6 +470,9 @@ __global__ void __launch_bounds__(512) quantize_window_rows_i8_kernel(const floa
   const int pieces = kp / 16, segw = seg / 4;
   const int quads = wc >> 2;
   const int T = blockDim.x;
+  const int rows_in = R + (G - 1) * stride;           // staged input rows per pass
+  const int groups_per_image = (Ho + G - 1) / G;
+  const int ngroups = B * groups_per_image;
   const uint32_t lastmask = 0xffffffffu >> (8 * (seg - R * C));   // the real bytes of a segment's last word
   // word indices of a piece's four words, 16 bits each (0: the zero words at the start of the
   // buffer, for k beyond the R segments), and the funnel shift of its pixel
@@ -488,7 +494,7 @@ __global__ void __launch_bounds__(512) quantize_window_rows_i8_kernel(const floa
     idx01[j] = w4[0] | (w4[1] << 16);
     idx23[j] = w4[2] | (w4[3] << 16);
   }
-  for (int t = threadIdx.x; t < R * (rowlen - wc); t += T) {
+  for (int t = threadIdx.x; t < rows_in * (rowlen - wc); t += T) {
     const int i = t / (rowlen - wc), o = t - i * (rowlen - wc);
     lv_s[i * rowlen + (o < lpad ? o : wc + o)] = 0;
   }
@@ -498,12 +504,12 @@ __global__ void __launch_bounds__(512) quantize_window_rows_i8_kernel(const floa
   for (int u = 0; u < NQ; u++) {
     const int t = threadIdx.x + u * T;
     const int i = t / quads, q = t - i * quads;
-    tap_row[u] = t < R * quads ? i : -1000000;      // never inside the image
+    tap_row[u] = t < rows_in * quads ? i : -1000000;      // never inside the image
     img_off[u] = i * wc + 4 * q;
     smem_off[u] = i * rowlen + lpad + 4 * q;
   }
-  auto fetch = [&](int orow) {
-    const int b = orow / Ho, ho = orow - b * Ho;
+  auto fetch = [&](int group) {
+    const int b = group / groups_per_image, ho = (group - b * groups_per_image) * G;
     const int hbase = ho * stride - pad;
     const float* first = img + ((long long)b * H + hbase) * wc;
 #pragma unroll
@@ -528,25 +534,32 @@ __global__ void __launch_bounds__(512) quantize_window_rows_i8_kernel(const floa
       }
     }
   };
-  int orow = blockIdx.x;
-  if (orow < B * Ho) fetch(orow);
-  for (; orow < B * Ho; orow += gridDim.x) {
-    __syncthreads();   // the previous row's readers are done
+  int group = blockIdx.x;
+  if (group < ngroups) fetch(group);
+  for (; group < ngroups; group += gridDim.x) {
+    __syncthreads();   // the previous pass's readers are done
     stash();
     __syncthreads();
-    if (orow + (int)gridDim.x < B * Ho) fetch(orow + gridDim.x);
-    uint4* orow_out = reinterpret_cast<uint4*>(out + (long long)orow * Wo * kp);
+    if (group + (int)gridDim.x < ngroups) fetch(group + gridDim.x);
+    const int b = group / groups_per_image, ho0 = (group - b * groups_per_image) * G;
 #pragma unroll
-    for (int j = 0; j < TPT; j++) {
-      const int task = threadIdx.x + j * T;
-      if (task < Wo * pieces) {
-        const uint32_t i0 = idx01[j] & 0xffffu, i1 = idx01[j] >> 16, i2 = idx23[j] & 0xffffu, i3 = idx23[j] >> 16;
-        uint4 v;
-        v.x = __funnelshift_r(lv32[i0], lv32[i0 + 1], shift[j]) & ((shift[j] & 0x100u) ? lastmask : 0xffffffffu);
-        v.y = __funnelshift_r(lv32[i1], lv32[i1 + 1], shift[j]) & ((shift[j] & 0x200u) ? lastmask : 0xffffffffu);
-        v.z = __funnelshift_r(lv32[i2], lv32[i2 + 1], shift[j]) & ((shift[j] & 0x400u) ? lastmask : 0xffffffffu);
-        v.w = __funnelshift_r(lv32[i3], lv32[i3 + 1], shift[j]) & ((shift[j] & 0x800u) ? lastmask : 0xffffffffu);
-        orow_out[task] = v;
+    for (int g = 0; g < G; g++) {
+      if (ho0 + g >= Ho) break;
+      // output row ho0 + g reads the staged rows from g*stride on; word 0 of every staged row is padding
+      const uint32_t* rows32 = lv32 + g * stride * (rowlen >> 2);
+      uint4* orow_out = reinterpret_cast<uint4*>(out + ((long long)b * Ho + ho0 + g) * Wo * kp);
+#pragma unroll
+      for (int j = 0; j < TPT; j++) {
+        const int task = threadIdx.x + j * T;
+        if (task < Wo * pieces) {
+          const uint32_t i0 = idx01[j] & 0xffffu, i1 = idx01[j] >> 16, i2 = idx23[j] & 0xffffu, i3 = idx23[j] >> 16;
+          uint4 v;
+          v.x = __funnelshift_r(rows32[i0], rows32[i0 + 1], shift[j]) & ((shift[j] & 0x100u) ? lastmask : 0xffffffffu);
+          v.y = __funnelshift_r(rows32[i1], rows32[i1 + 1], shift[j]) & ((shift[j] & 0x200u) ? lastmask : 0xffffffffu);
+          v.z = __funnelshift_r(rows32[i2], rows32[i2 + 1], shift[j]) & ((shift[j] & 0x400u) ? lastmask : 0xffffffffu);
+          v.w = __funnelshift_r(rows32[i3], rows32[i3 + 1], shift[j]) & ((shift[j] & 0x800u) ? lastmask : 0xffffffffu);
+          orow_out[task] = v;
+        }
       }
     }
   }
@@ -755,21 +768,35 @@ apnn_status apnn_quantize_window_rows_i8(void* stream, const float* images, void
   const int pad = (R - 1) / 2, wc = W * C;
   const int lpad = pad * C < 8 ? 8 : (pad * C + 3) / 4 * 4;   // words 0 and 1 of the buffer are always zero
   const int rowlen = (lpad + wc + pad * C + 8 + 15) / 16 * 16;
-  const size_t smem = (size_t)R * rowlen;
-  const int tasks = Wo * (kp / 16), quads_all = R * (wc >> 2);
-  // rows the fixed per-thread tasks do not cover: use apnn_quantize_im2col_i8
-  if ((wc & 3) || smem > 48 * 1024 || tasks > 4 * 512 || quads_all > 8 * 512) return APNN_ERR_UNSUPPORTED;
+  const int tasks = Wo * (kp / 16);
   const int tpt = tasks <= 512 ? 1 : (tasks <= 1024 ? 2 : 4);
   int threads = ((tasks + tpt - 1) / tpt + 31) / 32 * 32;
-  const int for_quads = ((quads_all + 3) / 4 + 31) / 32 * 32;   // four input quads per thread where 512 threads allow it
-  if (for_quads <= 512 && threads < for_quads) threads = for_quads;
   if (threads < 128) threads = 128;
-  const int nq = quads_all <= 4 * threads ? 4 : 8;
-  long long nb = (long long)B * Ho, cap = (long long)device_sm_count() * (2048 / threads);
+  // Output rows per pass: G rows stage R + (G-1)*stride input rows.  Four quads per thread keep
+  // two blocks resident per SM (64 registers); eight quads (about 120 registers, one block) pay
+  // only where sharing saves at least 40 % of the quantisation (11x11 filters).
+  const int quads = wc >> 2;
+  auto threads_for = [&](int g, int per_thread) { return (((R + (g - 1) * stride) * quads + per_thread - 1) / per_thread + 31) / 32 * 32; };
+  auto fits = [&](int g) { return (size_t)(R + (g - 1) * stride) * rowlen <= 48 * 1024 && Ho >= g; };
+  int G = 1, nq = 4;
+  if (fits(3) && threads_for(3, 4) <= 512) G = 3;
+  else if (fits(2) && threads_for(2, 4) <= 512) G = 2;
+  else if (fits(3) && threads_for(3, 8) <= 512 && 10 * (R + 2 * stride) <= 6 * 3 * R) { G = 3; nq = 8; }
+  else if (threads_for(1, 4) > 512) nq = 8;
+  if (threads < threads_for(G, nq) && threads_for(G, nq) <= 512) threads = threads_for(G, nq);
+  const int rows_in = R + (G - 1) * stride, quads_all = rows_in * quads;
+  const size_t smem = (size_t)rows_in * rowlen;
+  // rows the fixed per-thread tasks do not cover: use apnn_quantize_im2col_i8
+  if ((wc & 3) || smem > 48 * 1024 || tasks > 4 * 512 || quads_all > nq * threads) return APNN_ERR_UNSUPPORTED;
+  const int groups = B * ((Ho + G - 1) / G);
+  long long nb = groups, cap = (long long)device_sm_count() * (2048 / threads);
   if (nb > cap) nb = cap;
-  auto kern = tpt == 1 ? (nq == 4 ? quantize_window_rows_i8_kernel<1, 4> : quantize_window_rows_i8_kernel<1, 8>)
-            : tpt == 2 ? (nq == 4 ? quantize_window_rows_i8_kernel<2, 4> : quantize_window_rows_i8_kernel<2, 8>)
-                       : (nq == 4 ? quantize_window_rows_i8_kernel<4, 4> : quantize_window_rows_i8_kernel<4, 8>);
+#define APNN_WINDOW_KERNEL(TPT_) \
+  (G == 3 ? (nq == 4 ? quantize_window_rows_i8_kernel<TPT_, 4, 3> : quantize_window_rows_i8_kernel<TPT_, 8, 3>) \
+   : G == 2 ? quantize_window_rows_i8_kernel<TPT_, 4, 2>                                                           \
+            : (nq == 4 ? quantize_window_rows_i8_kernel<TPT_, 4, 1> : quantize_window_rows_i8_kernel<TPT_, 8, 1>))
+  auto kern = tpt == 1 ? APNN_WINDOW_KERNEL(1) : tpt == 2 ? APNN_WINDOW_KERNEL(2) : APNN_WINDOW_KERNEL(4);
+#undef APNN_WINDOW_KERNEL
   kern<<<(unsigned)nb, threads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
       images, reinterpret_cast<uint8_t*>(out_i8), B, H, W, C, R, stride, bits, Ho, Wo, kp, seg, rowlen, lpad,
       make_quant_steps(bits));
