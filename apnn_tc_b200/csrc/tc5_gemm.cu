@@ -1145,7 +1145,14 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   Tc5Params p;
   memset(&p, 0, sizeof(p));
   p.tiles_m = (M + BM - 1) / BM;
-  const int bn = pick_bn(p.tiles_m, N, sms);
+  int bn = pick_bn(p.tiles_m, N, sms);
+  const int out_mode_ = epi ? epi->out_mode : APNN_OUT_INT32;
+  const bool plain_int32 = out_mode_ == APNN_OUT_INT32 && !(epi && (epi->residual_in || epi->residual_out));
+  const long long t128 = (long long)p.tiles_m * ((N + 127) / 128);
+  const bool split_k = bn == 128 && plain_int32 && t128 * 8 <= sms && K / BK >= 32;
+  // a skinny problem that leaves more than half of the SMs idle even with 128-wide tiles is bound by
+  // streaming the B operand once: 64-wide tiles put twice as many SMs on that stream
+  if (bn == 128 && !split_k && t128 * 2 <= sms) bn = 64;
   CUtensorMap map_a, map_b;
   if (!make_operand_map(&map_a, A8, M, K, BM) || !make_operand_map(&map_b, B8, N, K, bn)) {
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -1167,8 +1174,7 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
   p.idesc = make_idesc(a_signed, b_signed, bn);
   long long tiles = (long long)p.tiles_m * p.tiles_n;
-  if (bn == 128 && p.out_mode == APNN_OUT_INT32 && !p.residual_in && !p.residual_out && tiles * 8 <= sms &&
-      p.kblocks >= 32) {
+  if (split_k) {
     // a handful of tiles with a long K (the first fully connected layer of a network at a small
     // batch): split K over the idle SMs; the parts meet in the zeroed output through atomic adds.
     // With 32 tiles or more the atomics cost more than the idle SMs gain (measured on AlexNet's
