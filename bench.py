@@ -455,7 +455,8 @@ NET_BATCH = {"resnet18": 1024, "vgg_variant": 1024, "alexnet": 128}
 
 
 def run_net(args) -> None:
-    """images/s of a whole w1a2 network (BASELINE configs 4/5): global batch sharded over the ranks
+    """images/s of a whole w1a2 network (the AlexNet / VGG-variant / ResNet-18 model lists of APNN-TC-nn):
+    global batch sharded over the ranks
     (no collective), one CUDA-graph replay of the layer sequence per step."""
     import numpy as np
     import torch
