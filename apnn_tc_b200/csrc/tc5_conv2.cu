@@ -7,7 +7,7 @@
 // block of 128 bytes each CTA loads ONE box of 128 + (R-1)*(Wp+1) consecutive rows (its half
 // of the pair's 256 positions plus the rows the taps reach) and all R*R taps read it through
 // row-shifted descriptors; the filter tile of a (tap, channel block) is split over the pair,
-// 128 of its 256 rows per CTA.  Against the single-CTA kernel every SM writes half the filter
+// 128 of its 256 rows per CTA, and the filter ring moves a whole filter row (R taps) per stage.  Against the single-CTA kernel every SM writes half the filter
 // bytes into shared memory per MMA, which is what bounds tcgen05.mma kind::i8 there.
 //
 // Synchronisation follows the CTA-pair GEMM (all waits time-bounded):
@@ -33,13 +33,17 @@ constexpr int TILE_M = 256;   // flattened positions per pair
 constexpr int TILE_N = 256;   // output channels per tile
 constexpr int HALF = 128;
 constexpr int NA = 2;         // activation buffers (one channel block each)
-constexpr int NB = 8;         // filter-tile ring
 constexpr int A_BUF_BYTES = 256 * BK;     // at most 256 rows
-constexpr int B_STAGE_BYTES = HALF * BK;  // 16 KiB per CTA
+constexpr int B_TAP_BYTES = HALF * BK;    // one tap's filter tile: 16 KiB per CTA
+// The filter ring moves one filter ROW (R taps of a channel block) per stage: one wait, 4*R MMAs of
+// straight-line code and one commit per stage keep the issuing thread off the critical path.
+constexpr int ring_depth(int RR) { return RR == 1 ? 8 : 3; }
+constexpr int B_RING_BYTES = 9 * B_TAP_BYTES;   // 3 stages x 3 taps (R = 3) or 8 stages x 1 tap (R = 1)
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 32 * (2 + EPI_WARPS);
 constexpr int THR_BYTES_PER_WARP = (TILE_N / 2) * 16;   // one int4 per column the warp drains
-constexpr int SMEM_BYTES = NA * A_BUF_BYTES + NB * B_STAGE_BYTES + 1024 + 256 + EPI_WARPS * THR_BYTES_PER_WARP;
+constexpr int SMEM_BYTES = NA * A_BUF_BYTES + B_RING_BYTES + 1024 + 256 + EPI_WARPS * THR_BYTES_PER_WARP;
+constexpr int MAX_NB = 8;
 
 struct ConvPairParams {
   uint8_t* out;                // int8 rows [B][Ho + 2*out_halo][Wo + 2*out_halo][N]
@@ -95,6 +99,7 @@ __device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t adesc, 
       : "memory");
 }
 
+template <int RR>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const ConvPairParams p) {
@@ -102,14 +107,16 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   const uint32_t bring = base + NA * A_BUF_BYTES;
-  const uint32_t bars = bring + NB * B_STAGE_BYTES;
+  constexpr int NB = ring_depth(RR);
+  constexpr int B_STAGE_BYTES = RR * B_TAP_BYTES;
+  const uint32_t bars = bring + B_RING_BYTES;
   auto afull_bar = [&](int i) { return bars + 8u * i; };
   auto aempty_bar = [&](int i) { return bars + 8u * (NA + i); };
   auto bfull_bar = [&](int s) { return bars + 8u * (2 * NA + s); };
-  auto bempty_bar = [&](int s) { return bars + 8u * (2 * NA + NB + s); };
-  auto tfull_bar = [&](int a) { return bars + 8u * (2 * NA + 2 * NB + a); };
-  auto tempty_bar = [&](int a) { return bars + 8u * (2 * NA + 2 * NB + 2 + a); };
-  const uint32_t tmem_slot = bars + 8u * (2 * NA + 2 * NB + 4);
+  auto bempty_bar = [&](int s) { return bars + 8u * (2 * NA + MAX_NB + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * NA + 2 * MAX_NB + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * NA + 2 * MAX_NB + 2 + a); };
+  const uint32_t tmem_slot = bars + 8u * (2 * NA + 2 * MAX_NB + 4);
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
   uint8_t* thr_stage = smem_raw + (bars + 256u - raw);
 
@@ -146,7 +153,6 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int taps = p.R * p.R;
 
   if (warp == 0) {
     // ---------------- TMA producer (one per CTA) ----------------
@@ -164,10 +170,13 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           tma_load_2d_pair(base + ia * A_BUF_BYTES, &map_a, cb * BK, q0, map_to_cta(afull_bar(ia), 0));
           if (++ia == NA) { ia = 0; pha ^= 1u; }
           int kcol = cb * BK;
-          for (int tap = 0; tap < taps; tap++, kcol += p.CIN) {
+          for (int ti = 0; ti < RR; ti++) {
             if (!mbar_wait(bempty_bar(sb), phb ^ 1u)) { ok = false; break; }
             if (rank == 0) mbar_expect_tx(bfull_bar(sb), 2 * B_STAGE_BYTES);
-            tma_load_2d_pair(bring + sb * B_STAGE_BYTES, &map_b, kcol, brow, map_to_cta(bfull_bar(sb), 0));
+            const uint32_t full = map_to_cta(bfull_bar(sb), 0);
+#pragma unroll
+            for (int tj = 0; tj < RR; tj++, kcol += p.CIN)
+              tma_load_2d_pair(bring + sb * B_STAGE_BYTES + tj * B_TAP_BYTES, &map_b, kcol, brow, full);
             if (++sb == NB) { sb = 0; phb ^= 1u; }
           }
         }
@@ -192,21 +201,25 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (!mbar_wait(afull_bar(ia), pha)) { ok = false; break; }
           tc_fence_after();
           const uint32_t abuf = base + ia * A_BUF_BYTES;
-          for (int ti = 0; ti < p.R && ok; ti++) {
+          const uint64_t a0 = make_smem_desc(abuf);
+#pragma unroll
+          for (int ti = 0; ti < RR; ti++) {
+            if (!mbar_wait(bfull_bar(sb), phb)) { ok = false; break; }
+            tc_fence_after();
             // tap (ti, tj) reads the box from row ti*Wp + tj on: descriptors shifted by whole rows
-            uint64_t adesc = make_smem_desc(abuf + (uint32_t)(ti * p.wp) * BK);
-            for (int tj = 0; tj < p.R; tj++, adesc += BK / 16) {
-              if (!mbar_wait(bfull_bar(sb), phb)) { ok = false; break; }
-              tc_fence_after();
-              const uint64_t bdesc = make_smem_desc(bring + sb * B_STAGE_BYTES);
+            const uint64_t adesc = a0 + (uint32_t)(ti * p.wp) * (BK / 16);
+            const uint64_t bdesc = make_smem_desc(bring + sb * B_STAGE_BYTES);
+#pragma unroll
+            for (int tj = 0; tj < RR; tj++) {
 #pragma unroll
               for (int k = 0; k < BK / 32; k++) {
-                tc_mma_i8_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, enable);
+                tc_mma_i8_pair(d_tmem, adesc + tj * (BK / 16) + 2u * k, bdesc + tj * (B_TAP_BYTES / 16) + 2u * k, p.idesc,
+                               enable);
                 enable = 1u;
               }
-              tc_commit_pair(bempty_bar(sb));  // frees the filter stage in both CTAs
-              if (++sb == NB) { sb = 0; phb ^= 1u; }
             }
+            tc_commit_pair(bempty_bar(sb));  // frees the filter stage in both CTAs
+            if (++sb == NB) { sb = 0; phb ^= 1u; }
           }
           if (ok) tc_commit_pair(aempty_bar(ia));  // frees the activation buffer in both CTAs
           if (++ia == NA) { ia = 0; pha ^= 1u; }
@@ -323,12 +336,11 @@ int box_rows_of(int R, int Wp) { return (HALF + (R - 1) * (Wp + 1) + 7) / 8 * 8;
 }  // namespace
 
 bool tc5_conv_pair_applies(int B, int Hin, int Win, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi) {
-  // Measured on B200 against the single-CTA flat kernel this pair kernel is 2 - 13 % slower on every
-  // layer shape it applies to (28x28 512->512: 3140 against 3200 effective TOP/s), so the dispatcher
-  // does not pick it by itself; APNN_CONV_PAIR=1 in the environment selects it (parity tests, timing).
-  static const bool enabled = [] { const char* v = getenv("APNN_CONV_PAIR"); return v && v[0] == '1'; }();
-  if (!enabled) return false;
-  if (!epi || stride != 1 || CIN % 128 != 0 || COUT % TILE_N != 0 || R < 1 || (R & 1) == 0) return false;
+  // APNN_CONV_PAIR=0 in the environment (read once) keeps these layers on the single-CTA kernel, for
+  // comparisons; measured on B200 the pair kernel is 7 - 16 % faster on every shape it takes.
+  static const bool disabled = [] { const char* v = getenv("APNN_CONV_PAIR"); return v && v[0] == '0'; }();
+  if (disabled) return false;
+  if (!epi || stride != 1 || CIN % 128 != 0 || COUT % TILE_N != 0 || (R != 1 && R != 3)) return false;
   if (epi->pool != APNN_POOL_NONE || epi->out_mode != APNN_OUT_THRESHOLDS || !epi->out_i8 || !epi->thresholds) return false;
   if (epi->out_bits != 1 && epi->out_bits != 2) return false;
   if (epi->residual_in || epi->residual_out || epi->n_peer_out) return false;
@@ -337,10 +349,10 @@ bool tc5_conv_pair_applies(int B, int Hin, int Win, int CIN, int COUT, int R, in
   const int Hp = Hin + 2 * in_halo, Wp = Win + 2 * in_halo;
   const long long flat_rows = (long long)B * Hp * Wp;
   if (flat_rows >= 0x7fffff00LL || box_rows_of(R, Wp) > 256) return false;
-  // enough pair tiles to fill every SM pair four times over; positions on the ring are computed and
-  // dropped, so tiny images stay on the pixel-box kernel
+  // at least one tile per SM pair; positions on the ring are computed and dropped, so small images
+  // (7x7: 49 of 81 positions useful) stay on the pixel-box kernel
   const long long tiles = ((flat_rows + TILE_M - 1) / TILE_M) * (COUT / TILE_N);
-  return tiles >= 4LL * (device_sm_count() / 2) && (long long)Hin * Win * 10 >= (long long)Hp * Wp * 7;
+  return tiles >= device_sm_count() / 2 && (long long)Hin * Win * 10 >= (long long)Hp * Wp * 7;
 }
 
 apnn_status tc5_conv_i8_pair(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int Hin, int Win,
@@ -359,7 +371,9 @@ apnn_status tc5_conv_i8_pair(cudaStream_t s, const uint8_t* X8, const uint8_t* W
   cudaGetDevice(&dev);
   cudaError_t e;
   if (dev >= 16 || !attr_set[dev]) {
-    e = cudaFuncSetAttribute(tc5_conv_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    e = cudaFuncSetAttribute(tc5_conv_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc5_conv_pair_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return cuda_fail(e, "tc5 conv pair smem attribute");
     if (dev < 16) attr_set[dev] = true;
   }
@@ -402,7 +416,8 @@ apnn_status tc5_conv_i8_pair(cudaStream_t s, const uint8_t* X8, const uint8_t* W
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, tc5_conv_pair_kernel, map_a, map_b, p);
+  e = R == 3 ? cudaLaunchKernelEx(&cfg, tc5_conv_pair_kernel<3>, map_a, map_b, p)
+             : cudaLaunchKernelEx(&cfg, tc5_conv_pair_kernel<1>, map_a, map_b, p);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_conv_pair launch");
   return APNN_OK;
 }

@@ -3,9 +3,6 @@ import sys
 
 import pytest
 
-# the CTA-pair flat convolution is an opt-in kernel: the library reads this once, at its first convolution
-os.environ.setdefault("APNN_CONV_PAIR", "1")
-
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
