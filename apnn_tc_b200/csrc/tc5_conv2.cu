@@ -272,6 +272,7 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       for (int i = 0; i < CHUNKS; i++) {
         const int c = half + 2 * i;
         uint32_t v[32];
+        __syncwarp();   // lanes that left the previous chunk early rejoin before the warp-wide TMEM load
         tmem_ld32(taddr + c * 32, v);
         tmem_ld_wait();
         if (!row_ok) continue;

@@ -702,6 +702,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int col0 = tn * BN + c * 32;
         if (col0 >= p.N) continue;  // uniform over the warp
         uint32_t v[32];
+        __syncwarp();   // lanes that left the previous chunk early rejoin before the warp-wide TMEM load
         tmem_ld32(taddr + c * 32, v);
         if (thr_staged) {
           __syncwarp();   // the previous chunk's readers are done
@@ -1311,20 +1312,28 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   };
   // (with many waves a few per cent more tiles still win: a flat tile loads 5-8x fewer rows)
   const long long cost_box = cost(p.tiles_m), cost_flat = cost((flat_rows + BM - 1) / BM);
-  const bool flat = stride == 1 && pool == APNN_POOL_NONE && flat_rows < 0x7fffff00LL &&
-                    (cost_flat <= cost_box || (cost_box >= 8 * 64 && cost_flat * 100 <= cost_box * 105));
+  bool flat = stride == 1 && pool == APNN_POOL_NONE && flat_rows < 0x7fffff00LL &&
+              (cost_flat <= cost_box || (cost_box >= 8 * 64 && cost_flat * 100 <= cost_box * 105));
   if (flat) {
-    p.is_conv = 2;
-    p.flat_wp = Wp;
-    p.flat_hpwp = Hp * Wp;
-    p.tiles_m = (int)((flat_rows + BM - 1) / BM);
+    // rows of input one (tile, channel block) needs: one box when it has at most 256 rows (the TMA
+    // limit), else one box per filter row
     const int all_rows = (BM + (R - 1) * (Wp + 1) + 7) / 8 * 8;
-    if (all_rows <= 256) {
-      p.flat_nblk = 1;
-      p.flat_blk_rows = all_rows;
+    const int nblk = all_rows <= 256 ? 1 : R;
+    const int blk_rows = all_rows <= 256 ? all_rows : (BM + R - 1 + 7) / 8 * 8;
+    // the flat plan needs one such buffer plus two filter tiles next to the fixed part; wide
+    // filters on wide images (R >= 9, or R = 7 with 256-column tiles) do not fit and take the pixel boxes
+    const long long flat_tiles_m = (flat_rows + BM - 1) / BM;
+    const int bn_flat = pick_bn(flat_tiles_m, COUT, sms);
+    const long long need = (long long)TileCfg<64, 64>::FIXED_BYTES + 2LL * bn_flat * span + (long long)nblk * blk_rows * span;
+    if (need > SMEM_LIMIT) {
+      flat = false;
     } else {
-      p.flat_nblk = R;
-      p.flat_blk_rows = (BM + R - 1 + 7) / 8 * 8;
+      p.is_conv = 2;
+      p.flat_wp = Wp;
+      p.flat_hpwp = Hp * Wp;
+      p.tiles_m = (int)flat_tiles_m;
+      p.flat_nblk = nblk;
+      p.flat_blk_rows = blk_rows;
     }
   }
   const int bn = pick_bn(p.tiles_m, COUT, sms);

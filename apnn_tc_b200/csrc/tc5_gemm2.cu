@@ -242,6 +242,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll 1
       for (int c = 0; c < TILE_N / 32; c++) {
         uint32_t v[32];
+        __syncwarp();   // lanes that left the previous chunk early rejoin before the warp-wide TMEM load
         tmem_ld32(taddr + c * 32, v);
         tmem_ld_wait();
         const int col0 = tn * TILE_N + c * 32;

@@ -49,26 +49,27 @@ def make_conv(rng, B, H, Wd, CIN, COUT, R, wb, xb):
 
 
 @pytest.mark.parametrize("wb,xb", [(1, 2), (1, 4), (2, 2), (1, 3)])
-@pytest.mark.parametrize("C", [128, 256, 384, 512, 1024])
+@pytest.mark.parametrize("C", [128, 256, 384, 512, 640, 768, 896, 1024])
 def test_config3_batch8_16x16(cuda_device, wb, xb, C):
-    """Batch 8, 16x16, C=O, 3x3, stride 1, pad 1, BN thresholds -> 2-bit packed output,
-    with +-1 weights for the 1-bit filters."""
+    """The convolution sweep as configured: batch 8, 16x16, C = O in 128..1024 step 128, 3x3, stride 1,
+    pad 1, BN thresholds (scale U[0.5,1.5], bias U[-1,1]) -> 2-bit packed output, with +-1 weights for
+    the 1-bit filters; int32 accumulators and packed outputs, on the warp-level and the tcgen05 path,
+    against one oracle evaluation."""
     import apnn_tc_b200 as ap
-    if C > 512 and (wb, xb) != (1, 2):
-        pytest.skip("largest size checked on w1a2 only to bound oracle time")
     rng = np.random.default_rng(0xA9117C + 3)
     X, Wt = make_conv(rng, 8, 16, 16, C, C, 3, wb, xb)
     acc = oracle.conv_popc(Wt, X, threads=8)
-    got = to_host(ap.apconv(to_dev(Wt), to_dev(X)), np.int32)
-    assert np.array_equal(got, acc)
     signed = "w" if wb == 1 else "none"
     v = oracle.signed_correct(acc, oracle.conv_window_sums(X, 3), 0) if wb == 1 else acc
     scale = rng.uniform(0.5, 1.5, C).astype(np.float32)
     bias = rng.uniform(-1, 1, C).astype(np.float32)
     T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, 2)
+    want = oracle.requant_pack(v, 2, 2, T)
     epi = ap.make_epilogue("thresholds", 2, signed=signed, thresholds=to_dev(T))
-    pk = to_host(ap.apconv(to_dev(Wt), to_dev(X), epilogue=epi))
-    assert np.array_equal(pk, oracle.requant_pack(v, 2, 2, T))
+    assert np.array_equal(to_host(ap.apconv(to_dev(Wt), to_dev(X)), np.int32), acc)
+    assert np.array_equal(to_host(ap.apconv(to_dev(Wt), to_dev(X), epilogue=epi)), want)
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X), np.int32), acc)
+    assert np.array_equal(to_host(run_tc5_conv(Wt, X, epi)), want)
 
 
 @pytest.mark.parametrize("R,stride", [(3, 1), (3, 2), (1, 1), (1, 2)])
@@ -140,21 +141,6 @@ def test_tcgen05_reference_inputs(cuda_device, wb, xb):
     assert np.array_equal(to_host(run_tc5_conv(Wt, X), np.int32), GOLD[key])
     assert np.array_equal(to_host(run_tc5_conv(Wt, X, ap.make_epilogue("lowbits", 2))), GOLD[key + "_pack"])
     assert np.array_equal(to_host(run_tc5_conv(Wt, X, ap.make_epilogue("lowbits", 2, pool="avg"))), GOLD[key + "_pool"])
-
-
-@pytest.mark.parametrize("C", [128, 256, 512, 1024])
-def test_tcgen05_config3_batch8_16x16(cuda_device, C):
-    import apnn_tc_b200 as ap
-    rng = np.random.default_rng(0xA9117C + 3)
-    X, Wt = make_conv(rng, 8, 16, 16, C, C, 3, 1, 2)
-    acc = oracle.conv_popc(Wt, X, threads=8)
-    assert np.array_equal(to_host(run_tc5_conv(Wt, X), np.int32), acc)
-    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, 3), 0)
-    scale = rng.uniform(0.5, 1.5, C).astype(np.float32)
-    bias = rng.uniform(-1, 1, C).astype(np.float32)
-    T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, 2)
-    epi = ap.make_epilogue("thresholds", 2, signed="w", thresholds=to_dev(T))
-    assert np.array_equal(to_host(run_tc5_conv(Wt, X, epi)), oracle.requant_pack(v, 2, 2, T))
 
 
 @pytest.mark.parametrize("B,H,Wd", [(3, 12, 20), (5, 8, 8), (2, 56, 56), (1, 4, 4), (2, 6, 130)])
@@ -444,3 +430,22 @@ def test_tcgen05_flat_conv_with_wider_input_ring(cuda_device, R, ring):
                 "conv")
     assert int(flag.item()) == 0
     assert np.array_equal(out.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("R,B,H,Wd,COUT", [(5, 2, 10, 40, 160), (5, 2, 12, 20, 320), (7, 2, 9, 30, 160), (7, 2, 8, 16, 288),
+                                           (9, 2, 12, 12, 160), (9, 2, 10, 34, 288), (11, 2, 12, 14, 160),
+                                           (11, 2, 11, 40, 192), (7, 8, 24, 40, 512), (9, 8, 24, 40, 512)])
+def test_tcgen05_wide_filters_stride1(cuda_device, R, B, H, Wd, COUT):
+    """Stride-1 convolutions with 5x5 ... 11x11 filters on the tcgen05 path: one input box per
+    (tile, channel block) while it has at most 256 rows, one box per filter row beyond that, and the
+    pixel-box formulation where neither fits in shared memory (11x11; 9x9 with 256-column tiles)."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(R * 100 + Wd)
+    X, Wt = make_conv(rng, B, H, Wd, 128, COUT, R, 1, 2)
+    acc = oracle.conv_popc(Wt, X, threads=8)
+    v = oracle.signed_correct(acc, oracle.conv_window_sums(X, R), 0)
+    got = run_tc5_conv(Wt, X, ap.make_epilogue("int32", signed="w"))
+    assert np.array_equal(to_host(got, np.int32), v)
+    T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
+    got = run_tc5_conv(Wt, X, ap.make_epilogue("thresholds", 2, signed="w", thresholds=to_dev(T)))
+    assert np.array_equal(to_host(got), oracle.requant_pack(v, 2, 2, T))

@@ -369,3 +369,45 @@ def test_tcgen05_split_k_and_requantize(cuda_device, M, N, K):
     outl = torch.zeros((3, M, N // 32), dtype=torch.int32, device="cuda")
     _cabi.check(_cabi.lib().apnn_requantize_i32(s, D.data_ptr(), outl.data_ptr(), M, N, ctypes.byref(q3)), "requantize")
     assert np.array_equal(to_host(outl), oracle.requant_pack(want, 3, 1))
+
+
+@pytest.mark.parametrize("M,N", [(2304, 2304), (2300, 2336)])
+@pytest.mark.parametrize("mode", ["thresholds", "lowbits", "int32"])
+def test_tcgen05_pair_kernel_epilogues(cuda_device, M, N, mode):
+    """81 pair tiles and K = 1024: the GEMM runs on CTA pairs (cta_group::2).  Its +-1 weights,
+    threshold / low-bit requantisation and residual in / out against the oracle, on a tile-aligned
+    and a ragged shape."""
+    import apnn_tc_b200 as ap
+    K = 1024
+    rng = np.random.default_rng(M + N)
+    W, _ = oracle.value_planes(rng, M, K, 1)
+    X, _ = oracle.value_planes(rng, N, K, 2)
+    v = oracle.signed_correct(oracle.gemm_popc(W, X, threads=8), oracle.row_sums(X), 1)
+    res = rng.integers(-400, 400, size=v.shape).astype(np.int32)
+    v = v + res
+    T = None
+    if mode == "thresholds":
+        scale = rng.uniform(0.5, 1.5, N).astype(np.float32)
+        bias = rng.uniform(-1, 1, N).astype(np.float32)
+        T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, 2)
+    res_out = torch.full((M, N), -1, dtype=torch.int32, device="cuda")
+    epi = ap.make_epilogue(mode, 2 if mode != "int32" else 0, signed="w", thresholds=to_dev(T) if T is not None else None,
+                           residual_in=to_dev(res), residual_out=res_out)
+    out = run_tc5(W, X, epi)
+    assert np.array_equal(to_host(res_out, np.int32), v)
+    if mode == "int32":
+        assert np.array_equal(to_host(out, np.int32), v)
+    else:
+        assert np.array_equal(to_host(out), oracle.requant_pack(v, 2, 1 if mode == "lowbits" else 2, T))
+        if mode == "thresholds":
+            assert len(np.unique(oracle.levels(v, 2, 2, T))) == 4
+    # the same without residuals, explicitly on the pair kernel
+    ws = torch.empty(ap.gemm_workspace_bytes(M, N, K), dtype=torch.uint8, device="cuda")
+    epi2 = ap.make_epilogue(mode, 2 if mode != "int32" else 0, signed="w", thresholds=to_dev(T) if T is not None else None)
+    out2 = ap.apmm(to_dev(W), to_dev(X), algo="tcgen05_pair", workspace=ws, epilogue=epi2)
+    ap.gemm_check(ws, M, N, K)
+    v0 = v - res
+    if mode == "int32":
+        assert np.array_equal(to_host(out2, np.int32), v0)
+    else:
+        assert np.array_equal(to_host(out2), oracle.requant_pack(v0, 2, 1 if mode == "lowbits" else 2, T))

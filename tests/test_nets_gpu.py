@@ -36,6 +36,54 @@ def test_model_logits_match_reference(cuda_device, model, hw, batch, use_tcgen05
     assert len(np.unique(levels[spec.layers[-2].name])) > 1
 
 
+@pytest.mark.parametrize("model", ["alexnet", "resnet18", "vgg_variant"])
+def test_full_size_models_match_reference(cuda_device, model):
+    """The model lists as the benchmark configurations state them -- 224x224x3 images, 1000 classes
+    (APNN-TC-nn/src/alexnet.cu:43-81, resnet18.cu:40-142, vgg.cu:49-127) -- on the tcgen05 path:
+    logits, every hidden layer and every saved residual bit for bit against the CPU restatement."""
+    from apnn_tc_b200 import nets
+    spec = nets.MODELS[model](n_classes=1000)
+    params = nets.make_params(spec, narrow=True)
+    rng = np.random.default_rng(224)
+    batch = 2
+    images = rng.uniform(-10, 10, size=(batch, 224, 224, 3)).astype(np.float32)
+    want, levels, values = forward_reference(spec, params, images)
+    net = nets.Network(spec, batch, params, use_tcgen05=True)
+    logits = net.forward(torch.from_numpy(images).cuda())
+    net.check()
+    for ls in spec.layers:
+        if ls.kind == "conv" and ls.quantise:
+            assert np.array_equal(net.levels_of(ls.name).cpu().numpy(), levels[ls.name]), ls.name
+        if ls.name in net.res:
+            got = net.res[ls.name].cpu().numpy().astype(np.int32)
+            assert np.array_equal(got.reshape(values[ls.name].shape), values[ls.name]), ls.name
+    assert np.array_equal(to_host(logits, np.int32), want)
+    assert len(np.unique(levels[spec.layers[-2].name])) > 1
+
+
+@pytest.mark.parametrize("model,batch", [("alexnet", 128), ("resnet18", 128), ("resnet18", 1024), ("vgg_variant", 128)])
+def test_benchmark_batches_match_reference(cuda_device, model, batch):
+    """The batches the benchmark runs (AlexNet 128; ResNet-18 1024 on one GPU and 128 per GPU on eight;
+    the VGG-variant) select other kernels than a batch of 2 does (CTA-pair convolutions, resident
+    filters, split-K): the batch is filled with copies of 8 distinct images, whose reference logits
+    every copy must reproduce (images are independent), through eager launches and a graph replay."""
+    from apnn_tc_b200 import nets
+    spec = nets.MODELS[model](n_classes=1000)
+    params = nets.make_params(spec, narrow=True)
+    rng = np.random.default_rng(batch)
+    distinct = rng.uniform(-10, 10, size=(8, 224, 224, 3)).astype(np.float32)
+    want, _, _ = forward_reference(spec, params, distinct)
+    net = nets.Network(spec, batch, params, use_tcgen05=True)
+    images = torch.from_numpy(distinct).cuda().repeat(batch // 8, 1, 1, 1).contiguous()
+    logits = net.forward(images).clone()
+    net.check()
+    expect = torch.from_numpy(want).cuda().repeat(batch // 8, 1)
+    assert torch.equal(logits, expect)
+    net.capture(images)
+    assert torch.equal(net.replay(), expect)
+    net.check()
+
+
 def test_graph_replay_matches_eager(cuda_device):
     from apnn_tc_b200 import nets
     spec = nets.resnet18_spec(n_classes=100)
