@@ -2,7 +2,11 @@
 // dispatch.  No entry point allocates device memory except the host-buffer front end's
 // handle (host_front.cu), and none falls back to a CPU path.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <utility>
+#include <vector>
 
 #include "../../include/apnn_b200.h"
 #include "api_internal.h"
@@ -57,6 +61,41 @@ apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, i
   for (int i = 0; i < e->n_peer_out; i++)
     if (!e->peer_out[i] || (reinterpret_cast<uintptr_t>(e->peer_out[i]) & 15u)) return APNN_ERR_INVALID_ARG;
   return APNN_OK;
+}
+
+cudaError_t ensure_max_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::vector<std::pair<const void*, int>> done;   // (kernel, device)
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const auto& d : done)
+    if (d.first == kernel && d.second == dev) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.emplace_back(kernel, dev);
+  return e;
+}
+
+void* tensor_map_encoder() {
+  static std::once_flag once;
+  static void* fn = nullptr;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = ptr;
+  });
+  return fn;
+}
+
+int pdl_attribute(cudaLaunchAttribute* attrs) {
+  static const bool enabled = [] { const char* v = getenv("APNN_PDL"); return !(v && v[0] == '0'); }();
+  if (!enabled) return 0;
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = 1;
+  return 1;
 }
 
 // Plane counts the int8 (tcgen05) path takes: every level of up to 8 bits fits one byte.

@@ -5,6 +5,8 @@
 // of each plane, the eight lanes that share an output word OR their slices together with
 // three shuffles, and one lane per word stores it.  Channel c lands in bit 31-(c%32) of
 // word c/32, planes outermost, rows padded with zero channels to a multiple of 128.
+#include <cstring>
+
 #include "../../include/apnn_b200.h"
 #include "api_internal.h"
 
@@ -603,6 +605,7 @@ __global__ void __launch_bounds__(256) maxpool2x2_i8_kernel(const uint8_t* __res
   const int cv = C >> 4;   // 16-byte vectors per pixel
   const long long total = (long long)B * Ho * Wo * cv;
   const int Wi = 2 * Wo + 2 * ih, Hi = 2 * Ho + 2 * ih, Wq = Wo + 2 * oh, Hq = Ho + 2 * oh;
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // launched as a programmatic dependent of the producing layer
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
     const int v = (int)(t % cv);
     long long pix = t / cv;
@@ -638,6 +641,7 @@ __global__ void __launch_bounds__(256) requantize_i32_kernel(const int32_t* __re
   const int pos = 4 * ((31 - lane) & 7) + ((31 - lane) >> 3);      // byte of element `lane` in the operand order
   const int g = warp % groups, r0 = warp / groups;
   if (r0 >= row_lanes) return;   // surplus warps of the last block (the whole warp leaves together)
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // launched as a programmatic dependent of the producing GEMM
   {
     int32_t thr[7];
 #pragma unroll
@@ -816,9 +820,16 @@ apnn_status apnn_maxpool2x2_i8(void* stream, const void* in_i8, void* out_i8, in
   const long long total = (long long)B * (H / 2) * (W / 2) * (C / 16);
   long long nb = (total + 255) / 256, cap = (long long)device_sm_count() * 32;
   if (nb > cap) nb = cap;
-  maxpool2x2_i8_kernel<<<(unsigned)nb, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint8_t*>(in_i8), reinterpret_cast<uint8_t*>(out_i8), B, H / 2, W / 2, C, in_halo, out_halo);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)nb, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  cfg.attrs = attr;
+  cfg.numAttrs = (unsigned)pdl_attribute(attr);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, maxpool2x2_i8_kernel, reinterpret_cast<const uint8_t*>(in_i8),
+                                     reinterpret_cast<uint8_t*>(out_i8), B, H / 2, W / 2, C, in_halo, out_halo);
   if (e != cudaSuccess) return cuda_fail(e, "maxpool2x2_i8 launch");
   return APNN_OK;
 }
@@ -836,15 +847,22 @@ apnn_status apnn_requantize_i32(void* stream, const int32_t* values, void* out, 
   if ((reinterpret_cast<uintptr_t>(values) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) return APNN_ERR_ALIGNMENT;
   // every column group gets the same number of warps; more of them when there are many rows
   const int groups = N / 32;
-  long long per_group = (rows + 63) / 64;
+  long long per_group = (rows + 7) / 8;   // at least 8 rows per warp, fewer warps only when the device is full
   const long long cap = (long long)device_sm_count() * 64 / groups;
   if (per_group > cap) per_group = cap;
   if (per_group < 1) per_group = 1;
   const long long warps = per_group * groups;
   const unsigned nb = (unsigned)((warps + 7) / 8);
-  requantize_i32_kernel<<<nb, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      values, out, rows, N, epi->out_mode, epi->out_bits, epi->thresholds, epi->out_i8);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(nb, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  cfg.attrs = attr;
+  cfg.numAttrs = (unsigned)pdl_attribute(attr);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, requantize_i32_kernel, values, out, (long long)rows, N, (int)epi->out_mode,
+                                     (int)epi->out_bits, epi->thresholds, (int)epi->out_i8);
   if (e != cudaSuccess) return cuda_fail(e, "requantize_i32 launch");
   return APNN_OK;
 }

@@ -127,7 +127,6 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const int num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    if (blockIdx.x == 0) *p.error_flag = 0;
     for (int i = 0; i < NA; i++) {
       mbar_init(afull_bar(i), 1);
       mbar_init(aempty_bar(i), 1);
@@ -151,6 +150,10 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   cluster_sync_all();  // both CTAs' barriers exist before anything remote touches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // everything above overlapped the previous kernel's tail; from here on its results are visible
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (threadIdx.x == 0 && blockIdx.x == 0) *p.error_flag = 0;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
 
@@ -314,15 +317,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 // int8 rows [rows][K], boxes of 128 bytes x box_rows rows, 128-byte swizzle
 bool make_rows_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return false;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
+  EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(tensor_map_encoder());
+  if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K};
   cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
@@ -367,17 +363,9 @@ apnn_status tc5_conv_i8_pair(cudaStream_t s, const uint8_t* X8, const uint8_t* W
   if (!make_rows_map(&map_a, X8, flat_rows, CIN, box_rows) ||
       !make_rows_map(&map_b, W8, COUT, (long long)R * R * CIN, HALF))
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
-  static bool attr_set[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  cudaError_t e;
-  if (dev >= 16 || !attr_set[dev]) {
-    e = cudaFuncSetAttribute(tc5_conv_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(tc5_conv_pair_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return cuda_fail(e, "tc5 conv pair smem attribute");
-    if (dev < 16) attr_set[dev] = true;
-  }
+  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_conv_pair_kernel<1>), SMEM_BYTES);
+  if (e == cudaSuccess) e = ensure_max_smem(reinterpret_cast<const void*>(tc5_conv_pair_kernel<3>), SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_fail(e, "tc5 conv pair smem attribute");
   ConvPairParams p;
   memset(&p, 0, sizeof(p));
   p.out = reinterpret_cast<uint8_t*>(Out);
@@ -410,13 +398,13 @@ apnn_status tc5_conv_i8_pair(cudaStream_t s, const uint8_t* X8, const uint8_t* W
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 1 + (unsigned)pdl_attribute(attr + 1);
   e = R == 3 ? cudaLaunchKernelEx(&cfg, tc5_conv_pair_kernel<3>, map_a, map_b, p)
              : cudaLaunchKernelEx(&cfg, tc5_conv_pair_kernel<1>, map_a, map_b, p);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_conv_pair launch");

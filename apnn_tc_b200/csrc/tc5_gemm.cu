@@ -35,6 +35,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "api_internal.h"
 #include "apnn_device.cuh"
@@ -159,8 +160,9 @@ struct Tc5Params {
   // shared-memory plan (chosen on the host)
   int stages;            // ring depth
   int kgroup;            // K blocks per stage (one barrier round trip and one commit per group)
-  int splits, kper;      // split-K instantiation only (GEMM, int32 output): `splits` CTAs share a tile, each sums
-                         // kper K blocks and adds its part to the zeroed output with atomic adds
+  int splits;            // split-K instantiation only: the `splits` CTAs of a cluster share one output tile, each
+                         // sums its share of the K blocks into its own TMEM; the partial sums meet in shared memory
+                         // (distributed shared memory stores) before the epilogue
   int b_resident;        // 1: the whole B operand (one tile column, all K blocks) stays in shared
                          // memory for the life of the CTA and the ring carries A tiles only
   // flat convolution (is_conv == 2): stride 1, no pooling.  Output positions are the flattened
@@ -311,6 +313,31 @@ __device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a
   return true;
 }
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Cluster-wide barrier with release / acquire semantics (all threads of all CTAs of the cluster).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
 // EPI selects an epilogue compiled for one family of uses (the code of the other paths is
 // compiled out; these warps are bound by instruction fetch and issue, so the smaller bodies
 // are measurably faster):
@@ -320,6 +347,13 @@ __device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a
 //   3  as 2 plus residual in / out of either width (second convolution of a ResNet block)
 //   4  as 3 with every residual tensor present being int16 (no int32 residual code)
 //   5  int32 output only (shortcut convolutions, logits)
+//
+// SPLITK: the kernel is launched as clusters of p.splits CTAs (2, 4 or 8) with one output tile per
+// cluster, for problems with fewer tiles than SMs and a long K.  CTA r of a cluster accumulates K
+// blocks [r*kper, (r+1)*kper) in its own TMEM.  Then, with the operand ring idle, every CTA splits
+// its 128 x BN partial tile into p.splits column slices and stores slice o into slot r of CTA o's
+// shared memory (st.shared::cluster); after a cluster barrier CTA o sums the slots of its slice
+// and runs the ordinary epilogue on those columns.  No atomics, no global scratch, no second launch.
 template <int BN, int BKB, bool SPLITK = false, int EPI = 0>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -358,7 +392,6 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    if (blockIdx.x == 0) *p.error_flag = 0;  // only ever raised after a 2 s wait, long after this store
     for (int s = 0; s < stages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -384,9 +417,23 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // everything above overlapped the previous kernel's tail; from here on its results are visible
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (threadIdx.x == 0 && blockIdx.x == 0) *p.error_flag = 0;  // only ever raised after a 2 s wait, long after this store
 
-  const int mn_tiles = p.tiles_m * p.tiles_n;
-  const int num_tiles = SPLITK ? mn_tiles * p.splits : mn_tiles;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  // split-K: one tile per cluster, K blocks [kb_first, kb_last) per CTA; otherwise tiles round-robin over the grid
+  uint32_t crank = 0;
+  int first_tile = blockIdx.x, tile_step = gridDim.x;
+  int kb_first = 0, kb_last = p.kblocks;
+  if constexpr (SPLITK) {
+    crank = cluster_ctarank();
+    first_tile = (int)blockIdx.x / p.splits;
+    tile_step = (int)gridDim.x / p.splits;
+    kb_first = (int)(((long long)crank * p.kblocks) / p.splits);       // even shares: none is empty
+    kb_last = (int)(((long long)(crank + 1) * p.kblocks) / p.splits);
+  }
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -394,7 +441,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      if (p.b_resident && (int)blockIdx.x < num_tiles) {
+      if (p.b_resident && first_tile < num_tiles) {
         // tiles_n == 1: every tile of this CTA uses the same B rows; fetch all K blocks once
         mbar_expect_tx(bres_bar, bres_bytes);
         for (int kb = 0; kb < p.kblocks; kb++)
@@ -409,7 +456,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t phb = 0;
         const int taps = p.R * p.R;
         const uint32_t blk_bytes = (uint32_t)p.flat_blk_rows * BKB;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
           int tm, tn;
           tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
           const int q0 = tm * BM + p.in_off * p.flat_wp + p.in_off;
@@ -432,17 +479,10 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
       } else
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         int tm, tn;
-        int kb0 = 0, kb1 = p.kblocks;
-        if constexpr (SPLITK) {
-          const int split = tile / mn_tiles;
-          tile_coords(tile - split * mn_tiles, p.tiles_m, p.tiles_n, tm, tn);
-          kb0 = split * p.kper;
-          kb1 = min(p.kblocks, kb0 + p.kper);
-        } else {
-          tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-        }
+        const int kb0 = kb_first, kb1 = kb_last;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         int w0 = 0, h0 = 0, b0 = 0;
         if (p.is_conv) {
           w0 = (tm % p.tiles_w) * p.bw;
@@ -451,6 +491,12 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           b0 = (t2 / p.tiles_h) * p.bb;
         }
         int ti = 0, tj = 0, cb = 0;  // conv: K block = (filter tap row, tap column, BKB-channel block)
+        if (SPLITK && p.is_conv) {
+          cb = kb0 % p.cblocks;
+          const int tap = kb0 / p.cblocks;
+          tj = tap % p.R;
+          ti = tap / p.R;
+        }
         const int wbase = w0 * p.stride + p.in_off, hbase = h0 * p.stride + p.in_off;
         for (int kb = kb0; kb < kb1; kb += kgroup) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
@@ -474,6 +520,11 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       if (!ok) atomicExch(p.error_flag, 1);
     }
+    if constexpr (SPLITK) {   // the two cluster barriers of the partial-sum exchange (every thread takes part)
+      __syncwarp();
+      cluster_sync_all();
+      cluster_sync_all();
+    }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
@@ -481,14 +532,14 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t ph = 0;
       uint32_t tl = 0;
       bool ok = true;
-      if (p.b_resident && (int)blockIdx.x < num_tiles) {
+      if (p.b_resident && first_tile < num_tiles) {
         ok = mbar_wait(bres_bar, 0u);
         tc_fence_after();
       }
       if (flat) {
         int sb = 0;
         uint32_t phb = 0;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, tl++) {
           const uint32_t acc = tl & 1u;
           const uint32_t aph = (tl >> 1) & 1u;
           if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
@@ -550,17 +601,13 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (ok) tc_commit(tfull_bar(acc));
         }
       } else
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, tl++) {
         const uint32_t acc = tl & 1u;
         const uint32_t aph = (tl >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        int kb0 = 0, kb1 = p.kblocks;
-        if constexpr (SPLITK) {
-          kb0 = (tile / mn_tiles) * p.kper;
-          kb1 = min(p.kblocks, kb0 + p.kper);
-        }
+        const int kb0 = kb_first, kb1 = kb_last;
         for (int kb = kb0; kb < kb1; kb += kgroup) {
           if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
           tc_fence_after();
@@ -579,6 +626,11 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (ok) tc_commit(tfull_bar(acc));  // accumulator complete
       }
       if (!ok) atomicExch(p.error_flag, 2);
+    }
+    if constexpr (SPLITK) {
+      __syncwarp();
+      cluster_sync_all();
+      cluster_sync_all();
     }
   } else {
     // ---------------- epilogue warps (2..9) ----------------
@@ -606,6 +658,11 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     constexpr int THR_CHUNKS = BN >= 64 ? BN / 64 : 1;   // chunks per epilogue warp
     int4 thr_of[THR_CHUNKS];
     int thr_tn = -1;
+    // 32-column chunks of the tile this CTA finishes: all of them, or (split-K) its slice of the cluster's tile
+    const int slice_chunks = SPLITK ? (BN / 32) / p.splits : BN / 32;
+    const int c_first = SPLITK ? (int)crank * slice_chunks : 0;
+    const int c_end = c_first + slice_chunks;
+    const int c_begin = c_first + half;   // this warp's first chunk; it takes every second one
     // Row destinations of a tile: this lane's own row, and (for int32 rows and residuals) the
     // rows it serves in the coalesced 4-lanes-per-row accesses.
     struct TileRows {
@@ -616,7 +673,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     };
     auto rows_of_tile = [&](int tile, TileRows& t) {
       int tm;
-      tile_coords(SPLITK ? tile % mn_tiles : tile, p.tiles_m, p.tiles_n, tm, t.tn);
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, t.tn);
       t.dst = row_destination(p, tm, quarter * 32 + lane, in_box);
       if constexpr (!(C_NORES && C_NOINT32)) {
 #pragma unroll
@@ -658,12 +715,12 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     };
     TileRows cur, nxt;
-    if ((int)blockIdx.x < num_tiles) {
-      rows_of_tile(blockIdx.x, cur);
-      if constexpr (!C_NORES) fetch_residual(cur, half);
+    if (first_tile < num_tiles) {
+      rows_of_tile(first_tile, cur);
+      if constexpr (!C_NORES) fetch_residual(cur, c_begin);
     }
     nxt = cur;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tl++) {
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, tl++) {
       const int tn = cur.tn;
       const uint32_t acc = tl & 1u;
       const uint32_t aph = (tl >> 1) & 1u;
@@ -671,7 +728,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // this lane's column of each chunk the warp drains; reloaded only when the tile column changes
 #pragma unroll
         for (int i = 0; i < THR_CHUNKS; i++) {
-          const int col = tn * BN + (half + 2 * i) * 32 + lane;
+          const int col = tn * BN + (c_begin + 2 * i) * 32 + lane;
           int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
           if (col < p.N) {
             const int32_t* T = p.thresholds + (long long)col * nl;
@@ -688,28 +745,73 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const long long(&row_of)[4] = cur.row_of;
       const long long(&dense_of)[4] = cur.dense_of;
       const bool(&ok_of)[4] = cur.ok_of;
-      const bool has_next = tile + (int)gridDim.x < num_tiles;
+      const bool has_next = tile + tile_step < num_tiles;
       bool nxt_ready = false, nxt_fetched = false;
       if (C_NORES && has_next) {   // no residuals: nothing to overlap, do it before the wait
-        rows_of_tile(tile + gridDim.x, nxt);
+        rows_of_tile(tile + tile_step, nxt);
         nxt_ready = true;
       }
-      if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
+      const bool acc_ok = mbar_wait(tfull_bar(acc), aph);
+      if (!acc_ok) ok = false;
+      if (!SPLITK && !acc_ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      // split-K exchange area: the operand ring, idle once every CTA of the cluster has its accumulator.
+      // Slot s (the partial sums of CTA s) of this CTA's slice: 16-byte groups of 4 columns, group g of row r
+      // at ((s * groups + g) * 128 + r) * 16 -- a warp's accesses are 512 contiguous bytes.
+      const uint32_t xch = ring;
+      const int row_in_tile = quarter * 32 + lane;
+      if constexpr (SPLITK) {
+        __syncwarp();
+        cluster_sync_all();   // all accumulators of the cluster are complete, all operand rings idle
+        const int groups = slice_chunks * 8;   // 16-byte groups per row of a slice
+        if (acc_ok) {
 #pragma unroll 1
-      for (int c = half; c < BN / 32; c += 2) {
+          for (int c = half; c < BN / 32; c += 2) {
+            uint32_t v[32];
+            tmem_ld32(taddr + c * 32, v);
+            tmem_ld_wait();
+            const int owner = c / slice_chunks;
+            const int g0 = (c - owner * slice_chunks) * 8;
+            const uint32_t dst = map_to_cta(xch, (uint32_t)owner) +
+                                 (uint32_t)((((int)crank * groups + g0) * BM + row_in_tile) * 16);
+#pragma unroll
+            for (int g = 0; g < 8; g++)
+              st_cluster_v4(dst + (uint32_t)(g * BM * 16), v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          }
+        }
+        __syncwarp();
+        cluster_sync_all();   // every slot of every slice has landed
+        if (!ok) break;
+      }
+#pragma unroll 1
+      for (int c = c_begin; c < c_end; c += 2) {
         const int col0 = tn * BN + c * 32;
         if (col0 >= p.N) continue;  // uniform over the warp
         uint32_t v[32];
         __syncwarp();   // lanes that left the previous chunk early rejoin before the warp-wide TMEM load
-        tmem_ld32(taddr + c * 32, v);
+        if constexpr (SPLITK) {
+          const int groups = slice_chunks * 8;
+          const int g0 = (c - c_first) * 8;
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = 0u;
+          for (int sl = 0; sl < p.splits; sl++) {
+            const uint32_t src = xch + (uint32_t)(((sl * groups + g0) * BM + row_in_tile) * 16);
+#pragma unroll
+            for (int g = 0; g < 8; g++) {
+              const uint4 x = ld_shared_v4(src + (uint32_t)(g * BM * 16));
+              v[4 * g] += x.x; v[4 * g + 1] += x.y; v[4 * g + 2] += x.z; v[4 * g + 3] += x.w;
+            }
+          }
+        } else {
+          tmem_ld32(taddr + c * 32, v);
+        }
         if (thr_staged) {
           __syncwarp();   // the previous chunk's readers are done
-          thr_s[lane] = thr_of[c >> 1];
+          thr_s[lane] = thr_of[(c - c_first) >> 1];
           __syncwarp();
         }
-        tmem_ld_wait();
+        if constexpr (!SPLITK) tmem_ld_wait();
         if (!C_NOPOOL && p.pool != POOL_NONE) {
           // the four pixels of a window are lanes l, l^1 (next column) and l^bw, l^bw^1 (next row)
 #pragma unroll
@@ -740,8 +842,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 v[8 * j + 4] += lo16(x.z); v[8 * j + 5] += hi16(x.z); v[8 * j + 6] += lo16(x.w); v[8 * j + 7] += hi16(x.w);
               }
               __syncwarp();
-              if (c + 2 < BN / 32) fetch_residual(cur, c + 2);
-              else if (has_next) { rows_of_tile(tile + gridDim.x, nxt); fetch_residual(nxt, half); nxt_ready = nxt_fetched = true; }
+              if (c + 2 < c_end) fetch_residual(cur, c + 2);
+              else if (has_next) { rows_of_tile(tile + tile_step, nxt); fetch_residual(nxt, c_begin); nxt_ready = nxt_fetched = true; }
             } else if (!C_RES16 && p.residual_in != nullptr) {
 #pragma unroll
               for (int hf = 0; hf < 2; hf++) {
@@ -756,8 +858,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
                 __syncwarp();
               }
-              if (c + 2 < BN / 32) fetch_residual(cur, c + 2);   // the next chunk's rows, in flight during this one's tail
-              else if (has_next) { rows_of_tile(tile + gridDim.x, nxt); fetch_residual(nxt, half); nxt_ready = nxt_fetched = true; }
+              if (c + 2 < c_end) fetch_residual(cur, c + 2);   // the next chunk's rows, in flight during this one's tail
+              else if (has_next) { rows_of_tile(tile + tile_step, nxt); fetch_residual(nxt, c_begin); nxt_ready = nxt_fetched = true; }
             }
             if (p.residual_out != nullptr && (C_RES16 || p.res16_out)) {
               int16_t* O16 = reinterpret_cast<int16_t*>(p.residual_out);
@@ -805,15 +907,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               }
           }
         }
-        if (SPLITK) {
-          // split-K (int32 output only): this CTA's part of the sum goes into the zeroed output
-          if (row_ok) {
-            int32_t* D = reinterpret_cast<int32_t*>(p.out) + row * p.N + col0;
-#pragma unroll
-            for (int j = 0; j < 32; j++)
-              if (col0 + j < p.N) atomicAdd(D + j, (int32_t)v[j]);
-          }
-        } else if (C_INT32 || (!C_NOINT32 && p.out_mode == OUT_INT32)) {
+        if (C_INT32 || (!C_NOINT32 && p.out_mode == OUT_INT32)) {
           if (whole) {
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
@@ -884,9 +978,9 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       if (has_next) {
-        if (!nxt_ready) rows_of_tile(tile + gridDim.x, nxt);
+        if (!nxt_ready) rows_of_tile(tile + tile_step, nxt);
         if constexpr (!C_NORES) {
-          if (!nxt_fetched) fetch_residual(nxt, half);
+          if (!nxt_fetched) fetch_residual(nxt, c_begin);
         }
         cur = nxt;
       }
@@ -908,17 +1002,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
+EncodeTiledFn encode_tiled_fn() { return reinterpret_cast<EncodeTiledFn>(tensor_map_encoder()); }
 
 // rows x K bytes, row-major; box = box_rows x span bytes (span = 128 or 64 = the swizzle span), zero fill outside
 bool make_operand_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows, int span = 128) {
@@ -964,7 +1048,7 @@ void plan_smem(Tc5Params& p, int* smem_bytes) {
   p.b_resident = 0;
   int stage = Cfg::A_STAGE_BYTES + Cfg::B_STAGE_BYTES;
   long long fixed = 0;
-  if (p.is_conv && p.tiles_n == 1 && p.tiles_m >= 4 * device_sm_count() &&
+  if (p.splits <= 1 && p.is_conv && p.tiles_n == 1 && p.tiles_m >= 4 * device_sm_count() &&
       bres + 3LL * Cfg::A_STAGE_BYTES <= room) {
     p.b_resident = 1;
     stage = Cfg::A_STAGE_BYTES;
@@ -975,7 +1059,7 @@ void plan_smem(Tc5Params& p, int* smem_bytes) {
   // not the MMA time, bounds tiles whose K block is only a few KiB
   int kgroup = 1;
   for (int g = 3; g >= 2; g--)
-    if (p.kblocks % g == 0 && stage <= 16384 && (room - fixed) / ((long long)g * stage) >= 4) { kgroup = g; break; }
+    if (p.splits <= 1 && p.kblocks % g == 0 && stage <= 16384 && (room - fixed) / ((long long)g * stage) >= 4) { kgroup = g; break; }
   p.kgroup = kgroup;
   stage *= kgroup;
   int stages = (int)((room - fixed) / stage);
@@ -1012,43 +1096,61 @@ void plan_flat(Tc5Params& p, int* smem_bytes) {
   *smem_bytes = (int)(Cfg::FIXED_BYTES + fixed + na * a_bytes);
 }
 
+// One launch through cudaLaunchKernelEx: programmatic dependent launch (the kernels wait with
+// griddepcontrol.wait before touching their inputs) and, for split-K, the cluster shape.
+template <class Kernel>
+cudaError_t launch_kernel(Kernel kernel, cudaStream_t s, int grid, int smem, int cluster, const CUtensorMap& map_a,
+                          const CUtensorMap& map_b, const Tc5Params& p) {
+  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(kernel), SMEM_LIMIT);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  int na = pdl_attribute(attr);
+  if (cluster > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)cluster;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    na++;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = (unsigned)na;
+  return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p);
+}
+
 template <int BN, int BKB>
 cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid) {
-  static bool attr_set[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 16 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tc5_gemm_kernel<BN, BKB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SMEM_LIMIT);
-    if (e != cudaSuccess) return e;
-    if (dev < 16) attr_set[dev] = true;
-  }
   int smem = 0;
   if (p.is_conv == 2) plan_flat<BN, BKB>(p, &smem);
   else plan_smem<BN, BKB>(p, &smem);
+  if (p.splits > 1) {
+    // split-K over clusters: one instantiation (run-time epilogue) per tile width with 128-byte rows
+    if constexpr (BKB == 128 && BN >= 128) {
+      if ((long long)p.stages * p.kgroup * (TileCfg<BN, BKB>::A_STAGE_BYTES + TileCfg<BN, BKB>::B_STAGE_BYTES) <
+          (long long)BM * BN * 4)
+        return cudaErrorInvalidConfiguration;   // the exchange area is the operand ring
+      return launch_kernel(tc5_gemm_kernel<BN, BKB, true, 0>, s, grid, smem, p.splits, map_a, map_b, p);
+    } else {
+      return cudaErrorInvalidConfiguration;
+    }
+  }
   const bool quantising = p.out_mode != APNN_OUT_INT32 && p.pool == APNN_POOL_NONE;
   const bool residuals = p.residual_in || p.residual_out;
   const bool thr_i8 = p.out_mode == APNN_OUT_THRESHOLDS && p.out_bits <= 2 && p.out_i8;
   const bool all16 = (!p.residual_in || p.res16_in) && (!p.residual_out || p.res16_out);
   const bool int32_only = p.out_mode == APNN_OUT_INT32 && p.pool == APNN_POOL_NONE && !residuals;
   const int epi = int32_only ? 5 : !quantising ? 0 : (thr_i8 ? (residuals ? (all16 ? 4 : 3) : 2) : (residuals ? 0 : 1));
-  auto launch = [&](auto kernel, bool* attr_done) -> cudaError_t {
-    if (dev >= 16 || !attr_done[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
-      if (e != cudaSuccess) return e;
-      if (dev < 16) attr_done[dev] = true;
-    }
-    kernel<<<grid, THREADS, smem, s>>>(map_a, map_b, p);
-    return cudaGetLastError();
-  };
-  static bool done1[16] = {}, done2[16] = {}, done3[16] = {}, done4[16] = {}, done5[16] = {};
-  if (epi == 1) return launch(tc5_gemm_kernel<BN, BKB, false, 1>, done1);
-  if (epi == 2) return launch(tc5_gemm_kernel<BN, BKB, false, 2>, done2);
-  if (epi == 3) return launch(tc5_gemm_kernel<BN, BKB, false, 3>, done3);
-  if (epi == 4) return launch(tc5_gemm_kernel<BN, BKB, false, 4>, done4);
-  if (epi == 5) return launch(tc5_gemm_kernel<BN, BKB, false, 5>, done5);
-  tc5_gemm_kernel<BN, BKB><<<grid, THREADS, smem, s>>>(map_a, map_b, p);
-  return cudaGetLastError();
+  if (epi == 1) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 1>, s, grid, smem, 1, map_a, map_b, p);
+  if (epi == 2) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 2>, s, grid, smem, 1, map_a, map_b, p);
+  if (epi == 3) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 3>, s, grid, smem, 1, map_a, map_b, p);
+  if (epi == 4) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 4>, s, grid, smem, 1, map_a, map_b, p);
+  if (epi == 5) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 5>, s, grid, smem, 1, map_a, map_b, p);
+  return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 0>, s, grid, smem, 1, map_a, map_b, p);
 }
 
 cudaError_t launch_tc5_any(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid,
@@ -1074,6 +1176,67 @@ int pick_bn(long long tiles_m, int N, int sms) {
   double w256 = (double)((t256 + sms - 1) / sms);
   double w128 = 0.5 * (double)((t128 + sms - 1) / sms);
   return w128 < w256 ? 128 : 256;
+}
+
+// How many clusters of `cs` CTAs of the split-K kernel the device holds at once (0 on error); cached.
+int cluster_capacity(int bn, int cs) {
+  static std::mutex mu;
+  static int cache[16][2][4] = {};   // [device][bn == 256][log2 cs], value + 1
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16) return 0;
+  const int li = cs == 2 ? 1 : cs == 4 ? 2 : 3, bi = bn == 256 ? 1 : 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev][bi][li]) return cache[dev][bi][li] - 1;
+  const void* kernel = bn == 256 ? reinterpret_cast<const void*>(tc5_gemm_kernel<256, 128, true, 0>)
+                                 : reinterpret_cast<const void*>(tc5_gemm_kernel<128, 128, true, 0>);
+  int n = 0;
+  if (ensure_max_smem(kernel, SMEM_LIMIT) == cudaSuccess) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(cs * device_sm_count()), 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_LIMIT;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+  }
+  cache[dev][bi][li] = n + 1;
+  return n;
+}
+
+// Split-K over clusters pays when a problem has far fewer tiles than SMs and a long K.  Cost of a
+// plan in shared-memory traffic units (what bounds the MMA loop): waves x K blocks per CTA x
+// (128 + bn) bytes per K byte, plus about four K blocks' worth for the partial-sum exchange.  Only
+// plans whose clusters are all resident at once are considered, and a split must beat the unsplit
+// plan by a tenth.  Returns the cluster size (1 = no split) and may widen *bn.
+int pick_split(long long tiles_m, int N, int kblocks, int sms, int* bn) {
+  static const bool disabled = [] { const char* v = getenv("APNN_SPLITK"); return v && v[0] == '0'; }();
+  if (disabled || N <= 64 || kblocks < 8) return 1;
+  const long long plain_tiles = tiles_m * ((N + *bn - 1) / *bn);
+  if (plain_tiles * 2 > sms) return 1;
+  const long long plain = ((plain_tiles + sms - 1) / sms) * kblocks * (128 + *bn);
+  long long best = plain * 9 / 10;
+  int best_bn = *bn, best_cs = 1;
+  for (int cand = 128; cand <= 256; cand *= 2) {
+    if (cand == 256 && N <= 128) break;
+    const long long tiles = tiles_m * ((N + cand - 1) / cand);
+    for (int cs = 2; cs <= 8; cs *= 2) {
+      if (cs > cand / 32 || kblocks / cs < 4 || tiles * cs > sms) break;
+      if (tiles > cluster_capacity(cand, cs)) break;
+      const long long cost = (long long)((kblocks + cs - 1) / cs + 4) * (128 + cand);
+      if (cost < best) { best = cost; best_bn = cand; best_cs = cs; }
+    }
+  }
+  *bn = best_bn;
+  return best_cs;
 }
 
 uint32_t make_idesc(bool a_signed, bool b_signed, int bn) {
@@ -1147,13 +1310,13 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   memset(&p, 0, sizeof(p));
   p.tiles_m = (M + BM - 1) / BM;
   int bn = pick_bn(p.tiles_m, N, sms);
-  const int out_mode_ = epi ? epi->out_mode : APNN_OUT_INT32;
-  const bool plain_int32 = out_mode_ == APNN_OUT_INT32 && !(epi && (epi->residual_in || epi->residual_out));
+  // few tiles and a long K (the fully connected layers of a network at a small batch): split K over
+  // the CTAs of a cluster, whatever the epilogue
+  const int splits = pick_split(p.tiles_m, N, K / BK, sms, &bn);
+  // otherwise a skinny problem that leaves more than half of the SMs idle even with 128-wide tiles is
+  // bound by streaming the B operand once: 64-wide tiles put twice as many SMs on that stream
   const long long t128 = (long long)p.tiles_m * ((N + 127) / 128);
-  const bool split_k = bn == 128 && plain_int32 && t128 * 8 <= sms && K / BK >= 32;
-  // a skinny problem that leaves more than half of the SMs idle even with 128-wide tiles is bound by
-  // streaming the B operand once: 64-wide tiles put twice as many SMs on that stream
-  if (bn == 128 && !split_k && t128 * 2 <= sms) bn = 64;
+  if (splits == 1 && bn == 128 && t128 * 2 <= sms) bn = 64;
   CUtensorMap map_a, map_b;
   if (!make_operand_map(&map_a, A8, M, K, BM) || !make_operand_map(&map_b, B8, N, K, bn)) {
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -1175,30 +1338,9 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
   p.idesc = make_idesc(a_signed, b_signed, bn);
   long long tiles = (long long)p.tiles_m * p.tiles_n;
-  if (split_k) {
-    // a handful of tiles with a long K (the first fully connected layer of a network at a small
-    // batch): split K over the idle SMs; the parts meet in the zeroed output through atomic adds.
-    // With 32 tiles or more the atomics cost more than the idle SMs gain (measured on AlexNet's
-    // 9216 -> 4096 layer at batch 128).
-    int splits = (int)(sms / tiles);
-    if (splits > p.kblocks / 8) splits = p.kblocks / 8;
-    p.kper = (p.kblocks + splits - 1) / splits;
-    p.splits = (p.kblocks + p.kper - 1) / p.kper;
-    e = cudaMemsetAsync(D, 0, (size_t)M * N * sizeof(int32_t), s);
-    if (e != cudaSuccess) return cuda_fail(e, "split-K output reset");
-    tiles *= p.splits;
-    static bool attr_set[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 16 || !attr_set[dev]) {
-      e = cudaFuncSetAttribute(tc5_gemm_kernel<128, 128, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
-      if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm attribute");
-      if (dev < 16) attr_set[dev] = true;
-    }
-    int smem = 0;
-    plan_smem<128, 128>(p, &smem);
-    tc5_gemm_kernel<128, 128, true, 0><<<(int)(tiles < sms ? tiles : sms), THREADS, smem, s>>>(map_a, map_b, p);
-    e = cudaGetLastError();
+  if (splits > 1) {
+    p.splits = splits;
+    e = launch_tc5_any(s, map_a, map_b, p, (int)tiles * splits, bn, 128);
     if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm split-K launch");
     return APNN_OK;
   }
@@ -1305,13 +1447,16 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   // ... unless that needs more waves of tiles over the SMs than the pixel boxes would (the ring
   // positions are computed and dropped: tiny images, or a tile count just past a multiple of the
   // SM count).  Cost of a formulation = waves x tile width.
-  auto cost = [&](long long tiles_m) {
-    const int bn_ = pick_bn(tiles_m, COUT, sms);
-    const long long tiles = tiles_m * ((COUT + bn_ - 1) / bn_);
-    return ((tiles + sms - 1) / sms) * bn_;
+  // The pixel-box formulation can also split K over the CTAs of a cluster when it has few tiles.
+  const int kblocks_all = R * R * p.cblocks;
+  auto cost = [&](long long tiles_m, bool may_split) {
+    int bn_ = pick_bn(tiles_m, COUT, sms);
+    const int cs = (may_split && span == 128) ? pick_split(tiles_m, COUT, kblocks_all, sms, &bn_) : 1;
+    const long long tiles = tiles_m * ((COUT + bn_ - 1) / bn_) * cs;
+    return ((tiles + sms - 1) / sms) * bn_ / cs;
   };
   // (with many waves a few per cent more tiles still win: a flat tile loads 5-8x fewer rows)
-  const long long cost_box = cost(p.tiles_m), cost_flat = cost((flat_rows + BM - 1) / BM);
+  const long long cost_box = cost(p.tiles_m, true), cost_flat = cost((flat_rows + BM - 1) / BM, false);
   bool flat = stride == 1 && pool == APNN_POOL_NONE && flat_rows < 0x7fffff00LL &&
               (cost_flat <= cost_box || (cost_box >= 8 * 64 && cost_flat * 100 <= cost_box * 105));
   if (flat) {
@@ -1336,7 +1481,8 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
       p.flat_blk_rows = blk_rows;
     }
   }
-  const int bn = pick_bn(p.tiles_m, COUT, sms);
+  int bn = pick_bn(p.tiles_m, COUT, sms);
+  const int splits = (!flat && span == 128) ? pick_split(p.tiles_m, COUT, kblocks_all, sms, &bn) : 1;
   CUtensorMap map_a, map_b;
   const bool maps_ok =
       (flat ? make_operand_map(&map_a, X8, flat_rows, CIN, p.flat_blk_rows, span)
@@ -1362,6 +1508,10 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.idesc = make_idesc(false, w_signed, bn);  // A = activations (unsigned), B = filter
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < sms ? tiles : sms);
+  if (splits > 1) {
+    p.splits = splits;
+    grid = (int)tiles * splits;
+  }
   e = launch_tc5_any(s, map_a, map_b, p, grid, bn, span);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_conv launch");
   return APNN_OK;

@@ -130,7 +130,6 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const int num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    if (blockIdx.x == 0) *p.error_flag = 0;
     for (int s = 0; s < STAGES; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -150,6 +149,10 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   cluster_sync_all();  // both CTAs' barriers exist before anything remote touches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // everything above overlapped the previous kernel's tail; from here on its results are visible
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (threadIdx.x == 0 && blockIdx.x == 0) *p.error_flag = 0;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
 
@@ -343,15 +346,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 bool make_half_map(CUtensorMap* map, const void* base, long long rows, long long K) {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return false;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
+  EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(tensor_map_encoder());
+  if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K};
   cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)HALF};
@@ -373,15 +369,8 @@ apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B
   CUtensorMap map_a, map_b;
   if (!make_half_map(&map_a, A8, M, K) || !make_half_map(&map_b, B8, N, K))
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
-  static bool attr_set[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  cudaError_t e;
-  if (dev >= 16 || !attr_set[dev]) {
-    e = cudaFuncSetAttribute(tc5_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return cuda_fail(e, "tc5 pair smem attribute");
-    if (dev < 16) attr_set[dev] = true;
-  }
+  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel), SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_fail(e, "tc5 pair smem attribute");
   PairParams p;
   memset(&p, 0, sizeof(p));
   p.out = D;
@@ -414,13 +403,13 @@ apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 1 + (unsigned)pdl_attribute(attr + 1);
   e = cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel, map_a, map_b, p);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm_pair launch");
   return APNN_OK;

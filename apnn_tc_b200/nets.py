@@ -388,19 +388,8 @@ class Network:
                 self.i8_out[ls.name] = True
         # pooled stride-1 layers whose output leaves as int8 rows run the (faster) flat convolution
         # unpooled into a scratch map and pool the level bytes afterwards: with ascending thresholds
-        # the maximum of the levels is the level of the maximum
-        # fully connected layers with few output tiles and a long K go through split-K + requantise
-        # (the same rule apnn_gemm_i8 applies to an int32 output)
-        self.fc_split: Dict[str, bool] = {}
-        acc_elems = 0
-        for ls in spec.layers:
-            if ls.kind != "conv" and use_tcgen05 and ls.quantise:
-                sh = self.params[ls.name].shape
-                tiles = ((B + 127) // 128) * ((sh["coutp"] + 127) // 128)
-                if tiles * 8 <= 148 and sh["K"] // 128 >= 32 and sh["coutp"] > 64:
-                    self.fc_split[ls.name] = True
-                    acc_elems = max(acc_elems, B * sh["coutp"])
-        self.fc_acc = torch.zeros(max(acc_elems, 4), dtype=torch.int32, device=self.device)
+        # the maximum of the levels is the level of the maximum.  (Fully connected layers with few
+        # output tiles and a long K need nothing here: apnn_gemm_i8 splits K over CTA clusters.)
         self.split_pool: Dict[str, bool] = {}
         pool_bytes = 0
         for ls in spec.layers:
@@ -507,15 +496,6 @@ class Network:
             if not self.i8_out.get(self.src_of[ls.name], False):
                 _cabi.check(self.L.apnn_expand_planes(s, X.data_ptr(), self.x8.data_ptr(), B, K, a, 0), "expand")
                 n, x8 = 2, self.x8
-            if ls.quantise and self.fc_split.get(ls.name, False):
-                # few output tiles, long K: int32 result by split-K over all SMs, then the quantiser
-                plain = make_epilogue("int32")
-                _cabi.check(self.L.apnn_gemm_i8(s, x8.data_ptr(), self.w8[ls.name].data_ptr(), self.fc_acc.data_ptr(), B,
-                                                N, K, 0, 1, ctypes.byref(plain), self.flag.data_ptr()),
-                            "apnn_gemm_i8 " + ls.name)
-                _cabi.check(self.L.apnn_requantize_i32(s, self.fc_acc.data_ptr(), out.data_ptr(), B, N, ctypes.byref(epi)),
-                            "apnn_requantize_i32 " + ls.name)
-                return n + 1
             _cabi.check(self.L.apnn_gemm_i8(s, x8.data_ptr(), self.w8[ls.name].data_ptr(), out.data_ptr(), B, N, K,
                                             0, 1, ctypes.byref(epi), self.flag.data_ptr()), "apnn_gemm_i8 " + ls.name)
             return n

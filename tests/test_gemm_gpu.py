@@ -411,3 +411,51 @@ def test_tcgen05_pair_kernel_epilogues(cuda_device, M, N, mode):
         assert np.array_equal(to_host(out2, np.int32), v0)
     else:
         assert np.array_equal(to_host(out2), oracle.requant_pack(v0, 2, 1 if mode == "lowbits" else 2, T))
+
+
+@pytest.mark.parametrize("M,N,K", [(130, 544, 4096), (128, 512, 25088), (64, 1024, 2048), (300, 4096, 1152), (128, 128, 8192)])
+def test_tcgen05_cluster_split_k_epilogues(cuda_device, M, N, K):
+    """Few tiles and a long K: the GEMM runs as clusters whose CTAs each sum a share of K and exchange
+    partial tiles through distributed shared memory before the ordinary epilogue.  int32, packed
+    thresholds, int8 rows and residual in / out (int32 and int16), against the oracle."""
+    import ctypes
+    import apnn_tc_b200 as ap
+    from apnn_tc_b200 import _cabi
+    from gpu_util import spread_bytes
+    rng = np.random.default_rng(M + N + K)
+    W, wl = oracle.value_planes(rng, M, K, 2)
+    X, xl = oracle.value_planes(rng, N, K, 1)
+    v = (wl.astype(np.int64) @ (2 * xl.astype(np.int64) - 1).T).astype(np.int32)     # +-1 second operand
+    a8 = ap.expand_planes(to_dev(W))
+    b8 = ap.expand_planes(to_dev(X), signed=True)
+    L = _cabi.lib()
+    s = torch.cuda.current_stream().cuda_stream
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def run(out, epi):
+        _cabi.check(L.apnn_gemm_i8(s, a8.data_ptr(), b8.data_ptr(), out.data_ptr(), M, N, K, 0, 1, ctypes.byref(epi),
+                                   flag.data_ptr()), "gemm_i8")
+        torch.cuda.synchronize()
+        assert int(flag.item()) == 0
+        return out
+
+    D = run(torch.full((M, N), 12345, dtype=torch.int32, device="cuda"), ap.make_epilogue("int32"))
+    assert np.array_equal(D.cpu().numpy(), v)
+    scale = rng.uniform(0.5, 1.5, N).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    T = oracle.fold_bn(scale, bias, float(v.mean()), float(v.std()) / 4, 2)
+    P = run(torch.zeros((2, M, N // 32), dtype=torch.int32, device="cuda"), ap.make_epilogue("thresholds", 2, thresholds=to_dev(T)))
+    assert np.array_equal(to_host(P), oracle.requant_pack(v, 2, 2, T))
+    O8 = run(torch.zeros((M, N), dtype=torch.uint8, device="cuda"),
+             ap.make_epilogue("thresholds", 2, thresholds=to_dev(T), out_i8=True))
+    assert np.array_equal(O8.cpu().numpy(), spread_bytes(oracle.levels(v, 2, 2, T).astype(np.uint8)))
+    res = rng.integers(-2000, 2000, size=v.shape).astype(np.int32)
+    v2 = v + res
+    for widths in (0, 3):
+        rin = torch.from_numpy(res.astype(np.int16) if widths & 1 else res).cuda()
+        rout = torch.zeros((M, N), dtype=torch.int16 if widths & 2 else torch.int32, device="cuda")
+        epi = ap.make_epilogue("lowbits", 3, residual_in=rin, residual_out=rout, residual_i16=widths)
+        P3 = run(torch.zeros((3, M, N // 32), dtype=torch.int32, device="cuda"), epi)
+        want_res = np.clip(v2, -32768, 32767) if widths & 2 else v2
+        assert np.array_equal(rout.cpu().numpy().astype(np.int32), want_res)
+        assert np.array_equal(to_host(P3), oracle.requant_pack(v2, 3, 1))
