@@ -21,7 +21,7 @@ constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // a wait that last
 // predecessor's tail; nothing the predecessor wrote may be read, and nothing it reads or writes may
 // be written, before the wait returns.  Without the attribute the wait returns at once.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// Lets the next kernel of the stream begin its own prologue as soon as SMs are free.
+// Lets the next kernel of the stream (if launched as a programmatic dependent) begin its prologue.
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

@@ -152,7 +152,6 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t tmem_base = *tmem_slot_ptr;
   // everything above overlapped the previous kernel's tail; from here on its results are visible
   grid_dependency_wait();
-  grid_launch_dependents();
   if (threadIdx.x == 0 && blockIdx.x == 0) *p.error_flag = 0;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
@@ -304,6 +303,10 @@ tc5_conv_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   // ---------------- tear-down ----------------
   tc_fence_before();
   __syncthreads();
+  // The next kernel of the stream may start its prologue now.  (Triggering at the top of the kernel
+  // instead lets its CTAs take SMs in the order they fall idle; measured on the ResNet-18 forward
+  // that scattering made every layer kernel 1 - 6 us slower, the late trigger saves 0.4 us per launch.)
+  grid_launch_dependents();
   cluster_sync_all();  // the peer may not leave while the leader's MMAs or arrivals can still reach it
   if (warp == 1) {
     tc_fence_after();

@@ -392,6 +392,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) *p.error_flag = 0;  // only ever raised after a 2 s wait, long after this store
     for (int s = 0; s < stages; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -417,31 +418,27 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  // everything above overlapped the previous kernel's tail; from here on its results are visible
-  grid_dependency_wait();
-  grid_launch_dependents();
-  if (threadIdx.x == 0 && blockIdx.x == 0) *p.error_flag = 0;  // only ever raised after a 2 s wait, long after this store
+  // Everything above may overlap the previous kernel's tail (programmatic dependent launch); the roles
+  // that touch global memory wait for that kernel below, each before its first access.
 
   const int num_tiles = p.tiles_m * p.tiles_n;
-  // split-K: one tile per cluster, K blocks [kb_first, kb_last) per CTA; otherwise tiles round-robin over the grid
-  uint32_t crank = 0;
-  int first_tile = blockIdx.x, tile_step = gridDim.x;
-  int kb_first = 0, kb_last = p.kblocks;
-  if constexpr (SPLITK) {
-    crank = cluster_ctarank();
-    first_tile = (int)blockIdx.x / p.splits;
-    tile_step = (int)gridDim.x / p.splits;
-    kb_first = (int)(((long long)crank * p.kblocks) / p.splits);       // even shares: none is empty
-    kb_last = (int)(((long long)(crank + 1) * p.kblocks) / p.splits);
-  }
+  // Tiles go round-robin over the grid; with split-K there is one tile per cluster and CTA r of the
+  // cluster takes K blocks [r*kblocks/splits, (r+1)*kblocks/splits).  These are evaluated inside each
+  // role (TILE_FIRST / TILE_STEP read %ctaid / %nctaid where they are used): hoisting them into
+  // variables shared by the roles made the epilogue-bound layer kernels up to 15 % slower.
+#define TILE_FIRST (SPLITK ? (int)blockIdx.x / p.splits : (int)blockIdx.x)
+#define TILE_STEP (SPLITK ? (int)gridDim.x / p.splits : (int)gridDim.x)
+#define KB_FIRST (SPLITK ? (int)(((long long)cluster_ctarank() * p.kblocks) / p.splits) : 0)
+#define KB_LAST (SPLITK ? (int)(((long long)(cluster_ctarank() + 1) * p.kblocks) / p.splits) : p.kblocks)
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
+      grid_dependency_wait();   // the first load of anything an earlier kernel wrote comes after this
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      if (p.b_resident && first_tile < num_tiles) {
+      if (p.b_resident && TILE_FIRST < num_tiles) {
         // tiles_n == 1: every tile of this CTA uses the same B rows; fetch all K blocks once
         mbar_expect_tx(bres_bar, bres_bytes);
         for (int kb = 0; kb < p.kblocks; kb++)
@@ -456,7 +453,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t phb = 0;
         const int taps = p.R * p.R;
         const uint32_t blk_bytes = (uint32_t)p.flat_blk_rows * BKB;
-        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        for (int tile = TILE_FIRST; tile < num_tiles && ok; tile += TILE_STEP) {
           int tm, tn;
           tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
           const int q0 = tm * BM + p.in_off * p.flat_wp + p.in_off;
@@ -479,9 +476,9 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
       } else
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      for (int tile = TILE_FIRST; tile < num_tiles && ok; tile += TILE_STEP) {
         int tm, tn;
-        const int kb0 = kb_first, kb1 = kb_last;
+        const int kb0 = KB_FIRST, kb1 = KB_LAST;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         int w0 = 0, h0 = 0, b0 = 0;
         if (p.is_conv) {
@@ -532,14 +529,14 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t ph = 0;
       uint32_t tl = 0;
       bool ok = true;
-      if (p.b_resident && first_tile < num_tiles) {
+      if (p.b_resident && TILE_FIRST < num_tiles) {
         ok = mbar_wait(bres_bar, 0u);
         tc_fence_after();
       }
       if (flat) {
         int sb = 0;
         uint32_t phb = 0;
-        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, tl++) {
+        for (int tile = TILE_FIRST; tile < num_tiles && ok; tile += TILE_STEP, tl++) {
           const uint32_t acc = tl & 1u;
           const uint32_t aph = (tl >> 1) & 1u;
           if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
@@ -601,13 +598,13 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (ok) tc_commit(tfull_bar(acc));
         }
       } else
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, tl++) {
+      for (int tile = TILE_FIRST; tile < num_tiles && ok; tile += TILE_STEP, tl++) {
         const uint32_t acc = tl & 1u;
         const uint32_t aph = (tl >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const int kb0 = kb_first, kb1 = kb_last;
+        const int kb0 = KB_FIRST, kb1 = KB_LAST;
         for (int kb = kb0; kb < kb1; kb += kgroup) {
           if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
           tc_fence_after();
@@ -636,6 +633,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ---------------- epilogue warps (2..9) ----------------
     constexpr bool C_NOPOOL = EPI >= 1, C_NORES = EPI == 1 || EPI == 2 || EPI == 5, C_NOINT32 = EPI >= 1 && EPI <= 4;
     constexpr bool C_I8THR = EPI >= 2 && EPI <= 4, C_RES16 = EPI == 4, C_INT32 = EPI == 5;
+    grid_dependency_wait();   // residual reads and every store of this kernel come after this
     const int ew = warp - 2;
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
     const int half = ew >> 2;      // this warp drains the tile's 32-column chunks half, half+2, ...
@@ -660,7 +658,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int thr_tn = -1;
     // 32-column chunks of the tile this CTA finishes: all of them, or (split-K) its slice of the cluster's tile
     const int slice_chunks = SPLITK ? (BN / 32) / p.splits : BN / 32;
-    const int c_first = SPLITK ? (int)crank * slice_chunks : 0;
+    const int crank = SPLITK ? (int)cluster_ctarank() : 0;
+    const int c_first = crank * slice_chunks;
     const int c_end = c_first + slice_chunks;
     const int c_begin = c_first + half;   // this warp's first chunk; it takes every second one
     // Row destinations of a tile: this lane's own row, and (for int32 rows and residuals) the
@@ -715,12 +714,12 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     };
     TileRows cur, nxt;
-    if (first_tile < num_tiles) {
-      rows_of_tile(first_tile, cur);
+    if (TILE_FIRST < num_tiles) {
+      rows_of_tile(TILE_FIRST, cur);
       if constexpr (!C_NORES) fetch_residual(cur, c_begin);
     }
     nxt = cur;
-    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, tl++) {
+    for (int tile = TILE_FIRST; tile < num_tiles && ok; tile += TILE_STEP, tl++) {
       const int tn = cur.tn;
       const uint32_t acc = tl & 1u;
       const uint32_t aph = (tl >> 1) & 1u;
@@ -745,10 +744,10 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const long long(&row_of)[4] = cur.row_of;
       const long long(&dense_of)[4] = cur.dense_of;
       const bool(&ok_of)[4] = cur.ok_of;
-      const bool has_next = tile + tile_step < num_tiles;
+      const bool has_next = tile + TILE_STEP < num_tiles;
       bool nxt_ready = false, nxt_fetched = false;
       if (C_NORES && has_next) {   // no residuals: nothing to overlap, do it before the wait
-        rows_of_tile(tile + tile_step, nxt);
+        rows_of_tile(tile + TILE_STEP, nxt);
         nxt_ready = true;
       }
       const bool acc_ok = mbar_wait(tfull_bar(acc), aph);
@@ -774,7 +773,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int owner = c / slice_chunks;
             const int g0 = (c - owner * slice_chunks) * 8;
             const uint32_t dst = map_to_cta(xch, (uint32_t)owner) +
-                                 (uint32_t)((((int)crank * groups + g0) * BM + row_in_tile) * 16);
+                                 (uint32_t)(((crank * groups + g0) * BM + row_in_tile) * 16);
 #pragma unroll
             for (int g = 0; g < 8; g++)
               st_cluster_v4(dst + (uint32_t)(g * BM * 16), v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
@@ -789,7 +788,6 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int col0 = tn * BN + c * 32;
         if (col0 >= p.N) continue;  // uniform over the warp
         uint32_t v[32];
-        __syncwarp();   // lanes that left the previous chunk early rejoin before the warp-wide TMEM load
         if constexpr (SPLITK) {
           const int groups = slice_chunks * 8;
           const int g0 = (c - c_first) * 8;
@@ -843,7 +841,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               }
               __syncwarp();
               if (c + 2 < c_end) fetch_residual(cur, c + 2);
-              else if (has_next) { rows_of_tile(tile + tile_step, nxt); fetch_residual(nxt, c_begin); nxt_ready = nxt_fetched = true; }
+              else if (has_next) { rows_of_tile(tile + TILE_STEP, nxt); fetch_residual(nxt, c_begin); nxt_ready = nxt_fetched = true; }
             } else if (!C_RES16 && p.residual_in != nullptr) {
 #pragma unroll
               for (int hf = 0; hf < 2; hf++) {
@@ -859,7 +857,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 __syncwarp();
               }
               if (c + 2 < c_end) fetch_residual(cur, c + 2);   // the next chunk's rows, in flight during this one's tail
-              else if (has_next) { rows_of_tile(tile + tile_step, nxt); fetch_residual(nxt, c_begin); nxt_ready = nxt_fetched = true; }
+              else if (has_next) { rows_of_tile(tile + TILE_STEP, nxt); fetch_residual(nxt, c_begin); nxt_ready = nxt_fetched = true; }
             }
             if (p.residual_out != nullptr && (C_RES16 || p.res16_out)) {
               int16_t* O16 = reinterpret_cast<int16_t*>(p.residual_out);
@@ -978,7 +976,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       if (has_next) {
-        if (!nxt_ready) rows_of_tile(tile + tile_step, nxt);
+        if (!nxt_ready) rows_of_tile(tile + TILE_STEP, nxt);
         if constexpr (!C_NORES) {
           if (!nxt_fetched) fetch_residual(nxt, c_begin);
         }
@@ -991,11 +989,20 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   // ---------------- tear-down ----------------
   tc_fence_before();
   __syncthreads();
+  // The next kernel of the stream may start its prologue now.  (Triggering at the top of the kernel
+  // instead lets its CTAs take SMs in the order they fall idle; measured on the ResNet-18 forward
+  // that scattering made every layer kernel 1 - 6 us slower, the late trigger saves 0.4 us per launch.)
+  grid_launch_dependents();
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS));
   }
 }
+
+#undef TILE_FIRST
+#undef TILE_STEP
+#undef KB_FIRST
+#undef KB_LAST
 
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
