@@ -1219,17 +1219,18 @@ int cluster_capacity(int bn, int cs) {
   return n;
 }
 
-// Split-K over clusters pays when a problem has far fewer tiles than SMs and a long K.  Cost of a
-// plan in shared-memory traffic units (what bounds the MMA loop): waves x K blocks per CTA x
-// (128 + bn) bytes per K byte, plus about four K blocks' worth for the partial-sum exchange.  Only
-// plans whose clusters are all resident at once are considered, and a split must beat the unsplit
-// plan by a tenth.  Returns the cluster size (1 = no split) and may widen *bn.
+// Split-K over clusters pays when a problem fits one wave of tiles with SMs to spare (or with tiles
+// narrower than they need be) and has a long K.  Cost of a plan in shared-memory traffic units (what
+// bounds the MMA loop): K blocks per CTA x (128 + bn) bytes per K byte, plus about four K blocks'
+// worth for the partial-sum exchange.  Only plans whose clusters are all resident at once are
+// considered, and a split must beat the unsplit plan by a tenth.  Returns the cluster size
+// (1 = no split) and may widen *bn.
 int pick_split(long long tiles_m, int N, int kblocks, int sms, int* bn) {
   static const bool disabled = [] { const char* v = getenv("APNN_SPLITK"); return v && v[0] == '0'; }();
   if (disabled || N <= 64 || kblocks < 8) return 1;
   const long long plain_tiles = tiles_m * ((N + *bn - 1) / *bn);
-  if (plain_tiles * 2 > sms) return 1;
-  const long long plain = ((plain_tiles + sms - 1) / sms) * kblocks * (128 + *bn);
+  if (plain_tiles > sms) return 1;   // more than one wave of tiles: nothing idle to split over
+  const long long plain = (long long)kblocks * (128 + *bn);
   long long best = plain * 9 / 10;
   int best_bn = *bn, best_cs = 1;
   for (int cand = 128; cand <= 256; cand *= 2) {

@@ -1,22 +1,29 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: w1a2 arbitrary-precision GEMM, M = N = K = 8192, on B200.
+"""Benchmark of the hot path on B200: w1a2 arbitrary-precision GEMM, M = N = K = 8192 (headline), plus
+the other workloads of the metric in the same JSON line.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--algo tcgen05|imma|bmma]
 
-One step = one pass of the GEMM over one batch of synthetic operands (uniform random bit
-planes: 1-bit weights W[1][M][K/32], 2-bit activations X[2][N][K/32], int32 output D[M][N]).
-With N > 1 GPUs (launched by torch.distributed.run) the problem is sharded along N: every
-rank owns the same weights and its own 8192 activation rows, i.e. a slice D[:, n0:n1] of a
-GEMM that is g times wider -- no data-path collective, weak scaling.
+Headline step = one GEMM over one batch of synthetic operands resident in HBM as packed bit planes
+(1-bit weights W[1][M][K/32], 2-bit activations X[2][N][K/32], int32 output D[M][N]).  The weights are a
+static operand: their int8 image is made once before the timed region (apnn_expand_planes); every
+step expands a fresh activation batch to int8 and runs the GEMM.  With N > 1 GPUs (torch.distributed.run) the problem is sharded along N: every rank
+owns the same weights and its own 8192 activation rows -- no data-path collective, weak scaling.
 
 Prints ONE JSON line (rank 0).  Keys beyond the usual ones:
-  roofline      tensor-pipe roofline of the dominant kernel (tc5_gemm_pair_kernel), timed with its
-                own CUDA events inside the timed steps; peak = the tcgen05 kind::i8 issue-loop
-                peak measured in this run (MEASURED_PEAKS.json's bf16 figure is quoted beside it)
-  cpu_baseline  the reference's own bit-serial compute_ref (compiled unmodified into
-                oracle/_ref) on a bounded sample of rows of the same problem
-  e2e           the same metric through the host-buffer C-ABI call (pinned host operands,
-                H2D + GEMM + D2H of the int32 result inside the timed region)
+  roofline      tensor-pipe roofline of the dominant kernel (tc5_gemm_pair_kernel), timed with its own
+                CUDA events inside the timed steps; peak = the tcgen05 kind::i8 issue-loop peak measured in
+                this run (MEASURED_PEAKS.json's bf16 figure is quoted beside it)
+  cpu_baseline  the reference's own bit-serial compute_ref (compiled unmodified into oracle/_ref) on a
+                bounded sample of rows of the same problem
+  e2e           the same metric through the host-buffer C-ABI call (pinned host operands, H2D + GEMM +
+                D2H of the int32 result inside the timed region)
+  sustained     the headline step repeated for at least two seconds, with the clocks sampled across it
+  resnet18      ResNet-18 w1a2 images/s at global batch 1024, batch-sharded over the ranks (every N)
+  allgather     N > 1: the N-sharded GEMM with its output gathered on every rank inside the step, fused
+                into the epilogue as peer stores (int32 slices and the 2-bit packed output) and by NCCL
+  pairs_8192, m64_sweep, conv_c3   N = 1: the other bit pairs at 8192^3, the M = 64 sweep and the
+                batch-8 16x16 convolution sweep (graph-replayed launches)
 """
 from __future__ import annotations
 
@@ -36,22 +43,25 @@ WBITS, XBITS = 1, 2
 METRIC = "w1a2_gemm_effective_tops"
 UNIT = "TOPS"  # 2*M*N*K / t, counted once whatever the plane count (the reference's formula)
 N_OPERAND_SETS = 4
+RESNET_GLOBAL_BATCH = 1024
+TRAFFIC_8192 = 578794000   # dram__bytes_read.sum + dram__bytes_write.sum per launch of tc5_gemm_pair_kernel at 8192^3
 
 
-def workload_config(n_gpus: int, algo: str) -> dict:
+def workload_config(n_gpus: int) -> dict:
+    """The same dictionary for both arms (ours and --impl reference)."""
     return {
         "workload": "gemm_w1a2_M8192_N8192_K8192_int32out",
         "M": M, "N_per_gpu": N, "K": K, "wbits": WBITS, "xbits": XBITS,
         "sharding": "replicated W, N-sharded X (g x 8192 rows), no collective" if n_gpus > 1 else "single GPU",
-        "algo": algo,
-        "l2": "4 rotating operand sets; each step rewrites 128 MiB of int8 workspace and 256 MiB of output (> 126 MB L2)",
+        "l2": "4 rotating activation sets; each step rewrites 64 MiB of int8 activations and 256 MiB of output (> 126 MB L2)",
+        "collective": "none",
     }
 
 
 # ----------------------------------------------------------------------------- reference arm
 def run_reference(args) -> None:
     """The reference's CPU implementation of this path: compute_ref of its w1a2 GEMM program,
-    compiled unmodified (oracle/_ref), all host threads, on a bounded sample of rows."""
+    compiled unmodified (oracle/_ref), all host threads, on a bounded sample of rows per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -59,15 +69,15 @@ def run_reference(args) -> None:
     import oracle
     from oracle import ref
     threads = os.cpu_count() or 1
-    rows_per_thread = 4
+    rows_per_thread = 1
     rows = threads * rows_per_thread
     rng = np.random.default_rng(0xA9117C + 1)
     W = rng.integers(0, 2**32, size=(WBITS, M, K // 32), dtype=np.uint32)
     X = rng.integers(0, 2**32, size=(XBITS, N, K // 32), dtype=np.uint32)
     kind = "reference" if ref.available(71) else "port"
+    from concurrent.futures import ThreadPoolExecutor
 
     def one_step():
-        from concurrent.futures import ThreadPoolExecutor
         if kind == "reference":
             fn = lambda i: ref.gemm_ref_rows(71, W, X, i * rows_per_thread, (i + 1) * rows_per_thread)
         else:
@@ -76,24 +86,24 @@ def run_reference(args) -> None:
         with ThreadPoolExecutor(threads) as ex:
             return list(ex.map(fn, range(threads)))
 
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(args.warmup):
         one_step()
-    steps = max(1, min(args.steps, 5))
     t0 = time.perf_counter()
-    for _ in range(steps):
+    for _ in range(args.steps):
         out = one_step()
-    dt = (time.perf_counter() - t0) / steps
+    dt = (time.perf_counter() - t0) / args.steps
     # spot-check the sample against the popcount form of the oracle
     chk = oracle.gemm_popc(W, X, rows=(0, rows_per_thread))[:rows_per_thread]
     if not np.array_equal(np.asarray(out[0]), chk):
         raise SystemExit("reference arm: bit-serial sample disagrees with the popcount form")
     tops = 2.0 * rows * N * K / dt / 1e12
-    sample = f"{rows} of {M} output rows per step ({rows_per_thread} per thread), full N and K"
+    sample = (f"{rows} of {M} output rows per step ({rows_per_thread} per thread), full N and K; one host's CPU "
+              f"whatever --gpus says")
     line = {
-        "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int32 bit-serial", "data": "synthetic",
-        "config": workload_config(args.gpus, "cpu:compute_ref"),
+        "config": workload_config(args.gpus), "algo": "cpu:compute_ref",
         "cpu_baseline": {"value": tops, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -149,12 +159,11 @@ class ClockSampler:
         except Exception as exc:  # NVML missing: report it rather than guess
             self.error = repr(exc)
 
-    def stop(self, t_begin: float, t_end: float) -> dict:
+    def window(self, t_begin: float, t_end: float) -> dict:
+        """Summary of the samples taken inside [t_begin, t_end] (the sampler keeps running)."""
         if self.thread is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + getattr(self, "error", "")]}
-        self.stop_flag.set()
-        self.thread.join(timeout=2)
-        inside = [x for x in self.samples if t_begin <= x[0] <= t_end]
+        inside = [x for x in list(self.samples) if t_begin <= x[0] <= t_end]
         if not inside:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no samples inside the timed region"]}
         mhz = sorted(x[1] for x in inside)
@@ -165,6 +174,11 @@ class ClockSampler:
                     reasons.add(nm)
         return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(reasons),
                 "samples": len(inside), "power_w_max": max(x[2] for x in inside)}
+
+    def stop(self) -> None:
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
 
 
 def measured_peaks() -> dict:
@@ -192,7 +206,124 @@ def probe_peak(torch, cabi, kind: int, iters: int) -> float:
     return ops.value / (e0.elapsed_time(e1) * 1e-3)
 
 
-# ----------------------------------------------------------------------------- our arm
+_FLUSH = None
+
+
+def flush_l2(torch):
+    """Rewrites a 256 MiB buffer (twice the L2) so the next measurement starts cold."""
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _FLUSH.fill_(1)
+
+
+def graph_time_us(torch, fn, launches: int = 20, replays: int = 5) -> float:
+    """Device time per call of fn when `launches` calls are replayed from one CUDA graph (no host launch
+    overhead), L2 flushed before each replay; best of `replays`."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(launches):
+                fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(replays):
+        flush_l2(torch)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e3 / launches)
+    return best
+
+
+def words(torch, shape, gen):
+    return torch.randint(-2**31, 2**31 - 1, shape, dtype=torch.int32, device="cuda", generator=gen)
+
+
+# ----------------------------------------------------------------------------- the headline GEMM
+class GemmPipeline:
+    """The 8192^3 step on device-resident operands: the static W is expanded to int8 once; every step
+    expands that step's activation planes and runs the GEMM, both on the current stream.  (Running the
+    expand of step i+1 on a second stream beside GEMM i was measured: the persistent GEMM's statically
+    scheduled tiles on the SMs that also host expand blocks become stragglers, 0.285 -> 0.300 ms per GEMM,
+    which cancels what the overlap hides.)"""
+
+    def __init__(self, torch, ap, cabi, dev, rank, wbits=WBITS, xbits=XBITS, algo="tcgen05", epilogue=None, D=None):
+        self.torch, self.ap, self.cabi, self.algo = torch, ap, cabi, algo
+        self.wbits, self.xbits = wbits, xbits
+        g = torch.Generator(device=dev).manual_seed(0xA9117C + 1 + rank)
+        gw = torch.Generator(device=dev).manual_seed(0xA9117C + 1)  # weights are the same on every rank
+        self.W = words(torch, (wbits, M, K // 32), gw)
+        self.Xs = [words(torch, (xbits, N, K // 32), g) for _ in range(N_OPERAND_SETS)]
+        self.D = D if D is not None else torch.empty((M, N), dtype=torch.int32, device=dev)
+        self.epilogue = epilogue
+        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.L = cabi.lib()
+        if algo == "tcgen05":
+            self.W8 = torch.empty((M, K), dtype=torch.uint8, device=dev)
+            self.X8 = torch.empty((N, K), dtype=torch.uint8, device=dev)
+            cabi.check(self.L.apnn_expand_planes(torch.cuda.current_stream().cuda_stream, self.W.data_ptr(),
+                                                 self.W8.data_ptr(), M, K, wbits, 0), "expand W")
+        self.launches_per_step = 2 if algo == "tcgen05" else 1
+        torch.cuda.synchronize()
+
+    def step(self, i: int, ev=None):
+        torch = self.torch
+        X = self.Xs[i % N_OPERAND_SETS]
+        if self.algo == "tcgen05":
+            self.cabi.check(self.L.apnn_expand_planes(torch.cuda.current_stream().cuda_stream, X.data_ptr(),
+                                                      self.X8.data_ptr(), N, K, self.xbits, 0), "expand X")
+        if ev is not None:
+            ev[0].record()
+        if self.algo == "tcgen05":
+            self.ap.gemm_i8(self.W8, self.X8, self.D, status_flag=self.flag, epilogue=self.epilogue)
+        else:
+            self.ap.apmm(self.W, X, self.D, algo=self.algo)
+        if ev is not None:
+            ev[1].record()
+
+    def begin(self, t0):
+        t0.record()
+
+    def end(self, t1):
+        t1.record()
+
+
+def timed_gemm_steps(torch, dist, pipe, steps, warmup, sampler=None):
+    for i in range(warmup):
+        pipe.step(i)
+    torch.cuda.synchronize()
+    if int(pipe.flag.item()) != 0:
+        raise SystemExit("tcgen05 kernel reported an expired wait during warm-up")
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    wall0 = time.perf_counter()
+    pipe.begin(t0)
+    for i in range(steps):
+        pipe.step(i, kev[i])
+    pipe.end(t1)
+    torch.cuda.synchronize()
+    wall1 = time.perf_counter()
+    if dist is not None:
+        dist.barrier()
+    if int(pipe.flag.item()) != 0:
+        raise SystemExit("tcgen05 kernel reported an expired wait")
+    elapsed_ms = t0.elapsed_time(t1)
+    kernel_ms = sum(a.elapsed_time(b) for a, b in kev) / steps
+    clocks = sampler.window(wall0, wall1) if sampler is not None else None
+    return elapsed_ms, kernel_ms, clocks
+
+
 def run_ours(args) -> None:
     import numpy as np
     import torch
@@ -215,139 +346,63 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", torch.cuda.current_device())
     algo = args.algo
 
-    # ---- synthetic operands, resident in HBM before the timed region
-    g = torch.Generator(device=dev).manual_seed(0xA9117C + 1 + rank)
-    gw = torch.Generator(device=dev).manual_seed(0xA9117C + 1)  # weights are the same on every rank
-    Ws = [torch.randint(-2**31, 2**31 - 1, (WBITS, M, K // 32), dtype=torch.int32, device=dev, generator=gw)
-          for _ in range(N_OPERAND_SETS)]
-    Xs = [torch.randint(-2**31, 2**31 - 1, (XBITS, N, K // 32), dtype=torch.int32, device=dev, generator=g)
-          for _ in range(N_OPERAND_SETS)]
-    D = torch.empty((M, N), dtype=torch.int32, device=dev)
-    W8 = torch.empty((M, K), dtype=torch.uint8, device=dev)
-    X8 = torch.empty((N, K), dtype=torch.uint8, device=dev)
-    flag = torch.zeros(1, dtype=torch.int32, device=dev)
-    ws = torch.empty(ap.gemm_workspace_bytes(M, N, K), dtype=torch.uint8, device=dev)
-
-    def step(i: int, ev=None):
-        W, X = Ws[i % N_OPERAND_SETS], Xs[i % N_OPERAND_SETS]
-        if algo == "tcgen05":
-            # the same two launches apnn_gemm_ex(APNN_ALGO_TCGEN05) makes, issued one by one
-            # so the GEMM kernel can be bracketed by its own events
-            _cabi.check(_cabi.lib().apnn_expand_planes_pair(torch.cuda.current_stream().cuda_stream, W.data_ptr(),
-                                                             W8.data_ptr(), M, WBITS, 0, X.data_ptr(), X8.data_ptr(), N,
-                                                             XBITS, 0, K), "apnn_expand_planes_pair")
-            if ev is not None:
-                ev[0].record()
-            ap.gemm_i8(W8, X8, D, status_flag=flag)
-            if ev is not None:
-                ev[1].record()
-        else:
-            if ev is not None:
-                ev[0].record()
-            ap.apmm(W, X, D, algo=algo)
-            if ev is not None:
-                ev[1].record()
-
-    launches_per_step = 2 if algo == "tcgen05" else 1
-    gathered = None
-    if args.allgather != "none" and dist is not None:
-        from apnn_tc_b200 import shard
-        if args.allgather == "nccl":
-            gathered = torch.empty((world, M, N), dtype=torch.int32, device=dev)
-            base_step = step
-
-            def step(i: int, ev=None):  # noqa: F811 -- the GEMM followed by an NCCL all-gather of the slices
-                base_step(i, ev)
-                shard.allgather_columns(D, out=gathered)
-        else:
-            # fused: the GEMM epilogue stores every tile into all ranks' buffers (peer stores over NVLink)
-            sg = shard.SymmetricGather(M, N, dev)
-            gathered = sg.buffer
-            D = sg.local_slot()
-            fused_epi = ap.make_epilogue("int32", peer_out=sg.peer_destinations())
-
-            def step(i: int, ev=None):  # noqa: F811
-                W, X = Ws[i % N_OPERAND_SETS], Xs[i % N_OPERAND_SETS]
-                _cabi.check(_cabi.lib().apnn_expand_planes_pair(torch.cuda.current_stream().cuda_stream, W.data_ptr(),
-                                                                 W8.data_ptr(), M, WBITS, 0, X.data_ptr(), X8.data_ptr(),
-                                                                 N, XBITS, 0, K), "apnn_expand_planes_pair")
-                if ev is not None:
-                    ev[0].record()
-                ap.gemm_i8(W8, X8, D, status_flag=flag, epilogue=fused_epi)
-                if ev is not None:
-                    ev[1].record()
-                sg.barrier()   # every rank's tiles have landed before the next step overwrites them
-
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    if int(flag.item()) != 0:
-        raise SystemExit("tcgen05 kernel reported an expired wait during warm-up")
+    def max_over_ranks(*vals):
+        if dist is None:
+            return vals
+        t = torch.tensor(list(vals), dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return tuple(float(x) for x in t)
 
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    pipe = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo)
     for i in range(2):  # keep the device busy while the sampler thread starts
-        step(i)
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    wall0 = time.perf_counter()
-    t0.record()
-    for i in range(args.steps):
-        step(i, kev[i])
-    t1.record()
-    torch.cuda.synchronize()
-    wall1 = time.perf_counter()
-    if dist is not None:
-        dist.barrier()
-    elapsed_ms = t0.elapsed_time(t1)
-    kernel_ms = sum(a.elapsed_time(b) for a, b in kev) / args.steps
-    if int(flag.item()) != 0:
-        raise SystemExit("tcgen05 kernel reported an expired wait")
-    if dist is not None:
-        t = torch.tensor([elapsed_ms, kernel_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, kernel_ms = float(t[0]), float(t[1])
-    clocks = sampler.stop(wall0, wall1) if sampler is not None else None
+        pipe.step(i)
+    elapsed_ms, kernel_ms, clocks = timed_gemm_steps(torch, dist, pipe, args.steps, args.warmup, sampler)
+    elapsed_ms, kernel_ms = max_over_ranks(elapsed_ms, kernel_ms)
+    flops_step = 2.0 * M * N * K
+    ms_per_step = elapsed_ms / args.steps
 
-    # ---- quick correctness guard on the last step's output (a few rows against the oracle)
+    # ---- correctness guard on the last step's output (a few rows against the oracle)
     if rank == 0:
         import oracle
         last = (args.steps - 1) % N_OPERAND_SETS
         rows = np.array([0, 4097, M - 1])
-        Wh = Ws[last].cpu().numpy().view(np.uint32)
-        Xh = Xs[last].cpu().numpy().view(np.uint32)
+        Wh = pipe.W.cpu().numpy().view(np.uint32)
+        Xh = pipe.Xs[last].cpu().numpy().view(np.uint32)
         want = oracle.gemm_popc(np.ascontiguousarray(Wh[:, rows]), Xh, threads=min(8, os.cpu_count() or 1))
-        got = D[torch.from_numpy(rows).to(dev)].cpu().numpy()
+        got = pipe.D[torch.from_numpy(rows).to(dev)].cpu().numpy()
         if not np.array_equal(got, want):
             raise SystemExit("bench output does not match the oracle")
 
-    if gathered is not None:
-        # every rank: the gathered buffer must equal an NCCL all-gather of the ranks' own slices
-        ref = torch.empty((world, M, N), dtype=torch.int32, device=dev)
-        dist.all_gather_into_tensor(ref.view(world * M, N), D.contiguous())
-        torch.cuda.synchronize()
-        if not torch.equal(ref, gathered):
-            raise SystemExit(f"rank {rank}: gathered output differs from the all-gather of the slices")
-        del ref
-
     if args.profile:
         if rank == 0:
-            ms = elapsed_ms / args.steps
-            print(json.dumps({"profile_run": True, "ms_per_step": ms, "kernel_ms": kernel_ms,
-                              "config": workload_config(world, algo)}), flush=True)
+            print(json.dumps({"profile_run": True, "ms_per_step": ms_per_step, "kernel_ms": kernel_ms,
+                              "config": workload_config(world)}), flush=True)
         if dist is not None:
             dist.destroy_process_group()
         return
 
+    # ---- sustained: the same step for at least two seconds, clocks sampled across the whole region
+    sustained = None
+    if algo == "tcgen05":
+        n_sus = max(args.steps, int(2.2e3 / ms_per_step))
+        s_ms, s_kernel_ms, s_clocks = timed_gemm_steps(torch, dist, pipe, n_sus, 1, sampler)
+        s_ms, s_kernel_ms = max_over_ranks(s_ms, s_kernel_ms)
+        sustained = {
+            "seconds": s_ms / 1e3, "steps": n_sus, "ms_per_step": s_ms / n_sus,
+            "tops": world * flops_step / (s_ms / n_sus * 1e-3) / 1e12, "kernel_ms": s_kernel_ms,
+            "kernel_tops": flops_step / (s_kernel_ms * 1e-3) / 1e12, "clocks": s_clocks,
+            "ms_x_mhz": (s_ms / n_sus) * s_clocks["sm_mhz"] if s_clocks and s_clocks.get("sm_mhz") else None,
+            "note": "the headline region lasts milliseconds at boost clocks; this one runs long enough for the power "
+                    "limit to set the clock",
+        }
+
     # ---- end-to-end through the host-buffer C-ABI call (pinned host operands, D2H of the result)
-    e2e = None
     e2e_steps = max(2, min(args.steps, 5))
     hW = torch.empty((WBITS, M, K // 32), dtype=torch.int32).pin_memory()
     hX = torch.empty((XBITS, N, K // 32), dtype=torch.int32).pin_memory()
-    hW.copy_(Ws[0].cpu())
-    hX.copy_(Xs[0].cpu())
+    hW.copy_(pipe.W.cpu())
+    hX.copy_(pipe.Xs[0].cpu())
     hD = torch.empty((M, N), dtype=torch.int32).pin_memory()
     handle = ap.HostHandle(torch.cuda.current_device())
     handle.gemm(hW, hX, hD, WBITS, XBITS, M, N, K, algo=algo)  # warm-up: arena allocation
@@ -359,16 +414,26 @@ def run_ours(args) -> None:
         handle.gemm(hW, hX, hD, WBITS, XBITS, M, N, K, algo=algo)  # synchronises before returning
     e2e_s = (time.perf_counter() - tt0) / e2e_steps
     handle.close()
-    if dist is not None:
-        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t[0])
-    if rank == 0 and not torch.equal(hD, ap.apmm(Ws[0], Xs[0], algo="imma").cpu()):
+    (e2e_s,) = max_over_ranks(e2e_s)
+    if rank == 0 and not torch.equal(hD, ap.apmm(pipe.W, pipe.Xs[0], algo="imma").cpu()):
         raise SystemExit("host-buffer path disagrees with the device path")
-    flops_step = 2.0 * M * N * K
     e2e = {"value": world * flops_step / e2e_s / 1e12, "unit": UNIT,
            "h2d_bytes_per_step": hW.numel() * 4 + hX.numel() * 4, "d2h_bytes_per_step": hD.numel() * 4,
-           "steps": e2e_steps, "timer": "host wall clock around the synchronous C-ABI call, max over ranks"}
+           "steps": e2e_steps, "timer": "host wall clock around the synchronous C-ABI call, max over ranks",
+           "bound": "PCIe: every rank of a node moves its 256 MiB result through the same host"}
+    del hW, hX, hD
+
+    # ---- the other workloads of the metric
+    Wkeep, Xkeep = pipe.W, pipe.Xs[0]
+    del pipe
+    torch.cuda.empty_cache()
+    resnet = resnet_block(torch, dist, dev, world, rank, args)
+    gather = allgather_block(torch, dist, ap, _cabi, dev, world, rank, args) if world > 1 else None
+    pairs = sweep = conv = None
+    if world == 1 and algo == "tcgen05" and not args.quick:
+        pairs = pairs_block(torch, ap, _cabi, dev, max(5, args.steps // 2))
+        sweep = m64_sweep_block(torch, ap)
+        conv = conv_c3_block(torch, ap, _cabi)
 
     if rank != 0:
         if dist is not None:
@@ -381,6 +446,7 @@ def run_ours(args) -> None:
     peak_ops = probe_peak(torch, _cabi, kind, 20000 if kind == 0 else 4000)
     ops_launch = flops_step * (WBITS * XBITS if algo == "bmma" else 1)  # bit-ops for the b1 path
     achieved = ops_launch / (kernel_ms * 1e-3) / 1e12
+    full_shape_one_gpu = world == 1 and algo == "tcgen05"
     roofline = {
         "bound": "tensor", "kernel": {"tcgen05": "tc5_gemm_pair_kernel (cta_group::2)", "imma": "plane_core_kernel<u8>",
                                       "bmma": "plane_core_kernel<b1>"}[algo],
@@ -390,18 +456,22 @@ def run_ours(args) -> None:
         "bf16_tflops_measured": peaks.get("bf16_tflops"), "bf16_tflops_sustained": peaks.get("bf16_tflops_sustained"),
         "frac_of_2x_bf16_burst": achieved / (2 * peaks["bf16_tflops"]) if peaks.get("bf16_tflops") else None,
         "kernel_ms": kernel_ms, "algorithmic_ops_per_launch": ops_launch,
-        "traffic": 578794000 if algo == "tcgen05" else None,
-        "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum per launch, ncu capture of `bench.py --profile` at full size",
+        "traffic": TRAFFIC_8192 if full_shape_one_gpu else None,
+        "traffic_source": ("constant from an earlier capture, not measured in this run: dram__bytes_read.sum + "
+                           "dram__bytes_write.sum per launch, profiles/tc5_gemm_pair_kernel_gemm_w1a2_8192.md")
+        if full_shape_one_gpu else None,
         "algorithmic_bytes_per_launch": M * K + N * K + 4 * M * N,
     }
+    if sustained is not None:
+        sustained["kernel_frac_of_probe_peak"] = sustained["kernel_tops"] / (peak_ops / 1e12)
 
     # ---- CPU baseline: the reference's compute_ref on a bounded sample of rows
     from oracle import ref
     import oracle
     threads = os.cpu_count() or 1
     rpt = 2
-    Wh = Ws[0].cpu().numpy().view(np.uint32)
-    Xh = Xs[0].cpu().numpy().view(np.uint32)
+    Wh = Wkeep.cpu().numpy().view(np.uint32)
+    Xh = Xkeep.cpu().numpy().view(np.uint32)
     kind_cpu = "reference" if ref.available(71) else "port"
     from concurrent.futures import ThreadPoolExecutor
     if kind_cpu == "reference":
@@ -412,7 +482,7 @@ def run_ours(args) -> None:
     with ThreadPoolExecutor(threads) as ex:
         cpu_out = list(ex.map(fn, range(threads)))
     cdt = time.perf_counter() - c0
-    if not np.array_equal(np.concatenate(cpu_out), ap.apmm(Ws[0], Xs[0], algo="imma")[: threads * rpt].cpu().numpy()):
+    if not np.array_equal(np.concatenate(cpu_out), ap.apmm(Wkeep, Xkeep, algo="imma")[: threads * rpt].cpu().numpy()):
         raise SystemExit("CPU baseline and GPU disagree on the sampled rows")
     cpu_baseline = {"value": 2.0 * threads * rpt * N * K / cdt / 1e12, "unit": UNIT, "cores": threads,
                     "kind": kind_cpu,
@@ -420,7 +490,7 @@ def run_ours(args) -> None:
 
     # beside the CPU loops: the reference's own GPU kernel for this pair, compiled unmodified for
     # sm_100a into oracle/_ref (part of the same baseline leg; absent -> omitted)
-    bar = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "bar_gemm_w1a2")
+    bar = os.path.join(ROOT, "oracle", "_ref", "bar_gemm_w1a2")
     if world == 1 and os.path.exists(bar) and (WBITS, XBITS) == (1, 2):
         try:
             import subprocess
@@ -434,20 +504,218 @@ def run_ours(args) -> None:
         except Exception as exc:   # the bar is optional
             cpu_baseline["reference_gpu_kernel"] = {"unavailable": str(exc)[:120]}
 
-    ms_per_step = elapsed_ms / args.steps
+    if sampler is not None:
+        sampler.stop()
     line = {
         "metric": METRIC, "value": world * flops_step / (ms_per_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8 operands, int32 accumulate (exact)", "data": "synthetic",
-        "config": dict(workload_config(world, algo), collective=("all_gather of the int32 output slices, "
-                       f"{(world - 1) * M * N * 4} B inbound per rank per step, mode " + args.allgather if gathered is not None
-                       else "none")),
+        "config": workload_config(world), "algo": algo,
+        "step": "activation expand (planes -> int8) + tcgen05 GEMM; the static weights' int8 image is made once "
+                "before the timed region",
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        "gpu_launches": (2 if algo == "tcgen05" else 1) * args.steps, "clocks": clocks,
+        "sustained": sustained, "resnet18": resnet, "allgather": gather,
+        "pairs_8192": pairs, "m64_sweep": sweep, "conv_c3": conv,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------- other blocks of the line
+def resnet_block(torch, dist, dev, world, rank, args):
+    """ResNet-18 w1a2, 224x224x3, global batch 1024 sharded over the ranks (no collective): one CUDA-graph
+    replay of the forward per step, max over ranks; end to end with pinned host images in and logits out."""
+    from apnn_tc_b200 import nets
+    batch = RESNET_GLOBAL_BATCH // world
+    steps = max(10, min(args.steps, 50))
+    spec = nets.resnet18_spec()
+    net = nets.Network(spec, batch, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0xA9117C + 5 + rank)
+    images = (torch.rand((batch, spec.image_hw, spec.image_hw, 3), device=dev, generator=g) * 20 - 10).contiguous()
+    net.capture(images)
+    for _ in range(max(3, args.warmup)):
+        net.replay()
+    net.check()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0.record()
+    for _ in range(steps):
+        net.replay()
+    t1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    net.check()
+    ms = t0.elapsed_time(t1) / steps
+    logits = net.out[spec.layers[-1].name]
+    himg = images.cpu().pin_memory()
+    hlog = torch.empty(logits.shape, dtype=logits.dtype).pin_memory()
+    e2e_steps = 5
+    torch.cuda.synchronize()
+    c0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        images.copy_(himg, non_blocking=True)
+        net.replay()
+        hlog.copy_(logits, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - c0) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([ms, e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+    out = {
+        "metric": "resnet18_w1a2_images_per_s", "images_per_s": batch * world / (ms * 1e-3), "ms_per_step": ms,
+        "steps": steps, "global_batch": batch * world, "per_gpu_batch": batch, "scaling": "strong",
+        "sharding": "batch-sharded, no collective", "launches_per_forward": net.launches_per_forward,
+        "e2e_images_per_s": batch * world / e2e_s, "h2d_bytes_per_step": himg.numel() * 4,
+        "d2h_bytes_per_step": hlog.numel() * hlog.element_size(),
+        "l2": "activations of one forward exceed L2 at every per-GPU batch used here",
+    }
+    del net, images, himg, hlog
+    torch.cuda.empty_cache()
+    return out
+
+
+def allgather_block(torch, dist, ap, cabi, dev, world, rank, args):
+    """N > 1: the N-sharded 8192^3 GEMM with its output gathered on every rank inside each step.  Fused: the
+    GEMM epilogue stores every tile into all ranks' [g][M][N/g] buffers (plain peer stores over NVLink), for the
+    int32 slices and for the 2-bit packed output; NCCL: all_gather_into_tensor after the GEMM.  Every fused
+    result is checked against an NCCL all-gather of the ranks' slices."""
+    from apnn_tc_b200 import shard
+    steps = max(5, min(args.steps, 20))
+    out = {"ranks": world}
+
+    def timed(pipe, after_step):
+        def one(i, ev=None):
+            pipe.step(i, ev)
+            after_step()
+        for i in range(3):
+            one(i)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        pipe.begin(t0)
+        for i in range(steps):
+            one(i)
+        pipe.end(t1)
+        torch.cuda.synchronize()
+        dist.barrier()
+        if int(pipe.flag.item()) != 0:
+            raise SystemExit("tcgen05 kernel reported an expired wait")
+        t = torch.tensor([t0.elapsed_time(t1) / steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def check(gathered, local):
+        ref = torch.empty_like(gathered)
+        dist.all_gather_into_tensor(ref.view(world * gathered.shape[1], -1), local.contiguous().view(gathered.shape[1], -1))
+        torch.cuda.synchronize()
+        if not torch.equal(ref, gathered):
+            raise SystemExit(f"rank {rank}: gathered output differs from the all-gather of the slices")
+
+    # int32 slices, fused
+    sg = shard.SymmetricGather(M, N, dev)
+    pipe = GemmPipeline(torch, ap, cabi, dev, rank, D=sg.local_slot(),
+                        epilogue=ap.make_epilogue("int32", peer_out=sg.peer_destinations()))
+    ms = timed(pipe, sg.barrier)   # every rank's tiles have landed before the next step overwrites them
+    check(sg.buffer, sg.local_slot())
+    egress = (world - 1) * M * N * 4
+    out["fused_int32"] = {"ms_per_step": ms, "bytes_leaving_each_gpu": egress, "egress_gb_s": egress / (ms * 1e-3) / 1e9,
+                          "tops": world * 2.0 * M * N * K / (ms * 1e-3) / 1e12, "verified_against_nccl": True}
+    # int32 slices, NCCL after the GEMM
+    gathered = torch.empty((world, M, N), dtype=torch.int32, device=dev)
+    pipe2 = GemmPipeline(torch, ap, cabi, dev, rank)
+    ms = timed(pipe2, lambda: shard.allgather_columns(pipe2.D, out=gathered))
+    out["nccl_int32"] = {"ms_per_step": ms, "bytes_leaving_each_gpu": egress, "egress_gb_s": egress / (ms * 1e-3) / 1e9,
+                         "tops": world * 2.0 * M * N * K / (ms * 1e-3) / 1e12}
+    del pipe, pipe2, gathered, sg
+    torch.cuda.empty_cache()
+    # the 2-bit packed output [2][M][N/32] (low bits, the reference's fused decompose kernels), fused
+    sgp = shard.SymmetricGather(2 * M, N // 32, dev)
+    pipe3 = GemmPipeline(torch, ap, cabi, dev, rank, D=sgp.local_slot(),
+                         epilogue=ap.make_epilogue("lowbits", 2, peer_out=sgp.peer_destinations()))
+    ms = timed(pipe3, sgp.barrier)
+    check(sgp.buffer, sgp.local_slot())
+    egress = (world - 1) * 2 * M * (N // 32) * 4
+    out["fused_packed_2bit"] = {"ms_per_step": ms, "bytes_leaving_each_gpu": egress,
+                                "egress_gb_s": egress / (ms * 1e-3) / 1e9,
+                                "tops": world * 2.0 * M * N * K / (ms * 1e-3) / 1e12, "verified_against_nccl": True}
+    out["link"] = "NVLink 5 through NVSwitch; 770 GB/s per direction measured peer copy on this pool (900 nominal)"
+    out["steps"] = steps
+    del pipe3, sgp
+    torch.cuda.empty_cache()
+    return out
+
+
+def pairs_block(torch, ap, cabi, dev, steps):
+    """The other bit pairs of the sweep at 8192^3 on the same kernel (one int8 byte per level whatever its
+    width): kernel time by events, effective TOPS."""
+    out = {}
+    for wb, xb in ((1, 3), (1, 4), (2, 2)):
+        pipe = GemmPipeline(torch, ap, cabi, dev, 0, wbits=wb, xbits=xb)
+        ms, kms, _ = timed_gemm_steps(torch, None, pipe, steps, 3)
+        out[f"w{wb}a{xb}"] = {"ms_per_step": ms / steps, "tops": 2.0 * M * N * K / (ms / steps * 1e-3) / 1e12,
+                              "kernel_ms": kms, "kernel_tops": 2.0 * M * N * K / (kms * 1e-3) / 1e12}
+        del pipe
+        torch.cuda.empty_cache()
+    return out
+
+
+def m64_sweep_block(torch, ap):
+    """M = 64, N = K = 128..1024 for the four bit pairs (the reference's GEMM sweep): microseconds per launch
+    from a graph of 20 launches (L2 flushed before each replay), against the HBM time of the algorithmic bytes."""
+    gen = torch.Generator(device="cuda").manual_seed(0xA9117C + 2)
+    hbm = (measured_peaks().get("hbm_gbs") or 6545.0) * 1e9
+    out = {"unit": "us per launch (graph replay)", "hbm_gbs_measured": hbm / 1e9, "rows": []}
+    for wb, xb in ((1, 2), (1, 3), (1, 4), (2, 2)):
+        for n in range(128, 1025, 128):
+            W, X = words(torch, (wb, 64, n // 32), gen), words(torch, (xb, n, n // 32), gen)
+            D = torch.empty((64, n), dtype=torch.int32, device="cuda")
+            us = graph_time_us(torch, lambda: ap.apmm(W, X, D, algo="imma"))
+            byts = wb * 64 * n // 8 + xb * n * n // 8 + 4 * 64 * n
+            out["rows"].append({"pair": f"w{wb}a{xb}", "n": n, "us": round(us, 2), "tops": round(2 * 64 * n * n / us / 1e6, 2),
+                                "algorithmic_bytes": byts, "hbm_frac": round(byts / (us * 1e-6) / hbm, 4)})
+    return out
+
+
+def conv_c3_block(torch, ap, cabi):
+    """Batch 8, 16x16, C = O = 128..1024, 3x3, BN thresholds -> 2-bit output: one launch as a network chains it
+    (int8 rows in, filter expanded once), and from packed planes through apnn_conv2d_ex (expand + conv)."""
+    from apnn_tc_b200.ops import _stream_ptr
+    gen = torch.Generator(device="cuda").manual_seed(0xA9117C + 3)
+    L = cabi.lib()
+    peak = probe_peak(torch, cabi, 0, 20000) / 1e12
+    out = {"unit": "us per launch (graph replay)", "tensor_peak_tops": peak, "rows": []}
+    B, H = 8, 16
+    for wb, xb in ((1, 2), (1, 4), (2, 2)):
+        for C in range(128, 1025, 128):
+            X = words(torch, (xb, B, H + 2, H + 2, C // 32), gen)
+            Wt = words(torch, (wb, C, 3, 3, C // 32), gen)
+            T = torch.sort(torch.randint(0, 9 * C * 3, (C, 3), dtype=torch.int32, device="cuda", generator=gen),
+                           dim=1).values.contiguous()
+            flops = 2.0 * B * H * H * C * 9 * C
+            x8 = ap.expand_planes(X.reshape(xb, -1, C // 32))
+            w8 = ap.expand_planes(Wt.reshape(wb, C, -1), signed=(wb == 1))
+            flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+            o8 = torch.zeros((B, H, H, C), dtype=torch.uint8, device="cuda")
+            epi8 = ap.make_epilogue("thresholds", 2, thresholds=T, out_i8=True)
+            us_chain = graph_time_us(torch, lambda: cabi.check(L.apnn_conv2d_i8(
+                _stream_ptr(), w8.data_ptr(), x8.data_ptr(), o8.data_ptr(), B, H, H, C, C, 3, 1, 1 if wb == 1 else 0,
+                ctypes.byref(epi8), flag.data_ptr()), "conv"))
+            ws = torch.empty(ap.conv_workspace_bytes(B, H, H, C, C, 3), dtype=torch.uint8, device="cuda")
+            outp = torch.empty((2, B, H, H, C // 32), dtype=torch.int32, device="cuda")
+            epi = ap.make_epilogue("thresholds", 2, signed="w" if wb == 1 else "none", thresholds=T)
+            us_planes = graph_time_us(torch, lambda: ap.apconv(Wt, X, outp, epilogue=epi, algo="tcgen05", workspace=ws))
+            out["rows"].append({"pair": f"w{wb}a{xb}", "C": C, "us_chained": round(us_chain, 2),
+                                "tops_chained": round(flops / us_chain / 1e6, 1),
+                                "tensor_frac_chained": round(flops / us_chain / 1e6 / peak, 3),
+                                "us_from_planes": round(us_planes, 2), "tops_from_planes": round(flops / us_planes / 1e6, 1)})
+    return out
 
 
 # ----------------------------------------------------------------------------- network workloads
@@ -456,9 +724,7 @@ NET_BATCH = {"resnet18": 1024, "vgg_variant": 1024, "alexnet": 128}
 
 def run_net(args) -> None:
     """images/s of a whole w1a2 network (the AlexNet / VGG-variant / ResNet-18 model lists of APNN-TC-nn):
-    global batch sharded over the ranks
-    (no collective), one CUDA-graph replay of the layer sequence per step."""
-    import numpy as np
+    global batch sharded over the ranks (no collective), one CUDA-graph replay of the layer sequence per step."""
     import torch
     from apnn_tc_b200 import nets
 
@@ -502,22 +768,25 @@ def run_net(args) -> None:
     net.check()
     ms = t0.elapsed_time(t1) / args.steps
     # end to end: pinned host images in, logits out, through the same layer sequence
+    logits = net.out[spec.layers[-1].name]
     himg = images.cpu().pin_memory()
-    hlog = torch.empty(net.out[spec.layers[-1].name].shape, dtype=torch.int32).pin_memory()
+    hlog = torch.empty(logits.shape, dtype=logits.dtype).pin_memory()
     e2e_steps = max(2, min(args.steps, 5))
     torch.cuda.synchronize()
     c0 = time.perf_counter()
     for _ in range(e2e_steps):
         images.copy_(himg, non_blocking=True)
         net.replay()
-        hlog.copy_(net.out[spec.layers[-1].name], non_blocking=True)
+        hlog.copy_(logits, non_blocking=True)
         torch.cuda.synchronize()
     e2e_s = (time.perf_counter() - c0) / e2e_steps
     if dist is not None:
         t = torch.tensor([ms, e2e_s], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_s = float(t[0]), float(t[1])
-    clocks = sampler.stop(wall0, wall1) if sampler is not None else None
+    clocks = sampler.window(wall0, wall1) if sampler is not None else None
+    if sampler is not None:
+        sampler.stop()
     if rank == 0:
         line = {
             "metric": f"{args.workload}_w1a2_images_per_s", "value": batch * world / (ms * 1e-3), "unit": "images/s",
@@ -528,7 +797,7 @@ def run_net(args) -> None:
                        "per_gpu_batch": batch, "algo": args.algo, "sharding": "batch-sharded, no collective",
                        "l2": "activations of one step exceed L2 at this batch"},
             "e2e": {"value": batch * world / e2e_s, "unit": "images/s", "h2d_bytes_per_step": himg.numel() * 4,
-                    "d2h_bytes_per_step": hlog.numel() * 4, "steps": e2e_steps},
+                    "d2h_bytes_per_step": hlog.numel() * hlog.element_size(), "steps": e2e_steps},
             "gpu_launches": net.launches_per_forward * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -539,25 +808,21 @@ def run_net(args) -> None:
 def main() -> None:
     ap_ = argparse.ArgumentParser()
     ap_.add_argument("--gpus", type=int, default=1)
-    ap_.add_argument("--steps", type=int, default=200)
+    ap_.add_argument("--steps", type=int, default=20)
     ap_.add_argument("--warmup", type=int, default=5)
     ap_.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap_.add_argument("--algo", default="tcgen05", choices=["tcgen05", "imma", "bmma"])
-    ap_.add_argument("--allgather", default="none", choices=["none", "nccl", "fused"],
-                     help="N > 1 only: gather the int32 output slices on every rank inside every timed step, by an "
-                          "NCCL all-gather after the GEMM or fused into the GEMM epilogue as peer stores")
     ap_.add_argument("--profile", action="store_true",
-                     help="timed steps only (no e2e, probe or CPU baseline): the command ncu captures")
+                     help="timed GEMM steps only (no e2e, probe, CPU baseline or other blocks): the command ncu captures")
+    ap_.add_argument("--quick", action="store_true", help="skip the N = 1 sweep blocks (pairs_8192, m64_sweep, conv_c3)")
     ap_.add_argument("--workload", default="gemm", choices=["gemm", "resnet18", "vgg_variant", "alexnet"],
-                     help="gemm (default, the headline line) or a whole w1a2 network (images/s)")
+                     help="gemm (default: the headline line with every block) or one whole w1a2 network (images/s)")
     ap_.add_argument("--batch", type=int, default=0, help="global batch of a network workload")
     args = ap_.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload != "gemm":
-        if args.steps == 200:
-            args.steps = 20
         run_net(args)
     else:
         run_ours(args)
