@@ -12,7 +12,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libapnn_b200.so")
 
 # enums of include/apnn_b200.h
-OUT_INT32, OUT_LOWBITS, OUT_THRESHOLDS = 0, 1, 2
+OUT_INT32, OUT_LOWBITS, OUT_THRESHOLDS, OUT_FLOAT = 0, 1, 2, 3
+QUANT_CENTRED = 0x100   # flag in the `bits` argument of the first-layer int8 gathers
 SIGN_NONE, SIGN_W, SIGN_X = 0, 1, 2
 POOL_NONE, POOL_AVG2, POOL_MAX2 = 0, 1, 2
 ALGO_AUTO, ALGO_BMMA, ALGO_IMMA, ALGO_TCGEN05, ALGO_TCGEN05_PAIR = 0, 1, 2, 3, 4
@@ -28,7 +29,9 @@ EXPORTS = (
 
 
 class Epilogue(ctypes.Structure):
+    """``apnn_epilogue``; ``struct_size`` is filled in on construction (APNN_EPILOGUE_INIT)."""
     _fields_ = [
+        ("struct_size", ctypes.c_uint32),
         ("out_mode", ctypes.c_int32),
         ("out_bits", ctypes.c_int32),
         ("signed_operand", ctypes.c_int32),
@@ -42,7 +45,13 @@ class Epilogue(ctypes.Structure):
         ("out_i8", ctypes.c_int32),
         ("peer_out", ctypes.c_void_p * 7),
         ("residual_i16", ctypes.c_int32),
+        ("affine_scale", ctypes.c_void_p),
+        ("affine_bias", ctypes.c_void_p),
     ]
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        self.struct_size = ctypes.sizeof(Epilogue)
 
 
 class ApnnError(RuntimeError):

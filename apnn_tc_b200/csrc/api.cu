@@ -40,12 +40,17 @@ int device_sm_count() {
 apnn_status check_epilogue(const apnn_epilogue* e, int channels, bool is_conv, int abits_signed_w, int abits_signed_x,
                            bool i8_rows_ok) {
   if (!e) return APNN_OK;
+  if (e->struct_size != sizeof(apnn_epilogue)) return APNN_ERR_INVALID_ARG;   // built against another layout
   if (e->residual_i16 != 0 && (e->residual_i16 < 0 || e->residual_i16 > 3 || !i8_rows_ok || e->n_peer_out != 0))
     return (e->residual_i16 > 0 && e->residual_i16 <= 3 && !i8_rows_ok) ? APNN_ERR_UNSUPPORTED : APNN_ERR_INVALID_ARG;
   if (e->out_i8 != 0 && (e->out_i8 != 1 || !i8_rows_ok || e->out_mode == APNN_OUT_INT32 || e->n_peer_out != 0))
     return e->out_i8 == 1 && !i8_rows_ok ? APNN_ERR_UNSUPPORTED : APNN_ERR_INVALID_ARG;
-  if (e->out_mode < APNN_OUT_INT32 || e->out_mode > APNN_OUT_THRESHOLDS) return APNN_ERR_INVALID_ARG;
-  if (e->out_mode != APNN_OUT_INT32) {
+  if (e->out_mode < APNN_OUT_INT32 || e->out_mode > APNN_OUT_FLOAT) return APNN_ERR_INVALID_ARG;
+  if (e->out_mode == APNN_OUT_FLOAT) {
+    // the float affine exists in the tcgen05 kernels' run-time epilogue and in apnn_requantize_i32
+    if (!i8_rows_ok) return APNN_ERR_UNSUPPORTED;
+    if (!e->affine_scale || !e->affine_bias || e->out_i8 || e->n_peer_out) return APNN_ERR_INVALID_ARG;
+  } else if (e->out_mode != APNN_OUT_INT32) {
     if (e->out_bits < 1 || e->out_bits > 8) return APNN_ERR_INVALID_ARG;
     if (channels % 32 != 0) return APNN_ERR_UNSUPPORTED;
     if (e->out_mode == APNN_OUT_THRESHOLDS && !e->thresholds) return APNN_ERR_INVALID_ARG;
@@ -206,6 +211,11 @@ apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const voi
   }
 
   if (epi && epi->n_peer_out != 0) return APNN_ERR_UNSUPPORTED;  // peer stores exist in the pair kernel only
+  if (workspace && workspace_bytes >= tc5_workspace_bytes(M, N, K)) {
+    // the warp-level kernels have no waits and never touch the flag apnn_gemm_check reads: clear it
+    cudaError_t ce = cudaMemsetAsync(tc5_flag_slot(workspace, M, N, K), 0, sizeof(int), s);
+    if (ce != cudaSuccess) return cuda_fail(ce, "status flag reset");
+  }
   CoreParams p;
   memset(&p, 0, sizeof(p));
   p.A = (const uint32_t*)W;
@@ -268,8 +278,9 @@ apnn_status apnn_conv2d_i8(void* stream, const void* W8, const void* X8, void* O
     if (epi->in_halo != 0 && epi->in_halo < (R - 1) / 2) return APNN_ERR_INVALID_ARG;
   }
   if (!tc5_conv_supported(H, W, R, stride, epi ? epi->pool : APNN_POOL_NONE)) return APNN_ERR_UNSUPPORTED;
+  if (w_signed < 0 || w_signed > 3) return APNN_ERR_INVALID_ARG;
   return tc5_conv_i8(reinterpret_cast<cudaStream_t>(stream), (const uint8_t*)X8, (const uint8_t*)W8, Out, B, H, W,
-                     CIN, COUT, R, stride, w_signed != 0, epi, status_flag);
+                     CIN, COUT, R, stride, (w_signed & 1) != 0, epi, status_flag, (w_signed & 2) != 0);
 }
 
 apnn_status apnn_conv2d(void* stream, int wbits, int xbits, const void* Wt, const void* X, void* Out, int B, int H,
@@ -321,6 +332,11 @@ apnn_status apnn_conv2d_ex(void* stream, int algo, int wbits, int xbits, const v
                     B, H, Wd, CIN, COUT, R, stride, epi, workspace);
   }
 
+  if (workspace && workspace_bytes >= tc5_conv_workspace_bytes(B, H, Wd, CIN, COUT, R)) {
+    cudaError_t ce = cudaMemsetAsync(tc5_conv_flag_slot(workspace, B, H, Wd, CIN, COUT, R), 0, sizeof(int),
+                                     reinterpret_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return cuda_fail(ce, "status flag reset");
+  }
   CoreParams p;
   memset(&p, 0, sizeof(p));
   p.A = (const uint32_t*)X;

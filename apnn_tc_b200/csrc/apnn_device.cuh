@@ -7,7 +7,7 @@
 namespace apnn {
 
 // Values mirror include/apnn_b200.h.
-enum { OUT_INT32 = 0, OUT_LOWBITS = 1, OUT_THRESHOLDS = 2 };
+enum { OUT_INT32 = 0, OUT_LOWBITS = 1, OUT_THRESHOLDS = 2, OUT_FLOAT = 3 };
 enum { SIGN_NONE = 0, SIGN_A = 1, SIGN_B = 2 };  // which core operand holds -1/+1 bits
 enum { POOL_NONE = 0, POOL_AVG2 = 1, POOL_MAX2 = 2 };
 

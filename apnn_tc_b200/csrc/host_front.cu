@@ -44,7 +44,7 @@ struct Carver {
 };
 
 size_t out_bytes_of(const apnn_epilogue* epi, long long rows, int channels) {
-  if (!epi || epi->out_mode == APNN_OUT_INT32) return (size_t)rows * channels * 4;
+  if (!epi || epi->out_mode == APNN_OUT_INT32 || epi->out_mode == APNN_OUT_FLOAT) return (size_t)rows * channels * 4;
   return (size_t)epi->out_bits * rows * (channels / 32) * 4;
 }
 
@@ -90,10 +90,12 @@ apnn_status apnn_gemm_host(apnn_handle h, int algo, int wbits, int xbits, const 
   if (K % 128 != 0) return APNN_ERR_ALIGNMENT;
   cudaError_t e = cudaSetDevice(h->device);
   if (e != cudaSuccess) return apnn::cuda_fail(e, "cudaSetDevice");
+  // the descriptor is validated before any size is derived from it
+  apnn_status st = apnn::check_epilogue(epi, N, false, wbits, xbits);
+  if (st != APNN_OK) return st;
   const size_t wb = (size_t)wbits * M * (K / 8), xb = (size_t)xbits * N * (K / 8);
   const size_t db = out_bytes_of(epi, M, N);
   const bool thr = epi && epi->out_mode == APNN_OUT_THRESHOLDS;
-  if (thr && !epi->thresholds) return APNN_ERR_INVALID_ARG;
   const size_t tb = thr ? (size_t)N * ((1u << epi->out_bits) - 1) * 4 : 0;
   int use_algo = algo;
   size_t ws = apnn_gemm_workspace_bytes(APNN_ALGO_TCGEN05, wbits, xbits, M, N, K);
@@ -101,7 +103,7 @@ apnn_status apnn_gemm_host(apnn_handle h, int algo, int wbits, int xbits, const 
 
   Carver sizing{nullptr, 0};
   sizing.take(wb); sizing.take(xb); sizing.take(db); sizing.take(tb); sizing.take(ws);
-  apnn_status st = ensure_arena(h, sizing.off);
+  st = ensure_arena(h, sizing.off);
   if (st != APNN_OK) return st;
   Carver c{(char*)h->arena, 0};
   void* dW = c.take(wb);
@@ -126,7 +128,11 @@ apnn_status apnn_gemm_host(apnn_handle h, int algo, int wbits, int xbits, const 
   st = apnn_gemm_ex(h->stream, use_algo, wbits, xbits, dW, dX, dD, M, N, K, pe, ws ? dWs : nullptr, ws);
   if (st != APNN_OK) return st;
   e = cudaMemcpyAsync(D_host, dD, db, cudaMemcpyDeviceToHost, h->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+  if (e != cudaSuccess) return apnn::cuda_fail(e, "device->host copy");
+  // synchronises; with a workspace it also reads the flag a bounded wait raises (apnn_gemm_ex clears the
+  // flag when it ends up on a kernel that has no waits), so an incomplete result is never returned as OK
+  if (ws) return apnn_gemm_check(h->stream, dWs, M, N, K);
+  e = cudaStreamSynchronize(h->stream);
   if (e != cudaSuccess) return apnn::cuda_fail(e, "device->host copy");
   return APNN_OK;
 }
@@ -141,6 +147,10 @@ apnn_status apnn_conv2d_host(apnn_handle h, int wbits, int xbits, const void* Wt
   if (CIN % 128 != 0) return APNN_ERR_ALIGNMENT;
   cudaError_t e = cudaSetDevice(h->device);
   if (e != cudaSuccess) return apnn::cuda_fail(e, "cudaSetDevice");
+  apnn_status st = apnn::check_epilogue(epi, COUT, true, wbits, xbits);
+  if (st != APNN_OK) return st;
+  // the host image is copied with exactly the ring the filter needs; a wider stored ring is a device-side notion
+  if (epi && epi->in_halo != 0 && epi->in_halo != (R - 1) / 2) return APNN_ERR_UNSUPPORTED;
   const int pad = (R - 1) / 2;
   const int Ho = (H - 1) / stride + 1, Wo = (W - 1) / stride + 1;
   const int pool = epi ? epi->pool : APNN_POOL_NONE;
@@ -150,18 +160,20 @@ apnn_status apnn_conv2d_host(apnn_handle h, int wbits, int xbits, const void* Wt
   const size_t wb = (size_t)wbits * COUT * R * R * (CIN / 8);
   const size_t ob = out_bytes_of(epi, (long long)B * oh * ow, COUT);
   const bool thr = epi && epi->out_mode == APNN_OUT_THRESHOLDS;
-  if (thr && !epi->thresholds) return APNN_ERR_INVALID_ARG;
   const size_t tb = thr ? (size_t)COUT * ((1u << epi->out_bits) - 1) * 4 : 0;
+  // with a workspace apnn_conv2d_ex(APNN_ALGO_AUTO) takes the tcgen05 path for sizeable problems
+  const size_t ws = apnn_conv2d_workspace_bytes(APNN_ALGO_TCGEN05, B, H, W, CIN, COUT, R);
 
   Carver sizing{nullptr, 0};
-  sizing.take(wb); sizing.take(xb); sizing.take(ob); sizing.take(tb);
-  apnn_status st = ensure_arena(h, sizing.off);
+  sizing.take(wb); sizing.take(xb); sizing.take(ob); sizing.take(tb); sizing.take(ws);
+  st = ensure_arena(h, sizing.off);
   if (st != APNN_OK) return st;
   Carver c{(char*)h->arena, 0};
   void* dW = c.take(wb);
   void* dX = c.take(xb);
   void* dO = c.take(ob);
   void* dT = c.take(tb);
+  void* dWs = c.take(ws);
   e = cudaMemcpyAsync(dW, Wt_host, wb, cudaMemcpyHostToDevice, h->stream);
   if (e == cudaSuccess) e = cudaMemcpyAsync(dX, X_host, xb, cudaMemcpyHostToDevice, h->stream);
   if (e == cudaSuccess && thr) e = cudaMemcpyAsync(dT, epi->thresholds, tb, cudaMemcpyHostToDevice, h->stream);
@@ -176,10 +188,13 @@ apnn_status apnn_conv2d_host(apnn_handle h, int wbits, int xbits, const void* Wt
     dev_epi.residual_out = nullptr;
     pe = &dev_epi;
   }
-  st = apnn_conv2d(h->stream, wbits, xbits, dW, dX, dO, B, H, W, CIN, COUT, R, stride, pe);
+  st = apnn_conv2d_ex(h->stream, APNN_ALGO_AUTO, wbits, xbits, dW, dX, dO, B, H, W, CIN, COUT, R, stride, pe,
+                      ws ? dWs : nullptr, ws);
   if (st != APNN_OK) return st;
   e = cudaMemcpyAsync(Out_host, dO, ob, cudaMemcpyDeviceToHost, h->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+  if (e != cudaSuccess) return apnn::cuda_fail(e, "device->host copy");
+  if (ws) return apnn_conv2d_check(h->stream, dWs, B, H, W, CIN, COUT, R);   // synchronises, reads the wait flag
+  e = cudaStreamSynchronize(h->stream);
   if (e != cudaSuccess) return apnn::cuda_fail(e, "device->host copy");
   return APNN_OK;
 }

@@ -157,6 +157,8 @@ struct Tc5Params {
   const int32_t* residual_in;  // optional dense int32 [rows][N], added before requantisation
   int32_t* residual_out;       // optional dense int32 [rows][N], the value after the add
   int res16_in, res16_out;     // residual_in / residual_out hold int16 (values saturate on the way out)
+  const float* affine_scale;   // OUT_FLOAT: out = float(value) * scale[c] + bias[c], [N] each
+  const float* affine_bias;
   // shared-memory plan (chosen on the host)
   int stages;            // ring depth
   int kgroup;            // K blocks per stage (one barrier round trip and one commit per group)
@@ -905,7 +907,16 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               }
           }
         }
-        if (C_INT32 || (!C_NOINT32 && p.out_mode == OUT_INT32)) {
+        if (!C_NOINT32 && !C_INT32 && p.out_mode == OUT_FLOAT) {
+          // batch-norm affine of an output layer: two separately rounded float operations per element (the
+          // CPU check computes the same two); the bits then leave through the 32-bit row stores below
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int col = min(col0 + j, p.N - 1);
+            v[j] = __float_as_uint(__fadd_rn(__fmul_rn((float)(int)v[j], __ldg(p.affine_scale + col)), __ldg(p.affine_bias + col)));
+          }
+        }
+        if (C_INT32 || (!C_NOINT32 && (p.out_mode == OUT_INT32 || p.out_mode == OUT_FLOAT))) {
           if (whole) {
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
@@ -1146,7 +1157,7 @@ cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorM
       return cudaErrorInvalidConfiguration;
     }
   }
-  const bool quantising = p.out_mode != APNN_OUT_INT32 && p.pool == APNN_POOL_NONE;
+  const bool quantising = p.out_mode != APNN_OUT_INT32 && p.out_mode != APNN_OUT_FLOAT && p.pool == APNN_POOL_NONE;
   const bool residuals = p.residual_in || p.residual_out;
   const bool thr_i8 = p.out_mode == APNN_OUT_THRESHOLDS && p.out_bits <= 2 && p.out_i8;
   const bool all16 = (!p.residual_in || p.res16_in) && (!p.residual_out || p.res16_out);
@@ -1310,7 +1321,8 @@ apnn_status tc5_expand2(cudaStream_t s, const uint32_t* pa, uint8_t* oa, long lo
 
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
-  if ((tc5_pair_worthwhile(M, N, K) && !(epi && (epi->out_i8 || epi->residual_i16))) || (epi && epi->n_peer_out > 0))
+  if ((tc5_pair_worthwhile(M, N, K) && !(epi && (epi->out_i8 || epi->residual_i16 || epi->out_mode == APNN_OUT_FLOAT))) ||
+      (epi && epi->n_peer_out > 0))
     return tc5_gemm_i8_pair(s, A8, B8, D, M, N, K, a_signed, b_signed, epi, status_flag);
   cudaError_t e;
   const int sms = device_sm_count();
@@ -1344,6 +1356,8 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.residual_out = epi ? epi->residual_out : nullptr;
   p.res16_in = epi ? (epi->residual_i16 & 1) : 0;
   p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
+  p.affine_scale = epi ? epi->affine_scale : nullptr;
+  p.affine_bias = epi ? epi->affine_bias : nullptr;
   p.idesc = make_idesc(a_signed, b_signed, bn);
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   if (splits > 1) {
@@ -1415,8 +1429,8 @@ bool tc5_conv_supported(int H, int W, int R, int stride, int pool) {
 
 apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int Hin, int Win,
                         int CIN, int COUT, int R, int stride, bool w_signed, const apnn_epilogue* epi,
-                        int* status_flag) {
-  if (tc5_conv_pair_applies(B, Hin, Win, CIN, COUT, R, stride, epi))
+                        int* status_flag, bool x_signed) {
+  if (!x_signed && tc5_conv_pair_applies(B, Hin, Win, CIN, COUT, R, stride, epi))
     return tc5_conv_i8_pair(s, X8, W8, Out, B, Hin, Win, CIN, COUT, R, w_signed, epi, status_flag);
   const int pad = (R - 1) / 2;
   const int in_halo = (epi && epi->in_halo) ? epi->in_halo : pad;
@@ -1513,7 +1527,9 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.residual_out = epi ? epi->residual_out : nullptr;
   p.res16_in = epi ? (epi->residual_i16 & 1) : 0;
   p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
-  p.idesc = make_idesc(false, w_signed, bn);  // A = activations (unsigned), B = filter
+  p.affine_scale = epi ? epi->affine_scale : nullptr;
+  p.affine_bias = epi ? epi->affine_bias : nullptr;
+  p.idesc = make_idesc(x_signed, w_signed, bn);  // A = activations (unsigned levels, or the centred signed bytes), B = filter
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < sms ? tiles : sms);
   if (splits > 1) {
@@ -1538,6 +1554,18 @@ apnn_status tc5_conv(cudaStream_t s, int wbits, int xbits, const uint32_t* Wt, c
   st = tc5_expand(s, Wt, w8, COUT, R * R * CIN, wbits, w_signed);
   if (st != APNN_OK) return st;
   return tc5_conv_i8(s, x8, w8, Out, B, H, W, CIN, COUT, R, stride, w_signed, epi, err);
+}
+
+int* tc5_flag_slot(void* workspace, int M, int N, int K) {
+  uint8_t* wa = reinterpret_cast<uint8_t*>(workspace);
+  return reinterpret_cast<int*>(wa + align_up((size_t)M * K, 256) + align_up((size_t)N * K, 256));
+}
+
+int* tc5_conv_flag_slot(void* workspace, int B, int H, int W, int CIN, int COUT, int R) {
+  const int pad = (R - 1) / 2;
+  uint8_t* x8 = reinterpret_cast<uint8_t*>(workspace);
+  return reinterpret_cast<int*>(x8 + align_up((size_t)B * (H + 2 * pad) * (W + 2 * pad) * CIN, 256) +
+                                align_up((size_t)COUT * R * R * CIN, 256));
 }
 
 int tc5_conv_read_error_flag(cudaStream_t s, const void* workspace, int B, int H, int W, int CIN, int COUT, int R) {

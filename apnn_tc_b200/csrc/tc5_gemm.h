@@ -28,7 +28,8 @@ bool tc5_conv_supported(int H, int W, int R, int stride, int pool);
 apnn_status tc5_conv(cudaStream_t s, int wbits, int xbits, const uint32_t* Wt, const uint32_t* X, void* Out, int B,
                      int H, int W, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi, void* workspace);
 apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int H, int W,
-                        int CIN, int COUT, int R, int stride, bool w_signed, const apnn_epilogue* epi, int* status_flag);
+                        int CIN, int COUT, int R, int stride, bool w_signed, const apnn_epilogue* epi, int* status_flag,
+                        bool x_signed = false);
 int tc5_conv_read_error_flag(cudaStream_t s, const void* workspace, int B, int H, int W, int CIN, int COUT, int R);
 // The same GEMM on CTA pairs (cta_group::2, 256 x 256 tiles); worthwhile once there are at
 // least as many pair tiles as SM pairs.
@@ -40,6 +41,9 @@ apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B
 bool tc5_conv_pair_applies(int B, int H, int W, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi);
 apnn_status tc5_conv_i8_pair(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, void* Out, int B, int H, int W,
                              int CIN, int COUT, int R, bool w_signed, const apnn_epilogue* epi, int* status_flag);
+// Where the status flag lives inside a GEMM / convolution workspace.
+int* tc5_flag_slot(void* workspace, int M, int N, int K);
+int* tc5_conv_flag_slot(void* workspace, int B, int H, int W, int CIN, int COUT, int R);
 // Flag raised by a bounded wait (0 = ran to completion); synchronises the stream.
 int tc5_read_error_flag(cudaStream_t s, const void* workspace, int M, int N, int K);
 }  // namespace apnn

@@ -35,7 +35,8 @@ constexpr int HALF = 128;     // rows of A and of B one CTA stages
 constexpr int STAGES = 6;
 constexpr int STAGE_BYTES = 2 * HALF * BK;  // 32 KiB per CTA
 constexpr int THR_BYTES_PER_WARP = 32 * 36 * 4;  // thresholds (256 x 16 B) or a padded 32 x 32 int32 block
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * THR_BYTES_PER_WARP;
+constexpr int WORD_BYTES_PER_WARP = 2 * 32 * 8 * 4;  // packed outputs of up to 2 bits: 8 words per row and plane, staged per tile
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * THR_BYTES_PER_WARP + 4 * WORD_BYTES_PER_WARP;
 constexpr int THREADS = 192;
 constexpr int GROUP_M = 8;    // bands of 8 pair-tiles (2048 rows) for L2 reuse
 
@@ -215,6 +216,11 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int nl = (1 << p.out_bits) - 1;
     const bool thr_staged = p.out_mode == OUT_THRESHOLDS && nl <= 3;
     int4* thr_s = reinterpret_cast<int4*>(thr_stage + (warp - 2) * THR_BYTES_PER_WARP);
+    // Packed outputs of one or two bits: a thread's eight words of a tile row (one per 32-column chunk) are
+    // collected here and leave as one 32-byte store per plane and destination -- whole sectors for HBM and
+    // for NVLink instead of eight scattered 4-byte stores.
+    uint32_t* word_s = reinterpret_cast<uint32_t*>(thr_stage + 4 * THR_BYTES_PER_WARP + (warp - 2) * WORD_BYTES_PER_WARP);
+    const bool words_staged = p.out_mode != OUT_INT32 && p.out_bits <= 2 && ((p.N >> 5) & 3) == 0;
     int staged_tn = -1;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, tl++) {
       int tm, tn;
@@ -314,12 +320,37 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               lv[j] = l;
             }
           }
+          const bool tile_whole = words_staged && (tn + 1) * TILE_N <= p.N;
           for (int b = 0; b < p.out_bits; b++) {
-            uint32_t word = 0;
+            uint32_t part[4] = {0u, 0u, 0u, 0u};   // four independent chains instead of one of 32 ORs
 #pragma unroll
-            for (int j = 0; j < 32; j++) word |= ((lv[j] >> b) & 1u) << (31 - j);
-            for (int q = 0; q < p.n_out; q++)
-              reinterpret_cast<uint32_t*>(p.outs[q])[b * p.out_plane_words + row * (p.N >> 5) + (col0 >> 5)] = word;
+            for (int j = 0; j < 32; j++) part[j & 3] |= ((lv[j] >> b) & 1u) << (31 - j);
+            const uint32_t word = (part[0] | part[1]) | (part[2] | part[3]);
+            if (tile_whole) {
+              word_s[(b * 32 + lane) * 8 + c] = word;
+            } else {
+              for (int q = 0; q < p.n_out; q++)
+                reinterpret_cast<uint32_t*>(p.outs[q])[b * p.out_plane_words + row * (p.N >> 5) + (col0 >> 5)] = word;
+            }
+          }
+        }
+      }
+      if (words_staged && row_ok && (tn + 1) * TILE_N <= p.N) {
+        // the row's eight words per plane: 32 contiguous, 32-byte aligned bytes of the packed output
+        for (int b = 0; b < p.out_bits; b++) {
+          const uint4 lo = *reinterpret_cast<const uint4*>(word_s + (b * 32 + lane) * 8);
+          const uint4 hi = *reinterpret_cast<const uint4*>(word_s + (b * 32 + lane) * 8 + 4);
+          const long long at = b * p.out_plane_words + row * (p.N >> 5) + tn * (TILE_N >> 5);
+          for (int q = 0; q < p.n_out; q++) {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(p.outs[q]) + at;   // 16-byte aligned: N/32 is a multiple of 4
+            if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+              asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+                           "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                           : "memory");
+            } else {
+              *reinterpret_cast<uint4*>(dst) = lo;
+              *reinterpret_cast<uint4*>(dst + 4) = hi;
+            }
           }
         }
       }
@@ -369,6 +400,7 @@ bool tc5_pair_worthwhile(int M, int N, int K) {
 
 apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                              bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
+  if (epi && epi->out_mode == APNN_OUT_FLOAT) return APNN_ERR_UNSUPPORTED;   // the float affine lives in the single-CTA kernel
   CUtensorMap map_a, map_b;
   if (!make_half_map(&map_a, A8, M, K) || !make_half_map(&map_b, B8, N, K))
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");

@@ -12,7 +12,9 @@ is project-defined): activations are ``a_bit`` levels in packed NHWC planes with
 for the next convolution, weights are 1-bit meaning -1/+1, every hidden layer requantises
 through per-channel int32 thresholds (batch-norm folded on the host), pooling is a 2x2
 maximum on the int32 value, a residual is the int32 value saved by an earlier layer, and
-the output layer returns int32 logits.  Channel counts are padded to multiples of 128 with
+the output layer returns float logits (int32 values times a per-class scale plus a bias; or the
+int32 values themselves), and the first layer reads the image at 8 bits (re-centred) unless
+``first_bits`` is 0.  Channel counts are padded to multiples of 128 with
 zero activations (padded output channels get thresholds no value reaches).
 
 Everything here is host plumbing: every tensor operation is a call into ``libapnn_b200.so``.
@@ -67,6 +69,11 @@ class ModelSpec:
     layers: List[LayerSpec]
     a_bit: int = 2
     w_bit: int = 1
+    # The reference's higher-precision first and last layers (InConv128Layer / Out128Layer,
+    # APNN-TC-nn/src/kernel.cuh:583-682, 397-447), as exact integer work plus one float affine:
+    first_bits: int = 8        # 8: the image enters at 8 bits, re-centred (level - 128, padding = 0), times the
+                               # -1/+1 filter on the int8 tensor-core path; 0: quantised to a_bit like a hidden map
+    float_logits: bool = True  # the output layer returns float(value) * scale[c] + bias[c] instead of int32
 
 
 def alexnet_spec(n_classes: int = 1000) -> ModelSpec:
@@ -134,6 +141,7 @@ class LayerParams:
     shape: Dict[str, int] = field(default_factory=dict)
     im2col_planes: Optional[np.ndarray] = None   # first layer only: [1][COUTp][PAD128(R*R*C)/32], k = (i*R+j)*C+c
     window_planes: Optional[np.ndarray] = None   # first layer only: the same filter for apnn_quantize_window_rows_i8
+    affine: Optional[tuple] = None               # output layer with float logits: (scale, bias), float32 [COUTp]
 
 
 def _pack_bits_msb(bits: np.ndarray) -> np.ndarray:
@@ -231,14 +239,23 @@ def make_params(spec: ModelSpec, seed: int = 0xA9117C + 5, image_hw: Optional[in
             dims[ls.name] = (1, 1, ls.cout)
             shape = {"K": K, "coutp": coutp}
         thr = None
+        affine = None
+        if ls.kind == "out" and spec.float_logits:
+            sc = np.zeros(coutp, dtype=np.float32)
+            bi = np.zeros(coutp, dtype=np.float32)
+            sc[: ls.cout] = rng.uniform(0.5, 1.5, ls.cout).astype(np.float32)
+            bi[: ls.cout] = rng.uniform(-1.0, 1.0, ls.cout).astype(np.float32)
+            affine = (sc, bi)
         if ls.quantise:
             scale = rng.uniform(0.5, 1.5, ls.cout).astype(np.float32)
             bias = rng.uniform(-1.0, 1.0, ls.cout).astype(np.float32)
             extra = 2.0 if ls.residual_from else 1.0
-            sigma = math.sqrt(3.5 * fan_in * extra) / 4.0
+            # second moment of one input element: uniform a_bit levels, or the centred 8-bit image
+            m2 = 5461.5 if (ls.kind == "conv" and src is None and spec.first_bits == 8) else 3.5
+            sigma = math.sqrt(m2 * fan_in * extra) / 4.0
             thr = np.full((coutp, (1 << spec.a_bit) - 1), INT_MAX, dtype=np.int32)
             thr[: ls.cout] = fold_thresholds(scale, bias, 0.0, sigma, spec.a_bit)
-        out[ls.name] = LayerParams(np.ascontiguousarray(planes), thr, shape)
+        out[ls.name] = LayerParams(np.ascontiguousarray(planes), thr, shape, affine=affine)
         if ls.kind == "conv" and src is None:
             out[ls.name].im2col_planes = im2col
             out[ls.name].window_planes = window
@@ -254,7 +271,8 @@ def value_bounds(spec: ModelSpec, params: Dict[str, LayerParams]) -> Dict[str, i
     for ls in spec.layers:
         sh = params[ls.name].shape
         fan = sh["K"] if ls.kind != "conv" else ls.R * ls.R * ls.cin
-        bound[ls.name] = ((1 << spec.a_bit) - 1) * fan + (bound[ls.residual_from] if ls.residual_from else 0)
+        top = 128 if (ls is spec.layers[0] and spec.first_bits == 8) else (1 << spec.a_bit) - 1
+        bound[ls.name] = top * fan + (bound[ls.residual_from] if ls.residual_from else 0)
     return bound
 
 
@@ -306,6 +324,12 @@ class Network:
         self.tc5_ok: Dict[str, bool] = {}
         self.first_im2col = None
         self.first_window_rows = False
+        self.affine: Dict[str, tuple] = {}
+        self.logit_acc = None
+        if spec.first_bits not in (0, 8):
+            raise ValueError("first_bits is 0 (a_bit levels) or 8 (centred 8-bit image)")
+        if spec.first_bits == 8 and not use_tcgen05:
+            raise ValueError("the 8-bit first layer runs on the tcgen05 path only")
         x8_bytes = 0
         for ls in spec.layers:
             p = self.params[ls.name]
@@ -349,7 +373,14 @@ class Network:
                 if ls.quantise:
                     self.out[ls.name] = torch.zeros((a, B, sh["coutp"] // 32), dtype=torch.int32, device=self.device)
                 else:
-                    self.out[ls.name] = torch.zeros((B, sh["coutp"]), dtype=torch.int32, device=self.device)
+                    as_float = p.affine is not None
+                    self.out[ls.name] = torch.zeros((B, sh["coutp"]), dtype=torch.float32 if as_float else torch.int32,
+                                                    device=self.device)
+                    if as_float:
+                        self.affine[ls.name] = (torch.from_numpy(p.affine[0]).to(self.device),
+                                                torch.from_numpy(p.affine[1]).to(self.device))
+                        if not use_tcgen05:   # warp-level GEMM -> int32, then the affine as a pass of its own
+                            self.logit_acc = torch.zeros((B, sh["coutp"]), dtype=torch.int32, device=self.device)
                 if use_tcgen05:
                     x8_bytes = max(x8_bytes, B * sh["K"])
             if self.tc5_ok[ls.name]:
@@ -360,6 +391,8 @@ class Network:
                 _cabi.check(self.L.apnn_expand_planes(_stream_ptr(), wp.data_ptr(), w8.data_ptr(), rows, k, 1, 1),
                             "expand weights")
                 self.w8[ls.name] = w8
+        if spec.first_bits == 8 and self.first_im2col is None:
+            raise ValueError("the 8-bit first layer needs the gathered (im2col) form of the first convolution")
         # a quantised output feeds the next layers as int8 rows, written by the producing kernel's
         # epilogue, when producer and every consumer run on the tcgen05 path: no packed planes in
         # between and no expand pass
@@ -432,6 +465,9 @@ class Network:
         return self.out[src]
 
     def _epilogue(self, ls: LayerSpec, conv: bool):
+        if ls.name in self.affine:
+            sc, bi = self.affine[ls.name]
+            return make_epilogue("float", affine_scale=sc, affine_bias=bi)
         mode = "thresholds" if ls.quantise else "int32"
         res_in = self.res[ls.residual_from] if ls.residual_from else None
         res_out = self.res.get(ls.name) if (ls.save_residual and ls.quantise) else None
@@ -464,8 +500,9 @@ class Network:
         if self.first_im2col and self.first_im2col[0] == ls.name:
             _, Hc, Wc, kp = self.first_im2col
             epi.in_halo = 0
+            signs = 3 if self.spec.first_bits == 8 else 1   # bit 0: -1/+1 filter bytes; bit 1: centred (signed) image bytes
             _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), self.x8.data_ptr(), out.data_ptr(), B,
-                                              Hc, Wc, kp, sh["coutp"], 1, 1, 1, ctypes.byref(epi), self.flag.data_ptr()),
+                                              Hc, Wc, kp, sh["coutp"], 1, 1, signs, ctypes.byref(epi), self.flag.data_ptr()),
                         "apnn_conv2d_i8 " + ls.name)
             return 1
         if self.tc5_ok[ls.name]:
@@ -499,6 +536,14 @@ class Network:
             _cabi.check(self.L.apnn_gemm_i8(s, x8.data_ptr(), self.w8[ls.name].data_ptr(), out.data_ptr(), B, N, K,
                                             0, 1, ctypes.byref(epi), self.flag.data_ptr()), "apnn_gemm_i8 " + ls.name)
             return n
+        if ls.name in self.affine:
+            plain = make_epilogue("int32", signed="x")
+            _cabi.check(self.L.apnn_gemm_ex(s, _cabi.ALGO_IMMA, a, 1, X.data_ptr(), self.w_planes[ls.name].data_ptr(),
+                                            self.logit_acc.data_ptr(), B, N, K, ctypes.byref(plain), None, 0),
+                        "apnn_gemm_ex " + ls.name)
+            _cabi.check(self.L.apnn_requantize_i32(s, self.logit_acc.data_ptr(), out.data_ptr(), B, N, ctypes.byref(epi)),
+                        "apnn_requantize_i32 " + ls.name)
+            return 2
         epi.signed_operand = _cabi.SIGN_X
         _cabi.check(self.L.apnn_gemm_ex(s, _cabi.ALGO_IMMA, a, 1, X.data_ptr(), self.w_planes[ls.name].data_ptr(),
                                         out.data_ptr(), B, N, K, ctypes.byref(epi), None, 0), "apnn_gemm_ex " + ls.name)
@@ -506,7 +551,8 @@ class Network:
 
     # -- whole model -----------------------------------------------------------------
     def forward(self, images: torch.Tensor) -> torch.Tensor:
-        """images: float32 [B, H, W, C] on the device.  Returns int32 logits [B, PAD128(classes)]."""
+        """images: float32 [B, H, W, C] on the device.  Returns the logits [B, PAD128(classes)]: float32 with
+        ``float_logits`` (the default), else the int32 values."""
         a = self.spec.a_bit
         s = _stream_ptr()
         rows = self.batch * self.hw * self.hw
@@ -516,8 +562,9 @@ class Network:
             # quantise + gather the first layer's windows straight into the int8 operand buffer
             first = self.by_name[self.first_im2col[0]]
             gather = self.L.apnn_quantize_window_rows_i8 if self.first_window_rows else self.L.apnn_quantize_im2col_i8
+            bits = (8 | _cabi.QUANT_CENTRED) if self.spec.first_bits == 8 else a
             _cabi.check(gather(s, images.data_ptr(), self.x8.data_ptr(), self.batch, self.hw, self.hw,
-                               self.spec.image_channels, first.R, first.stride, a, self.first_im2col[3]),
+                               self.spec.image_channels, first.R, first.stride, bits, self.first_im2col[3]),
                         "first-layer gather")
         else:
             target = self.image_levels if h0 else self.image_planes

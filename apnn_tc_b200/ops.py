@@ -41,17 +41,19 @@ def _dev_words(t: torch.Tensor, name: str) -> torch.Tensor:
 def make_epilogue(out_mode: str = "int32", out_bits: int = 0, signed: str = "none", pool: str = "none",
                   out_halo: int = 0, in_halo: int = 0, thresholds: Optional[torch.Tensor] = None,
                   residual_in: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None,
-                  peer_out: Optional[list] = None, out_i8: bool = False, residual_i16: int = 0) -> Epilogue:
+                  peer_out: Optional[list] = None, out_i8: bool = False, residual_i16: int = 0,
+                  affine_scale: Optional[torch.Tensor] = None, affine_bias: Optional[torch.Tensor] = None) -> Epilogue:
     """Build the fused-epilogue descriptor.
 
-    out_mode: "int32" | "lowbits" (the reference's ``val & (2^bits-1)``) | "thresholds"
+    out_mode: "int32" | "lowbits" (the reference's ``val & (2^bits-1)``) | "thresholds" |
+              "float" (float(value) * affine_scale[c] + affine_bias[c]; gemm_i8 / conv2d_i8 only)
     signed:   "none" | "w" | "x" -- which argument's bits mean -1/+1
     pool:     "none" | "avg" (reference: truncating (a+b+c+d)/4 before requantisation) | "max"
     residual_in / residual_out: dense int32 [rows, channels] added before / saved after the add
     peer_out: raw device addresses that also receive every output tile (tcgen05 pair GEMM only)
     """
     e = Epilogue()
-    e.out_mode = {"int32": 0, "lowbits": 1, "thresholds": 2}[out_mode]
+    e.out_mode = {"int32": 0, "lowbits": 1, "thresholds": 2, "float": 3}[out_mode]
     e.out_bits = out_bits
     e.signed_operand = {"none": 0, "w": 1, "x": 2}[signed]
     e.pool = {"none": 0, "avg": 1, "max": 2}[pool]
@@ -68,7 +70,9 @@ def make_epilogue(out_mode: str = "int32", out_bits: int = 0, signed: str = "non
         e.n_peer_out = len(peer_out)
         for i, ptr in enumerate(peer_out):   # raw device addresses (peer-mapped memory)
             e.peer_out[i] = int(ptr)
-    e._keepalive = (thresholds, residual_in, residual_out)
+    e.affine_scale = affine_scale.data_ptr() if affine_scale is not None else None
+    e.affine_bias = affine_bias.data_ptr() if affine_bias is not None else None
+    e._keepalive = (thresholds, residual_in, residual_out, affine_scale, affine_bias)
     return e
 
 
@@ -101,10 +105,11 @@ def gemm_i8(W8: torch.Tensor, X8: torch.Tensor, out: Optional[torch.Tensor] = No
     N, K2 = X8.shape
     if K != K2:
         raise ValueError("operands disagree on K")
-    packed = epilogue is not None and epilogue.out_mode != 0
+    packed = epilogue is not None and epilogue.out_mode in (1, 2)
     if out is None:
         shape = (epilogue.out_bits, M, N // 32) if packed else (M, N)
-        out = torch.empty(shape, dtype=torch.int32, device=W8.device)
+        is_float = epilogue is not None and epilogue.out_mode == 3
+        out = torch.empty(shape, dtype=torch.float32 if is_float else torch.int32, device=W8.device)
     if status_flag is None:
         status_flag = torch.empty(1, dtype=torch.int32, device=W8.device)
     st = _cabi.lib().apnn_gemm_i8(_stream_ptr(), W8.data_ptr(), X8.data_ptr(), out.data_ptr(), M, N, K,

@@ -43,8 +43,13 @@ enum {
   APNN_OUT_INT32 = 0,     /* int32 value per output element */
   APNN_OUT_LOWBITS = 1,   /* low out_bits bits of the value, plane-split and packed (the
                              reference's fused kernels) */
-  APNN_OUT_THRESHOLDS = 2 /* level = number of per-channel int32 thresholds the value reaches
-                             (batch-norm + quantiser folded on the host), packed */
+  APNN_OUT_THRESHOLDS = 2, /* level = number of per-channel int32 thresholds the value reaches
+                              (batch-norm + quantiser folded on the host), packed */
+  APNN_OUT_FLOAT = 3      /* float per output element: float(value) * affine_scale[c] + affine_bias[c], the
+                             multiply and the add rounded separately (no fused multiply-add) -- the output
+                             layer's batch-norm affine, Out128Layer of NN/kernel.cuh:397-447, whose
+                             (K - 2*popc) is the +-1 dot product `value`.  apnn_gemm_i8, apnn_conv2d_i8 and
+                             apnn_requantize_i32 only */
 };
 /* Which operand's bits mean -1/+1 instead of 0/1 (that operand must be 1-bit). */
 enum { APNN_SIGN_NONE = 0, APNN_SIGN_W = 1, APNN_SIGN_X = 2 };
@@ -64,6 +69,9 @@ enum {
 };
 
 typedef struct apnn_epilogue {
+  uint32_t struct_size;      /* sizeof(apnn_epilogue), as APNN_EPILOGUE_INIT sets it: a caller compiled against
+                                another layout of this structure is refused with APNN_ERR_INVALID_ARG instead of
+                                being misread */
   int32_t out_mode;          /* APNN_OUT_* */
   int32_t out_bits;          /* 1..8 for the packed modes */
   int32_t signed_operand;    /* APNN_SIGN_*: value = 2*acc - (sum of the other operand's row) */
@@ -103,7 +111,11 @@ typedef struct apnn_epilogue {
                                  ResNet block).  The caller guarantees the values fit (|value| <=
                                  (2^xbits - 1) * K plus the bound of the added residual); stores
                                  saturate.  No reference counterpart. */
+  const float *affine_scale;  /* APNN_OUT_FLOAT: device, [channels] */
+  const float *affine_bias;   /* APNN_OUT_FLOAT: device, [channels] */
 } apnn_epilogue;
+/* Initialiser that zeroes every field and records the structure's size: apnn_epilogue e = APNN_EPILOGUE_INIT; */
+#define APNN_EPILOGUE_INIT {(uint32_t)sizeof(apnn_epilogue)}
 
 const char *apnn_status_string(apnn_status s);
 /* Text of the last CUDA error seen by this thread inside the library ("" if none). */
@@ -213,13 +225,16 @@ apnn_status apnn_conv2d_ex(void *stream, int algo, int wbits, int xbits, const v
 size_t apnn_conv2d_workspace_bytes(int algo, int B, int H, int W, int CIN, int COUT, int R);
 apnn_status apnn_conv2d_check(void *stream, const void *workspace, int B, int H, int W, int CIN, int COUT,
                               int R);
+/* w_signed: bit 0 = the filter bytes are signed (-1/+1 weights), bit 1 = the activation bytes are signed
+ * (the centred 8-bit first layer, APNN_QUANT_CENTRED below). */
 apnn_status apnn_conv2d_i8(void *stream, const void *W8, const void *X8, void *Out, int B, int H, int W,
                            int CIN, int COUT, int R, int stride, int w_signed,
                            const apnn_epilogue *epi, int *status_flag);
 
 /* The quantising part of the epilogue on its own: int32 values[rows][N] -> levels (out_mode
  * APNN_OUT_LOWBITS or APNN_OUT_THRESHOLDS with epi->thresholds [N][2^out_bits - 1]) -> packed
- * planes [out_bits][rows][N/32], or int8 rows [rows][N] when epi->out_i8 is set.  It follows a
+ * planes [out_bits][rows][N/32], or int8 rows [rows][N] when epi->out_i8 is set; with APNN_OUT_FLOAT
+ * -> float[rows][N] = float(value) * affine_scale[n] + affine_bias[n].  It follows a
  * GEMM whose int32 result was produced by split-K (apnn_gemm_i8 splits K over idle SMs when a
  * problem has few tiles and a long K, which needs the int32 output).  N % 32 == 0; pooling,
  * residuals and sign correction are not taken here.  Semantics of `val & 3` / thresholds as in
@@ -262,6 +277,12 @@ apnn_status apnn_quantize_im2col(void *stream, const float *images, uint32_t *pl
  * byte order of apnn_expand_planes, zero beyond R*R*C.  kp: a multiple of 64, >= R*R*C.
  * Replaces images_quantization + Bit_compression + the expand pass for the first layer
  * (NN/kernel.cuh:129-161); no counterpart of the window gather in the reference. */
+/* bits may carry APNN_QUANT_CENTRED (with 8 bits only): every level is stored as level - 128 in a signed byte,
+ * elements outside the image stay 0 -- the image at 8-bit precision with zero meaning zero, as the
+ * reference's full-precision first layer skips out-of-frame pixels (InConv128Layer, NN/kernel.cuh:583-682:
+ * float image x +-1 filter).  With +-1 filter bytes the int32 accumulator is exact and equals 12.8 x the
+ * reference's float sum of the quantised image.  Run the convolution with bit 1 of w_signed set. */
+#define APNN_QUANT_CENTRED 0x100
 apnn_status apnn_quantize_im2col_i8(void *stream, const float *images, void *out_i8, int B, int H,
                                     int W, int C, int R, int stride, int bits, int kp);
 

@@ -39,10 +39,21 @@ inline void apmm_w1a4(const int4* W, const int4* X, int* D, int M, int N, int K,
 inline void apmm_w2a2(const int4* W, const int4* X, int* D, int M, int N, int K, int wb = 2, int xb = 2,
                       cudaStream_t s = 0) { apmm(W, X, D, M, N, K, wb, xb, s); }
 
+/* The reference's fused kernels keep the low bits of the accumulator: the epilogue descriptor for that,
+ * every field named (nothing here depends on the order of the structure's members). */
+inline apnn_epilogue apnn_shim_lowbits(int out_bits, int pool) {
+  apnn_epilogue e = APNN_EPILOGUE_INIT;
+  e.out_mode = APNN_OUT_LOWBITS;
+  e.out_bits = out_bits;
+  e.signed_operand = APNN_SIGN_NONE;
+  e.pool = pool;
+  return e;
+}
+
 /* LIB/66_bmmaTensorCoreGemm.cuh:81, LIB/73_...cuh:81: accumulator & 3, plane-split, packed along N */
 inline void apmm_decompose(const int4* W, const int4* X, int* D, int M, int N, int K, int wb, int xb, int out_bits,
                            cudaStream_t s = 0) {
-  apnn_epilogue e = {APNN_OUT_LOWBITS, out_bits, APNN_SIGN_NONE, APNN_POOL_NONE, 0, 0, nullptr};
+  apnn_epilogue e = apnn_shim_lowbits(out_bits, APNN_POOL_NONE);
   APNN_SHIM_CHECK(apnn_gemm_ex(s, APNN_ALGO_AUTO, wb, xb, W, X, D, M, N, K, &e, nullptr, 0));
 }
 inline void apmm_w1a2_decompose(const int4* W, const int4* X, int* D, int M, int N, int K, int wb = 1, int xb = 2,
@@ -60,7 +71,7 @@ inline void compute_conv_imma(const int4* W, const int4* X, int* Output, int Hei
 /* LIB/67_...cu:58, LIB/68_...cu:58, LIB/70_...cu:58, LIB/69_...cuh:59 */
 inline void APConv_pack(const int4* W, const int4* X, int* Output, int Height, int Width, int CIN, int COUT, int wb,
                         int xb, int pool, cudaStream_t s = 0) {
-  apnn_epilogue e = {APNN_OUT_LOWBITS, 2, APNN_SIGN_NONE, pool ? APNN_POOL_AVG2 : APNN_POOL_NONE, 0, 0, nullptr};
+  apnn_epilogue e = apnn_shim_lowbits(2, pool ? APNN_POOL_AVG2 : APNN_POOL_NONE);
   APNN_SHIM_CHECK(apnn_conv2d(s, wb, xb, W, X, Output, 1, Height, Width, CIN, COUT, 3, 1, &e));
 }
 inline void APConv_w1a2_pack(const int4* W, const int4* X, int* O, int H, int Wd, int CIN, int COUT,

@@ -341,3 +341,40 @@ def quantize_im2col(images, R, stride, bits):
     lib().apnn_oracle_quantize_im2col(images.ctypes.data_as(_f32p), out.ctypes.data_as(_u32p), B, H, Wd, C, R, stride,
                                       bits)
     return out
+
+
+# ----------------------------------------------------------------------------- first / last layer (unpinned)
+def centred_first_layer(Wt, levels8, real_channels: int, stride=1, threads: int = 1):
+    """First layer at 8-bit precision ("parity unpinned": the reference's InConv128Layer,
+    APNN-TC-nn/src/kernel.cuh:583-682, multiplies the float image by +-1 weights and accumulates in
+    float, an order-dependent sum no test pins).  Defined here on exact integers: the image is
+    quantised to 8 bits by ``quantize`` (clip to [-10, 10], 256 steps), re-centred to
+    a = level - 128 so that zero means zero, padding contributes nothing (as the reference skips
+    out-of-frame pixels), weights are -1/+1:
+
+        value = sum w * a = (sum w * level) - 128 * (sum of w over the in-frame taps)
+
+    both sums built from the pinned popcount convolution.  ``levels8``: uint [B, H, W, Cp] whose first
+    ``real_channels`` channels are the image (the rest is storage padding and counts as zero);
+    ``Wt``: 1-bit planes [1][COUT][R][R][Cp/32].  Returns int32 [B, Ho, Wo, COUT]."""
+    R = Wt.shape[2]
+    pad = (R - 1) // 2
+    B, H, W, Cp = levels8.shape
+    real = np.zeros((B, H, W, Cp), dtype=np.uint32)
+    real[..., :real_channels] = 1
+    xp = np.zeros((B, H + 2 * pad, W + 2 * pad, Cp), dtype=np.uint32)
+    ip = np.zeros_like(xp)
+    xp[:, pad:pad + H, pad:pad + W] = levels8
+    ip[:, pad:pad + H, pad:pad + W] = real
+    X8, X1 = pack_levels(xp, 8), pack_levels(ip, 1)
+    first = signed_correct(conv_popc(Wt, X8, stride=stride, threads=threads), conv_window_sums(X8, R, stride), 0)
+    second = signed_correct(conv_popc(Wt, X1, stride=stride, threads=threads), conv_window_sums(X1, R, stride), 0)
+    return (first.astype(np.int64) - 128 * second.astype(np.int64)).astype(np.int32)
+
+
+def affine_f32(V, scale, bias):
+    """Output layer ("parity unpinned"; Out128Layer, APNN-TC-nn/src/kernel.cuh:397-447, whose
+    (K - 2*popc) is the +-1 dot product V): float32(V) * scale[c] + bias[c], the multiply and the
+    add each rounded to float32 (two IEEE operations, no fused multiply-add)."""
+    prod = np.asarray(V).astype(np.float32) * np.asarray(scale, dtype=np.float32)
+    return (prod + np.asarray(bias, dtype=np.float32)).astype(np.float32)

@@ -10,10 +10,12 @@ import oracle
 
 
 def forward_reference(spec, params, images, threads=8):
-    """images: float32 [B, H, W, C].  Returns (logits int32 [B, PAD128(classes)], levels, values)."""
+    """images: float32 [B, H, W, C].  Returns (logits [B, PAD128(classes)] -- float32 with float_logits, else
+    int32 --, levels, values)."""
     a = spec.a_bit
     B = images.shape[0]
-    lv0 = oracle.quantize(images, a)
+    first8 = spec.first_bits == 8
+    lv0 = oracle.quantize(images, 8 if first8 else a)
     cp = params[spec.layers[0].name].shape["cinp"]   # stored channels of the image (zero-padded)
     x0 = np.zeros(images.shape[:3] + (cp,), dtype=np.uint32)
     x0[..., : spec.image_channels] = lv0
@@ -23,7 +25,13 @@ def forward_reference(spec, params, images, threads=8):
     for ls in spec.layers:
         src = ls.src or prev
         p = params[ls.name]
-        if ls.kind == "conv":
+        if ls.kind == "conv" and src is None and first8:
+            # the image at 8 bits, re-centred, times the -1/+1 filter (oracle.centred_first_layer)
+            v = oracle.centred_first_layer(p.weight_planes, levels[None], spec.image_channels, stride=ls.stride,
+                                           threads=threads)
+            if ls.pool == 2:
+                v = oracle.pool2x2(v, 2)
+        elif ls.kind == "conv":
             x = levels[src]
             pad = (ls.R - 1) // 2
             xp = np.zeros((B, x.shape[1] + 2 * pad, x.shape[2] + 2 * pad, x.shape[3]), dtype=np.uint32)
@@ -44,4 +52,8 @@ def forward_reference(spec, params, images, threads=8):
         if ls.quantise:
             levels[ls.name] = oracle.levels(v, a, 2, p.thresholds).astype(np.uint32)
         prev = ls.name
-    return values[spec.layers[-1].name], levels, values
+    last = spec.layers[-1].name
+    logits = values[last]
+    if params[last].affine is not None:
+        logits = oracle.affine_f32(logits, params[last].affine[0], params[last].affine[1])
+    return logits, levels, values

@@ -53,6 +53,15 @@ def test_argument_validation_returns_status_codes():
     assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 128, ctypes.byref(e), None, 0) == 2
     e = _cabi.Epilogue(out_mode=2, out_bits=2)  # thresholds missing
     assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 128, ctypes.byref(e), None, 0) == 1
+    # a descriptor whose recorded size is not this library's structure (a caller built against another layout)
+    e = _cabi.Epilogue(out_mode=1, out_bits=2)
+    e.struct_size = 64
+    assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 128, ctypes.byref(e), None, 0) == 1
+    # the float affine output exists on the int8 entry points only; there it needs both vectors
+    e = _cabi.Epilogue(out_mode=3)
+    assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 128, ctypes.byref(e), None, 0) == 2
+    flag = (ctypes.c_int * 1)()
+    assert L.apnn_gemm_i8(None, p, p, p, 64, 64, 128, 0, 0, ctypes.byref(e), ctypes.addressof(flag)) == 1
     # tcgen05 path without a workspace
     assert L.apnn_gemm_ex(None, 3, 1, 2, p, p, p, 128, 256, 128, None, None, 0) == 4
     assert L.apnn_gemm_workspace_bytes(3, 1, 2, 128, 256, 128) >= (128 + 256) * 128

@@ -16,6 +16,8 @@ pytestmark = pytest.mark.gpu
 def test_model_logits_match_reference(cuda_device, model, hw, batch, use_tcgen05):
     from apnn_tc_b200 import nets
     spec = nets.MODELS[model](n_classes=200)
+    if not use_tcgen05:
+        spec.first_bits = 0      # the 8-bit first layer exists on the tcgen05 path; float logits run on both
     params = nets.make_params(spec, image_hw=hw, narrow=use_tcgen05)
     rng = np.random.default_rng(123)
     images = rng.uniform(-10, 10, size=(batch, hw, hw, 3)).astype(np.float32)
@@ -23,7 +25,7 @@ def test_model_logits_match_reference(cuda_device, model, hw, batch, use_tcgen05
     net = nets.Network(spec, batch, params, image_hw=hw, use_tcgen05=use_tcgen05)
     logits = net.forward(torch.from_numpy(images).cuda())
     net.check()
-    assert np.array_equal(to_host(logits, np.int32), want)
+    assert logits.dtype == torch.float32 and np.array_equal(logits.cpu().numpy(), want)   # bit-exact floats
     # every hidden layer too: packed planes (inside their ring) and saved residuals
     for ls in spec.layers:
         if ls.kind == "conv" and ls.quantise:
@@ -57,8 +59,24 @@ def test_full_size_models_match_reference(cuda_device, model):
         if ls.name in net.res:
             got = net.res[ls.name].cpu().numpy().astype(np.int32)
             assert np.array_equal(got.reshape(values[ls.name].shape), values[ls.name]), ls.name
-    assert np.array_equal(to_host(logits, np.int32), want)
+    assert logits.dtype == torch.float32 and np.array_equal(logits.cpu().numpy(), want)
     assert len(np.unique(levels[spec.layers[-2].name])) > 1
+    assert len(np.unique(levels[spec.layers[0].name])) == 4        # the 8-bit first layer uses every output level
+
+
+def test_quantised_first_layer_and_integer_logits(cuda_device):
+    """first_bits = 0 / float_logits = False: the image quantised to a_bit like a hidden map and int32 logits."""
+    from apnn_tc_b200 import nets
+    spec = nets.resnet18_spec(n_classes=200)
+    spec.first_bits, spec.float_logits = 0, False
+    params = nets.make_params(spec, image_hw=64)
+    images = np.random.default_rng(5).uniform(-10, 10, size=(3, 64, 64, 3)).astype(np.float32)
+    want, levels, _ = forward_reference(spec, params, images)
+    net = nets.Network(spec, 3, params, image_hw=64)
+    logits = net.forward(torch.from_numpy(images).cuda())
+    net.check()
+    assert logits.dtype == torch.int32 and np.array_equal(logits.cpu().numpy(), want)
+    assert np.array_equal(net.levels_of("Conv1").cpu().numpy(), levels["Conv1"])
 
 
 @pytest.mark.parametrize("model,batch", [("alexnet", 128), ("resnet18", 128), ("resnet18", 1024), ("vgg_variant", 128)])

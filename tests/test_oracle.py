@@ -176,10 +176,26 @@ def test_network_value_bounds_decide_int16_residuals():
     spec = nets.resnet18_spec(n_classes=10)
     params = nets.make_params(spec, image_hw=32)
     b = nets.value_bounds(spec, params)
-    assert b["Conv1"] == 3 * 7 * 7 * 3
+    assert b["Conv1"] == 128 * 7 * 7 * 3          # the 8-bit, re-centred first layer: |a| <= 128
     assert b["L1B1C2"] == 3 * 9 * 64 + b["Conv1"]
     assert max(v for k, v in b.items() if k.endswith("C2")) == b["L4B2C2"] == 28416
     spec4 = nets.resnet18_spec(n_classes=10)
     spec4.a_bit = 4
     b4 = nets.value_bounds(spec4, nets.make_params(spec4, image_hw=32))
     assert b4["L4B2C2"] > 32767 and b4["L1B1C2"] <= 32767
+
+
+def test_eight_bit_quantiser_needs_no_division(tmp_path):
+    """oracle/check_quantise8.c: for every float t in [0, 20], rint((t * 256) / 20) == rint(t * 12.8f) -- the form
+    the GPU packers use for the 8-bit first layer is the reference quantiser's, exhaustively."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("gcc not on PATH")
+    src = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "check_quantise8.c")
+    exe = str(tmp_path / "check_quantise8")
+    subprocess.check_call([gcc, "-O2", "-mfma", "-ffp-contract=off", "-o", exe, src, "-lm"])
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout
+    assert "checked=1101004801 mismatches=0" in r.stdout
