@@ -718,6 +718,128 @@ def conv_c3_block(torch, ap, cabi):
     return out
 
 
+# ----------------------------------------------------------------------------- single kernels (profiling cases)
+def kernel_cases(torch, ap, cabi):
+    """name -> (kernel it exercises, set-up returning (call, algorithmic bytes, algorithmic ops)).  Small enough for
+    an ncu capture (inputs above the 126 MB L2 where the kernel is memory-bound, a few hundred MB at most)."""
+    from apnn_tc_b200.ops import _stream_ptr
+    L = cabi.lib()
+    gen = torch.Generator(device="cuda").manual_seed(0xA9117C + 9)
+
+    def gemm(M_, N_, K_, algo, wb=1, xb=2):
+        def setup():
+            W, X = words(torch, (wb, M_, K_ // 32), gen), words(torch, (xb, N_, K_ // 32), gen)
+            D = torch.empty((M_, N_), dtype=torch.int32, device="cuda")
+            ws = torch.empty(ap.gemm_workspace_bytes(M_, N_, K_), dtype=torch.uint8, device="cuda") if algo == "tcgen05" else None
+            return (lambda: ap.apmm(W, X, D, algo=algo, workspace=ws)), wb * M_ * K_ // 8 + xb * N_ * K_ // 8 + 4 * M_ * N_, 2.0 * M_ * N_ * K_
+        return setup
+
+    def pack(from_float):
+        def setup():
+            rows, C = 65536, 512
+            src = (torch.rand((rows, C), device="cuda", generator=gen) * 20 - 10) if from_float else \
+                torch.randint(0, 4, (rows, C), dtype=torch.int32, device="cuda", generator=gen)
+            out = torch.empty((2, rows, C // 32), dtype=torch.int32, device="cuda")
+            fn = (lambda: ap.images_quantization(src, 2, out)) if from_float else (lambda: ap.Bit_compression(src, 2, out))
+            return fn, 4 * rows * C + 2 * rows * C // 8, 0.0
+        return setup
+
+    def expand():
+        P = words(torch, (2, 8192, 8192 // 32), gen)
+        out = torch.empty((8192, 8192), dtype=torch.uint8, device="cuda")
+        return (lambda: ap.expand_planes(P, out=out)), 2 * 8192 * 8192 // 8 + 8192 * 8192, 0.0
+
+    def window_rows():
+        B_ = 128
+        img = (torch.rand((B_, 224, 224, 3), device="cuda", generator=gen) * 20 - 10).contiguous()
+        kp = 192
+        out = torch.empty((B_ * 56 * 56, kp), dtype=torch.uint8, device="cuda")
+        fn = lambda: cabi.check(L.apnn_quantize_window_rows_i8(_stream_ptr(), img.data_ptr(), out.data_ptr(), B_, 224, 224, 3, 7, 4,
+                                                               8 | cabi.QUANT_CENTRED, kp), "gather")
+        return fn, img.numel() * 4 + out.numel(), 0.0
+
+    def maxpool():
+        B_, H_, C_ = 64, 112, 128
+        x = torch.randint(0, 4, (B_, H_, H_, C_), dtype=torch.uint8, device="cuda", generator=gen)
+        out = torch.empty((B_, H_ // 2, H_ // 2, C_), dtype=torch.uint8, device="cuda")
+        fn = lambda: cabi.check(L.apnn_maxpool2x2_i8(_stream_ptr(), x.data_ptr(), out.data_ptr(), B_, H_, H_, C_, 0, 0), "maxpool")
+        return fn, x.numel() + out.numel(), 0.0
+
+    def requantize():
+        rows, N_ = 16384, 4096
+        acc = torch.randint(-3000, 3000, (rows, N_), dtype=torch.int32, device="cuda", generator=gen)
+        T = torch.sort(torch.randint(-2000, 2000, (N_, 3), dtype=torch.int32, device="cuda", generator=gen), dim=1).values.contiguous()
+        out = torch.empty((rows, N_), dtype=torch.uint8, device="cuda")
+        epi = ap.make_epilogue("thresholds", 2, thresholds=T, out_i8=True)
+        fn = lambda: cabi.check(L.apnn_requantize_i32(_stream_ptr(), acc.data_ptr(), out.data_ptr(), rows, N_, ctypes.byref(epi)), "requantize")
+        return fn, 4 * rows * N_ + rows * N_, 0.0
+
+    def conv(B_, H_, CIN, COUT, R=3):
+        def setup():
+            pad = (R - 1) // 2
+            x8 = torch.zeros((B_, H_ + 2 * pad, H_ + 2 * pad, CIN), dtype=torch.uint8, device="cuda")
+            x8[:, pad:pad + H_, pad:pad + H_] = torch.randint(0, 4, (B_, H_, H_, CIN), dtype=torch.uint8, device="cuda", generator=gen)
+            w8 = (torch.randint(0, 2, (COUT, R * R * CIN), dtype=torch.int8, device="cuda", generator=gen) * 2 - 1).contiguous()
+            T = torch.sort(torch.randint(-300, 300, (COUT, 3), dtype=torch.int32, device="cuda", generator=gen), dim=1).values.contiguous()
+            out = torch.zeros((B_, H_ + 2, H_ + 2, COUT), dtype=torch.uint8, device="cuda")
+            flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+            epi = ap.make_epilogue("thresholds", 2, thresholds=T, out_i8=True, out_halo=1)
+            fn = lambda: cabi.check(L.apnn_conv2d_i8(_stream_ptr(), w8.data_ptr(), x8.data_ptr(), out.data_ptr(), B_, H_, H_, CIN, COUT,
+                                                     R, 1, 1, ctypes.byref(epi), flag.data_ptr()), "conv")
+            return fn, x8.numel() + w8.numel() + B_ * H_ * H_ * COUT, 2.0 * B_ * H_ * H_ * COUT * R * R * CIN
+        return setup
+
+    return {
+        "gemm_u8_m64": ("plane_core_kernel<u8> (GEMM, small tile class)", gemm(64, 1024, 1024, "imma")),
+        "gemm_u8_2048": ("plane_core_kernel<u8> (GEMM)", gemm(2048, 2048, 2048, "imma")),
+        "gemm_b1_m64": ("plane_core_kernel<b1> (GEMM, small tile class)", gemm(64, 1024, 1024, "bmma")),
+        "gemm_b1_2048": ("plane_core_kernel<b1> (GEMM)", gemm(2048, 2048, 2048, "bmma")),
+        "pair_gemm_4096": ("expand_planes_kernel + tc5_gemm_pair_kernel", gemm(4096, 4096, 4096, "tcgen05")),
+        "pack_planes": ("pack_planes_kernel<levels>", pack(False)),
+        "quantize_pack": ("pack_planes_kernel<float>", pack(True)),
+        "expand_planes": ("expand_planes_kernel", expand),
+        "window_rows": ("quantize_window_rows_i8_kernel (ResNet-18 first layer, 128 images, centred 8-bit)", window_rows),
+        "maxpool": ("maxpool2x2_i8_kernel", maxpool),
+        "requantize": ("requantize_i32_kernel", requantize),
+        "conv_c3_1024": ("tc5_gemm_kernel<256,128,split-K> (batch 8, 16x16, 1024 -> 1024)", conv(8, 16, 1024, 1024)),
+        "conv_l1": ("tc5_gemm_kernel<64,64> flat (128 images, 56x56, 64 -> 64)", conv(128, 56, 64, 64)),
+        "conv_l4": ("tc5_gemm_kernel<256,128> boxes (128 images, 7x7, 512 -> 512)", conv(128, 7, 512, 512)),
+        "pair_conv": ("tc5_conv_pair_kernel<3> (64 images, 28x28, 512 -> 512)", conv(64, 28, 512, 512)),
+    }
+
+
+def run_case(args) -> None:
+    """One kernel on one fixed small problem: `--steps` launches after three warm-up launches, device time per launch by
+    CUDA events.  The command the ncu captures under profiles/ run."""
+    import torch
+    import apnn_tc_b200 as ap
+    from apnn_tc_b200 import _cabi
+    torch.cuda.set_device(0)
+    cases = kernel_cases(torch, ap, _cabi)
+    if args.case not in cases:
+        raise SystemExit("--case is one of: " + ", ".join(sorted(cases)))
+    kernel, setup = cases[args.case]
+    fn, byts, ops = setup()
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    for _ in range(args.steps):
+        flush_l2(torch)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    us = total * 1e3 / args.steps
+    hbm = (measured_peaks().get("hbm_gbs") or 6545.0)
+    print(json.dumps({"case": args.case, "kernel": kernel, "us_per_call": round(us, 2), "steps": args.steps,
+                      "algorithmic_bytes": int(byts), "gb_s": round(byts / us / 1e3, 1), "hbm_frac_of_measured": round(byts / us / 1e3 / hbm, 3),
+                      "algorithmic_ops": ops, "tops": round(ops / us / 1e6, 1) if ops else None,
+                      "l2": "256 MiB rewritten before every launch"}), flush=True)
+
+
 # ----------------------------------------------------------------------------- network workloads
 NET_BATCH = {"resnet18": 1024, "vgg_variant": 1024, "alexnet": 128}
 
@@ -818,9 +940,12 @@ def main() -> None:
     ap_.add_argument("--workload", default="gemm", choices=["gemm", "resnet18", "vgg_variant", "alexnet"],
                      help="gemm (default: the headline line with every block) or one whole w1a2 network (images/s)")
     ap_.add_argument("--batch", type=int, default=0, help="global batch of a network workload")
+    ap_.add_argument("--case", default="", help="time one kernel on a fixed small problem (see kernel_cases) and exit")
     args = ap_.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.workload != "gemm":
         run_net(args)
