@@ -56,10 +56,12 @@ constexpr int SMEM_LIMIT = 232448;   // 227 KiB of dynamic shared memory per CTA
 
 // Tile shape: 128 rows x BN columns; BKB bytes of K per stage row (= the swizzle span: 128,
 // or 64 for operands whose K is a multiple of 64 only, e.g. 64-channel feature maps).
-template <int BN, int BKB>
+template <int BN, int BKB, bool PAIR = false>
 struct TileCfg {
   static constexpr int A_STAGE_BYTES = BM * BKB;
-  static constexpr int B_STAGE_BYTES = BN * BKB;
+  // rows of the B tile one CTA stages: all BN, or its half when two CTAs share the tile (cta_group::2)
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;
+  static constexpr int B_STAGE_BYTES = B_ROWS * BKB;
   static constexpr int TMEM_COLS = 2 * BN;
   // after the operand tiles: barriers, then per epilogue warp 32 threshold entries of 16 bytes
   // and a 32 x 16-word transposition block
@@ -165,6 +167,7 @@ struct Tc5Params {
   int splits;            // split-K instantiation only: the `splits` CTAs of a cluster share one output tile, each
                          // sums its share of the K blocks into its own TMEM; the partial sums meet in shared memory
                          // (distributed shared memory stores) before the epilogue
+  int pair;              // host-side note of the PAIR instantiation: tiles_m then counts pairs of tile rows
   int b_resident;        // 1: the whole B operand (one tile column, all K blocks) stays in shared
                          // memory for the life of the CTA and the ring carries A tiles only
   // flat convolution (is_conv == 2): stride 1, no pooling.  Output positions are the flattened
@@ -246,75 +249,6 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / rows;
 }
 
-// The MMAs of G consecutive K blocks: A tiles G x 128 rows at sa, B tiles G x BN rows at sb.
-template <int BN, int BKB, int G>
-__device__ __forceinline__ void issue_group(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc, bool accumulate) {
-  constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB;
-#pragma unroll
-  for (int g = 0; g < G; g++) {
-    const uint64_t adesc = make_smem_desc_k<BKB>(sa + g * A_BYTES);
-    const uint64_t bdesc = make_smem_desc_k<BKB>(sb + g * B_BYTES);
-#pragma unroll
-    for (int k = 0; k < BKB / 32; k++) {
-      // advancing 32 bytes along K inside the swizzle row = +2 in 16-byte units
-      tc_mma_i8(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (accumulate || (g | k) != 0) ? 1u : 0u);
-    }
-  }
-}
-
-// Flat convolution, resident filter: the MMAs of all RR x RR taps of one channel block as
-// straight-line code.  Descriptors differ only in their 14-bit address field, so they are
-// advanced as 32-bit adds on the low word.  a_lo / b_lo: low descriptor words of the buffer and
-// of tap 0's filter tile; row_step: 16-byte units between filter rows in the buffer;
-// b_step: 16-byte units between consecutive taps' filter tiles.
-template <int BKB, int RR>
-__device__ __forceinline__ void flat_issue_taps(uint32_t d_tmem, uint32_t a_lo, uint32_t row_step, uint32_t b_lo,
-                                                uint32_t b_step, uint32_t desc_hi, uint32_t idesc, uint32_t& enable) {
-#pragma unroll
-  for (int ti = 0; ti < RR; ti++) {
-#pragma unroll
-    for (int tj = 0; tj < RR; tj++) {
-      const uint32_t a_tap = a_lo + ti * row_step + tj * (BKB / 16);
-      const uint32_t b_tap = b_lo + (ti * RR + tj) * b_step;
-#pragma unroll
-      for (int k = 0; k < BKB / 32; k++) {
-        const uint64_t adesc = ((uint64_t)desc_hi << 32) | (a_tap + 2u * k);
-        const uint64_t bdesc = ((uint64_t)desc_hi << 32) | (b_tap + 2u * k);
-        tc_mma_i8(d_tmem, adesc, bdesc, idesc, enable);
-        enable = 1u;
-      }
-    }
-  }
-}
-
-// The same with the filter tiles arriving through their ring: wait, issue, release per tap.
-// Returns false when a wait ran out of time.
-template <int BKB, int RR>
-__device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a_lo, uint32_t row_step, uint32_t lo0,
-                                                     uint32_t bring, uint32_t b_bytes, uint32_t bfull0, uint32_t bempty0,
-                                                     int nb, int& sb, uint32_t& phb, uint32_t desc_hi, uint32_t idesc,
-                                                     uint32_t& enable) {
-#pragma unroll
-  for (int ti = 0; ti < RR; ti++) {
-#pragma unroll
-    for (int tj = 0; tj < RR; tj++) {
-      const uint32_t a_tap = a_lo + ti * row_step + tj * (BKB / 16);
-      if (!mbar_wait(bfull0 + 8u * sb, phb)) return false;
-      tc_fence_after();
-      const uint32_t b_tap = lo0 | (((bring + (uint32_t)sb * b_bytes) & 0x3FFFFu) >> 4);
-#pragma unroll
-      for (int k = 0; k < BKB / 32; k++) {
-        tc_mma_i8(d_tmem, ((uint64_t)desc_hi << 32) | (a_tap + 2u * k), ((uint64_t)desc_hi << 32) | (b_tap + 2u * k), idesc,
-                  enable);
-        enable = 1u;
-      }
-      tc_commit(bempty0 + 8u * sb);
-      if (++sb == nb) { sb = 0; phb ^= 1u; }
-    }
-  }
-  return true;
-}
-
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -331,6 +265,61 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
   return r;
 }
+// ---- CTA pairs (cta_group::2).  PAIR = true: the even CTA of a pair (the leader) issues every MMA over 256 rows
+// (its own 128-row A tile and the peer's) and both halves of the B tile; TMA loads of both CTAs complete on the
+// leader's barrier; the leader's commits arrive on the barrier at the same offset in both CTAs.
+template <bool PAIR>
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (PAIR) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    tc_mma_i8(d_tmem, adesc, bdesc, idesc, accumulate);
+  }
+}
+// pair_mask: the two CTAs of this pair as bits of the cluster rank (3 << leader rank)
+template <bool PAIR>
+__device__ __forceinline__ void commit_to(uint32_t bar, uint16_t pair_mask) {
+  if constexpr (PAIR) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(pair_mask)
+                 : "memory");
+  } else {
+    tc_commit(bar);
+  }
+}
+// TMA tile loads whose bytes complete on `bar`: this CTA's own barrier, or (PAIR) the leader's barrier given as a
+// shared::cluster address.  No multicast.
+template <bool PAIR>
+__device__ __forceinline__ void load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  if constexpr (PAIR) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], "
+        "[%4];" ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+  } else {
+    tma_load_2d(dst, map, x, y, bar);
+  }
+}
+template <bool PAIR>
+__device__ __forceinline__ void load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  if constexpr (PAIR) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, "
+        "%5}], [%6];" ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+  } else {
+    tma_load_4d(dst, map, c0, c1, c2, c3, bar);
+  }
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -338,6 +327,75 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
+}
+
+// The MMAs of G consecutive K blocks: A tiles G x 128 rows at sa, B tiles G x BN rows at sb.
+template <int BN, int BKB, int G, bool PAIR>
+__device__ __forceinline__ void issue_group(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t idesc, bool accumulate) {
+  constexpr int A_BYTES = BM * BKB, B_BYTES = TileCfg<BN, BKB, PAIR>::B_STAGE_BYTES;
+#pragma unroll
+  for (int g = 0; g < G; g++) {
+    const uint64_t adesc = make_smem_desc_k<BKB>(sa + g * A_BYTES);
+    const uint64_t bdesc = make_smem_desc_k<BKB>(sb + g * B_BYTES);
+#pragma unroll
+    for (int k = 0; k < BKB / 32; k++) {
+      // advancing 32 bytes along K inside the swizzle row = +2 in 16-byte units
+      mma_i8<PAIR>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (accumulate || (g | k) != 0) ? 1u : 0u);
+    }
+  }
+}
+
+// Flat convolution, resident filter: the MMAs of all RR x RR taps of one channel block as
+// straight-line code.  Descriptors differ only in their 14-bit address field, so they are
+// advanced as 32-bit adds on the low word.  a_lo / b_lo: low descriptor words of the buffer and
+// of tap 0's filter tile; row_step: 16-byte units between filter rows in the buffer;
+// b_step: 16-byte units between consecutive taps' filter tiles.
+template <int BKB, int RR, bool PAIR>
+__device__ __forceinline__ void flat_issue_taps(uint32_t d_tmem, uint32_t a_lo, uint32_t row_step, uint32_t b_lo,
+                                                uint32_t b_step, uint32_t desc_hi, uint32_t idesc, uint32_t& enable) {
+#pragma unroll
+  for (int ti = 0; ti < RR; ti++) {
+#pragma unroll
+    for (int tj = 0; tj < RR; tj++) {
+      const uint32_t a_tap = a_lo + ti * row_step + tj * (BKB / 16);
+      const uint32_t b_tap = b_lo + (ti * RR + tj) * b_step;
+#pragma unroll
+      for (int k = 0; k < BKB / 32; k++) {
+        const uint64_t adesc = ((uint64_t)desc_hi << 32) | (a_tap + 2u * k);
+        const uint64_t bdesc = ((uint64_t)desc_hi << 32) | (b_tap + 2u * k);
+        mma_i8<PAIR>(d_tmem, adesc, bdesc, idesc, enable);
+        enable = 1u;
+      }
+    }
+  }
+}
+
+// The same with the filter tiles arriving through their ring: wait, issue, release per tap.
+// Returns false when a wait ran out of time.
+template <int BKB, int RR, bool PAIR>
+__device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a_lo, uint32_t row_step, uint32_t lo0,
+                                                     uint32_t bring, uint32_t b_bytes, uint32_t bfull0, uint32_t bempty0,
+                                                     int nb, int& sb, uint32_t& phb, uint32_t desc_hi, uint32_t idesc,
+                                                     uint32_t& enable, uint16_t pair_mask) {
+#pragma unroll
+  for (int ti = 0; ti < RR; ti++) {
+#pragma unroll
+    for (int tj = 0; tj < RR; tj++) {
+      const uint32_t a_tap = a_lo + ti * row_step + tj * (BKB / 16);
+      if (!mbar_wait(bfull0 + 8u * sb, phb)) return false;
+      tc_fence_after();
+      const uint32_t b_tap = lo0 | (((bring + (uint32_t)sb * b_bytes) & 0x3FFFFu) >> 4);
+#pragma unroll
+      for (int k = 0; k < BKB / 32; k++) {
+        mma_i8<PAIR>(d_tmem, ((uint64_t)desc_hi << 32) | (a_tap + 2u * k), ((uint64_t)desc_hi << 32) | (b_tap + 2u * k), idesc,
+                     enable);
+        enable = 1u;
+      }
+      commit_to<PAIR>(bempty0 + 8u * sb, pair_mask);
+      if (++sb == nb) { sb = 0; phb ^= 1u; }
+    }
+  }
+  return true;
 }
 
 // EPI selects an epilogue compiled for one family of uses (the code of the other paths is
@@ -356,11 +414,18 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
 // its 128 x BN partial tile into p.splits column slices and stores slice o into slot r of CTA o's
 // shared memory (st.shared::cluster); after a cluster barrier CTA o sums the slots of its slice
 // and runs the ordinary epilogue on those columns.  No atomics, no global scratch, no second launch.
-template <int BN, int BKB, bool SPLITK = false, int EPI = 0>
+//
+// PAIR: two CTAs of a cluster share every B tile (tcgen05 cta_group::2).  Output tiles are taken in pairs of
+// adjacent tile rows: CTA `rank & 1` of a pair owns tile row 2*t + (rank & 1), stages its own 128-row A tile
+// and its half of the B tile, and drains its own TMEM; the even CTA issues the MMAs for both (M = 256).  Per
+// MMA every SM writes and reads a third fewer operand bytes than alone, which is what bounds the wide
+// layers.  With SPLITK the cluster holds `splits` such pairs, and a CTA exchanges partial sums with the
+// CTAs of the other pairs that own the same tile row.
+template <int BN, int BKB, bool SPLITK = false, int EPI = 0, bool PAIR = false>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Tc5Params p) {
-  using Cfg = TileCfg<BN, BKB>;
+  using Cfg = TileCfg<BN, BKB, PAIR>;
   constexpr int A_STAGE_BYTES = Cfg::A_STAGE_BYTES;
   constexpr int B_STAGE_BYTES = Cfg::B_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -401,7 +466,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), EPI_WARPS);
+      mbar_init(tempty_bar(a), PAIR ? 2 * EPI_WARPS : EPI_WARPS);   // the leader's collects both CTAs' epilogue warps
     }
     mbar_init(bres_bar, 1);
     if (flat)
@@ -412,12 +477,19 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
-                 "r"(Cfg::TMEM_COLS));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                   "r"(Cfg::TMEM_COLS));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                   "r"(Cfg::TMEM_COLS));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // the peer's barriers exist before anything remote touches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
   // Everything above may overlap the previous kernel's tail (programmatic dependent launch); the roles
@@ -428,10 +500,15 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   // cluster takes K blocks [r*kblocks/splits, (r+1)*kblocks/splits).  These are evaluated inside each
   // role (TILE_FIRST / TILE_STEP read %ctaid / %nctaid where they are used): hoisting them into
   // variables shared by the roles made the epilogue-bound layer kernels up to 15 % slower.
-#define TILE_FIRST (SPLITK ? (int)blockIdx.x / p.splits : (int)blockIdx.x)
-#define TILE_STEP (SPLITK ? (int)gridDim.x / p.splits : (int)gridDim.x)
-#define KB_FIRST (SPLITK ? (int)(((long long)cluster_ctarank() * p.kblocks) / p.splits) : 0)
-#define KB_LAST (SPLITK ? (int)(((long long)(cluster_ctarank() + 1) * p.kblocks) / p.splits) : p.kblocks)
+  // PAIR: p.tiles_m counts pairs of tile rows, a "tile" below is such a pair x one tile column, and this CTA's own
+  // tile row is 2 * tm + PRANK.
+#define CLUSTER_CTAS ((PAIR ? 2 : 1) * (SPLITK ? p.splits : 1))
+#define TILE_FIRST ((SPLITK || PAIR) ? (int)blockIdx.x / CLUSTER_CTAS : (int)blockIdx.x)
+#define TILE_STEP ((SPLITK || PAIR) ? (int)gridDim.x / CLUSTER_CTAS : (int)gridDim.x)
+#define PRANK (PAIR ? (cluster_ctarank() & 1u) : 0u)                     /* 0: the pair's leader */
+#define SPLIT_RANK (PAIR ? (cluster_ctarank() >> 1) : cluster_ctarank()) /* which share of K */
+#define KB_FIRST (SPLITK ? (int)(((long long)SPLIT_RANK * p.kblocks) / p.splits) : 0)
+#define KB_LAST (SPLITK ? (int)(((long long)(SPLIT_RANK + 1) * p.kblocks) / p.splits) : p.kblocks)
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -440,11 +517,18 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      // PAIR: every load of either CTA completes its bytes on the leader's barrier (same offset, CTA rank & ~1);
+      // the leader announces both CTAs' bytes
+      const uint32_t prank = PRANK;
+      const bool announces = !PAIR || prank == 0;
+      const uint32_t tx_mult = PAIR ? 2u : 1u;
+      const uint32_t bar_delta = PAIR ? map_to_cta(bars, cluster_ctarank() & ~1u) - bars : 0u;   // own -> leader's window
+      const int b_row0 = (int)prank * Cfg::B_ROWS;   // this CTA's rows inside a B tile
       if (p.b_resident && TILE_FIRST < num_tiles) {
         // tiles_n == 1: every tile of this CTA uses the same B rows; fetch all K blocks once
-        mbar_expect_tx(bres_bar, bres_bytes);
+        if (announces) mbar_expect_tx(bres_bar, tx_mult * bres_bytes);
         for (int kb = 0; kb < p.kblocks; kb++)
-          tma_load_2d(base + (uint32_t)kb * B_STAGE_BYTES, &map_b, kb * BKB, 0, bres_bar);
+          load_2d<PAIR>(base + (uint32_t)kb * B_STAGE_BYTES, &map_b, kb * BKB, b_row0, bres_bar + bar_delta);
       }
       const uint32_t stage_tx = (uint32_t)kgroup * ((p.is_conv ? p.a_box_bytes : (uint32_t)A_STAGE_BYTES) +
                                                     (p.b_resident ? 0u : (uint32_t)B_STAGE_BYTES));
@@ -458,20 +542,21 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int tile = TILE_FIRST; tile < num_tiles && ok; tile += TILE_STEP) {
           int tm, tn;
           tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+          if constexpr (PAIR) tm = 2 * tm + (int)prank;
           const int q0 = tm * BM + p.in_off * p.flat_wp + p.in_off;
           for (int cb = 0; cb < p.cblocks && ok; cb++) {
             if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
             const uint32_t sa = ring + (uint32_t)s * stage_bytes;
-            mbar_expect_tx(full_bar(s), flat_a_bytes);
+            if (announces) mbar_expect_tx(full_bar(s), tx_mult * flat_a_bytes);
             for (int blk = 0; blk < p.flat_nblk; blk++)
-              tma_load_2d(sa + blk * blk_bytes, &map_a, cb * BKB, q0 + blk * p.flat_wp, full_bar(s));
+              load_2d<PAIR>(sa + blk * blk_bytes, &map_a, cb * BKB, q0 + blk * p.flat_wp, full_bar(s) + bar_delta);
             if (++s == stages) { s = 0; ph ^= 1u; }
             if (!p.b_resident) {
               for (int tap = 0; tap < taps; tap++) {
                 if (!mbar_wait(bempty_bar(sb), phb ^ 1u)) { ok = false; break; }
-                mbar_expect_tx(bfull_bar(sb), B_STAGE_BYTES);
-                tma_load_2d(bring + (uint32_t)sb * B_STAGE_BYTES, &map_b, (tap * p.cblocks + cb) * BKB, tn * BN,
-                            bfull_bar(sb));
+                if (announces) mbar_expect_tx(bfull_bar(sb), tx_mult * B_STAGE_BYTES);
+                load_2d<PAIR>(bring + (uint32_t)sb * B_STAGE_BYTES, &map_b, (tap * p.cblocks + cb) * BKB, tn * BN + b_row0,
+                              bfull_bar(sb) + bar_delta);
                 if (++sb == p.flat_nb) { sb = 0; phb ^= 1u; }
               }
             }
@@ -482,6 +567,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         int tm, tn;
         const int kb0 = KB_FIRST, kb1 = KB_LAST;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        if constexpr (PAIR) tm = 2 * tm + (int)prank;
         int w0 = 0, h0 = 0, b0 = 0;
         if (p.is_conv) {
           w0 = (tm % p.tiles_w) * p.bw;
@@ -501,18 +587,19 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
           const uint32_t sa = ring + (uint32_t)s * stage_bytes;
           const uint32_t sb = sa + (uint32_t)kgroup * A_STAGE_BYTES;
-          mbar_expect_tx(full_bar(s), stage_tx);
+          if (announces) mbar_expect_tx(full_bar(s), tx_mult * stage_tx);
           for (int g = 0; g < kgroup; g++) {
             if (!p.is_conv) {
-              tma_load_2d(sa + g * A_STAGE_BYTES, &map_a, (kb + g) * BKB, tm * BM, full_bar(s));
+              load_2d<PAIR>(sa + g * A_STAGE_BYTES, &map_a, (kb + g) * BKB, tm * BM, full_bar(s) + bar_delta);
             } else {
-              tma_load_4d(sa + g * A_STAGE_BYTES, &map_a, cb * BKB, wbase + tj, hbase + ti, b0, full_bar(s));
+              load_4d<PAIR>(sa + g * A_STAGE_BYTES, &map_a, cb * BKB, wbase + tj, hbase + ti, b0, full_bar(s) + bar_delta);
               if (++cb == p.cblocks) {
                 cb = 0;
                 if (++tj == p.R) { tj = 0; ti++; }
               }
             }
-            if (!p.b_resident) tma_load_2d(sb + g * B_STAGE_BYTES, &map_b, (kb + g) * BKB, tn * BN, full_bar(s));
+            if (!p.b_resident)
+              load_2d<PAIR>(sb + g * B_STAGE_BYTES, &map_b, (kb + g) * BKB, tn * BN + b_row0, full_bar(s) + bar_delta);
           }
           if (++s == stages) { s = 0; ph ^= 1u; }
         }
@@ -525,8 +612,9 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       cluster_sync_all();
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // ---------------- MMA issuer (PAIR: the pair's leader only) ----------------
+    if (lane == 0 && PRANK == 0) {
+      const uint16_t pair_mask = PAIR ? (uint16_t)(3u << (cluster_ctarank() & ~1u)) : (uint16_t)0;   // both CTAs of this pair
       int s = 0;
       uint32_t ph = 0;
       uint32_t tl = 0;
@@ -557,16 +645,18 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               if (p.b_resident) {
                 const uint32_t b_lo = lo0 | (((base + (uint32_t)cb * B_STAGE_BYTES) & 0x3FFFFu) >> 4);
                 const uint32_t b_step = (uint32_t)p.cblocks * (B_STAGE_BYTES / 16);
-                if (p.R == 3) flat_issue_taps<BKB, 3>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
-                else flat_issue_taps<BKB, 1>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
+                if (p.R == 3) flat_issue_taps<BKB, 3, PAIR>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
+                else flat_issue_taps<BKB, 1, PAIR>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
               } else {
-                ok = p.R == 3 ? flat_issue_taps_ring<BKB, 3>(d_tmem, a_lo, row_step, lo0, bring, B_STAGE_BYTES, bfull_bar(0),
-                                                             bempty_bar(0), p.flat_nb, sb, phb, desc_hi, p.idesc, enable)
-                              : flat_issue_taps_ring<BKB, 1>(d_tmem, a_lo, row_step, lo0, bring, B_STAGE_BYTES, bfull_bar(0),
-                                                             bempty_bar(0), p.flat_nb, sb, phb, desc_hi, p.idesc, enable);
+                ok = p.R == 3 ? flat_issue_taps_ring<BKB, 3, PAIR>(d_tmem, a_lo, row_step, lo0, bring, B_STAGE_BYTES, bfull_bar(0),
+                                                                   bempty_bar(0), p.flat_nb, sb, phb, desc_hi, p.idesc, enable,
+                                                                   pair_mask)
+                              : flat_issue_taps_ring<BKB, 1, PAIR>(d_tmem, a_lo, row_step, lo0, bring, B_STAGE_BYTES, bfull_bar(0),
+                                                                   bempty_bar(0), p.flat_nb, sb, phb, desc_hi, p.idesc, enable,
+                                                                   pair_mask);
                 if (!ok) break;
               }
-              tc_commit(empty_bar(s));
+              commit_to<PAIR>(empty_bar(s), pair_mask);
               if (++s == stages) { s = 0; ph ^= 1u; }
               continue;
             }
@@ -587,17 +677,17 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
 #pragma unroll
                 for (int k = 0; k < BKB / 32; k++)
-                  tc_mma_i8(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (cb | tap | k) != 0 ? 1u : 0u);
+                  mma_i8<PAIR>(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (cb | tap | k) != 0 ? 1u : 0u);
                 if (!p.b_resident) {
-                  tc_commit(bempty_bar(sb));
+                  commit_to<PAIR>(bempty_bar(sb), pair_mask);
                   if (++sb == p.flat_nb) { sb = 0; phb ^= 1u; }
                 }
               }
             }
-            tc_commit(empty_bar(s));  // the buffer is free once every tap has read it
+            commit_to<PAIR>(empty_bar(s), pair_mask);  // the buffer is free once every tap has read it
             if (++s == stages) { s = 0; ph ^= 1u; }
           }
-          if (ok) tc_commit(tfull_bar(acc));
+          if (ok) commit_to<PAIR>(tfull_bar(acc), pair_mask);
         }
       } else
       for (int tile = TILE_FIRST; tile < num_tiles && ok; tile += TILE_STEP, tl++) {
@@ -615,14 +705,14 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t b0addr = p.b_resident ? base + (uint32_t)kb * B_STAGE_BYTES : sb;
           // unrolled per group size: this thread's instruction stream is on the critical path
           switch (kgroup) {
-            case 1: issue_group<BN, BKB, 1>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
-            case 2: issue_group<BN, BKB, 2>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
-            default: issue_group<BN, BKB, 3>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
+            case 1: issue_group<BN, BKB, 1, PAIR>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
+            case 2: issue_group<BN, BKB, 2, PAIR>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
+            default: issue_group<BN, BKB, 3, PAIR>(d_tmem, sa, b0addr, p.idesc, kb != kb0); break;
           }
-          tc_commit(empty_bar(s));  // frees the stage when these MMAs have read it
+          commit_to<PAIR>(empty_bar(s), pair_mask);  // frees the stage (in both CTAs of a pair) when these MMAs have read it
           if (++s == stages) { s = 0; ph ^= 1u; }
         }
-        if (ok) tc_commit(tfull_bar(acc));  // accumulator complete
+        if (ok) commit_to<PAIR>(tfull_bar(acc), pair_mask);  // accumulator complete (both CTAs of a pair)
       }
       if (!ok) atomicExch(p.error_flag, 2);
     }
@@ -660,7 +750,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int thr_tn = -1;
     // 32-column chunks of the tile this CTA finishes: all of them, or (split-K) its slice of the cluster's tile
     const int slice_chunks = SPLITK ? (BN / 32) / p.splits : BN / 32;
-    const int crank = SPLITK ? (int)cluster_ctarank() : 0;
+    const int crank = SPLITK ? (int)SPLIT_RANK : 0;   // this CTA's share of K = its slot in the exchange
     const int c_first = crank * slice_chunks;
     const int c_end = c_first + slice_chunks;
     const int c_begin = c_first + half;   // this warp's first chunk; it takes every second one
@@ -675,6 +765,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     auto rows_of_tile = [&](int tile, TileRows& t) {
       int tm;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, t.tn);
+      if constexpr (PAIR) tm = 2 * tm + (int)PRANK;
       t.dst = row_destination(p, tm, quarter * 32 + lane, in_box);
       if constexpr (!(C_NORES && C_NOINT32)) {
 #pragma unroll
@@ -774,8 +865,9 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tmem_ld_wait();
             const int owner = c / slice_chunks;
             const int g0 = (c - owner * slice_chunks) * 8;
-            const uint32_t dst = map_to_cta(xch, (uint32_t)owner) +
-                                 (uint32_t)(((crank * groups + g0) * BM + row_in_tile) * 16);
+            // the CTA of split `owner` that holds the same tile row: same position inside its pair
+            const uint32_t owner_cta = PAIR ? (((uint32_t)owner << 1) | PRANK) : (uint32_t)owner;
+            const uint32_t dst = map_to_cta(xch, owner_cta) + (uint32_t)(((crank * groups + g0) * BM + row_in_tile) * 16);
 #pragma unroll
             for (int g = 0; g < 8; g++)
               st_cluster_v4(dst + (uint32_t)(g * BM * 16), v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
@@ -985,7 +1077,10 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), cluster_ctarank() & ~1u));   // the leader's barrier
+        else mbar_arrive(tempty_bar(acc));
+      }
       if (has_next) {
         if (!nxt_ready) rows_of_tile(tile + TILE_STEP, nxt);
         if constexpr (!C_NORES) {
@@ -1004,14 +1099,21 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   // instead lets its CTAs take SMs in the order they fall idle; measured on the ResNet-18 forward
   // that scattering made every layer kernel 1 - 6 us slower, the late trigger saves 0.4 us per launch.)
   grid_launch_dependents();
+  if constexpr (PAIR) cluster_sync_all();   // the peer may not leave while the leader's MMAs or arrivals can still reach it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS));
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS));
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS));
   }
 }
 
+#undef CLUSTER_CTAS
 #undef TILE_FIRST
 #undef TILE_STEP
+#undef PRANK
+#undef SPLIT_RANK
 #undef KB_FIRST
 #undef KB_LAST
 
@@ -1058,15 +1160,15 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Shared-memory plan: keep the whole B operand resident when the problem has one tile column
 // and its K blocks leave room for at least three A stages; otherwise a ring of A+B stages.
-template <int BN, int BKB>
+template <int BN, int BKB, bool PAIR>
 void plan_smem(Tc5Params& p, int* smem_bytes) {
-  using Cfg = TileCfg<BN, BKB>;
+  using Cfg = TileCfg<BN, BKB, PAIR>;
   const int room = SMEM_LIMIT - Cfg::FIXED_BYTES;
   const long long bres = (long long)p.kblocks * Cfg::B_STAGE_BYTES;
   p.b_resident = 0;
   int stage = Cfg::A_STAGE_BYTES + Cfg::B_STAGE_BYTES;
   long long fixed = 0;
-  if (p.splits <= 1 && p.is_conv && p.tiles_n == 1 && p.tiles_m >= 4 * device_sm_count() &&
+  if (p.splits <= 1 && p.is_conv && p.tiles_n == 1 && p.tiles_m * (PAIR ? 2 : 1) >= 4 * device_sm_count() &&
       bres + 3LL * Cfg::A_STAGE_BYTES <= room) {
     p.b_resident = 1;
     stage = Cfg::A_STAGE_BYTES;
@@ -1087,16 +1189,16 @@ void plan_smem(Tc5Params& p, int* smem_bytes) {
 }
 
 // Flat convolution: A-buffer ring plus (unless the filter is resident) a ring of B tiles.
-template <int BN, int BKB>
+template <int BN, int BKB, bool PAIR>
 void plan_flat(Tc5Params& p, int* smem_bytes) {
-  using Cfg = TileCfg<BN, BKB>;
+  using Cfg = TileCfg<BN, BKB, PAIR>;
   const long long room = SMEM_LIMIT - Cfg::FIXED_BYTES;
   const long long a_bytes = (long long)p.flat_nblk * p.flat_blk_rows * BKB;
   const long long bres = (long long)p.kblocks * Cfg::B_STAGE_BYTES;
   p.kgroup = 1;
   p.b_resident = 0;
   long long fixed = 0;
-  if (p.tiles_n == 1 && p.tiles_m >= 4 * device_sm_count() && bres + 2 * a_bytes <= room) {
+  if (p.tiles_n == 1 && p.tiles_m * (PAIR ? 2 : 1) >= 4 * device_sm_count() && bres + 2 * a_bytes <= room) {
     p.b_resident = 1;
     p.flat_nb = 0;
     fixed = bres;
@@ -1141,18 +1243,19 @@ cudaError_t launch_kernel(Kernel kernel, cudaStream_t s, int grid, int smem, int
   return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p);
 }
 
-template <int BN, int BKB>
-cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid) {
+template <int BN, int BKB, bool PAIR>
+cudaError_t launch_tc5_p(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid) {
   int smem = 0;
-  if (p.is_conv == 2) plan_flat<BN, BKB>(p, &smem);
-  else plan_smem<BN, BKB>(p, &smem);
+  if (p.is_conv == 2) plan_flat<BN, BKB, PAIR>(p, &smem);
+  else plan_smem<BN, BKB, PAIR>(p, &smem);
+  const int pair_ctas = PAIR ? 2 : 1;
   if (p.splits > 1) {
     // split-K over clusters: one instantiation (run-time epilogue) per tile width with 128-byte rows
     if constexpr (BKB == 128 && BN >= 128) {
-      if ((long long)p.stages * p.kgroup * (TileCfg<BN, BKB>::A_STAGE_BYTES + TileCfg<BN, BKB>::B_STAGE_BYTES) <
-          (long long)BM * BN * 4)
+      using Cfg = TileCfg<BN, BKB, PAIR>;
+      if ((long long)p.stages * p.kgroup * (Cfg::A_STAGE_BYTES + Cfg::B_STAGE_BYTES) < (long long)BM * BN * 4)
         return cudaErrorInvalidConfiguration;   // the exchange area is the operand ring
-      return launch_kernel(tc5_gemm_kernel<BN, BKB, true, 0>, s, grid, smem, p.splits, map_a, map_b, p);
+      return launch_kernel(tc5_gemm_kernel<BN, BKB, true, 0, PAIR>, s, grid, smem, pair_ctas * p.splits, map_a, map_b, p);
     } else {
       return cudaErrorInvalidConfiguration;
     }
@@ -1163,12 +1266,22 @@ cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorM
   const bool all16 = (!p.residual_in || p.res16_in) && (!p.residual_out || p.res16_out);
   const bool int32_only = p.out_mode == APNN_OUT_INT32 && p.pool == APNN_POOL_NONE && !residuals;
   const int epi = int32_only ? 5 : !quantising ? 0 : (thr_i8 ? (residuals ? (all16 ? 4 : 3) : 2) : (residuals ? 0 : 1));
-  if (epi == 1) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 1>, s, grid, smem, 1, map_a, map_b, p);
-  if (epi == 2) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 2>, s, grid, smem, 1, map_a, map_b, p);
-  if (epi == 3) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 3>, s, grid, smem, 1, map_a, map_b, p);
-  if (epi == 4) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 4>, s, grid, smem, 1, map_a, map_b, p);
-  if (epi == 5) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 5>, s, grid, smem, 1, map_a, map_b, p);
-  return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 0>, s, grid, smem, 1, map_a, map_b, p);
+  if (epi == 1) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 1, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
+  if (epi == 2) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 2, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
+  if (epi == 3) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 3, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
+  if (epi == 4) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 4, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
+  if (epi == 5) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 5, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
+  return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 0, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
+}
+
+template <int BN, int BKB>
+cudaError_t launch_tc5(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid) {
+  if (p.pair) {
+    // CTA pairs exist for the widest tile with 128-byte rows only
+    if constexpr (BN == 256 && BKB == 128) return launch_tc5_p<BN, BKB, true>(s, map_a, map_b, p, grid);
+    else return cudaErrorInvalidConfiguration;
+  }
+  return launch_tc5_p<BN, BKB, false>(s, map_a, map_b, p, grid);
 }
 
 cudaError_t launch_tc5_any(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, Tc5Params& p, int grid,
@@ -1196,27 +1309,29 @@ int pick_bn(long long tiles_m, int N, int sms) {
   return w128 < w256 ? 128 : 256;
 }
 
-// How many clusters of `cs` CTAs of the split-K kernel the device holds at once (0 on error); cached.
-int cluster_capacity(int bn, int cs) {
+// How many clusters of `ctas` CTAs of the split-K kernel (single-CTA or CTA-pair form) the device holds at once
+// (0 on error); cached.
+int cluster_capacity(int bn, bool pair, int ctas) {
   static std::mutex mu;
-  static int cache[16][2][4] = {};   // [device][bn == 256][log2 cs], value + 1
+  static int cache[16][3][4] = {};   // [device][128 / 256 / 256 pair][log2 ctas], value + 1
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16) return 0;
-  const int li = cs == 2 ? 1 : cs == 4 ? 2 : 3, bi = bn == 256 ? 1 : 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 16 || ctas < 2 || ctas > 8) return 0;
+  const int li = ctas == 2 ? 1 : ctas == 4 ? 2 : 3, bi = pair ? 2 : (bn == 256 ? 1 : 0);
   std::lock_guard<std::mutex> lock(mu);
   if (cache[dev][bi][li]) return cache[dev][bi][li] - 1;
-  const void* kernel = bn == 256 ? reinterpret_cast<const void*>(tc5_gemm_kernel<256, 128, true, 0>)
-                                 : reinterpret_cast<const void*>(tc5_gemm_kernel<128, 128, true, 0>);
+  const void* kernel = pair ? reinterpret_cast<const void*>(tc5_gemm_kernel<256, 128, true, 0, true>)
+                            : bn == 256 ? reinterpret_cast<const void*>(tc5_gemm_kernel<256, 128, true, 0, false>)
+                                        : reinterpret_cast<const void*>(tc5_gemm_kernel<128, 128, true, 0, false>);
   int n = 0;
   if (ensure_max_smem(kernel, SMEM_LIMIT) == cudaSuccess) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3((unsigned)(cs * device_sm_count()), 1, 1);
+    cfg.gridDim = dim3((unsigned)(ctas * device_sm_count()), 1, 1);
     cfg.blockDim = dim3(THREADS, 1, 1);
     cfg.dynamicSmemBytes = SMEM_LIMIT;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)cs;
+    attr[0].val.clusterDim.x = (unsigned)ctas;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
@@ -1230,38 +1345,50 @@ int cluster_capacity(int bn, int cs) {
   return n;
 }
 
-// Split-K over clusters pays when a problem fits one wave of tiles with SMs to spare (or with tiles
-// narrower than they need be) and has a long K.  Cost of a plan in shared-memory traffic units (what
-// bounds the MMA loop): K blocks per CTA x (128 + bn) bytes per K byte, plus about four K blocks'
-// worth for the partial-sum exchange.  Only plans whose clusters are all resident at once are
-// considered, and a split must beat the unsplit plan by a tenth.  Returns the cluster size
-// (1 = no split) and may widen *bn.
-int pick_split(long long tiles_m, int N, int kblocks, int sms, int* bn) {
-  static const bool disabled = [] { const char* v = getenv("APNN_SPLITK"); return v && v[0] == '0'; }();
-  if (disabled || N <= 64 || kblocks < 8) return 1;
-  const long long plain_tiles = tiles_m * ((N + *bn - 1) / *bn);
-  if (plain_tiles > sms) return 1;   // more than one wave of tiles: nothing idle to split over
-  const long long plain = (long long)kblocks * (128 + *bn);
-  long long best = plain * 9 / 10;
-  int best_bn = *bn, best_cs = 1;
-  for (int cand = 128; cand <= 256; cand *= 2) {
-    if (cand == 256 && N <= 128) break;
-    const long long tiles = tiles_m * ((N + cand - 1) / cand);
-    for (int cs = 2; cs <= 8; cs *= 2) {
-      if (cs > cand / 32 || kblocks / cs < 4 || tiles * cs > sms) break;
-      if (tiles > cluster_capacity(cand, cs)) break;
-      const long long cost = (long long)((kblocks + cs - 1) / cs + 4) * (128 + cand);
-      if (cost < best) { best = cost; best_bn = cand; best_cs = cs; }
+// Tile plan of one launch: tile width, whether CTA pairs share the B tile, and how many ways K is split over a
+// cluster.  Cost of a plan in shared-memory traffic units (what bounds the MMA loop): waves x K blocks per CTA x
+// operand rows a CTA stages per K block (128 of A plus its rows of B), plus about four K blocks' worth for the
+// partial-sum exchange of a split.  The unsplit single-CTA plan with the width pick_bn chose is kept unless
+// another plan is at least a tenth cheaper; splits are only taken when every cluster is resident at once.
+struct TilePlan {
+  int bn, pair, splits;
+  long long cost;   // waves x K blocks per CTA x operand rows per K block
+};
+TilePlan pick_plan(long long tiles_m, int N, int kblocks, int sms, int bn_plain, bool rows128, bool may_split = true) {
+  static const bool no_split = [] { const char* v = getenv("APNN_SPLITK"); return v && v[0] == '0'; }();
+  static const bool no_pair = [] { const char* v = getenv("APNN_PAIR_MODE"); return v && v[0] == '0'; }();
+  auto waves = [](long long units, long long slots) { return (units + slots - 1) / slots; };
+  const long long plain_tiles = tiles_m * ((N + bn_plain - 1) / bn_plain);
+  const long long plain = waves(plain_tiles, sms) * kblocks * (128 + bn_plain);
+  TilePlan best = {bn_plain, 0, 1, plain};
+  if (!rows128 || N <= 64) return best;
+  long long best_cost = plain * 9 / 10;
+  for (int pair = 0; pair <= 1; pair++) {
+    if (pair && (no_pair || N <= 128 || tiles_m < 2)) break;
+    for (int cand = pair ? 256 : 128; cand <= 256; cand *= 2) {
+      if (cand == 256 && N <= 128) break;
+      const long long units = (pair ? (tiles_m + 1) / 2 : tiles_m) * ((N + cand - 1) / cand);
+      const long long slots = pair ? sms / 2 : sms;
+      const int rows = 128 + (pair ? cand / 2 : cand);
+      for (int cs = 1; cs <= 8; cs *= 2) {
+        if (cs == 1 && !pair) continue;                       // the plain plans are pick_bn's business
+        if (cs > 1 && (no_split || !may_split || kblocks < 8 || cs > cand / 32 || kblocks / cs < 4 || (pair ? 2 : 1) * cs > 8)) break;
+        if (cs > 1 && (units * cs > slots || units > cluster_capacity(cand, pair != 0, (pair ? 2 : 1) * cs))) break;
+        const long long cost = waves(units * cs, slots) * ((kblocks + cs - 1) / cs + (cs > 1 ? 4 : 0)) * rows;
+        if (cost < best_cost) {
+          best_cost = cost;
+          best = {cand, pair, cs, cost};
+        }
+      }
     }
   }
-  *bn = best_bn;
-  return best_cs;
+  return best;
 }
 
-uint32_t make_idesc(bool a_signed, bool b_signed, int bn) {
-  // D = s32, A/B = u8 or s8, both K-major, N = bn, M = 128
+uint32_t make_idesc(bool a_signed, bool b_signed, int bn, bool pair = false) {
+  // D = s32, A/B = u8 or s8, both K-major, N = bn, M = 128 (256 over a CTA pair)
   return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(bn >> 3) << 17) |
-         ((uint32_t)(BM >> 4) << 24);
+         ((uint32_t)((pair ? 2 * BM : BM) >> 4) << 24);
 }
 
 }  // namespace
@@ -1328,17 +1455,20 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   const int sms = device_sm_count();
   Tc5Params p;
   memset(&p, 0, sizeof(p));
-  p.tiles_m = (M + BM - 1) / BM;
-  int bn = pick_bn(p.tiles_m, N, sms);
-  // few tiles and a long K (the fully connected layers of a network at a small batch): split K over
-  // the CTAs of a cluster, whatever the epilogue
-  const int splits = pick_split(p.tiles_m, N, K / BK, sms, &bn);
+  const int tiles_m = (M + BM - 1) / BM;
+  int bn = pick_bn(tiles_m, N, sms);
+  // few tiles and a long K (the fully connected layers of a network at a small batch): K split over the CTAs of
+  // a cluster, whatever the epilogue; wide tiles: CTA pairs sharing the B tile
+  const TilePlan plan = pick_plan(tiles_m, N, K / BK, sms, bn, true);
+  bn = plan.bn;
   // otherwise a skinny problem that leaves more than half of the SMs idle even with 128-wide tiles is
   // bound by streaming the B operand once: 64-wide tiles put twice as many SMs on that stream
-  const long long t128 = (long long)p.tiles_m * ((N + 127) / 128);
-  if (splits == 1 && bn == 128 && t128 * 2 <= sms) bn = 64;
+  const long long t128 = (long long)tiles_m * ((N + 127) / 128);
+  if (plan.splits == 1 && !plan.pair && bn == 128 && t128 * 2 <= sms) bn = 64;
+  p.pair = plan.pair;
+  p.tiles_m = plan.pair ? (tiles_m + 1) / 2 : tiles_m;
   CUtensorMap map_a, map_b;
-  if (!make_operand_map(&map_a, A8, M, K, BM) || !make_operand_map(&map_b, B8, N, K, bn)) {
+  if (!make_operand_map(&map_a, A8, M, K, BM) || !make_operand_map(&map_b, B8, N, K, plan.pair ? bn / 2 : bn)) {
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   }
   p.out = D;
@@ -1358,15 +1488,17 @@ apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, vo
   p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
   p.affine_scale = epi ? epi->affine_scale : nullptr;
   p.affine_bias = epi ? epi->affine_bias : nullptr;
-  p.idesc = make_idesc(a_signed, b_signed, bn);
-  long long tiles = (long long)p.tiles_m * p.tiles_n;
-  if (splits > 1) {
-    p.splits = splits;
-    e = launch_tc5_any(s, map_a, map_b, p, (int)tiles * splits, bn, 128);
+  p.idesc = make_idesc(a_signed, b_signed, bn, plan.pair != 0);
+  const long long tiles = (long long)p.tiles_m * p.tiles_n;   // tiles, or pairs of tiles
+  const int per_tile = plan.pair ? 2 : 1;
+  if (plan.splits > 1) {
+    p.splits = plan.splits;
+    e = launch_tc5_any(s, map_a, map_b, p, (int)tiles * plan.splits * per_tile, bn, 128);
     if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm split-K launch");
     return APNN_OK;
   }
-  int grid = (int)(tiles < sms ? tiles : sms);
+  const long long slots = plan.pair ? sms / 2 : sms;
+  int grid = (int)(tiles < slots ? tiles : slots) * per_tile;
   e = launch_tc5_any(s, map_a, map_b, p, grid, bn, 128);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm launch");
   return APNN_OK;
@@ -1471,16 +1603,17 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   // SM count).  Cost of a formulation = waves x tile width.
   // The pixel-box formulation can also split K over the CTAs of a cluster when it has few tiles.
   const int kblocks_all = R * R * p.cblocks;
-  auto cost = [&](long long tiles_m, bool may_split) {
-    int bn_ = pick_bn(tiles_m, COUT, sms);
-    const int cs = (may_split && span == 128) ? pick_split(tiles_m, COUT, kblocks_all, sms, &bn_) : 1;
-    const long long tiles = tiles_m * ((COUT + bn_ - 1) / bn_) * cs;
-    return ((tiles + sms - 1) / sms) * bn_ / cs;
+  // (the flat kernel path does not split K)
+  auto plan_for = [&](long long tiles_m, bool may_split) {
+    return pick_plan(tiles_m, COUT, kblocks_all, sms, pick_bn(tiles_m, COUT, sms), span == 128 && !x_signed, may_split);
   };
+  const int tiles_m_box = p.tiles_m;
+  const TilePlan pl_box = plan_for(tiles_m_box, true), pl_flat = plan_for((flat_rows + BM - 1) / BM, false);
   // (with many waves a few per cent more tiles still win: a flat tile loads 5-8x fewer rows)
-  const long long cost_box = cost(p.tiles_m, true), cost_flat = cost((flat_rows + BM - 1) / BM, false);
+  const long long cost_box = pl_box.cost, cost_flat = pl_flat.cost;
+  const long long many = 8LL * kblocks_all * 256;   // about eight waves of 128-wide tiles
   bool flat = stride == 1 && pool == APNN_POOL_NONE && flat_rows < 0x7fffff00LL &&
-              (cost_flat <= cost_box || (cost_box >= 8 * 64 && cost_flat * 100 <= cost_box * 105));
+              (cost_flat <= cost_box || (cost_box >= many && cost_flat * 100 <= cost_box * 105));
   if (flat) {
     // rows of input one (tile, channel block) needs: one box when it has at most 256 rows (the TMA
     // limit), else one box per filter row
@@ -1490,8 +1623,8 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
     // the flat plan needs one such buffer plus two filter tiles next to the fixed part; wide
     // filters on wide images (R >= 9, or R = 7 with 256-column tiles) do not fit and take the pixel boxes
     const long long flat_tiles_m = (flat_rows + BM - 1) / BM;
-    const int bn_flat = pick_bn(flat_tiles_m, COUT, sms);
-    const long long need = (long long)TileCfg<64, 64>::FIXED_BYTES + 2LL * bn_flat * span + (long long)nblk * blk_rows * span;
+    const int b_rows_flat = pl_flat.pair ? pl_flat.bn / 2 : pl_flat.bn;
+    const long long need = (long long)TileCfg<64, 64>::FIXED_BYTES + 2LL * b_rows_flat * span + (long long)nblk * blk_rows * span;
     if (need > SMEM_LIMIT) {
       flat = false;
     } else {
@@ -1503,13 +1636,15 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
       p.flat_blk_rows = blk_rows;
     }
   }
-  int bn = pick_bn(p.tiles_m, COUT, sms);
-  const int splits = (!flat && span == 128) ? pick_split(p.tiles_m, COUT, kblocks_all, sms, &bn) : 1;
+  const TilePlan plan = flat ? pl_flat : pl_box;
+  const int bn = plan.bn, splits = plan.splits;
+  p.pair = plan.pair;
+  if (plan.pair) p.tiles_m = (p.tiles_m + 1) / 2;   // pairs of tile rows
   CUtensorMap map_a, map_b;
   const bool maps_ok =
       (flat ? make_operand_map(&map_a, X8, flat_rows, CIN, p.flat_blk_rows, span)
             : make_activation_map(&map_a, X8, B, Hp, Wp, CIN, bw, bh, bb, stride, span)) &&
-      make_operand_map(&map_b, W8, COUT, (long long)R * R * CIN, bn, span);
+      make_operand_map(&map_b, W8, COUT, (long long)R * R * CIN, plan.pair ? bn / 2 : bn, span);
   if (!maps_ok) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   p.out = Out;
   p.thresholds = epi ? epi->thresholds : nullptr;
@@ -1529,12 +1664,14 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
   p.res16_out = epi ? ((epi->residual_i16 >> 1) & 1) : 0;
   p.affine_scale = epi ? epi->affine_scale : nullptr;
   p.affine_bias = epi ? epi->affine_bias : nullptr;
-  p.idesc = make_idesc(x_signed, w_signed, bn);  // A = activations (unsigned levels, or the centred signed bytes), B = filter
-  long long tiles = (long long)p.tiles_m * p.tiles_n;
-  int grid = (int)(tiles < sms ? tiles : sms);
+  p.idesc = make_idesc(x_signed, w_signed, bn, plan.pair != 0);  // A = activations (unsigned levels, or the centred signed bytes), B = filter
+  const long long tiles = (long long)p.tiles_m * p.tiles_n;   // tiles, or pairs of tiles
+  const int per_tile = plan.pair ? 2 : 1;
+  const long long slots = plan.pair ? sms / 2 : sms;
+  int grid = (int)(tiles < slots ? tiles : slots) * per_tile;
   if (splits > 1) {
     p.splits = splits;
-    grid = (int)tiles * splits;
+    grid = (int)tiles * splits * per_tile;
   }
   e = launch_tc5_any(s, map_a, map_b, p, grid, bn, span);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_conv launch");
