@@ -1372,6 +1372,10 @@ TilePlan pick_plan(long long tiles_m, int N, int kblocks, int sms, int bn_plain,
       const int rows = 128 + (pair ? cand / 2 : cand);
       for (int cs = 1; cs <= 8; cs *= 2) {
         if (cs == 1 && !pair) continue;                       // the plain plans are pick_bn's business
+        // measured on the ResNet-18 layers: unsplit pairs pay from 18 K blocks on (short K: the cluster set-up and
+        // the remote barrier arrivals cost more than the halved filter traffic saves) and with more than one
+        // wave of tiles (a single tile per CTA is latency-bound either way)
+        if (cs == 1 && pair && (kblocks < 18 || units <= slots)) continue;
         if (cs > 1 && (no_split || !may_split || kblocks < 8 || cs > cand / 32 || kblocks / cs < 4 || (pair ? 2 : 1) * cs > 8)) break;
         if (cs > 1 && (units * cs > slots || units > cluster_capacity(cand, pair != 0, (pair ? 2 : 1) * cs))) break;
         const long long cost = waves(units * cs, slots) * ((kblocks + cs - 1) / cs + (cs > 1 ? 4 : 0)) * rows;
