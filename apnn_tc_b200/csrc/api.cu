@@ -182,6 +182,22 @@ apnn_status apnn_gemm_i8(void* stream, const void* W8, const void* X8, void* D, 
                      w_signed != 0, x_signed != 0, epi, status_flag);
 }
 
+apnn_status apnn_gemm_w8(void* stream, const void* W8, int xbits, const void* X, void* D, int M, int N, int K,
+                         int w_signed, int x_signed, const apnn_epilogue* epi, int* status_flag) {
+  if (!W8 || !X || !D || !status_flag || M <= 0 || N <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
+  if (xbits < 1 || xbits > 4 || (x_signed && xbits != 1)) return APNN_ERR_UNSUPPORTED;
+  if (K % 128 != 0 || !aligned16(W8) || !aligned16(X) || !aligned16(D)) return APNN_ERR_ALIGNMENT;
+  if (epi) {
+    if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;
+    apnn_status st = check_epilogue(epi, N, false, 1, 1, true);
+    if (st != APNN_OK) return st;
+    // epilogues of the single-CTA kernel only
+    if (epi->out_i8 || epi->residual_i16 || epi->out_mode == APNN_OUT_FLOAT) return APNN_ERR_UNSUPPORTED;
+  }
+  return tc5_gemm_i8_pair(reinterpret_cast<cudaStream_t>(stream), (const uint8_t*)W8, nullptr, D, M, N, K, w_signed != 0,
+                          x_signed != 0, epi, status_flag, (const uint32_t*)X, xbits);
+}
+
 apnn_status apnn_gemm_ex(void* stream, int algo, int wbits, int xbits, const void* W, const void* X, void* D, int M,
                          int N, int K, const apnn_epilogue* epi, void* workspace, size_t workspace_bytes) {
   if (!W || !X || !D) return APNN_ERR_INVALID_ARG;

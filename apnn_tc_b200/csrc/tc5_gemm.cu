@@ -410,10 +410,11 @@ __device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a
 //
 // SPLITK: the kernel is launched as clusters of p.splits CTAs (2, 4 or 8) with one output tile per
 // cluster, for problems with fewer tiles than SMs and a long K.  CTA r of a cluster accumulates K
-// blocks [r*kper, (r+1)*kper) in its own TMEM.  Then, with the operand ring idle, every CTA splits
-// its 128 x BN partial tile into p.splits column slices and stores slice o into slot r of CTA o's
-// shared memory (st.shared::cluster); after a cluster barrier CTA o sums the slots of its slice
-// and runs the ordinary epilogue on those columns.  No atomics, no global scratch, no second launch.
+// blocks [r*kblocks/splits, (r+1)*kblocks/splits) in its own TMEM.  Then, with the operand ring idle, every
+// CTA splits its 128 x BN partial tile into p.splits column slices, keeps its own slice in TMEM and stores
+// slice o into slot r of CTA o's shared memory (st.shared::cluster); after a cluster barrier CTA o adds the
+// slots of its slice to its own partial sums and runs the ordinary epilogue on those columns.  No atomics,
+// no global scratch, no second launch.
 //
 // PAIR: two CTAs of a cluster share every B tile (tcgen05 cta_group::2).  Output tiles are taken in pairs of
 // adjacent tile rows: CTA `rank & 1` of a pair owns tile row 2*t + (rank & 1), stages its own 128-row A tile
@@ -860,10 +861,11 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (acc_ok) {
 #pragma unroll 1
           for (int c = half; c < BN / 32; c += 2) {
+            const int owner = c / slice_chunks;
+            if (owner == crank) continue;   // this CTA's own slice stays in its TMEM until the sums are formed below
             uint32_t v[32];
             tmem_ld32(taddr + c * 32, v);
             tmem_ld_wait();
-            const int owner = c / slice_chunks;
             const int g0 = (c - owner * slice_chunks) * 8;
             // the CTA of split `owner` that holds the same tile row: same position inside its pair
             const uint32_t owner_cta = PAIR ? (((uint32_t)owner << 1) | PRANK) : (uint32_t)owner;
@@ -883,11 +885,14 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (col0 >= p.N) continue;  // uniform over the warp
         uint32_t v[32];
         if constexpr (SPLITK) {
+          // own partial sums from TMEM, the other CTAs' from their slots of the exchange area
           const int groups = slice_chunks * 8;
           const int g0 = (c - c_first) * 8;
-#pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = 0u;
+          __syncwarp();   // lanes that left the previous chunk early rejoin before the warp-wide TMEM load
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
           for (int sl = 0; sl < p.splits; sl++) {
+            if (sl == crank) continue;
             const uint32_t src = xch + (uint32_t)(((sl * groups + g0) * BM + row_in_tile) * 16);
 #pragma unroll
             for (int g = 0; g < 8; g++) {
@@ -896,6 +901,9 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
           }
         } else {
+          // (lanes whose row is outside the output skip the stores of a chunk but meet the others again at the
+          // loop increment, so this warp-wide load runs converged; an explicit __syncwarp() here was measured
+          // to cost 2 % on the epilogue-bound 64-channel layers)
           tmem_ld32(taddr + c * 32, v);
         }
         if (thr_staged) {
@@ -1357,6 +1365,7 @@ struct TilePlan {
 TilePlan pick_plan(long long tiles_m, int N, int kblocks, int sms, int bn_plain, bool rows128, bool may_split = true) {
   static const bool no_split = [] { const char* v = getenv("APNN_SPLITK"); return v && v[0] == '0'; }();
   static const bool no_pair = [] { const char* v = getenv("APNN_PAIR_MODE"); return v && v[0] == '0'; }();
+  static const bool pair_split = [] { const char* v = getenv("APNN_PAIR_SPLIT"); return v && v[0] == '1'; }();
   auto waves = [](long long units, long long slots) { return (units + slots - 1) / slots; };
   const long long plain_tiles = tiles_m * ((N + bn_plain - 1) / bn_plain);
   const long long plain = waves(plain_tiles, sms) * kblocks * (128 + bn_plain);
@@ -1376,6 +1385,10 @@ TilePlan pick_plan(long long tiles_m, int N, int kblocks, int sms, int bn_plain,
         // the remote barrier arrivals cost more than the halved filter traffic saves) and with more than one
         // wave of tiles (a single tile per CTA is latency-bound either way)
         if (cs == 1 && pair && (kblocks < 18 || units <= slots)) continue;
+        // split plans of CTA pairs run, and are tested with APNN_PAIR_SPLIT=1, but are not chosen: a split problem
+        // is one tile per CTA, bound by the MMA chain and the exchange rather than by operand traffic, and measured
+        // 1 - 20 % slower as pairs (batch 8, 16x16 convolutions of 640 - 1024 channels)
+        if (cs > 1 && pair && !pair_split) break;
         if (cs > 1 && (no_split || !may_split || kblocks < 8 || cs > cand / 32 || kblocks / cs < 4 || (pair ? 2 : 1) * cs > 8)) break;
         if (cs > 1 && (units * cs > slots || units > cluster_capacity(cand, pair != 0, (pair ? 2 : 1) * cs))) break;
         const long long cost = waves(units * cs, slots) * ((kblocks + cs - 1) / cs + (cs > 1 ? 4 : 0)) * rows;
@@ -1450,10 +1463,16 @@ apnn_status tc5_expand2(cudaStream_t s, const uint32_t* pa, uint8_t* oa, long lo
   return APNN_OK;
 }
 
+// Problems the 256 x 256 CTA-pair kernel takes: enough tiles for every SM pair (or peer destinations, which only
+// that kernel writes) and an epilogue it implements.
+static bool takes_pair_kernel(int M, int N, int K, const apnn_epilogue* epi) {
+  return (tc5_pair_worthwhile(M, N, K) && !(epi && (epi->out_i8 || epi->residual_i16 || epi->out_mode == APNN_OUT_FLOAT))) ||
+         (epi && epi->n_peer_out > 0);
+}
+
 apnn_status tc5_gemm_i8(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                         bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
-  if ((tc5_pair_worthwhile(M, N, K) && !(epi && (epi->out_i8 || epi->residual_i16 || epi->out_mode == APNN_OUT_FLOAT))) ||
-      (epi && epi->n_peer_out > 0))
+  if (takes_pair_kernel(M, N, K, epi))
     return tc5_gemm_i8_pair(s, A8, B8, D, M, N, K, a_signed, b_signed, epi, status_flag);
   cudaError_t e;
   const int sms = device_sm_count();
@@ -1514,6 +1533,15 @@ apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, co
   uint8_t* wb = wa + align_up((size_t)M * K, 256);
   int* err = reinterpret_cast<int*>(wb + align_up((size_t)N * K, 256));
   const int sign = epi ? epi->signed_operand : APNN_SIGN_NONE;
+  // The CTA-pair kernel spreads the activation planes itself: only W goes through the expand pass and the
+  // activation part of the workspace stays untouched (APNN_XPLANES=0 restores the two-operand expand).
+  static const bool planes_ok = [] { const char* v = getenv("APNN_XPLANES"); return !(v && v[0] == '0'); }();
+  if (planes_ok && xbits <= 4 && (pair || takes_pair_kernel(M, N, K, epi)) &&
+      !(epi && epi->out_mode == APNN_OUT_FLOAT)) {
+    apnn_status st1 = tc5_expand(s, W, wa, M, K, wbits, sign == APNN_SIGN_W);
+    if (st1 != APNN_OK) return st1;
+    return tc5_gemm_i8_pair(s, wa, nullptr, D, M, N, K, sign == APNN_SIGN_W, sign == APNN_SIGN_X, epi, err, X, xbits);
+  }
   apnn_status st = tc5_expand2(s, W, wa, M, wbits, sign == APNN_SIGN_W, X, wb, N, xbits, sign == APNN_SIGN_X, K);
   if (st != APNN_OK) return st;
   if (pair) return tc5_gemm_i8_pair(s, wa, wb, D, M, N, K, sign == APNN_SIGN_W, sign == APNN_SIGN_X, epi, err);

@@ -35,7 +35,8 @@ int tc5_conv_read_error_flag(cudaStream_t s, const void* workspace, int B, int H
 // least as many pair tiles as SM pairs.
 bool tc5_pair_worthwhile(int M, int N, int K);
 apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
-                             bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag);
+                             bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag,
+                             const uint32_t* xplanes = nullptr, int xbits = 0);
 // The flat convolution on CTA pairs (256 positions x 256 channels per pair): stride 1, no pooling,
 // CIN % 128 == 0, COUT % 256 == 0, thresholds -> int8 rows, no residuals.  H, W: input extent.
 bool tc5_conv_pair_applies(int B, int H, int W, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi);

@@ -17,6 +17,13 @@
 //                through mapa + a cluster-scope arrive)
 // The loads carry no cluster multicast.  A cluster barrier closes the kernel so neither CTA
 // exits while the other may still touch its shared memory or barriers.
+//
+// B from packed planes (template parameter XP = number of planes, 0 = int8 rows through TMA):
+// four more warps per CTA read the B operand's bit planes from global memory (16 bytes per
+// row, plane and K block, fetched several K blocks ahead into registers), spread them to one
+// byte per element and store them into the stage in the 128-byte-swizzled layout the TMA would
+// have produced.  full[s] then also counts one arrival per expanding warp of both CTAs (after a
+// generic -> async proxy fence), so the activation operand never exists as int8 rows in HBM.
 #include <cstring>
 
 #include "api_internal.h"
@@ -38,6 +45,8 @@ constexpr int THR_BYTES_PER_WARP = 32 * 36 * 4;  // thresholds (256 x 16 B) or a
 constexpr int WORD_BYTES_PER_WARP = 2 * 32 * 8 * 4;  // packed outputs of up to 2 bits: 8 words per row and plane, staged per tile
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * THR_BYTES_PER_WARP + 4 * WORD_BYTES_PER_WARP;
 constexpr int THREADS = 192;
+constexpr int EXPAND_WARPS = 4;                      // B-from-planes instantiations: warps 6..9, 32 rows of B each
+constexpr int THREADS_XP = THREADS + 32 * EXPAND_WARPS;
 constexpr int GROUP_M = 8;    // bands of 8 pair-tiles (2048 rows) for L2 reuse
 
 struct PairParams {
@@ -53,6 +62,11 @@ struct PairParams {
   int* error_flag;
   int n_out;       // destinations of every output tile: out itself, then peer-mapped copies
   void* outs[8];
+  // B from packed planes: plane j of row n starts at xplanes + j * xplane_words + n * kwords
+  const uint32_t* xplanes;
+  long long xplane_words;
+  int kwords;
+  int x_signed;    // one plane holding -1 / +1
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -82,6 +96,9 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       "[%4];" ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
       : "memory");
 }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
   // arrive on the barrier at this offset in both CTAs once the MMAs issued so far are done
   asm volatile(
@@ -109,7 +126,46 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
   tn = r / rows;
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+// mbar_wait with acquire semantics at cluster scope: the waiter goes on to have the tensor cores read
+// shared memory that threads of the peer CTA wrote before their (release.cluster) arrival
+__device__ __forceinline__ bool mbar_wait_cluster_acquire(uint32_t bar, uint32_t parity) {
+  unsigned long long t0 = 0;
+  for (uint32_t spin = 0;; spin++) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 255u) == 255u) {
+      unsigned long long now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+
+// One 32-k word of XP planes -> 32 bytes (eight 32-bit words of four elements each), in the byte order of
+// expand_planes_kernel: output word q, byte i holds the element whose bit sits at position 8*i + q.
+template <int XP>
+__device__ __forceinline__ void spread_word(const uint32_t (&w)[XP > 0 ? XP : 1], bool is_signed, uint32_t (&r)[8]) {
+#pragma unroll
+  for (int q = 0; q < 8; q++) {
+    uint32_t v = 0;
+#pragma unroll
+    for (int j = 0; j < XP; j++) {
+      const uint32_t sft = (q >= j) ? (w[j] >> (q - j)) : (w[j] << (j - q));
+      v |= sft & (0x01010101u << j);
+    }
+    r[q] = (XP == 1 && is_signed) ? (0xFFFFFFFFu ^ (v * 0xFEu)) : v;
+  }
+}
+
+template <int XP>
+__global__ void __launch_bounds__(XP ? THREADS_XP : THREADS, 1)
 tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -132,7 +188,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), XP ? 1 + 2 * EXPAND_WARPS : 1);   // the producer's expect_tx (+ the expanding warps of both CTAs)
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; a++) {
@@ -171,10 +227,10 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
           const uint32_t leader_full = map_to_cta(full_bar(s), 0);
-          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);  // both CTAs' bytes
+          if (rank == 0) mbar_expect_tx(full_bar(s), XP ? 2 * HALF * BK : 2 * STAGE_BYTES);  // both CTAs' bytes
           const uint32_t sa = base + s * STAGE_BYTES;
           tma_load_2d_pair(sa, &map_a, kb * BK, arow, leader_full);
-          tma_load_2d_pair(sa + HALF * BK, &map_b, kb * BK, brow, leader_full);
+          if (XP == 0) tma_load_2d_pair(sa + HALF * BK, &map_b, kb * BK, brow, leader_full);
         }
       }
       if (!ok) atomicExch(p.error_flag, 1);
@@ -194,7 +250,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         for (int kb = 0; kb < p.kblocks; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
+          if (!(XP ? mbar_wait_cluster_acquire(full_bar(s), ph) : mbar_wait(full_bar(s), ph))) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = base + s * STAGE_BYTES;
           const uint64_t adesc = make_smem_desc(sa);
@@ -208,6 +264,71 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
       if (!ok) atomicExch(p.error_flag, 2);
     }
+  } else if (warp >= 6) {
+    // ---------------- B expanders (warps 6..9 of both CTAs, XP > 0 only) ----------------
+    constexpr int XPN = XP > 0 ? XP : 1;
+    constexpr int DEPTH = XP <= 2 ? 6 : 4;   // K blocks held in registers ahead of the one being spread
+    const int r = (warp - 6) * 32 + lane;    // this thread's row of the CTA's half of the B tile
+    const uint32_t xr = (uint32_t)(r & 7);
+    const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
+    const int my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
+    const long long total = (long long)my_tiles * p.kblocks;
+    // fetch cursor: runs DEPTH K blocks ahead of the spreading cursor, through the same tile sequence
+    int ptile = pair, pkb = 0;
+    const uint32_t* prow = nullptr;
+    auto seek_row = [&]() {
+      prow = nullptr;
+      if (ptile < num_tiles) {
+        int tm, tn;
+        pair_tile_coords(ptile, p.tiles_m, p.tiles_n, tm, tn);
+        const long long n = (long long)tn * TILE_N + (int)rank * HALF + r;
+        if (n < p.N) prow = p.xplanes + n * p.kwords;
+      }
+    };
+    seek_row();
+    uint4 q[DEPTH][XPN];
+    auto fetch = [&](uint4 (&dst)[XPN]) {
+#pragma unroll
+      for (int j = 0; j < XPN; j++)
+        dst[j] = prow ? __ldg(reinterpret_cast<const uint4*>(prow + j * p.xplane_words + 4 * pkb)) : make_uint4(0u, 0u, 0u, 0u);
+      if (++pkb == p.kblocks) {
+        pkb = 0;
+        ptile += num_pairs;
+        seek_row();
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < DEPTH; d++) fetch(q[d]);
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (long long i0 = 0; i0 < total && ok; i0 += DEPTH) {
+#pragma unroll
+      for (int d = 0; d < DEPTH; d++) {
+        if (i0 + d < total && ok) {   // uniform over the warp
+          ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u));
+          if (ok) {
+            const uint32_t row_s = base + s * STAGE_BYTES + HALF * BK + (uint32_t)r * 128u;
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+              uint32_t w[XPN], o[8];
+#pragma unroll
+              for (int j = 0; j < XPN; j++) w[j] = g == 0 ? q[d][j].x : g == 1 ? q[d][j].y : g == 2 ? q[d][j].z : q[d][j].w;
+              spread_word<XP>(w, p.x_signed != 0, o);
+              // 16-byte chunk c of a 128-byte row lives at chunk position c ^ (row & 7) (128-byte swizzle)
+              st_shared_v4(row_s + (((uint32_t)(2 * g) ^ xr) << 4), o[0], o[1], o[2], o[3]);
+              st_shared_v4(row_s + (((uint32_t)(2 * g + 1) ^ xr) << 4), o[4], o[5], o[6], o[7]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_full0 + 8u * (uint32_t)s);
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+            fetch(q[d]);
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(p.error_flag, 4);
   } else {
     // ---------------- epilogue warps (2..5) of both CTAs ----------------
     const int quarter = warp & 3;
@@ -391,6 +512,26 @@ bool make_half_map(CUtensorMap* map, const void* base, long long rows, long long
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <int XP>
+cudaError_t launch_pair(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const PairParams& p, int pairs) {
+  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel<XP>), SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(XP ? THREADS_XP : THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1 + (unsigned)pdl_attribute(attr + 1);
+  return cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel<XP>, map_a, map_b, p);
+}
+
 }  // namespace
 
 bool tc5_pair_worthwhile(int M, int N, int K) {
@@ -398,14 +539,17 @@ bool tc5_pair_worthwhile(int M, int N, int K) {
   return tiles >= device_sm_count() / 2 && K >= 1024;
 }
 
+// xplanes == nullptr: B8 holds the int8 rows of B.  Otherwise B8 is ignored and the kernel spreads the xbits
+// (1..4) planes at xplanes, [xbits][N][K/32] words, into its stages itself.
 apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
-                             bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag) {
+                             bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag,
+                             const uint32_t* xplanes, int xbits) {
   if (epi && epi->out_mode == APNN_OUT_FLOAT) return APNN_ERR_UNSUPPORTED;   // the float affine lives in the single-CTA kernel
+  if (xplanes && (xbits < 1 || xbits > 4)) return APNN_ERR_UNSUPPORTED;
   CUtensorMap map_a, map_b;
-  if (!make_half_map(&map_a, A8, M, K) || !make_half_map(&map_b, B8, N, K))
-    return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
-  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel), SMEM_BYTES);
-  if (e != cudaSuccess) return cuda_fail(e, "tc5 pair smem attribute");
+  if (!make_half_map(&map_a, A8, M, K)) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  if (xplanes) map_b = map_a;   // not read
+  else if (!make_half_map(&map_b, B8, N, K)) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   PairParams p;
   memset(&p, 0, sizeof(p));
   p.out = D;
@@ -425,27 +569,24 @@ apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B
   p.outs[0] = D;
   if (epi)
     for (int i = 0; i < epi->n_peer_out && p.n_out < 8; i++) p.outs[p.n_out++] = epi->peer_out[i];
+  p.xplanes = xplanes;
+  p.xplane_words = (long long)N * (K / 32);
+  p.kwords = K / 32;
+  p.x_signed = b_signed ? 1 : 0;
   // D = s32, A/B = u8 or s8, K-major, N = 256, M = 256 over the pair
   p.idesc = (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(TILE_N >> 3) << 17) |
             ((uint32_t)(TILE_M >> 4) << 24);
   const int sms = device_sm_count();
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
-
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cfg.blockDim = dim3(THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1 + (unsigned)pdl_attribute(attr + 1);
-  e = cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel, map_a, map_b, p);
+  cudaError_t e;
+  switch (xplanes ? xbits : 0) {
+    case 0: e = launch_pair<0>(s, map_a, map_b, p, pairs); break;
+    case 1: e = launch_pair<1>(s, map_a, map_b, p, pairs); break;
+    case 2: e = launch_pair<2>(s, map_a, map_b, p, pairs); break;
+    case 3: e = launch_pair<3>(s, map_a, map_b, p, pairs); break;
+    default: e = launch_pair<4>(s, map_a, map_b, p, pairs); break;
+  }
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm_pair launch");
   return APNN_OK;
 }

@@ -119,6 +119,29 @@ def gemm_i8(W8: torch.Tensor, X8: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
+def gemm_w8(W8: torch.Tensor, X: torch.Tensor, out: Optional[torch.Tensor] = None, *, w_signed: bool = False,
+            x_signed: bool = False, epilogue: Optional[Epilogue] = None,
+            status_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """GEMM of a layer with static weights: ``W8`` from ``expand_planes`` (made once), the activations ``X``
+    as packed planes [xbits, N, K/32]; the CTA-pair kernel spreads the planes itself."""
+    X = _dev_words(X, "X")
+    M, K = W8.shape
+    xbits, N, kw = X.shape
+    if K != kw * 32:
+        raise ValueError("operands disagree on K")
+    packed = epilogue is not None and epilogue.out_mode in (1, 2)
+    if out is None:
+        shape = (epilogue.out_bits, M, N // 32) if packed else (M, N)
+        out = torch.empty(shape, dtype=torch.int32, device=W8.device)
+    if status_flag is None:
+        status_flag = torch.empty(1, dtype=torch.int32, device=W8.device)
+    st = _cabi.lib().apnn_gemm_w8(_stream_ptr(), W8.data_ptr(), xbits, X.data_ptr(), out.data_ptr(), M, N, K,
+                                  1 if w_signed else 0, 1 if x_signed else 0,
+                                  ctypes.byref(epilogue) if epilogue is not None else None, status_flag.data_ptr())
+    _cabi.check(st, "apnn_gemm_w8")
+    return out
+
+
 def apmm(W: torch.Tensor, X: torch.Tensor, out: Optional[torch.Tensor] = None, *, epilogue: Optional[Epilogue] = None,
          algo: str = "auto", workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """D[m][n] = sum_wb sum_xb 2^(wb+xb) popcount(W[wb][m] & X[xb][n]).

@@ -53,7 +53,7 @@ def workload_config(n_gpus: int) -> dict:
         "workload": "gemm_w1a2_M8192_N8192_K8192_int32out",
         "M": M, "N_per_gpu": N, "K": K, "wbits": WBITS, "xbits": XBITS,
         "sharding": "replicated W, N-sharded X (g x 8192 rows), no collective" if n_gpus > 1 else "single GPU",
-        "l2": "4 rotating activation sets; each step rewrites 64 MiB of int8 activations and 256 MiB of output (> 126 MB L2)",
+        "l2": "4 rotating activation sets; each step writes 256 MiB of output (> 126 MB L2) between two reads of an operand",
         "collective": "none",
     }
 
@@ -249,14 +249,15 @@ def words(torch, shape, gen):
 
 # ----------------------------------------------------------------------------- the headline GEMM
 class GemmPipeline:
-    """The 8192^3 step on device-resident operands: the static W is expanded to int8 once; every step
-    expands that step's activation planes and runs the GEMM, both on the current stream.  (Running the
-    expand of step i+1 on a second stream beside GEMM i was measured: the persistent GEMM's statically
-    scheduled tiles on the SMs that also host expand blocks become stragglers, 0.285 -> 0.300 ms per GEMM,
-    which cancels what the overlap hides.)"""
+    """The 8192^3 step on device-resident operands: the static W is expanded to int8 once; every step is
+    ONE launch that reads that step's activation planes as they are (apnn_gemm_w8: the kernel's own warps
+    spread the bits into its shared-memory stages).  expand_pass=True runs the older two-launch step
+    (activation planes -> int8 rows in HBM, then apnn_gemm_i8) for comparison."""
 
-    def __init__(self, torch, ap, cabi, dev, rank, wbits=WBITS, xbits=XBITS, algo="tcgen05", epilogue=None, D=None):
+    def __init__(self, torch, ap, cabi, dev, rank, wbits=WBITS, xbits=XBITS, algo="tcgen05", epilogue=None, D=None,
+                 expand_pass=False):
         self.torch, self.ap, self.cabi, self.algo = torch, ap, cabi, algo
+        self.expand_pass = expand_pass or xbits > 4
         self.wbits, self.xbits = wbits, xbits
         g = torch.Generator(device=dev).manual_seed(0xA9117C + 1 + rank)
         gw = torch.Generator(device=dev).manual_seed(0xA9117C + 1)  # weights are the same on every rank
@@ -268,22 +269,25 @@ class GemmPipeline:
         self.L = cabi.lib()
         if algo == "tcgen05":
             self.W8 = torch.empty((M, K), dtype=torch.uint8, device=dev)
-            self.X8 = torch.empty((N, K), dtype=torch.uint8, device=dev)
+            if self.expand_pass:
+                self.X8 = torch.empty((N, K), dtype=torch.uint8, device=dev)
             cabi.check(self.L.apnn_expand_planes(torch.cuda.current_stream().cuda_stream, self.W.data_ptr(),
                                                  self.W8.data_ptr(), M, K, wbits, 0), "expand W")
-        self.launches_per_step = 2 if algo == "tcgen05" else 1
+        self.launches_per_step = 2 if (algo == "tcgen05" and self.expand_pass) else 1
         torch.cuda.synchronize()
 
     def step(self, i: int, ev=None):
         torch = self.torch
         X = self.Xs[i % N_OPERAND_SETS]
-        if self.algo == "tcgen05":
+        if self.algo == "tcgen05" and self.expand_pass:
             self.cabi.check(self.L.apnn_expand_planes(torch.cuda.current_stream().cuda_stream, X.data_ptr(),
                                                       self.X8.data_ptr(), N, K, self.xbits, 0), "expand X")
         if ev is not None:
             ev[0].record()
-        if self.algo == "tcgen05":
+        if self.algo == "tcgen05" and self.expand_pass:
             self.ap.gemm_i8(self.W8, self.X8, self.D, status_flag=self.flag, epilogue=self.epilogue)
+        elif self.algo == "tcgen05":
+            self.ap.gemm_w8(self.W8, X, self.D, status_flag=self.flag, epilogue=self.epilogue)
         else:
             self.ap.apmm(self.W, X, self.D, algo=self.algo)
         if ev is not None:
@@ -354,7 +358,7 @@ def run_ours(args) -> None:
         return tuple(float(x) for x in t)
 
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-    pipe = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo)
+    pipe = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo, expand_pass=args.expand_pass)
     for i in range(2):  # keep the device busy while the sampler thread starts
         pipe.step(i)
     elapsed_ms, kernel_ms, clocks = timed_gemm_steps(torch, dist, pipe, args.steps, args.warmup, sampler)
@@ -511,10 +515,11 @@ def run_ours(args) -> None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8 operands, int32 accumulate (exact)", "data": "synthetic",
         "config": workload_config(world), "algo": algo,
-        "step": "activation expand (planes -> int8) + tcgen05 GEMM; the static weights' int8 image is made once "
-                "before the timed region",
+        "step": ("activation expand (planes -> int8) + tcgen05 GEMM" if pipe.expand_pass else
+                 "one launch: tcgen05 GEMM reading the packed activation planes (bits spread to int8 inside the kernel)")
+                + "; the static weights' int8 image is made once before the timed region",
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": (2 if algo == "tcgen05" else 1) * args.steps, "clocks": clocks,
+        "gpu_launches": pipe.launches_per_step * args.steps, "clocks": clocks,
         "sustained": sustained, "resnet18": resnet, "allgather": gather,
         "pairs_8192": pairs, "m64_sweep": sweep, "conv_c3": conv,
     }
@@ -936,6 +941,8 @@ def main() -> None:
     ap_.add_argument("--algo", default="tcgen05", choices=["tcgen05", "imma", "bmma"])
     ap_.add_argument("--profile", action="store_true",
                      help="timed GEMM steps only (no e2e, probe, CPU baseline or other blocks): the command ncu captures")
+    ap_.add_argument("--expand-pass", action="store_true",
+                     help="headline step as two launches (activation planes -> int8 rows in HBM, then the GEMM)")
     ap_.add_argument("--quick", action="store_true", help="skip the N = 1 sweep blocks (pairs_8192, m64_sweep, conv_c3)")
     ap_.add_argument("--workload", default="gemm", choices=["gemm", "resnet18", "vgg_variant", "alexnet"],
                      help="gemm (default: the headline line with every block) or one whole w1a2 network (images/s)")

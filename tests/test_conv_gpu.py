@@ -449,3 +449,45 @@ def test_tcgen05_wide_filters_stride1(cuda_device, R, B, H, Wd, COUT):
     T = oracle.fold_bn(np.ones(COUT, np.float32), np.zeros(COUT, np.float32), float(v.mean()), float(v.std()) / 4, 2)
     got = run_tc5_conv(Wt, X, ap.make_epilogue("thresholds", 2, signed="w", thresholds=to_dev(T)))
     assert np.array_equal(to_host(got), oracle.requant_pack(v, 2, 2, T))
+
+
+def test_tcgen05_pair_split_plans_forced():
+    """Split-K over clusters of CTA pairs (two pairs = four CTAs sharing a pair of tile rows) is not a plan the
+    library picks on its own (it measured slower than the single-CTA split); APNN_PAIR_SPLIT=1 forces it, read
+    once per process, so the check runs in a child process: the batch-8 16x16 convolution of 512 channels and a
+    skinny GEMM against the oracle."""
+    import subprocess
+    import sys
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    code = r'''
+import sys, os, ctypes
+import numpy as np, torch
+sys.path.insert(0, os.getcwd()); sys.path.insert(0, os.path.join(os.getcwd(), "tests"))
+import oracle, apnn_tc_b200 as ap
+from apnn_tc_b200 import _cabi
+from test_conv_gpu import make_conv, run_tc5_conv
+from gpu_util import to_dev, to_host, spread_bytes
+rng = np.random.default_rng(7)
+X, Wt = make_conv(rng, 8, 16, 16, 512, 512, 3, 1, 2)
+acc = oracle.conv_popc(Wt, X, threads=8)
+v = oracle.signed_correct(acc, oracle.conv_window_sums(X, 3), 0)
+T = oracle.fold_bn(np.ones(512, np.float32), np.zeros(512, np.float32), float(v.mean()), float(v.std()) / 4, 2)
+got = run_tc5_conv(Wt, X, ap.make_epilogue("thresholds", 2, signed="w", thresholds=to_dev(T)))
+assert np.array_equal(to_host(got), oracle.requant_pack(v, 2, 2, T)), "conv"
+M, N, K = 256, 512, 8192
+W, wl = oracle.value_planes(rng, M, K, 2); Xg, xl = oracle.value_planes(rng, N, K, 1)
+want = (wl.astype(np.int64) @ (2 * xl.astype(np.int64) - 1).T).astype(np.int32)
+a8 = ap.expand_planes(to_dev(W)); b8 = ap.expand_planes(to_dev(Xg), signed=True)
+D = torch.zeros((M, N), dtype=torch.int32, device="cuda"); flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+epi = ap.make_epilogue("int32")
+_cabi.check(_cabi.lib().apnn_gemm_i8(torch.cuda.current_stream().cuda_stream, a8.data_ptr(), b8.data_ptr(), D.data_ptr(), M, N, K, 0, 1, ctypes.byref(epi), flag.data_ptr()), "gemm")
+torch.cuda.synchronize()
+assert int(flag.item()) == 0 and np.array_equal(D.cpu().numpy(), want), "gemm"
+print("pair split ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=dict(os.environ, APNN_PAIR_SPLIT="1"), capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0 and "pair split ok" in r.stdout, r.stdout + r.stderr
