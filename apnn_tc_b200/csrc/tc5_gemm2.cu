@@ -19,11 +19,15 @@
 // exits while the other may still touch its shared memory or barriers.
 //
 // B from packed planes (template parameter XP = number of planes, 0 = int8 rows through TMA):
-// four more warps per CTA read the B operand's bit planes from global memory (16 bytes per
-// row, plane and K block, fetched several K blocks ahead into registers), spread them to one
-// byte per element and store them into the stage in the 128-byte-swizzled layout the TMA would
-// have produced.  full[s] then also counts one arrival per expanding warp of both CTAs (after a
-// generic -> async proxy fence), so the activation operand never exists as int8 rows in HBM.
+// the stage ring splits into a ring of NA_XP A tiles (TMA, as above) and a ring of NB_XP B tiles
+// that eight more warps per CTA fill.  They read the B operand's bit planes from global memory
+// in groups of four K blocks (64 contiguous bytes per row and plane: a warp-wide load touches
+// eight lines instead of thirty-two), one group ahead in registers, spread them to one byte per
+// element and store them in the 128-byte-swizzled layout the TMA would have produced; each
+// writer then runs a generic -> async proxy fence.  A warp that never loads meets them on a
+// named barrier per group and arrives on full_b[t] of the leader (a release at cluster scope
+// waits for every memory operation its warp has in flight, prefetched planes included -- hence
+// not the expanders themselves).  The activation operand never exists as int8 rows in HBM.
 #include <cstring>
 
 #include "api_internal.h"
@@ -45,8 +49,11 @@ constexpr int THR_BYTES_PER_WARP = 32 * 36 * 4;  // thresholds (256 x 16 B) or a
 constexpr int WORD_BYTES_PER_WARP = 2 * 32 * 8 * 4;  // packed outputs of up to 2 bits: 8 words per row and plane, staged per tile
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * THR_BYTES_PER_WARP + 4 * WORD_BYTES_PER_WARP;
 constexpr int THREADS = 192;
-constexpr int EXPAND_WARPS = 4;                      // B-from-planes instantiations: warps 6..9, 32 rows of B each
-constexpr int THREADS_XP = THREADS + 32 * EXPAND_WARPS;
+// B-from-planes instantiations
+constexpr int EXPAND_WARPS = 8;                      // warps 6..13, 16 rows of the CTA's B half each
+constexpr int THREADS_XP = THREADS + 32 * EXPAND_WARPS + 32;   // + the signalling warp (14)
+constexpr int XP_TILES = 12;                         // A tiles + B tiles of 16 KiB: the single ring's shared memory
+static_assert(XP_TILES * HALF * BK == STAGES * STAGE_BYTES, "the two rings use the single ring's shared memory");
 constexpr int GROUP_M = 8;    // bands of 8 pair-tiles (2048 rows) for L2 reuse
 
 struct PairParams {
@@ -95,6 +102,12 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], "
       "[%4];" ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
       : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -164,7 +177,8 @@ __device__ __forceinline__ void spread_word(const uint32_t (&w)[XP > 0 ? XP : 1]
   }
 }
 
-template <int XP>
+// XG: K blocks per expander group (2 or 4); the B ring holds two groups, the A ring the other tiles
+template <int XP, int XG = 4>
 __global__ void __launch_bounds__(XP ? THREADS_XP : THREADS, 1)
 tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const PairParams p) {
@@ -172,11 +186,26 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   const uint32_t bars = base + STAGES * STAGE_BYTES;
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+  // XP == 0: one ring of STAGES stages (A tile then B tile); XP > 0: NA ring slots of A tiles, then NB of B tiles
+  constexpr int XGROUP = XG;
+  constexpr int NB_XP = 2 * XGROUP;          // B tiles: two groups
+  constexpr int NA_XP = XP_TILES - NB_XP;    // A tiles in flight
+  constexpr int KQ_LANES = 32 / XGROUP;      // lanes (rows) per K block of a warp-wide load
+  constexpr int XTASKS = 16 / KQ_LANES;      // (row, K block) pieces a thread spreads per group
+  static_assert((NB_XP & (NB_XP - 1)) == 0 && XTASKS >= 1, "slot arithmetic below");
+  constexpr int NA = XP ? NA_XP : STAGES;
+  constexpr int NB = XP ? NB_XP : 0;
+  constexpr int A_SLOT_BYTES = XP ? HALF * BK : STAGE_BYTES;
+  constexpr int RING_BARS = 2 * NA + 2 * NB;
+  auto full_bar = [&](int s) { return bars + 8u * s; };                       // A (XP == 0: A and B) landed
+  auto empty_bar = [&](int s) { return bars + 8u * (NA + s); };
+  auto fullb_bar = [&](int t) { return bars + 8u * (2 * NA + t); };           // XP > 0: B tile t spread
+  auto emptyb_bar = [&](int t) { return bars + 8u * (2 * NA + NB + t); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (RING_BARS + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (RING_BARS + 2 + a); };
+  const uint32_t tmem_slot = bars + 8u * (RING_BARS + 4);
+  static_assert(8 * (RING_BARS + 4) + 4 <= 256, "barrier block");
+  const uint32_t b_ring = base + NA_XP * HALF * BK;   // XP > 0: first B tile
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
   uint8_t* thr_stage = smem_raw + (bars + 256u - raw);
 
@@ -187,9 +216,13 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const int num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) {
-      mbar_init(full_bar(s), XP ? 1 + 2 * EXPAND_WARPS : 1);   // the producer's expect_tx (+ the expanding warps of both CTAs)
-      mbar_init(empty_bar(s), 1);
+    for (int s = 0; s < NA; s++) {
+      mbar_init(full_bar(s), 1);    // the leader producer's expect_tx
+      mbar_init(empty_bar(s), 1);   // the MMA issuer's commit
+    }
+    for (int t = 0; t < NB; t++) {
+      mbar_init(fullb_bar(t), 2);   // the signalling warp of each CTA
+      mbar_init(emptyb_bar(t), 1);
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
@@ -223,12 +256,12 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int arow = tm * TILE_M + (int)rank * HALF;
         const int brow = tn * TILE_N + (int)rank * HALF;
         for (int kb = 0; kb < p.kblocks; kb++, it++) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+          const int s = it % NA;
+          const uint32_t ph = (it / NA) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
           const uint32_t leader_full = map_to_cta(full_bar(s), 0);
-          if (rank == 0) mbar_expect_tx(full_bar(s), XP ? 2 * HALF * BK : 2 * STAGE_BYTES);  // both CTAs' bytes
-          const uint32_t sa = base + s * STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * A_SLOT_BYTES);  // both CTAs' bytes
+          const uint32_t sa = base + s * A_SLOT_BYTES;
           tma_load_2d_pair(sa, &map_a, kb * BK, arow, leader_full);
           if (XP == 0) tma_load_2d_pair(sa + HALF * BK, &map_b, kb * BK, brow, leader_full);
         }
@@ -248,87 +281,129 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TILE_N;
         for (int kb = 0; kb < p.kblocks; kb++, it++) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!(XP ? mbar_wait_cluster_acquire(full_bar(s), ph) : mbar_wait(full_bar(s), ph))) { ok = false; break; }
+          const int s = it % NA;
+          const uint32_t ph = (it / NA) & 1u;
+          const int t = XP ? (int)(it % NB_XP) : 0;
+          if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
+          // the peer's expanders wrote their half of the B tile with ordinary stores: acquire at cluster scope
+          if (XP && !mbar_wait_cluster_acquire(fullb_bar(t), (it / NB_XP) & 1u)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = base + s * STAGE_BYTES;
+          const uint32_t sa = base + s * A_SLOT_BYTES;
           const uint64_t adesc = make_smem_desc(sa);
-          const uint64_t bdesc = make_smem_desc(sa + HALF * BK);
+          const uint64_t bdesc = make_smem_desc(XP ? b_ring + t * (HALF * BK) : sa + HALF * BK);
 #pragma unroll
           for (int k = 0; k < BK / 32; k++)
             tc_mma_i8_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
-          tc_commit_pair(empty_bar(s));  // frees the stage in both CTAs
+          tc_commit_pair(empty_bar(s));  // frees the stage (the A tile) in both CTAs
+          if (XP) tc_commit_pair(emptyb_bar(t));
         }
         if (ok) tc_commit_pair(tfull_bar(acc));  // accumulators complete in both CTAs
       }
       if (!ok) atomicExch(p.error_flag, 2);
     }
   } else if (warp >= 6) {
-    // ---------------- B expanders (warps 6..9 of both CTAs, XP > 0 only) ----------------
+    // ---------------- B expanders (warps 6..13) and their signalling warp (14), XP > 0 only ----------------
     constexpr int XPN = XP > 0 ? XP : 1;
-    constexpr int DEPTH = XP <= 2 ? 6 : 4;   // K blocks held in registers ahead of the one being spread
-    const int r = (warp - 6) * 32 + lane;    // this thread's row of the CTA's half of the B tile
-    const uint32_t xr = (uint32_t)(r & 7);
-    const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
+    constexpr int BAR_THREADS = 32 * EXPAND_WARPS + 32;
     const int my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0;
-    const long long total = (long long)my_tiles * p.kblocks;
-    // fetch cursor: runs DEPTH K blocks ahead of the spreading cursor, through the same tile sequence
-    int ptile = pair, pkb = 0;
-    const uint32_t* prow = nullptr;
-    auto seek_row = [&]() {
-      prow = nullptr;
-      if (ptile < num_tiles) {
-        int tm, tn;
-        pair_tile_coords(ptile, p.tiles_m, p.tiles_n, tm, tn);
-        const long long n = (long long)tn * TILE_N + (int)rank * HALF + r;
-        if (n < p.N) prow = p.xplanes + n * p.kwords;
+    const int groups_per_tile = (p.kblocks + XGROUP - 1) / XGROUP;
+    const long long total_groups = (long long)my_tiles * groups_per_tile;
+    const uint32_t leader_fullb0 = map_to_cta(fullb_bar(0), 0);
+    // K blocks of a group sit in consecutive B tiles, kcount = K blocks before the group (over all tiles of this CTA).
+    // Group g meets on named barrier 1 + g % 8: an expander reaches group g + 8 only after a B tile written in
+    // group g or later was consumed, hence after the signalling warp left the barrier for group g.
+    uint32_t kcount = 0;
+    if (warp == 6 + EXPAND_WARPS) {
+      int gk = 0;   // group within its tile
+      for (long long g = 0; g < total_groups; g++) {
+        const int nvalid = min(XGROUP, p.kblocks - gk * XGROUP);
+        named_bar_sync(1 + (int)(g & 7), BAR_THREADS);
+        if (lane < nvalid) mbar_arrive_cluster(leader_fullb0 + 8u * ((kcount + (uint32_t)lane) & (NB_XP - 1)));
+        kcount += (uint32_t)nvalid;
+        if (++gk == groups_per_tile) gk = 0;
       }
-    };
-    seek_row();
-    uint4 q[DEPTH][XPN];
-    auto fetch = [&](uint4 (&dst)[XPN]) {
+    } else {
+      // A thread spreads, per group, K block kq of two rows: a warp-wide 16-byte load then reads 64 contiguous
+      // bytes of each of eight rows, and the eight lanes of a quarter warp store to eight consecutive rows of one
+      // tile (conflict-free under the 128-byte swizzle).
+      const int kq = lane / KQ_LANES;
+      const int r0 = (warp - 6) * 16 + (lane % KQ_LANES);   // rows r0 + i * KQ_LANES of the CTA's half of the B tile
+      // fetch cursor: one group ahead of the spreading cursor
+      int ptile = pair, pgk = 0;
+      const uint32_t* prow[XTASKS];
+      auto seek_rows = [&]() {
 #pragma unroll
-      for (int j = 0; j < XPN; j++)
-        dst[j] = prow ? __ldg(reinterpret_cast<const uint4*>(prow + j * p.xplane_words + 4 * pkb)) : make_uint4(0u, 0u, 0u, 0u);
-      if (++pkb == p.kblocks) {
-        pkb = 0;
-        ptile += num_pairs;
-        seek_row();
-      }
-    };
+        for (int i = 0; i < XTASKS; i++) prow[i] = nullptr;
+        if (ptile < num_tiles) {
+          int tm, tn;
+          pair_tile_coords(ptile, p.tiles_m, p.tiles_n, tm, tn);
+          const long long n = (long long)tn * TILE_N + (int)rank * HALF + r0;
 #pragma unroll
-    for (int d = 0; d < DEPTH; d++) fetch(q[d]);
-    int s = 0;
-    uint32_t ph = 0;
-    bool ok = true;
-    for (long long i0 = 0; i0 < total && ok; i0 += DEPTH) {
+          for (int i = 0; i < XTASKS; i++)
+            if (n + i * KQ_LANES < p.N) prow[i] = p.xplanes + (n + i * KQ_LANES) * p.kwords;
+        }
+      };
+      seek_rows();
+      auto fetch_group = [&](uint4 (&dst)[XTASKS][XPN]) {
+        const int kb = pgk * XGROUP + kq;
 #pragma unroll
-      for (int d = 0; d < DEPTH; d++) {
-        if (i0 + d < total && ok) {   // uniform over the warp
-          ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1u));
-          if (ok) {
-            const uint32_t row_s = base + s * STAGE_BYTES + HALF * BK + (uint32_t)r * 128u;
+        for (int i = 0; i < XTASKS; i++)
 #pragma unroll
-            for (int g = 0; g < 4; g++) {
+          for (int j = 0; j < XPN; j++)
+            dst[i][j] = (prow[i] && kb < p.kblocks) ? __ldg(reinterpret_cast<const uint4*>(prow[i] + j * p.xplane_words + 4 * kb))
+                                                    : make_uint4(0u, 0u, 0u, 0u);
+        if (++pgk == groups_per_tile) {
+          pgk = 0;
+          ptile += num_pairs;
+          seek_rows();
+        }
+      };
+      bool ok = true;
+      int gk = 0;
+      // After an expired wait the warp keeps meeting the named barriers without touching the tiles, so the
+      // signalling warp drains and everyone reaches the tear-down.
+      auto spread_group = [&](const uint4 (&src)[XTASKS][XPN], long long g) {
+        const int nvalid = min(XGROUP, p.kblocks - gk * XGROUP);
+        const bool mine = kq < nvalid;
+        const uint32_t idx = kcount + (uint32_t)kq;
+        const uint32_t t = idx & (NB_XP - 1);
+        if (ok) ok = __all_sync(0xffffffffu, !mine || mbar_wait(emptyb_bar((int)t), ((idx / NB_XP) & 1u) ^ 1u));
+        if (ok && mine) {
+#pragma unroll
+          for (int i = 0; i < XTASKS; i++) {
+            const int r = r0 + KQ_LANES * i;
+            const uint32_t xr = (uint32_t)(r & 7);
+            const uint32_t row_s = b_ring + t * (HALF * BK) + (uint32_t)r * 128u;
+#pragma unroll
+            for (int gw = 0; gw < 4; gw++) {
               uint32_t w[XPN], o[8];
 #pragma unroll
-              for (int j = 0; j < XPN; j++) w[j] = g == 0 ? q[d][j].x : g == 1 ? q[d][j].y : g == 2 ? q[d][j].z : q[d][j].w;
+              for (int j = 0; j < XPN; j++)
+                w[j] = gw == 0 ? src[i][j].x : gw == 1 ? src[i][j].y : gw == 2 ? src[i][j].z : src[i][j].w;
               spread_word<XP>(w, p.x_signed != 0, o);
               // 16-byte chunk c of a 128-byte row lives at chunk position c ^ (row & 7) (128-byte swizzle)
-              st_shared_v4(row_s + (((uint32_t)(2 * g) ^ xr) << 4), o[0], o[1], o[2], o[3]);
-              st_shared_v4(row_s + (((uint32_t)(2 * g + 1) ^ xr) << 4), o[4], o[5], o[6], o[7]);
+              st_shared_v4(row_s + (((uint32_t)(2 * gw) ^ xr) << 4), o[0], o[1], o[2], o[3]);
+              st_shared_v4(row_s + (((uint32_t)(2 * gw + 1) ^ xr) << 4), o[4], o[5], o[6], o[7]);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_full0 + 8u * (uint32_t)s);
-            if (++s == STAGES) { s = 0; ph ^= 1u; }
-            fetch(q[d]);
           }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+        }
+        named_bar_arrive(1 + (int)(g & 7), BAR_THREADS);
+        kcount += (uint32_t)nvalid;
+        if (++gk == groups_per_tile) gk = 0;
+      };
+      uint4 qa[XTASKS][XPN], qb[XTASKS][XPN];
+      fetch_group(qa);
+      for (long long g = 0; g < total_groups; g += 2) {
+        fetch_group(qb);
+        spread_group(qa, g);
+        if (g + 1 < total_groups) {
+          fetch_group(qa);
+          spread_group(qb, g + 1);
         }
       }
+      if (!ok && lane == 0) atomicExch(p.error_flag, 4);
     }
-    if (!ok && lane == 0) atomicExch(p.error_flag, 4);
   } else {
     // ---------------- epilogue warps (2..5) of both CTAs ----------------
     const int quarter = warp & 3;
@@ -512,9 +587,9 @@ bool make_half_map(CUtensorMap* map, const void* base, long long rows, long long
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int XP>
+template <int XP, int XG = 4>
 cudaError_t launch_pair(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const PairParams& p, int pairs) {
-  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel<XP>), SMEM_BYTES);
+  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel<XP, XG>), SMEM_BYTES);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -529,7 +604,7 @@ cudaError_t launch_pair(cudaStream_t s, const CUtensorMap& map_a, const CUtensor
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1 + (unsigned)pdl_attribute(attr + 1);
-  return cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel<XP>, map_a, map_b, p);
+  return cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel<XP, XG>, map_a, map_b, p);
 }
 
 }  // namespace

@@ -53,7 +53,7 @@ def workload_config(n_gpus: int) -> dict:
         "workload": "gemm_w1a2_M8192_N8192_K8192_int32out",
         "M": M, "N_per_gpu": N, "K": K, "wbits": WBITS, "xbits": XBITS,
         "sharding": "replicated W, N-sharded X (g x 8192 rows), no collective" if n_gpus > 1 else "single GPU",
-        "l2": "4 rotating activation sets; each step writes 256 MiB of output (> 126 MB L2) between two reads of an operand",
+        "l2": "4 rotating activation sets; each step rewrites 64 MiB of int8 activations and 256 MiB of output (> 126 MB L2)",
         "collective": "none",
     }
 
@@ -249,13 +249,16 @@ def words(torch, shape, gen):
 
 # ----------------------------------------------------------------------------- the headline GEMM
 class GemmPipeline:
-    """The 8192^3 step on device-resident operands: the static W is expanded to int8 once; every step is
-    ONE launch that reads that step's activation planes as they are (apnn_gemm_w8: the kernel's own warps
-    spread the bits into its shared-memory stages).  expand_pass=True runs the older two-launch step
-    (activation planes -> int8 rows in HBM, then apnn_gemm_i8) for comparison."""
+    """The 8192^3 step on device-resident operands: the static W is expanded to int8 once; every step
+    expands that step's activation planes and runs the GEMM, both on the current stream.  (Running the
+    expand of step i+1 on a second stream beside GEMM i was measured: the persistent GEMM's statically
+    scheduled tiles on the SMs that also host expand blocks become stragglers, 0.285 -> 0.300 ms per GEMM,
+    which cancels what the overlap hides.)  expand_pass=False makes the step ONE launch that reads the
+    activation planes as they are (apnn_gemm_w8: the kernel's own warps spread the bits into its
+    shared-memory stages): no int8 activation image in HBM, but 0.45 ms per step."""
 
     def __init__(self, torch, ap, cabi, dev, rank, wbits=WBITS, xbits=XBITS, algo="tcgen05", epilogue=None, D=None,
-                 expand_pass=False):
+                 expand_pass=True):
         self.torch, self.ap, self.cabi, self.algo = torch, ap, cabi, algo
         self.expand_pass = expand_pass or xbits > 4
         self.wbits, self.xbits = wbits, xbits
@@ -358,7 +361,7 @@ def run_ours(args) -> None:
         return tuple(float(x) for x in t)
 
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-    pipe = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo, expand_pass=args.expand_pass)
+    pipe = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo, expand_pass=not args.planes_in_kernel)
     for i in range(2):  # keep the device busy while the sampler thread starts
         pipe.step(i)
     elapsed_ms, kernel_ms, clocks = timed_gemm_steps(torch, dist, pipe, args.steps, args.warmup, sampler)
@@ -429,6 +432,7 @@ def run_ours(args) -> None:
 
     # ---- the other workloads of the metric
     Wkeep, Xkeep = pipe.W, pipe.Xs[0]
+    two_launch_step, launches_per_step = pipe.expand_pass, pipe.launches_per_step
     del pipe
     torch.cuda.empty_cache()
     resnet = resnet_block(torch, dist, dev, world, rank, args)
@@ -515,11 +519,11 @@ def run_ours(args) -> None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8 operands, int32 accumulate (exact)", "data": "synthetic",
         "config": workload_config(world), "algo": algo,
-        "step": ("activation expand (planes -> int8) + tcgen05 GEMM" if pipe.expand_pass else
+        "step": ("activation expand (planes -> int8) + tcgen05 GEMM" if two_launch_step else
                  "one launch: tcgen05 GEMM reading the packed activation planes (bits spread to int8 inside the kernel)")
                 + "; the static weights' int8 image is made once before the timed region",
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": pipe.launches_per_step * args.steps, "clocks": clocks,
+        "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "sustained": sustained, "resnet18": resnet, "allgather": gather,
         "pairs_8192": pairs, "m64_sweep": sweep, "conv_c3": conv,
     }
@@ -941,8 +945,8 @@ def main() -> None:
     ap_.add_argument("--algo", default="tcgen05", choices=["tcgen05", "imma", "bmma"])
     ap_.add_argument("--profile", action="store_true",
                      help="timed GEMM steps only (no e2e, probe, CPU baseline or other blocks): the command ncu captures")
-    ap_.add_argument("--expand-pass", action="store_true",
-                     help="headline step as two launches (activation planes -> int8 rows in HBM, then the GEMM)")
+    ap_.add_argument("--planes-in-kernel", action="store_true",
+                     help="headline step as one launch (apnn_gemm_w8: the GEMM kernel spreads the activation planes itself)")
     ap_.add_argument("--quick", action="store_true", help="skip the N = 1 sweep blocks (pairs_8192, m64_sweep, conv_c3)")
     ap_.add_argument("--workload", default="gemm", choices=["gemm", "resnet18", "vgg_variant", "alexnet"],
                      help="gemm (default: the headline line with every block) or one whole w1a2 network (images/s)")

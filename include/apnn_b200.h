@@ -174,13 +174,15 @@ apnn_status apnn_expand_planes_pair(void *stream, const void *planes_w, void *w_
                                     long rows_x, int xbits, int x_signed, int K);
 apnn_status apnn_gemm_i8(void *stream, const void *W8, const void *X8, void *D, int M, int N, int K,
                          int w_signed, int x_signed, const apnn_epilogue *epi, int *status_flag);
-/* apnn_gemm_w8: the layer form of apmm_w1a2 and its siblings (LIB/71_bmmaTensorCoreGemm.cu:80, 72, 78):
- * static weights as the int8 rows apnn_expand_planes made once, activations straight from their packed
- * planes X[xbits][N][K/32] as the producing layer (or apnn_bit_compress) left them.  The CTA-pair kernel's
- * own warps spread the bits into its shared-memory stages, so no expand pass runs per call and the
- * activations need no workspace.  xbits in 1..4 (x_signed only with xbits == 1); every M and N (ragged edges
- * handled), sized for problems with at least as many 256x256 tiles as SM pairs.  Epilogue as apnn_gemm_i8
- * without out_i8, residual_i16 and APNN_OUT_FLOAT.  apnn_gemm_ex takes the same route for X on that kernel. */
+/* apnn_gemm_w8: the layer form of apmm_w1a2 and its siblings (LIB/71_bmmaTensorCoreGemm.cu:80, 72, 78) for
+ * callers short of device memory: static weights as the int8 rows apnn_expand_planes made once, activations
+ * straight from their packed planes X[xbits][N][K/32] as the producing layer (or apnn_bit_compress) left
+ * them.  The CTA-pair kernel's own warps spread the bits into its shared-memory stages, so no expand pass
+ * runs and the activations never exist as int8 rows in HBM (no workspace beyond the status flag).  The price
+ * is speed: at 8192^3 w1a2 0.45 ms per call against 0.31 ms for apnn_expand_planes + apnn_gemm_i8.
+ * xbits in 1..4 (x_signed only with xbits == 1); every M and N (ragged edges handled).  Epilogue as
+ * apnn_gemm_i8 without out_i8, residual_i16 and APNN_OUT_FLOAT.  With APNN_XPLANES=1 in the environment
+ * apnn_gemm_ex takes this route for X whenever it runs the CTA-pair kernel. */
 apnn_status apnn_gemm_w8(void *stream, const void *W8, int xbits, const void *X, void *D, int M, int N, int K,
                          int w_signed, int x_signed, const apnn_epilogue *epi, int *status_flag);
 

@@ -62,6 +62,11 @@ def test_argument_validation_returns_status_codes():
     assert L.apnn_gemm_ex(None, 0, 1, 2, p, p, p, 64, 64, 128, ctypes.byref(e), None, 0) == 2
     flag = (ctypes.c_int * 1)()
     assert L.apnn_gemm_i8(None, p, p, p, 64, 64, 128, 0, 0, ctypes.byref(e), ctypes.addressof(flag)) == 1
+    # activations from planes: 1..4 planes, a -1/+1 plane only alone, no int8-row / float outputs
+    assert L.apnn_gemm_w8(None, p, 5, p, p, 64, 64, 128, 0, 0, None, ctypes.addressof(flag)) == 2
+    assert L.apnn_gemm_w8(None, p, 2, p, p, 64, 64, 128, 0, 1, None, ctypes.addressof(flag)) == 2
+    assert L.apnn_gemm_w8(None, p, 2, p, p, 64, 64, 100, 0, 0, None, ctypes.addressof(flag)) == 3
+    assert L.apnn_gemm_w8(None, p, 2, p, p, 64, 64, 128, 0, 0, None, None) == 1
     # tcgen05 path without a workspace
     assert L.apnn_gemm_ex(None, 3, 1, 2, p, p, p, 128, 256, 128, None, None, 0) == 4
     assert L.apnn_gemm_workspace_bytes(3, 1, 2, 128, 256, 128) >= (128 + 256) * 128

@@ -459,3 +459,35 @@ def test_tcgen05_cluster_split_k_epilogues(cuda_device, M, N, K):
         want_res = np.clip(v2, -32768, 32767) if widths & 2 else v2
         assert np.array_equal(rout.cpu().numpy().astype(np.int32), want_res)
         assert np.array_equal(to_host(P3), oracle.requant_pack(v2, 3, 1))
+
+
+@pytest.mark.parametrize("xb,x_signed", [(1, False), (1, True), (2, False), (3, False), (4, False)])
+@pytest.mark.parametrize("M,N,K", [(100, 70, 128), (2304, 2304, 1152), (2300, 2336, 1024), (256, 512, 3200)])
+def test_tcgen05_activation_planes_in_kernel(cuda_device, M, N, K, xb, x_signed):
+    """apnn_gemm_w8: weights as int8 rows made once, activations straight from their packed planes -- the
+    CTA-pair kernel's own warps spread the bits into its stages.  One K block, K blocks that are no
+    multiple of the register prefetch depth, more tiles than SM pairs (two tiles per pair for some),
+    ragged M and N, every activation width and a -1/+1 activation plane, against the oracle."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(M + N + K + 7 * xb)
+    wb = 2 if x_signed else 1
+    W, wl = oracle.value_planes(rng, M, K, wb)
+    X, xl = oracle.value_planes(rng, N, K, xb)
+    wv = wl.astype(np.int64) if x_signed else 2 * wl.astype(np.int64) - 1   # +-1 weights unless the activations are
+    xv = 2 * xl.astype(np.int64) - 1 if x_signed else xl.astype(np.int64)
+    want = (wv @ xv.T).astype(np.int32)
+    w8 = ap.expand_planes(to_dev(W), signed=not x_signed)
+    flag = torch.ones(1, dtype=torch.int32, device="cuda")
+    out = ap.gemm_w8(w8, to_dev(X), w_signed=not x_signed, x_signed=x_signed, status_flag=flag)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    assert np.array_equal(to_host(out, np.int32), want)
+    if N % 32 == 0 and not x_signed:
+        scale = rng.uniform(0.5, 1.5, N).astype(np.float32)
+        bias = rng.uniform(-1, 1, N).astype(np.float32)
+        T = oracle.fold_bn(scale, bias, float(want.mean()), float(want.std()) / 4, 2)
+        epi = ap.make_epilogue("thresholds", 2, thresholds=to_dev(T))
+        packed = ap.gemm_w8(w8, to_dev(X), w_signed=True, epilogue=epi, status_flag=flag)
+        torch.cuda.synchronize()
+        assert int(flag.item()) == 0
+        assert np.array_equal(to_host(packed), oracle.requant_pack(want, 2, 2, T))
