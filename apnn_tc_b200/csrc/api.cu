@@ -182,6 +182,28 @@ apnn_status apnn_gemm_i8(void* stream, const void* W8, const void* X8, void* D, 
                      w_signed != 0, x_signed != 0, epi, status_flag);
 }
 
+apnn_status apnn_expand_planes_fp4(void* stream, const void* planes, void* out_fp4, long rows, int K, int bits, int is_signed) {
+  if (!planes || !out_fp4 || rows <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
+  if (bits < 1 || bits > 2 || (is_signed && bits != 1)) return APNN_ERR_UNSUPPORTED;
+  if (K % 256 != 0 || !aligned16(planes) || !aligned16(out_fp4)) return APNN_ERR_ALIGNMENT;
+  return tc5_expand_fp4(reinterpret_cast<cudaStream_t>(stream), (const uint32_t*)planes, (uint8_t*)out_fp4, rows, K, bits,
+                        is_signed != 0);
+}
+
+apnn_status apnn_gemm_fp4(void* stream, const void* W4, const void* X4, void* D, int M, int N, int K,
+                          const apnn_epilogue* epi, int* status_flag) {
+  if (!W4 || !X4 || !D || !status_flag || M <= 0 || N <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
+  if (K % 256 != 0 || !aligned16(W4) || !aligned16(X4) || !aligned16(D)) return APNN_ERR_ALIGNMENT;
+  if (epi) {
+    if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;
+    apnn_status st = check_epilogue(epi, N, false, 1, 1, true);
+    if (st != APNN_OK) return st;
+    if (epi->out_i8 || epi->residual_i16 || epi->out_mode == APNN_OUT_FLOAT) return APNN_ERR_UNSUPPORTED;
+  }
+  return tc5_gemm_fp4_pair(reinterpret_cast<cudaStream_t>(stream), (const uint8_t*)W4, (const uint8_t*)X4, D, M, N, K, epi,
+                           status_flag);
+}
+
 apnn_status apnn_gemm_w8(void* stream, const void* W8, int xbits, const void* X, void* D, int M, int N, int K,
                          int w_signed, int x_signed, const apnn_epilogue* epi, int* status_flag) {
   if (!W8 || !X || !D || !status_flag || M <= 0 || N <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;

@@ -37,6 +37,10 @@ bool tc5_pair_worthwhile(int M, int N, int K);
 apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B8, void* D, int M, int N, int K,
                              bool a_signed, bool b_signed, const apnn_epilogue* epi, int* status_flag,
                              const uint32_t* xplanes = nullptr, int xbits = 0);
+apnn_status tc5_expand_fp4(cudaStream_t s, const uint32_t* planes, uint8_t* out, long long rows, int K, int bits,
+                           bool is_signed);
+apnn_status tc5_gemm_fp4_pair(cudaStream_t s, const uint8_t* A4, const uint8_t* B4, void* D, int M, int N, int K,
+                              const apnn_epilogue* epi, int* status_flag);
 // The flat convolution on CTA pairs (256 positions x 256 channels per pair): stride 1, no pooling,
 // CIN % 128 == 0, COUT % 256 == 0, thresholds -> int8 rows, no residuals.  H, W: input extent.
 bool tc5_conv_pair_applies(int B, int H, int W, int CIN, int COUT, int R, int stride, const apnn_epilogue* epi);

@@ -45,9 +45,12 @@ constexpr int TILE_N = 256;
 constexpr int HALF = 128;     // rows of A and of B one CTA stages
 constexpr int STAGES = 6;
 constexpr int STAGE_BYTES = 2 * HALF * BK;  // 32 KiB per CTA
-constexpr int THR_BYTES_PER_WARP = 32 * 36 * 4;  // thresholds (256 x 16 B) or a padded 32 x 32 int32 block
+// per epilogue warp, 1024-byte aligned: thresholds (256 x 16 B), or a padded 32 x 32 int32 block, or the swizzled
+// 32 x 32 int32 block a bulk tensor store reads
+constexpr int THR_BYTES_PER_WARP = 5 * 1024;
 constexpr int WORD_BYTES_PER_WARP = 2 * 32 * 8 * 4;  // packed outputs of up to 2 bits: 8 words per row and plane, staged per tile
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * THR_BYTES_PER_WARP + 4 * WORD_BYTES_PER_WARP;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 1024 + 4 * THR_BYTES_PER_WARP + 4 * WORD_BYTES_PER_WARP;
+static_assert(32 * 36 * 4 <= THR_BYTES_PER_WARP, "padded transposition block");
 constexpr int THREADS = 192;
 // B-from-planes instantiations
 constexpr int EXPAND_WARPS = 8;                      // warps 6..13, 16 rows of the CTA's B half each
@@ -74,6 +77,7 @@ struct PairParams {
   long long xplane_words;
   int kwords;
   int x_signed;    // one plane holding -1 / +1
+  int tma_out;     // int32 output with one destination and N % 4 == 0: 32 x 32 blocks leave by bulk tensor stores
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -129,6 +133,23 @@ __device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t adesc, 
       : "memory");
 }
 
+// Block-scaled 4-bit floating-point MMA (e2m1 operands packed two per byte, fp32 accumulate), K = 64 per
+// instruction: twice the int8 rate.  Scale factors (ue8m0, one per 32 elements) are read from TMEM.
+__device__ __forceinline__ void tc_mma_mxf4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// eight 32-bit columns of this warp's 32 TMEM lanes <- one value
+__device__ __forceinline__ void tmem_fill8(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int band = GROUP_M * tiles_n;
   const int g = tile / band;
@@ -178,10 +199,13 @@ __device__ __forceinline__ void spread_word(const uint32_t (&w)[XP > 0 ? XP : 1]
 }
 
 // XG: K blocks per expander group (2 or 4); the B ring holds two groups, the A ring the other tiles
-template <int XP, int XG = 4>
+// MX: operands are e2m1 nibbles (two per byte, 256 elements per 128-byte K block), kind::mxf4 with unit scale
+// factors, fp32 accumulators converted to int32 in the epilogue; one accumulator (the other TMEM columns hold
+// the scale factors), so the epilogue of a tile does not overlap the next tile's MMAs.
+template <int XP, int XG = 4, bool MX = false>
 __global__ void __launch_bounds__(XP ? THREADS_XP : THREADS, 1)
 tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const PairParams p) {
+                     const __grid_constant__ CUtensorMap map_d, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -207,7 +231,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   static_assert(8 * (RING_BARS + 4) + 4 <= 256, "barrier block");
   const uint32_t b_ring = base + NA_XP * HALF * BK;   // XP > 0: first B tile
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
-  uint8_t* thr_stage = smem_raw + (bars + 256u - raw);
+  uint8_t* thr_stage = smem_raw + (bars + 1024u - raw);   // 1024-byte aligned, as is every warp's part of it
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -239,6 +263,19 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   cluster_sync_all();  // both CTAs' barriers exist before anything remote touches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  constexpr uint32_t SF_COL = 256;   // MX: scale factors, 32 columns of every lane, every byte ue8m0 1.0 (0x7F)
+  if (MX) {
+    if (warp >= 2 && warp < 6) {
+      const uint32_t t0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SF_COL;
+#pragma unroll
+      for (int i = 0; i < 4; i++) tmem_fill8(t0 + 8 * i, 0x7F7F7F7Fu);
+      tmem_st_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+  }
   // everything above overlapped the previous kernel's tail; from here on its results are visible
   grid_dependency_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) *p.error_flag = 0;
@@ -275,8 +312,8 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       uint32_t tl = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, tl++) {
-        const uint32_t acc = tl & 1u;
-        const uint32_t aph = (tl >> 1) & 1u;
+        const uint32_t acc = MX ? 0u : (tl & 1u);
+        const uint32_t aph = MX ? (tl & 1u) : ((tl >> 1) & 1u);
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TILE_N;
@@ -292,8 +329,11 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint64_t adesc = make_smem_desc(sa);
           const uint64_t bdesc = make_smem_desc(XP ? b_ring + t * (HALF * BK) : sa + HALF * BK);
 #pragma unroll
-          for (int k = 0; k < BK / 32; k++)
-            tc_mma_i8_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BK / 32; k++) {
+            if (MX) tc_mma_mxf4_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, tmem_base + SF_COL, tmem_base + SF_COL + 16,
+                                     (kb | k) != 0 ? 1u : 0u);
+            else tc_mma_i8_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
           tc_commit_pair(empty_bar(s));  // frees the stage (the A tile) in both CTAs
           if (XP) tc_commit_pair(emptyb_bar(t));
         }
@@ -436,8 +476,8 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         __syncwarp();
         staged_tn = tn;
       }
-      const uint32_t acc = tl & 1u;
-      const uint32_t aph = (tl >> 1) & 1u;
+      const uint32_t acc = MX ? 0u : (tl & 1u);
+      const uint32_t aph = MX ? (tl & 1u) : ((tl >> 1) & 1u);
       if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
       tc_fence_after();
       const long long row = (long long)tm * TILE_M + (int)rank * HALF + quarter * 32 + lane;
@@ -449,6 +489,11 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         __syncwarp();   // lanes that left the previous chunk early rejoin before the warp-wide TMEM load
         tmem_ld32(taddr + c * 32, v);
         tmem_ld_wait();
+        if (MX) {
+          // sums of small integers: exact in fp32 below 2^24
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = (uint32_t)__float2int_rn(__uint_as_float(v[j]));
+        }
         const int col0 = tn * TILE_N + c * 32;
         if (col0 >= p.N) continue;                        // uniform over the warp
         if (p.out_mode != OUT_INT32 && !row_ok) continue;  // packed modes: a thread writes only its own row
@@ -461,7 +506,29 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               if (p.residual_out != nullptr) p.residual_out[at + j] = (int32_t)v[j];
             }
         }
-        if (p.out_mode == OUT_INT32) {
+        if (p.out_mode == OUT_INT32 && p.tma_out) {
+          // The warp's 32 x 32 block goes to shared memory as 32 rows of 128 bytes in the 128-byte swizzle (a thread
+          // writes its own row: conflict-free) and leaves as one bulk tensor store, which clips at the matrix edges.
+          const long long row0 = (long long)tm * TILE_M + (int)rank * HALF + quarter * 32;
+          if (row0 < p.M) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous store has read the block
+            __syncwarp();
+            const uint32_t blk = smem_u32(thr_s);
+            const uint32_t row_s = blk + (uint32_t)lane * 128u;
+            const uint32_t xr = (uint32_t)(lane & 7);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+              st_shared_v4(row_s + (((uint32_t)j ^ xr) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_d), "r"(col0),
+                           "r"((int)row0), "r"(blk)
+                           : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        } else if (p.out_mode == OUT_INT32) {
           // Transpose the warp's 32 x 32 block through shared memory (rows padded to 36 words,
           // 16-byte accesses, conflict-free) so that every store instruction writes four whole
           // 128-byte row segments: full lines for HBM and, for the fused all-gather, for NVLink.
@@ -554,6 +621,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));  // the leader's barrier
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // bulk stores complete before the kernel ends
     if (!ok && lane == 0) atomicExch(p.error_flag, 3);
   }
 
@@ -568,6 +636,25 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+  }
+}
+
+// planes[bits][rows][K/32] -> e2m1 nibbles, two elements per byte, 16 bytes per 32-k word.  Levels 0..3 of one or
+// two planes (0 -> 0000, 1 -> 0010, 2 -> 0100, 3 -> 0101), or -1 / +1 of a single plane (bit 0 -> 1010, 1 -> 0010).
+// Nibble i of output word q holds the element whose bit sits at position 4*i + q: a fixed permutation inside each
+// group of 32 k, the same for both operands.
+__global__ void __launch_bounds__(256) expand_nibbles_kernel(const uint32_t* __restrict__ planes, uint8_t* __restrict__ out,
+                                                             long long total, int bits, int is_signed) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const uint32_t w0 = __ldg(planes + i);
+    const uint32_t w1 = bits > 1 ? __ldg(planes + total + i) : 0u;
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const uint32_t t0 = (w0 >> q) & 0x11111111u, t1 = (w1 >> q) & 0x11111111u;
+      o[q] = is_signed ? (0x22222222u | ((t0 ^ 0x11111111u) << 3)) : ((t1 << 2) | ((t0 & ~t1) << 1) | (t0 & t1));
+    }
+    *reinterpret_cast<uint4*>(out + i * 16) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -587,9 +674,10 @@ bool make_half_map(CUtensorMap* map, const void* base, long long rows, long long
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int XP, int XG = 4>
-cudaError_t launch_pair(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const PairParams& p, int pairs) {
-  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel<XP, XG>), SMEM_BYTES);
+template <int XP, int XG = 4, bool MX = false>
+cudaError_t launch_pair(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d,
+                        const PairParams& p, int pairs) {
+  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel<XP, XG, MX>), SMEM_BYTES);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -604,7 +692,31 @@ cudaError_t launch_pair(cudaStream_t s, const CUtensorMap& map_a, const CUtensor
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1 + (unsigned)pdl_attribute(attr + 1);
-  return cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel<XP, XG>, map_a, map_b, p);
+  return cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel<XP, XG, MX>, map_a, map_b, map_d, p);
+}
+
+// int32 [M][N] output seen as 32 x 32 boxes (128-byte rows, 128-byte swizzle on the shared-memory side)
+bool make_out_map(CUtensorMap* map, void* D, long long M, long long N) {
+  EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(tensor_map_encoder());
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, D, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Decides whether the int32 output leaves by bulk tensor stores and builds the map for it (a copy of map_a otherwise:
+// the kernel takes three maps whatever it uses).  APNN_TMA_STORE=0 keeps the per-thread stores.
+bool plan_out_map(CUtensorMap* map_d, const CUtensorMap& map_a, PairParams* p, void* D, int M, int N) {
+  static const bool on = [] { const char* v = getenv("APNN_TMA_STORE"); return !(v && v[0] == '0'); }();
+  *map_d = map_a;
+  p->tma_out = 0;
+  if (!on || p->out_mode != APNN_OUT_INT32 || p->n_out != 1 || (N & 3) != 0) return true;
+  if (!make_out_map(map_d, D, M, N)) return false;
+  p->tma_out = 1;
+  return true;
 }
 
 }  // namespace
@@ -651,18 +763,71 @@ apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B
   // D = s32, A/B = u8 or s8, K-major, N = 256, M = 256 over the pair
   p.idesc = (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(TILE_N >> 3) << 17) |
             ((uint32_t)(TILE_M >> 4) << 24);
+  CUtensorMap map_d;
+  if (!plan_out_map(&map_d, map_a, &p, D, M, N)) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   const int sms = device_sm_count();
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
   cudaError_t e;
   switch (xplanes ? xbits : 0) {
-    case 0: e = launch_pair<0>(s, map_a, map_b, p, pairs); break;
-    case 1: e = launch_pair<1>(s, map_a, map_b, p, pairs); break;
-    case 2: e = launch_pair<2>(s, map_a, map_b, p, pairs); break;
-    case 3: e = launch_pair<3>(s, map_a, map_b, p, pairs); break;
-    default: e = launch_pair<4>(s, map_a, map_b, p, pairs); break;
+    case 0: e = launch_pair<0>(s, map_a, map_b, map_d, p, pairs); break;
+    case 1: e = launch_pair<1>(s, map_a, map_b, map_d, p, pairs); break;
+    case 2: e = launch_pair<2>(s, map_a, map_b, map_d, p, pairs); break;
+    case 3: e = launch_pair<3>(s, map_a, map_b, map_d, p, pairs); break;
+    default: e = launch_pair<4>(s, map_a, map_b, map_d, p, pairs); break;
   }
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm_pair launch");
+  return APNN_OK;
+}
+
+apnn_status tc5_expand_fp4(cudaStream_t s, const uint32_t* planes, uint8_t* out, long long rows, int K, int bits,
+                           bool is_signed) {
+  const long long total = rows * (K / 32);
+  long long blocks = (total + 255) / 256, cap = (long long)device_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  expand_nibbles_kernel<<<(int)blocks, 256, 0, s>>>(planes, out, total, bits, is_signed ? 1 : 0);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "expand_nibbles launch");
+  return APNN_OK;
+}
+
+// D = A4 * B4^T over e2m1 nibble rows (K/2 bytes per row, K a multiple of 256), int32 or packed outputs.
+apnn_status tc5_gemm_fp4_pair(cudaStream_t s, const uint8_t* A4, const uint8_t* B4, void* D, int M, int N, int K,
+                              const apnn_epilogue* epi, int* status_flag) {
+  if (epi && epi->out_mode == APNN_OUT_FLOAT) return APNN_ERR_UNSUPPORTED;
+  CUtensorMap map_a, map_b;
+  if (!make_half_map(&map_a, A4, M, K / 2) || !make_half_map(&map_b, B4, N, K / 2))
+    return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  PairParams p;
+  memset(&p, 0, sizeof(p));
+  p.out = D;
+  p.thresholds = epi ? epi->thresholds : nullptr;
+  p.residual_in = epi ? epi->residual_in : nullptr;
+  p.residual_out = epi ? epi->residual_out : nullptr;
+  p.M = M;
+  p.N = N;
+  p.kblocks = (K / 2) / BK;
+  p.tiles_m = (M + TILE_M - 1) / TILE_M;
+  p.tiles_n = (N + TILE_N - 1) / TILE_N;
+  p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
+  p.out_bits = epi ? epi->out_bits : 0;
+  p.out_plane_words = (long long)M * (N / 32);
+  p.error_flag = status_flag;
+  p.n_out = 1;
+  p.outs[0] = D;
+  if (epi)
+    for (int i = 0; i < epi->n_peer_out && p.n_out < 8; i++) p.outs[p.n_out++] = epi->peer_out[i];
+  // block-scaled instruction descriptor: a / b format e2m1 (1) at bits 7 and 10, both K-major, N >> 3 at bit 17,
+  // scale format ue8m0 (1) at bit 23, M >> 4 at bit 24, scale-factor ids 0
+  p.idesc = (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | (1u << 23) | ((uint32_t)(TILE_M >> 4) << 24);
+  CUtensorMap map_d;
+  if (!plan_out_map(&map_d, map_a, &p, D, M, N)) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  const int sms = device_sm_count();
+  long long tiles = (long long)p.tiles_m * p.tiles_n;
+  int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
+  cudaError_t e = launch_pair<0, 4, true>(s, map_a, map_b, map_d, p, pairs);
+  if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm_fp4_pair launch");
   return APNN_OK;
 }
 
