@@ -10,7 +10,7 @@ from . import _cabi
 from ._cabi import ApnnError, Epilogue  # noqa: F401
 from .ops import (  # noqa: F401
     APConv_w1a2_pack, APConv_w1a2_pack_pool, APConv_w2a2_pack, APConv_w2a2_pack_pool, Bit_compression, HostHandle,
-    apconv, apmm, conv_check, conv_workspace_bytes, apmm_w1a2, apmm_w1a2_decompose, apmm_w1a3, apmm_w1a4, apmm_w2a2, apmm_w2a2_decompose, expand_planes, gemm_i8, gemm_w8,
+    apconv, apmm, conv_check, conv_workspace_bytes, apmm_w1a2, apmm_w1a2_decompose, apmm_w1a3, apmm_w1a4, apmm_w2a2, apmm_w2a2_decompose, expand_planes, expand_planes_fp4, gemm_fp4, gemm_i8, gemm_w8,
     gemm_check, gemm_workspace_bytes, images_quantization, make_epilogue,
 )
 

@@ -22,7 +22,7 @@ ALGOS = {"auto": ALGO_AUTO, "bmma": ALGO_BMMA, "imma": ALGO_IMMA, "tcgen05": ALG
 # every symbol the header declares; the CPU test-suite checks the library exports them all
 EXPORTS = (
     "apnn_status_string", "apnn_last_cuda_error", "apnn_version", "apnn_gemm", "apnn_gemm_ex",
-    "apnn_gemm_workspace_bytes", "apnn_gemm_check", "apnn_expand_planes", "apnn_expand_planes_pair", "apnn_gemm_i8", "apnn_gemm_w8", "apnn_gemm_static_scratch", "apnn_conv2d", "apnn_conv2d_ex",
+    "apnn_gemm_workspace_bytes", "apnn_gemm_check", "apnn_expand_planes", "apnn_expand_planes_pair", "apnn_gemm_i8", "apnn_gemm_w8", "apnn_expand_planes_fp4", "apnn_gemm_fp4", "apnn_gemm_static_scratch", "apnn_conv2d", "apnn_conv2d_ex",
     "apnn_conv2d_workspace_bytes", "apnn_conv2d_check", "apnn_conv2d_i8", "apnn_bit_compress", "apnn_quantize_pack", "apnn_quantize_im2col", "apnn_create",
     "apnn_destroy", "apnn_gemm_host", "apnn_conv2d_host", "apnn_probe_peak", "apnn_quantize_im2col_i8", "apnn_quantize_window_rows_i8", "apnn_maxpool2x2_i8", "apnn_requantize_i32",
 )
@@ -86,6 +86,8 @@ def lib() -> ctypes.CDLL:
     L.apnn_expand_planes_pair.argtypes = [vp, vp, vp, lg, i, i, vp, vp, lg, i, i, i]
     L.apnn_gemm_i8.argtypes = [vp, vp, vp, vp, i, i, i, i, i, ep, vp]
     L.apnn_gemm_w8.argtypes = [vp, vp, i, vp, vp, i, i, i, i, i, ep, vp]
+    L.apnn_expand_planes_fp4.argtypes = [vp, vp, vp, lg, i, i, i]
+    L.apnn_gemm_fp4.argtypes = [vp, vp, vp, vp, i, i, i, ep, vp]
     L.apnn_gemm_static_scratch.argtypes = [vp, i, i, vp, vp, vp, i, i, i, ep, vp]
     L.apnn_conv2d.argtypes = [vp, i, i, vp, vp, vp, i, i, i, i, i, i, i, ep]
     L.apnn_conv2d_ex.argtypes = [vp, i, i, i, vp, vp, vp, i, i, i, i, i, i, i, ep, vp, sz]

@@ -194,6 +194,7 @@ apnn_status apnn_gemm_fp4(void* stream, const void* W4, const void* X4, void* D,
                           const apnn_epilogue* epi, int* status_flag) {
   if (!W4 || !X4 || !D || !status_flag || M <= 0 || N <= 0 || K <= 0) return APNN_ERR_INVALID_ARG;
   if (K % 256 != 0 || !aligned16(W4) || !aligned16(X4) || !aligned16(D)) return APNN_ERR_ALIGNMENT;
+  if ((long long)K * 9 >= (1ll << 24)) return APNN_ERR_UNSUPPORTED;   // sums must stay exact in fp32
   if (epi) {
     if (epi->signed_operand != APNN_SIGN_NONE) return APNN_ERR_INVALID_ARG;
     apnn_status st = check_epilogue(epi, N, false, 1, 1, true);

@@ -1533,6 +1533,17 @@ apnn_status tc5_gemm(cudaStream_t s, int wbits, int xbits, const uint32_t* W, co
   uint8_t* wb = wa + align_up((size_t)M * K, 256);
   int* err = reinterpret_cast<int*>(wb + align_up((size_t)N * K, 256));
   const int sign = epi ? epi->signed_operand : APNN_SIGN_NONE;
+  // Operands of at most two bits are exact e2m1 values (levels 0..3, or -1 / +1): the block-scaled 4-bit MMA runs them
+  // at twice the int8 rate with every sum exact in fp32 (APNN_FP4=0 keeps the int8 path).
+  static const bool fp4_on = [] { const char* v = getenv("APNN_FP4"); return !(v && v[0] == '0'); }();
+  if (fp4_on && wbits <= 2 && xbits <= 2 && K % 256 == 0 && (long long)K * 9 < (1ll << 24) &&
+      (pair || takes_pair_kernel(M, N, K, epi)) && !(epi && epi->out_mode == APNN_OUT_FLOAT)) {
+    uint8_t* xb4 = wa + align_up((size_t)M * (K / 2), 256);
+    apnn_status s4 = tc5_expand_fp4(s, W, wa, M, K, wbits, sign == APNN_SIGN_W);
+    if (s4 == APNN_OK) s4 = tc5_expand_fp4(s, X, xb4, N, K, xbits, sign == APNN_SIGN_X);
+    if (s4 != APNN_OK) return s4;
+    return tc5_gemm_fp4_pair(s, wa, xb4, D, M, N, K, epi, err);
+  }
   // APNN_XPLANES=1: the CTA-pair kernel spreads the activation planes itself, so only W goes through the expand
   // pass and the activation part of the workspace stays untouched.  Off by default: at 8192^3 that kernel takes
   // 0.45 ms against 0.017 + 0.288 ms for the expand pass and the GEMM over int8 rows.

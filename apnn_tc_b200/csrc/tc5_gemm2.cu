@@ -202,6 +202,9 @@ __device__ __forceinline__ void spread_word(const uint32_t (&w)[XP > 0 ? XP : 1]
 // MX: operands are e2m1 nibbles (two per byte, 256 elements per 128-byte K block), kind::mxf4 with unit scale
 // factors, fp32 accumulators converted to int32 in the epilogue; one accumulator (the other TMEM columns hold
 // the scale factors), so the epilogue of a tile does not overlap the next tile's MMAs.
+// MX: operands are e2m1 nibbles (two per byte, 256 elements per 128-byte K block), kind::mxf4 with unit scale
+// factors, fp32 accumulators converted to int32 in the epilogue; tiles are 224 wide so that two accumulators and
+// the scale factors (32 columns of 0x7F bytes, whatever their layout) fit the 512 TMEM columns.
 template <int XP, int XG = 4, bool MX = false>
 __global__ void __launch_bounds__(XP ? THREADS_XP : THREADS, 1)
 tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -211,6 +214,9 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t base = (raw + 1023u) & ~1023u;
   const uint32_t bars = base + STAGES * STAGE_BYTES;
   // XP == 0: one ring of STAGES stages (A tile then B tile); XP > 0: NA ring slots of A tiles, then NB of B tiles
+  // tile width over the pair: 256, or 224 for MX (two accumulators and the scale factors share the 512 TMEM columns)
+  constexpr int TN = MX ? 224 : 256;
+  constexpr int BHALF = TN / 2;              // rows of B one CTA stages
   constexpr int XGROUP = XG;
   constexpr int NB_XP = 2 * XGROUP;          // B tiles: two groups
   constexpr int NA_XP = XP_TILES - NB_XP;    // A tiles in flight
@@ -263,7 +269,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   cluster_sync_all();  // both CTAs' barriers exist before anything remote touches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  constexpr uint32_t SF_COL = 256;   // MX: scale factors, 32 columns of every lane, every byte ue8m0 1.0 (0x7F)
+  constexpr uint32_t SF_COL = 2 * TN;   // MX: scale factors, 32 columns of every lane, every byte ue8m0 1.0 (0x7F)
   if (MX) {
     if (warp >= 2 && warp < 6) {
       const uint32_t t0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SF_COL;
@@ -291,13 +297,13 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         int tm, tn;
         pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int arow = tm * TILE_M + (int)rank * HALF;
-        const int brow = tn * TILE_N + (int)rank * HALF;
+        const int brow = tn * TN + (int)rank * BHALF;
         for (int kb = 0; kb < p.kblocks; kb++, it++) {
           const int s = it % NA;
           const uint32_t ph = (it / NA) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
           const uint32_t leader_full = map_to_cta(full_bar(s), 0);
-          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * A_SLOT_BYTES);  // both CTAs' bytes
+          if (rank == 0) mbar_expect_tx(full_bar(s), XP ? 2 * A_SLOT_BYTES : 2 * (HALF + BHALF) * BK);  // both CTAs' bytes
           const uint32_t sa = base + s * A_SLOT_BYTES;
           tma_load_2d_pair(sa, &map_a, kb * BK, arow, leader_full);
           if (XP == 0) tma_load_2d_pair(sa + HALF * BK, &map_b, kb * BK, brow, leader_full);
@@ -312,11 +318,11 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       uint32_t tl = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, tl++) {
-        const uint32_t acc = MX ? 0u : (tl & 1u);
-        const uint32_t aph = MX ? (tl & 1u) : ((tl >> 1) & 1u);
+        const uint32_t acc = tl & 1u;
+        const uint32_t aph = (tl >> 1) & 1u;
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * TILE_N;
+        const uint32_t d_tmem = tmem_base + acc * TN;
         for (int kb = 0; kb < p.kblocks; kb++, it++) {
           const int s = it % NA;
           const uint32_t ph = (it / NA) & 1u;
@@ -377,7 +383,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (ptile < num_tiles) {
           int tm, tn;
           pair_tile_coords(ptile, p.tiles_m, p.tiles_n, tm, tn);
-          const long long n = (long long)tn * TILE_N + (int)rank * HALF + r0;
+          const long long n = (long long)tn * TN + (int)rank * HALF + r0;
 #pragma unroll
           for (int i = 0; i < XTASKS; i++)
             if (n + i * KQ_LANES < p.N) prow[i] = p.xplanes + (n + i * KQ_LANES) * p.kwords;
@@ -456,15 +462,15 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // collected here and leave as one 32-byte store per plane and destination -- whole sectors for HBM and
     // for NVLink instead of eight scattered 4-byte stores.
     uint32_t* word_s = reinterpret_cast<uint32_t*>(thr_stage + 4 * THR_BYTES_PER_WARP + (warp - 2) * WORD_BYTES_PER_WARP);
-    const bool words_staged = p.out_mode != OUT_INT32 && p.out_bits <= 2 && ((p.N >> 5) & 3) == 0;
+    const bool words_staged = !MX && p.out_mode != OUT_INT32 && p.out_bits <= 2 && ((p.N >> 5) & 3) == 0;   // eight words per tile row
     int staged_tn = -1;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, tl++) {
       int tm, tn;
       pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (thr_staged && tn != staged_tn) {
         __syncwarp();
-        for (int cidx = lane; cidx < TILE_N; cidx += 32) {
-          const int col = tn * TILE_N + cidx;
+        for (int cidx = lane; cidx < TN; cidx += 32) {
+          const int col = tn * TN + cidx;
           int4 t4 = make_int4(0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff);
           if (col < p.N) {
             const int32_t* T = p.thresholds + (long long)col * nl;
@@ -476,15 +482,15 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         __syncwarp();
         staged_tn = tn;
       }
-      const uint32_t acc = MX ? 0u : (tl & 1u);
-      const uint32_t aph = MX ? (tl & 1u) : ((tl >> 1) & 1u);
+      const uint32_t acc = tl & 1u;
+      const uint32_t aph = (tl >> 1) & 1u;
       if (!mbar_wait(tfull_bar(acc), aph)) { ok = false; break; }
       tc_fence_after();
       const long long row = (long long)tm * TILE_M + (int)rank * HALF + quarter * 32 + lane;
       const bool row_ok = row < p.M;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TILE_N;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * TN;
 #pragma unroll 1
-      for (int c = 0; c < TILE_N / 32; c++) {
+      for (int c = 0; c < TN / 32; c++) {
         uint32_t v[32];
         __syncwarp();   // lanes that left the previous chunk early rejoin before the warp-wide TMEM load
         tmem_ld32(taddr + c * 32, v);
@@ -494,7 +500,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = (uint32_t)__float2int_rn(__uint_as_float(v[j]));
         }
-        const int col0 = tn * TILE_N + c * 32;
+        const int col0 = tn * TN + c * 32;
         if (col0 >= p.N) continue;                        // uniform over the warp
         if (p.out_mode != OUT_INT32 && !row_ok) continue;  // packed modes: a thread writes only its own row
         if (row_ok && (p.residual_in != nullptr || p.residual_out != nullptr)) {
@@ -583,7 +589,7 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               lv[j] = l;
             }
           }
-          const bool tile_whole = words_staged && (tn + 1) * TILE_N <= p.N;
+          const bool tile_whole = words_staged && (tn + 1) * TN <= p.N;
           for (int b = 0; b < p.out_bits; b++) {
             uint32_t part[4] = {0u, 0u, 0u, 0u};   // four independent chains instead of one of 32 ORs
 #pragma unroll
@@ -598,12 +604,12 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           }
         }
       }
-      if (words_staged && row_ok && (tn + 1) * TILE_N <= p.N) {
+      if (words_staged && row_ok && (tn + 1) * TN <= p.N) {
         // the row's eight words per plane: 32 contiguous, 32-byte aligned bytes of the packed output
         for (int b = 0; b < p.out_bits; b++) {
           const uint4 lo = *reinterpret_cast<const uint4*>(word_s + (b * 32 + lane) * 8);
           const uint4 hi = *reinterpret_cast<const uint4*>(word_s + (b * 32 + lane) * 8 + 4);
-          const long long at = b * p.out_plane_words + row * (p.N >> 5) + tn * (TILE_N >> 5);
+          const long long at = b * p.out_plane_words + row * (p.N >> 5) + tn * (TN >> 5);
           for (int q = 0; q < p.n_out; q++) {
             uint32_t* dst = reinterpret_cast<uint32_t*>(p.outs[q]) + at;   // 16-byte aligned: N/32 is a multiple of 4
             if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
@@ -662,12 +668,12 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-bool make_half_map(CUtensorMap* map, const void* base, long long rows, long long K) {
+bool make_half_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows = HALF) {
   EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(tensor_map_encoder());
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)HALF};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -797,7 +803,8 @@ apnn_status tc5_gemm_fp4_pair(cudaStream_t s, const uint8_t* A4, const uint8_t* 
                               const apnn_epilogue* epi, int* status_flag) {
   if (epi && epi->out_mode == APNN_OUT_FLOAT) return APNN_ERR_UNSUPPORTED;
   CUtensorMap map_a, map_b;
-  if (!make_half_map(&map_a, A4, M, K / 2) || !make_half_map(&map_b, B4, N, K / 2))
+  constexpr int TN_MX = 224;   // the MX instantiation's tile width
+  if (!make_half_map(&map_a, A4, M, K / 2) || !make_half_map(&map_b, B4, N, K / 2, TN_MX / 2))
     return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   PairParams p;
   memset(&p, 0, sizeof(p));
@@ -809,7 +816,7 @@ apnn_status tc5_gemm_fp4_pair(cudaStream_t s, const uint8_t* A4, const uint8_t* 
   p.N = N;
   p.kblocks = (K / 2) / BK;
   p.tiles_m = (M + TILE_M - 1) / TILE_M;
-  p.tiles_n = (N + TILE_N - 1) / TILE_N;
+  p.tiles_n = (N + TN_MX - 1) / TN_MX;
   p.out_mode = epi ? epi->out_mode : APNN_OUT_INT32;
   p.out_bits = epi ? epi->out_bits : 0;
   p.out_plane_words = (long long)M * (N / 32);
@@ -820,7 +827,7 @@ apnn_status tc5_gemm_fp4_pair(cudaStream_t s, const uint8_t* A4, const uint8_t* 
     for (int i = 0; i < epi->n_peer_out && p.n_out < 8; i++) p.outs[p.n_out++] = epi->peer_out[i];
   // block-scaled instruction descriptor: a / b format e2m1 (1) at bits 7 and 10, both K-major, N >> 3 at bit 17,
   // scale format ue8m0 (1) at bit 23, M >> 4 at bit 24, scale-factor ids 0
-  p.idesc = (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | (1u << 23) | ((uint32_t)(TILE_M >> 4) << 24);
+  p.idesc = (1u << 7) | (1u << 10) | ((uint32_t)(TN_MX >> 3) << 17) | (1u << 23) | ((uint32_t)(TILE_M >> 4) << 24);
   CUtensorMap map_d;
   if (!plan_out_map(&map_d, map_a, &p, D, M, N)) return cuda_fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
   const int sms = device_sm_count();

@@ -119,6 +119,38 @@ def gemm_i8(W8: torch.Tensor, X8: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
+def expand_planes_fp4(planes: torch.Tensor, signed: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """planes [bits <= 2, rows, K/32] -> e2m1 nibbles [rows, K/2] (two elements per byte) for ``gemm_fp4``."""
+    planes = _dev_words(planes, "planes")
+    bits, rows, kw = planes.shape
+    if out is None:
+        out = torch.empty((rows, kw * 16), dtype=torch.uint8, device=planes.device)
+    st = _cabi.lib().apnn_expand_planes_fp4(_stream_ptr(), planes.data_ptr(), out.data_ptr(), rows, kw * 32, bits,
+                                            1 if signed else 0)
+    _cabi.check(st, "apnn_expand_planes_fp4")
+    return out
+
+
+def gemm_fp4(W4: torch.Tensor, X4: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+             epilogue: Optional[Epilogue] = None, status_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Exact GEMM of operands of at most two bits on the 4-bit floating-point tensor path (kind::mxf4, unit
+    scales): twice the int8 rate, sums exact in fp32.  Operands from ``expand_planes_fp4``."""
+    M, kb = W4.shape
+    N, kb2 = X4.shape
+    if kb != kb2:
+        raise ValueError("operands disagree on K")
+    packed = epilogue is not None and epilogue.out_mode in (1, 2)
+    if out is None:
+        shape = (epilogue.out_bits, M, N // 32) if packed else (M, N)
+        out = torch.empty(shape, dtype=torch.int32, device=W4.device)
+    if status_flag is None:
+        status_flag = torch.empty(1, dtype=torch.int32, device=W4.device)
+    st = _cabi.lib().apnn_gemm_fp4(_stream_ptr(), W4.data_ptr(), X4.data_ptr(), out.data_ptr(), M, N, kb * 2,
+                                   ctypes.byref(epilogue) if epilogue is not None else None, status_flag.data_ptr())
+    _cabi.check(st, "apnn_gemm_fp4")
+    return out
+
+
 def gemm_w8(W8: torch.Tensor, X: torch.Tensor, out: Optional[torch.Tensor] = None, *, w_signed: bool = False,
             x_signed: bool = False, epilogue: Optional[Epilogue] = None,
             status_flag: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -186,6 +186,24 @@ apnn_status apnn_gemm_i8(void *stream, const void *W8, const void *X8, void *D, 
 apnn_status apnn_gemm_w8(void *stream, const void *W8, int xbits, const void *X, void *D, int M, int N, int K,
                          int w_signed, int x_signed, const apnn_epilogue *epi, int *status_flag);
 
+/* ---- operands of at most two bits on the 4-bit floating-point tensor path ----------
+ * No counterpart in the reference.  tcgen05.mma kind::mxf4 multiplies e2m1 operands (4-bit floats: 0, 0.5, 1,
+ * 1.5, 2, 3, 4, 6 and their negatives) at twice the int8 rate and accumulates in fp32.  The levels 0..3 of a
+ * one- or two-plane operand and the -1 / +1 of a signed one-plane operand are e2m1 values; with every block scale
+ * factor set to 1 all products and partial sums are small integers, exact in fp32 while |sum| < 2^24.  So for
+ * wbits, xbits <= 2 the contraction of apmm_w1a2 / apmm_w2a2 (LIB/71_, 72_bmmaTensorCoreGemm.cu:80) runs there
+ * bit for bit (tests compare with the oracle and with the int8 path, sums up to 786432 included).
+ * apnn_expand_planes_fp4: planes[bits][rows][K/32] -> out_fp4[rows][K/2], two elements per byte (bits 1 or 2;
+ *   is_signed only with bits == 1), K % 256 == 0, a fixed permutation inside each group of 32 k.
+ * apnn_gemm_fp4: D = W4 * X4^T over such operands on CTA pairs (256 x 224 tiles), epilogue as apnn_gemm_i8
+ *   without out_i8, residual_i16 and APNN_OUT_FLOAT; K % 256 == 0 and 9 * K < 2^24, else APNN_ERR_UNSUPPORTED.
+ * apnn_gemm_ex / apnn_gemm_host take this path by themselves when the widths allow and the problem is large
+ * enough for CTA pairs (APNN_FP4=0 in the environment keeps int8). */
+apnn_status apnn_expand_planes_fp4(void *stream, const void *planes, void *out_fp4, long rows, int K,
+                                   int bits, int is_signed);
+apnn_status apnn_gemm_fp4(void *stream, const void *W4, const void *X4, void *D, int M, int N, int K,
+                          const apnn_epilogue *epi, int *status_flag);
+
 /* A tcgen05 GEMM that allocates nothing and needs no workspace argument.  No counterpart
  * in the reference.  It exists for callers that cannot cudaMalloc a workspace: code running
  * inside a host application whose own memory pool already owns the device's memory, or a
@@ -312,7 +330,8 @@ apnn_status apnn_quantize_window_rows_i8(void *stream, const float *images, void
  * returns the operations one launch performs; the caller times the launch with events to
  * get the device's peak for that path (the roofline denominator).  kind 0: tcgen05.mma
  * kind::i8 (128x256x32, operands fixed in shared memory), 1: mma.sync m16n8k32 u8,
- * 2: mma.sync m16n8k256 b1 and.popc (bit operations), 3 / 4: kind 0 with N = 128 / 64.
+ * 2: mma.sync m16n8k256 b1 and.popc (bit operations), 3 / 4: kind 0 with N = 128 / 64,
+ * 5: tcgen05.mma kind::mxf4 (128x224x64, e2m1 operands, unit scale factors).
  * scratch_flag: 4 bytes of device
  * memory.  No counterpart in the reference. */
 apnn_status apnn_probe_peak(void *stream, int kind, int iters, int *scratch_flag,

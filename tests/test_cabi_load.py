@@ -67,6 +67,12 @@ def test_argument_validation_returns_status_codes():
     assert L.apnn_gemm_w8(None, p, 2, p, p, 64, 64, 128, 0, 1, None, ctypes.addressof(flag)) == 2
     assert L.apnn_gemm_w8(None, p, 2, p, p, 64, 64, 100, 0, 0, None, ctypes.addressof(flag)) == 3
     assert L.apnn_gemm_w8(None, p, 2, p, p, 64, 64, 128, 0, 0, None, None) == 1
+    # 4-bit floating-point path: one or two planes, K a multiple of 256 and small enough for exact fp32 sums
+    assert L.apnn_expand_planes_fp4(None, p, p, 64, 256, 3, 0) == 2
+    assert L.apnn_expand_planes_fp4(None, p, p, 64, 256, 2, 1) == 2
+    assert L.apnn_expand_planes_fp4(None, p, p, 64, 128, 2, 0) == 3
+    assert L.apnn_gemm_fp4(None, p, p, p, 64, 64, 128, None, ctypes.addressof(flag)) == 3
+    assert L.apnn_gemm_fp4(None, p, p, p, 64, 64, 1 << 21, None, ctypes.addressof(flag)) == 2
     # tcgen05 path without a workspace
     assert L.apnn_gemm_ex(None, 3, 1, 2, p, p, p, 128, 256, 128, None, None, 0) == 4
     assert L.apnn_gemm_workspace_bytes(3, 1, 2, 128, 256, 128) >= (128 + 256) * 128

@@ -258,6 +258,11 @@ def test_large_shape_properties(cuda_device):
     assert torch.equal(D, D0 + 2 * D1)
     del D0, D1
     assert torch.equal(D, ap.apmm(W, X, algo="bmma"))
+    # the workspace route took the 4-bit floating-point path (two-bit operands); the int8 pair kernel explicitly
+    flag = torch.ones(1, dtype=torch.int32, device="cuda")
+    D8 = ap.gemm_i8(ap.expand_planes(W), ap.expand_planes(X), status_flag=flag)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0 and torch.equal(D, D8)
 
 
 @pytest.mark.parametrize("algo", ["imma", "bmma", "tcgen05"])
@@ -371,17 +376,19 @@ def test_tcgen05_split_k_and_requantize(cuda_device, M, N, K):
     assert np.array_equal(to_host(outl), oracle.requant_pack(want, 3, 1))
 
 
+@pytest.mark.parametrize("xb", [2, 3])
 @pytest.mark.parametrize("M,N", [(2304, 2304), (2300, 2336)])
 @pytest.mark.parametrize("mode", ["thresholds", "lowbits", "int32"])
-def test_tcgen05_pair_kernel_epilogues(cuda_device, M, N, mode):
-    """81 pair tiles and K = 1024: the GEMM runs on CTA pairs (cta_group::2).  Its +-1 weights,
+def test_tcgen05_pair_kernel_epilogues(cuda_device, M, N, mode, xb):
+    """81 pair tiles and K = 1024: the GEMM runs on CTA pairs (cta_group::2) -- with two-bit activations as
+    e2m1 operands on the 4-bit floating-point path, with three-bit ones on the int8 path.  Its +-1 weights,
     threshold / low-bit requantisation and residual in / out against the oracle, on a tile-aligned
     and a ragged shape."""
     import apnn_tc_b200 as ap
     K = 1024
     rng = np.random.default_rng(M + N)
     W, _ = oracle.value_planes(rng, M, K, 1)
-    X, _ = oracle.value_planes(rng, N, K, 2)
+    X, _ = oracle.value_planes(rng, N, K, xb)
     v = oracle.signed_correct(oracle.gemm_popc(W, X, threads=8), oracle.row_sums(X), 1)
     res = rng.integers(-400, 400, size=v.shape).astype(np.int32)
     v = v + res
@@ -491,3 +498,64 @@ def test_tcgen05_activation_planes_in_kernel(cuda_device, M, N, K, xb, x_signed)
         torch.cuda.synchronize()
         assert int(flag.item()) == 0
         assert np.array_equal(to_host(packed), oracle.requant_pack(want, 2, 2, T))
+
+
+@pytest.mark.parametrize("wb,xb,signed", [(1, 2, "w"), (2, 2, "none"), (1, 1, "x"), (2, 1, "none"), (1, 2, "none")])
+@pytest.mark.parametrize("M,N,K", [(100, 70, 256), (300, 520, 1024), (2300, 2340, 768), (2304, 2464, 1024)])
+def test_fp4_path_against_oracle(cuda_device, M, N, K, wb, xb, signed):
+    """Operands of at most two bits as e2m1 values on tcgen05.mma kind::mxf4 with unit scale factors
+    (apnn_expand_planes_fp4 + apnn_gemm_fp4): one tile, ragged tiles, more 256 x 224 tiles than SM pairs,
+    unsigned and -1/+1 operands on either side, int32 and thresholded packed outputs, against the oracle."""
+    import apnn_tc_b200 as ap
+    rng = np.random.default_rng(M + N + K + 5 * wb + xb)
+    W, wl = oracle.value_planes(rng, M, K, wb)
+    X, xl = oracle.value_planes(rng, N, K, xb)
+    acc = oracle.gemm_popc(W, X, threads=8)
+    if signed == "w":
+        want = oracle.signed_correct(acc, oracle.row_sums(X), 1)
+    elif signed == "x":
+        want = oracle.signed_correct(acc, oracle.row_sums(W), 0)
+    else:
+        want = acc
+    w4 = ap.expand_planes_fp4(to_dev(W), signed=signed == "w")
+    x4 = ap.expand_planes_fp4(to_dev(X), signed=signed == "x")
+    flag = torch.ones(1, dtype=torch.int32, device="cuda")
+    out = ap.gemm_fp4(w4, x4, status_flag=flag)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    assert np.array_equal(to_host(out, np.int32), want)
+    if N % 32 == 0:
+        scale = rng.uniform(0.5, 1.5, N).astype(np.float32)
+        bias = rng.uniform(-1, 1, N).astype(np.float32)
+        T = oracle.fold_bn(scale, bias, float(want.mean()), float(want.std()) / 4, 2)
+        res = rng.integers(-300, 300, size=want.shape).astype(np.int32)
+        res_out = torch.full((M, N), -1, dtype=torch.int32, device="cuda")
+        epi = ap.make_epilogue("thresholds", 2, thresholds=to_dev(T), residual_in=to_dev(res), residual_out=res_out)
+        packed = ap.gemm_fp4(w4, x4, epilogue=epi, status_flag=flag)
+        torch.cuda.synchronize()
+        assert int(flag.item()) == 0
+        assert np.array_equal(to_host(res_out, np.int32), want + res)
+        assert np.array_equal(to_host(packed), oracle.requant_pack(want + res, 2, 2, T))
+
+
+@pytest.mark.parametrize("extreme", [False, True])
+def test_fp4_path_long_k_sums_stay_exact(cuda_device, extreme):
+    """K = 262144: sums reach 3 * K = 786432 (all-ones planes) -- fp32 accumulation of these integers is exact
+    below 2^24.  Against a float64 matrix product of the levels (exact at this size)."""
+    import apnn_tc_b200 as ap
+    M, N, K = 256, 448, 262144
+    rng = np.random.default_rng(11 + int(extreme))
+    W, wl = oracle.value_planes(rng, M, K, 2)
+    X, xl = oracle.value_planes(rng, N, K, 2)
+    if extreme:
+        W[:] = 0xFFFFFFFF
+        X[:] = 0xFFFFFFFF
+        wl[:] = 3
+        xl[:] = 3
+    want = (wl.astype(np.float64) @ xl.astype(np.float64).T).astype(np.int64)
+    assert want.max() < 2 ** 24
+    flag = torch.ones(1, dtype=torch.int32, device="cuda")
+    out = ap.gemm_fp4(ap.expand_planes_fp4(to_dev(W)), ap.expand_planes_fp4(to_dev(X)), status_flag=flag)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    assert np.array_equal(to_host(out, np.int32).astype(np.int64), want)
