@@ -6,14 +6,18 @@ the other workloads of the metric in the same JSON line.
 
 Headline step = one GEMM over one batch of synthetic operands resident in HBM as packed bit planes
 (1-bit weights W[1][M][K/32], 2-bit activations X[2][N][K/32], int32 output D[M][N]).  The weights are a
-static operand: their int8 image is made once before the timed region (apnn_expand_planes); every
-step expands a fresh activation batch to int8 and runs the GEMM.  With N > 1 GPUs (torch.distributed.run) the problem is sharded along N: every rank
-owns the same weights and its own 8192 activation rows -- no data-path collective, weak scaling.
+static operand: their tensor-core image is made once before the timed region; every step converts a fresh
+activation batch and runs the GEMM.  Operands of at most two bits are exact e2m1 values, so the default
+path is tcgen05.mma kind::mxf4 with unit scale factors (sums of small integers in fp32: exact, checked
+against the oracle after the timed region); --path int8 times the kind::i8 kernel, whose numbers the line
+also carries as int8_path.  With N > 1 GPUs (torch.distributed.run) the problem is sharded along N: every
+rank owns the same weights and its own 8192 activation rows -- no data-path collective, weak scaling.
 
 Prints ONE JSON line (rank 0).  Keys beyond the usual ones:
   roofline      tensor-pipe roofline of the dominant kernel (tc5_gemm_pair_kernel), timed with its own
-                CUDA events inside the timed steps; peak = the tcgen05 kind::i8 issue-loop peak measured in
-                this run (MEASURED_PEAKS.json's bf16 figure is quoted beside it)
+                CUDA events inside the timed steps; peak = the issue-loop peak of the same tcgen05.mma kind
+                measured in this run (MEASURED_PEAKS.json's bf16 figure is quoted beside it)
+  int8_path     the same step on the kind::i8 kernel (one byte per level), with its own roofline fraction
   cpu_baseline  the reference's own bit-serial compute_ref (compiled unmodified into oracle/_ref) on a
                 bounded sample of rows of the same problem
   e2e           the same metric through the host-buffer C-ABI call (pinned host operands, H2D + GEMM +
@@ -53,7 +57,8 @@ def workload_config(n_gpus: int) -> dict:
         "workload": "gemm_w1a2_M8192_N8192_K8192_int32out",
         "M": M, "N_per_gpu": N, "K": K, "wbits": WBITS, "xbits": XBITS,
         "sharding": "replicated W, N-sharded X (g x 8192 rows), no collective" if n_gpus > 1 else "single GPU",
-        "l2": "4 rotating activation sets; each step rewrites 64 MiB of int8 activations and 256 MiB of output (> 126 MB L2)",
+        "l2": "4 rotating activation sets; each step rewrites the activations' tensor-core image (32 MiB e2m1 or 64 MiB int8) "
+              "and 256 MiB of output (> 126 MB L2)",
         "collective": "none",
     }
 
@@ -249,18 +254,25 @@ def words(torch, shape, gen):
 
 # ----------------------------------------------------------------------------- the headline GEMM
 class GemmPipeline:
-    """The 8192^3 step on device-resident operands: the static W is expanded to int8 once; every step
-    expands that step's activation planes and runs the GEMM, both on the current stream.  (Running the
-    expand of step i+1 on a second stream beside GEMM i was measured: the persistent GEMM's statically
-    scheduled tiles on the SMs that also host expand blocks become stragglers, 0.285 -> 0.300 ms per GEMM,
-    which cancels what the overlap hides.)  expand_pass=False makes the step ONE launch that reads the
-    activation planes as they are (apnn_gemm_w8: the kernel's own warps spread the bits into its
-    shared-memory stages): no int8 activation image in HBM, but 0.45 ms per step."""
+    """The 8192^3 step on device-resident operands.  The weights are a layer's static operand: their tensor-core
+    image is made once before the timed region; every step converts that step's activation planes and runs
+    the GEMM, both on the current stream.  (Running the conversion of step i+1 on a second stream beside
+    GEMM i was measured: the persistent GEMM's statically scheduled tiles on the SMs that also host the
+    conversion blocks become stragglers, which cancels what the overlap hides.)
+
+    path "fp4" (both operands of at most two bits): e2m1 nibble images, tcgen05.mma kind::mxf4 with unit
+    scale factors -- exact, twice the int8 rate.  path "int8": one byte per level, kind::i8.  path
+    "planes": ONE launch, apnn_gemm_w8 spreads the activation planes inside the GEMM kernel (no activation
+    image in HBM; slower)."""
 
     def __init__(self, torch, ap, cabi, dev, rank, wbits=WBITS, xbits=XBITS, algo="tcgen05", epilogue=None, D=None,
-                 expand_pass=True):
+                 path=None):
         self.torch, self.ap, self.cabi, self.algo = torch, ap, cabi, algo
-        self.expand_pass = expand_pass or xbits > 4
+        if path is None:
+            path = "fp4" if (wbits <= 2 and xbits <= 2) else "int8"
+        if path == "planes" and xbits > 4:
+            path = "int8"
+        self.path = path if algo == "tcgen05" else algo
         self.wbits, self.xbits = wbits, xbits
         g = torch.Generator(device=dev).manual_seed(0xA9117C + 1 + rank)
         gw = torch.Generator(device=dev).manual_seed(0xA9117C + 1)  # weights are the same on every rank
@@ -270,27 +282,30 @@ class GemmPipeline:
         self.epilogue = epilogue
         self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
         self.L = cabi.lib()
-        if algo == "tcgen05":
-            self.W8 = torch.empty((M, K), dtype=torch.uint8, device=dev)
-            if self.expand_pass:
-                self.X8 = torch.empty((N, K), dtype=torch.uint8, device=dev)
-            cabi.check(self.L.apnn_expand_planes(torch.cuda.current_stream().cuda_stream, self.W.data_ptr(),
-                                                 self.W8.data_ptr(), M, K, wbits, 0), "expand W")
-        self.launches_per_step = 2 if (algo == "tcgen05" and self.expand_pass) else 1
+        if self.path == "fp4":
+            self.Wt = ap.expand_planes_fp4(self.W)
+            self.Xt = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+        elif self.path in ("int8", "planes"):
+            self.Wt = ap.expand_planes(self.W)
+            if self.path == "int8":
+                self.Xt = torch.empty((N, K), dtype=torch.uint8, device=dev)
+        self.launches_per_step = 2 if self.path in ("fp4", "int8") else 1
         torch.cuda.synchronize()
 
     def step(self, i: int, ev=None):
-        torch = self.torch
         X = self.Xs[i % N_OPERAND_SETS]
-        if self.algo == "tcgen05" and self.expand_pass:
-            self.cabi.check(self.L.apnn_expand_planes(torch.cuda.current_stream().cuda_stream, X.data_ptr(),
-                                                      self.X8.data_ptr(), N, K, self.xbits, 0), "expand X")
+        if self.path == "fp4":
+            self.ap.expand_planes_fp4(X, out=self.Xt)
+        elif self.path == "int8":
+            self.ap.expand_planes(X, out=self.Xt)
         if ev is not None:
             ev[0].record()
-        if self.algo == "tcgen05" and self.expand_pass:
-            self.ap.gemm_i8(self.W8, self.X8, self.D, status_flag=self.flag, epilogue=self.epilogue)
-        elif self.algo == "tcgen05":
-            self.ap.gemm_w8(self.W8, X, self.D, status_flag=self.flag, epilogue=self.epilogue)
+        if self.path == "fp4":
+            self.ap.gemm_fp4(self.Wt, self.Xt, self.D, status_flag=self.flag, epilogue=self.epilogue)
+        elif self.path == "int8":
+            self.ap.gemm_i8(self.Wt, self.Xt, self.D, status_flag=self.flag, epilogue=self.epilogue)
+        elif self.path == "planes":
+            self.ap.gemm_w8(self.Wt, X, self.D, status_flag=self.flag, epilogue=self.epilogue)
         else:
             self.ap.apmm(self.W, X, self.D, algo=self.algo)
         if ev is not None:
@@ -361,7 +376,7 @@ def run_ours(args) -> None:
         return tuple(float(x) for x in t)
 
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-    pipe = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo, expand_pass=not args.planes_in_kernel)
+    pipe = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo, path=args.path or None)
     for i in range(2):  # keep the device busy while the sampler thread starts
         pipe.step(i)
     elapsed_ms, kernel_ms, clocks = timed_gemm_steps(torch, dist, pipe, args.steps, args.warmup, sampler)
@@ -404,6 +419,18 @@ def run_ours(args) -> None:
                     "limit to set the clock",
         }
 
+    # ---- the same step on the int8 path (kind::i8), for comparison with the 4-bit floating-point headline
+    int8_block = None
+    if algo == "tcgen05" and pipe.path == "fp4" and not args.profile:
+        p8 = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo, path="int8")
+        e8, k8, _ = timed_gemm_steps(torch, dist, p8, args.steps, args.warmup, None)
+        e8, k8 = max_over_ranks(e8, k8)
+        int8_block = {"ms_per_step": e8 / args.steps, "tops": world * flops_step / (e8 / args.steps * 1e-3) / 1e12,
+                      "kernel_ms": k8, "kernel_tops": flops_step / (k8 * 1e-3) / 1e12,
+                      "kernel": "tc5_gemm_pair_kernel (cta_group::2, kind::i8)"}
+        del p8
+        torch.cuda.empty_cache()
+
     # ---- end-to-end through the host-buffer C-ABI call (pinned host operands, D2H of the result)
     e2e_steps = max(2, min(args.steps, 5))
     hW = torch.empty((WBITS, M, K // 32), dtype=torch.int32).pin_memory()
@@ -432,7 +459,7 @@ def run_ours(args) -> None:
 
     # ---- the other workloads of the metric
     Wkeep, Xkeep = pipe.W, pipe.Xs[0]
-    two_launch_step, launches_per_step = pipe.expand_pass, pipe.launches_per_step
+    step_path, launches_per_step = pipe.path, pipe.launches_per_step
     del pipe
     torch.cuda.empty_cache()
     resnet = resnet_block(torch, dist, dev, world, rank, args)
@@ -450,14 +477,17 @@ def run_ours(args) -> None:
 
     # ---- roofline of the dominant kernel
     peaks = measured_peaks()
-    kind = {"tcgen05": 0, "imma": 1, "bmma": 2}[algo]
-    peak_ops = probe_peak(torch, _cabi, kind, 20000 if kind == 0 else 4000)
+    kind = {"tcgen05": 5 if step_path == "fp4" else 0, "imma": 1, "bmma": 2}[algo]
+    peak_ops = probe_peak(torch, _cabi, kind, 20000 if kind in (0, 5) else 4000)
+    peak_i8 = probe_peak(torch, _cabi, 0, 20000) if kind == 5 else peak_ops
     ops_launch = flops_step * (WBITS * XBITS if algo == "bmma" else 1)  # bit-ops for the b1 path
     achieved = ops_launch / (kernel_ms * 1e-3) / 1e12
-    full_shape_one_gpu = world == 1 and algo == "tcgen05"
+    full_shape_one_gpu = world == 1 and algo == "tcgen05" and step_path == "int8"
+    operand_bytes = (M * K + N * K) // 2 if step_path == "fp4" else M * K + N * K
     roofline = {
-        "bound": "tensor", "kernel": {"tcgen05": "tc5_gemm_pair_kernel (cta_group::2)", "imma": "plane_core_kernel<u8>",
-                                      "bmma": "plane_core_kernel<b1>"}[algo],
+        "bound": "tensor", "kernel": {"tcgen05": "tc5_gemm_pair_kernel (cta_group::2, kind::mxf4: e2m1 operands, unit scales)"
+                                      if step_path == "fp4" else "tc5_gemm_pair_kernel (cta_group::2, kind::i8)",
+                                      "imma": "plane_core_kernel<u8>", "bmma": "plane_core_kernel<b1>"}[algo],
         "achieved": achieved, "peak": peak_ops / 1e12, "unit": "TOP/s" if algo != "bmma" else "Tbitop/s",
         "frac": achieved / (peak_ops / 1e12),
         "peak_source": "issue-loop peak of this instruction measured in this run (apnn_probe_peak)",
@@ -468,8 +498,11 @@ def run_ours(args) -> None:
         "traffic_source": ("constant from an earlier capture, not measured in this run: dram__bytes_read.sum + "
                            "dram__bytes_write.sum per launch, profiles/tc5_gemm_pair_kernel_gemm_w1a2_8192.md")
         if full_shape_one_gpu else None,
-        "algorithmic_bytes_per_launch": M * K + N * K + 4 * M * N,
+        "algorithmic_bytes_per_launch": operand_bytes + 4 * M * N,
     }
+    if int8_block is not None:
+        int8_block["kernel_frac_of_i8_probe_peak"] = int8_block["kernel_tops"] / (peak_i8 / 1e12)
+        int8_block["i8_probe_peak_tops"] = peak_i8 / 1e12
     if sustained is not None:
         sustained["kernel_frac_of_probe_peak"] = sustained["kernel_tops"] / (peak_ops / 1e12)
 
@@ -517,14 +550,18 @@ def run_ours(args) -> None:
     line = {
         "metric": METRIC, "value": world * flops_step / (ms_per_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "u8 operands, int32 accumulate (exact)", "data": "synthetic",
-        "config": workload_config(world), "algo": algo,
-        "step": ("activation expand (planes -> int8) + tcgen05 GEMM" if two_launch_step else
-                 "one launch: tcgen05 GEMM reading the packed activation planes (bits spread to int8 inside the kernel)")
-                + "; the static weights' int8 image is made once before the timed region",
+        "scaling": "weak", "vs_baseline": None, "dtype": {"fp4": "e2m1 operands holding the integer levels, fp32 accumulate (sums of small integers: exact), int32 out",
+                                                     "int8": "u8/s8 operands, int32 accumulate (exact)",
+                                                     "planes": "u8/s8 operands, int32 accumulate (exact)"}.get(step_path, "int32 (exact)"),
+        "data": "synthetic", "config": workload_config(world), "algo": algo, "path": step_path,
+        "step": {"fp4": "activation planes -> e2m1 nibbles, then the tcgen05 kind::mxf4 GEMM",
+                 "int8": "activation planes -> int8 rows, then the tcgen05 kind::i8 GEMM",
+                 "planes": "one launch: tcgen05 kind::i8 GEMM reading the packed activation planes (bits spread inside the kernel)"
+                 }.get(step_path, "one launch of the warp-level kernel")
+                + "; the static weights' tensor-core image is made once before the timed region",
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
         "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
-        "sustained": sustained, "resnet18": resnet, "allgather": gather,
+        "sustained": sustained, "int8_path": int8_block, "resnet18": resnet, "allgather": gather,
         "pairs_8192": pairs, "m64_sweep": sweep, "conv_c3": conv,
     }
     print(json.dumps(line), flush=True)
@@ -662,13 +699,13 @@ def allgather_block(torch, dist, ap, cabi, dev, world, rank, args):
 
 
 def pairs_block(torch, ap, cabi, dev, steps):
-    """The other bit pairs of the sweep at 8192^3 on the same kernel (one int8 byte per level whatever its
-    width): kernel time by events, effective TOPS."""
+    """The other bit pairs of the sweep at 8192^3: w2a2 on the 4-bit floating-point path like w1a2, w1a3 and
+    w1a4 on the int8 path (one byte per level whatever its width); kernel time by events, effective TOPS."""
     out = {}
     for wb, xb in ((1, 3), (1, 4), (2, 2)):
         pipe = GemmPipeline(torch, ap, cabi, dev, 0, wbits=wb, xbits=xb)
         ms, kms, _ = timed_gemm_steps(torch, None, pipe, steps, 3)
-        out[f"w{wb}a{xb}"] = {"ms_per_step": ms / steps, "tops": 2.0 * M * N * K / (ms / steps * 1e-3) / 1e12,
+        out[f"w{wb}a{xb}"] = {"path": pipe.path, "ms_per_step": ms / steps, "tops": 2.0 * M * N * K / (ms / steps * 1e-3) / 1e12,
                               "kernel_ms": kms, "kernel_tops": 2.0 * M * N * K / (kms * 1e-3) / 1e12}
         del pipe
         torch.cuda.empty_cache()
@@ -945,8 +982,9 @@ def main() -> None:
     ap_.add_argument("--algo", default="tcgen05", choices=["tcgen05", "imma", "bmma"])
     ap_.add_argument("--profile", action="store_true",
                      help="timed GEMM steps only (no e2e, probe, CPU baseline or other blocks): the command ncu captures")
-    ap_.add_argument("--planes-in-kernel", action="store_true",
-                     help="headline step as one launch (apnn_gemm_w8: the GEMM kernel spreads the activation planes itself)")
+    ap_.add_argument("--path", default="", choices=["", "fp4", "int8", "planes"],
+                     help="tensor path of the headline step: fp4 (default for w1a2: e2m1 operands, kind::mxf4, exact), int8 "
+                          "(kind::i8), planes (one launch, apnn_gemm_w8 spreads the activation planes in the GEMM kernel)")
     ap_.add_argument("--quick", action="store_true", help="skip the N = 1 sweep blocks (pairs_8192, m64_sweep, conv_c3)")
     ap_.add_argument("--workload", default="gemm", choices=["gemm", "resnet18", "vgg_variant", "alexnet"],
                      help="gemm (default: the headline line with every block) or one whole w1a2 network (images/s)")
