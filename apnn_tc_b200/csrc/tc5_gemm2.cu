@@ -51,6 +51,14 @@ constexpr int THR_BYTES_PER_WARP = 5 * 1024;
 constexpr int WORD_BYTES_PER_WARP = 2 * 32 * 8 * 4;  // packed outputs of up to 2 bits: 8 words per row and plane, staged per tile
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 1024 + 4 * THR_BYTES_PER_WARP + 4 * WORD_BYTES_PER_WARP;
 static_assert(32 * 36 * 4 <= THR_BYTES_PER_WARP, "padded transposition block");
+// MX: a stage is 16 KiB of A and 14 KiB of B.  With the deep ring (seven stages) the epilogue keeps 4 KiB per warp
+// (thresholds of a 224-wide tile, or the block of a bulk tensor store) and the layout fills the 227 KiB of an SM
+// exactly, so the dynamic shared memory must itself start on a 1024-byte boundary (checked in the kernel).
+constexpr int MX_STAGE_BYTES = (HALF + 112) * BK;
+constexpr int MX_DEEP_STAGES = 7;
+constexpr int MX_DEEP_EPI_BYTES = 4096;
+constexpr int SMEM_BYTES_MX = MX_DEEP_STAGES * MX_STAGE_BYTES + 1024 + 4 * MX_DEEP_EPI_BYTES;
+static_assert(SMEM_BYTES_MX <= 232448 && SMEM_BYTES_MX >= 6 * MX_STAGE_BYTES + 1024 + 4 * THR_BYTES_PER_WARP, "MX layouts");
 constexpr int THREADS = 192;
 // B-from-planes instantiations
 constexpr int EXPAND_WARPS = 8;                      // warps 6..13, 16 rows of the CTA's B half each
@@ -78,6 +86,7 @@ struct PairParams {
   int kwords;
   int x_signed;    // one plane holding -1 / +1
   int tma_out;     // int32 output with one destination and N % 4 == 0: 32 x 32 blocks leave by bulk tensor stores
+  int stages;      // MX: ring depth, 7 (4 KiB of epilogue staging per warp) or 6 (5 KiB: the padded transposition block)
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -209,10 +218,18 @@ template <int XP, int XG = 4, bool MX = false>
 __global__ void __launch_bounds__(XP ? THREADS_XP : THREADS, 1)
 tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_d, const PairParams p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t bars = base + STAGES * STAGE_BYTES;
+  // MX fills the SM's shared memory exactly and has no room for alignment slack
+  const uint32_t base = MX ? raw : ((raw + 1023u) & ~1023u);
+  const int nst = MX ? p.stages : (XP ? 0 : STAGES);                     // depth of the single ring
+  const uint32_t stage_bytes = MX ? MX_STAGE_BYTES : STAGE_BYTES;
+  const uint32_t bars = base + (MX ? (uint32_t)p.stages * MX_STAGE_BYTES : STAGES * STAGE_BYTES);
+  const uint32_t epi_bytes = (MX && p.stages == MX_DEEP_STAGES) ? MX_DEEP_EPI_BYTES : THR_BYTES_PER_WARP;
+  if (MX && (raw & 1023u) != 0) {   // never seen; the swizzled tiles and the bulk stores need the alignment
+    if (threadIdx.x == 0) atomicExch(p.error_flag, 9);
+    return;
+  }
   // XP == 0: one ring of STAGES stages (A tile then B tile); XP > 0: NA ring slots of A tiles, then NB of B tiles
   // tile width over the pair: 256, or 224 for MX (two accumulators and the scale factors share the 512 TMEM columns)
   constexpr int TN = MX ? 224 : 256;
@@ -223,9 +240,9 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   constexpr int KQ_LANES = 32 / XGROUP;      // lanes (rows) per K block of a warp-wide load
   constexpr int XTASKS = 16 / KQ_LANES;      // (row, K block) pieces a thread spreads per group
   static_assert((NB_XP & (NB_XP - 1)) == 0 && XTASKS >= 1, "slot arithmetic below");
-  constexpr int NA = XP ? NA_XP : STAGES;
+  constexpr int NA = XP ? NA_XP : (MX ? MX_DEEP_STAGES : STAGES);   // barriers laid out for the deepest ring
   constexpr int NB = XP ? NB_XP : 0;
-  constexpr int A_SLOT_BYTES = XP ? HALF * BK : STAGE_BYTES;
+  constexpr int A_SLOT_BYTES = HALF * BK;   // XP: size of an A ring slot
   constexpr int RING_BARS = 2 * NA + 2 * NB;
   auto full_bar = [&](int s) { return bars + 8u * s; };                       // A (XP == 0: A and B) landed
   auto empty_bar = [&](int s) { return bars + 8u * (NA + s); };
@@ -291,20 +308,20 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   if (warp == 0) {
     // ---------------- TMA producer (one per CTA) ----------------
     if (lane == 0) {
-      uint32_t it = 0;
+      const int ring = XP ? NA : nst;
+      int s = 0;          // ring slot and its phase, stepped instead of divided: the ring depth may be a run-time value
+      uint32_t ph = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
         pair_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int arow = tm * TILE_M + (int)rank * HALF;
         const int brow = tn * TN + (int)rank * BHALF;
-        for (int kb = 0; kb < p.kblocks; kb++, it++) {
-          const int s = it % NA;
-          const uint32_t ph = (it / NA) & 1u;
+        for (int kb = 0; kb < p.kblocks; kb++, s = (s + 1 == ring) ? 0 : s + 1, ph ^= (s == 0) ? 1u : 0u) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u)) { ok = false; break; }
           const uint32_t leader_full = map_to_cta(full_bar(s), 0);
           if (rank == 0) mbar_expect_tx(full_bar(s), XP ? 2 * A_SLOT_BYTES : 2 * (HALF + BHALF) * BK);  // both CTAs' bytes
-          const uint32_t sa = base + s * A_SLOT_BYTES;
+          const uint32_t sa = base + s * (XP ? A_SLOT_BYTES : stage_bytes);
           tma_load_2d_pair(sa, &map_a, kb * BK, arow, leader_full);
           if (XP == 0) tma_load_2d_pair(sa + HALF * BK, &map_b, kb * BK, brow, leader_full);
         }
@@ -316,6 +333,9 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     if (lane == 0 && rank == 0) {
       uint32_t it = 0;
       uint32_t tl = 0;
+      const int ring = XP ? NA : nst;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, tl++) {
         const uint32_t acc = tl & 1u;
@@ -323,15 +343,13 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TN;
-        for (int kb = 0; kb < p.kblocks; kb++, it++) {
-          const int s = it % NA;
-          const uint32_t ph = (it / NA) & 1u;
+        for (int kb = 0; kb < p.kblocks; kb++, it++, s = (s + 1 == ring) ? 0 : s + 1, ph ^= (s == 0) ? 1u : 0u) {
           const int t = XP ? (int)(it % NB_XP) : 0;
           if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
           // the peer's expanders wrote their half of the B tile with ordinary stores: acquire at cluster scope
           if (XP && !mbar_wait_cluster_acquire(fullb_bar(t), (it / NB_XP) & 1u)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = base + s * A_SLOT_BYTES;
+          const uint32_t sa = base + s * (XP ? A_SLOT_BYTES : stage_bytes);
           const uint64_t adesc = make_smem_desc(sa);
           const uint64_t bdesc = make_smem_desc(XP ? b_ring + t * (HALF * BK) : sa + HALF * BK);
 #pragma unroll
@@ -457,11 +475,11 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     bool ok = true;
     const int nl = (1 << p.out_bits) - 1;
     const bool thr_staged = p.out_mode == OUT_THRESHOLDS && nl <= 3;
-    int4* thr_s = reinterpret_cast<int4*>(thr_stage + (warp - 2) * THR_BYTES_PER_WARP);
+    int4* thr_s = reinterpret_cast<int4*>(thr_stage + (warp - 2) * epi_bytes);
     // Packed outputs of one or two bits: a thread's eight words of a tile row (one per 32-column chunk) are
     // collected here and leave as one 32-byte store per plane and destination -- whole sectors for HBM and
     // for NVLink instead of eight scattered 4-byte stores.
-    uint32_t* word_s = reinterpret_cast<uint32_t*>(thr_stage + 4 * THR_BYTES_PER_WARP + (warp - 2) * WORD_BYTES_PER_WARP);
+    uint32_t* word_s = reinterpret_cast<uint32_t*>(thr_stage + 4 * THR_BYTES_PER_WARP + (warp - 2) * WORD_BYTES_PER_WARP);   // unused by MX
     const bool words_staged = !MX && p.out_mode != OUT_INT32 && p.out_bits <= 2 && ((p.N >> 5) & 3) == 0;   // eight words per tile row
     int staged_tn = -1;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, tl++) {
@@ -683,13 +701,14 @@ bool make_half_map(CUtensorMap* map, const void* base, long long rows, long long
 template <int XP, int XG = 4, bool MX = false>
 cudaError_t launch_pair(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d,
                         const PairParams& p, int pairs) {
-  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel<XP, XG, MX>), SMEM_BYTES);
+  constexpr int smem_bytes = MX ? SMEM_BYTES_MX : SMEM_BYTES;
+  cudaError_t e = ensure_max_smem(reinterpret_cast<const void*>(tc5_gemm_pair_kernel<XP, XG, MX>), smem_bytes);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cfg.blockDim = dim3(XP ? THREADS_XP : THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -833,6 +852,10 @@ apnn_status tc5_gemm_fp4_pair(cudaStream_t s, const uint8_t* A4, const uint8_t* 
   const int sms = device_sm_count();
   long long tiles = (long long)p.tiles_m * p.tiles_n;
   int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
+  // the deep ring leaves 4 KiB of staging per epilogue warp: enough for everything but the padded transposition
+  // block of int32 tiles that go to several destinations
+  static const bool deep = [] { const char* v = getenv("APNN_MX_STAGES"); return v && v[0] == '7'; }();
+  p.stages = (deep && (p.tma_out || p.out_mode != APNN_OUT_INT32)) ? MX_DEEP_STAGES : 6;
   cudaError_t e = launch_pair<0, 4, true>(s, map_a, map_b, map_d, p, pairs);
   if (e != cudaSuccess) return cuda_fail(e, "tc5_gemm_fp4_pair launch");
   return APNN_OK;

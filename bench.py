@@ -48,7 +48,10 @@ METRIC = "w1a2_gemm_effective_tops"
 UNIT = "TOPS"  # 2*M*N*K / t, counted once whatever the plane count (the reference's formula)
 N_OPERAND_SETS = 4
 RESNET_GLOBAL_BATCH = 1024
-TRAFFIC_8192 = 578794000   # dram__bytes_read.sum + dram__bytes_write.sum per launch of tc5_gemm_pair_kernel at 8192^3
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of tc5_gemm_pair_kernel at 8192^3, from the ncu captures
+# summarised in profiles/ (kind::i8: before its tiles left by bulk tensor stores)
+TRAFFIC_8192 = {"int8": (578794000, "profiles/tc5_gemm_pair_kernel_gemm_w1a2_8192.md"),
+                "fp4": (384500000, "profiles/tc5_gemm_pair_kernel_mxf4_gemm_w1a2_8192.md")}
 
 
 def workload_config(n_gpus: int) -> dict:
@@ -482,7 +485,7 @@ def run_ours(args) -> None:
     peak_i8 = probe_peak(torch, _cabi, 0, 20000) if kind == 5 else peak_ops
     ops_launch = flops_step * (WBITS * XBITS if algo == "bmma" else 1)  # bit-ops for the b1 path
     achieved = ops_launch / (kernel_ms * 1e-3) / 1e12
-    full_shape_one_gpu = world == 1 and algo == "tcgen05" and step_path == "int8"
+    full_shape_one_gpu = world == 1 and algo == "tcgen05" and step_path in TRAFFIC_8192
     operand_bytes = (M * K + N * K) // 2 if step_path == "fp4" else M * K + N * K
     roofline = {
         "bound": "tensor", "kernel": {"tcgen05": "tc5_gemm_pair_kernel (cta_group::2, kind::mxf4: e2m1 operands, unit scales)"
@@ -494,9 +497,9 @@ def run_ours(args) -> None:
         "bf16_tflops_measured": peaks.get("bf16_tflops"), "bf16_tflops_sustained": peaks.get("bf16_tflops_sustained"),
         "frac_of_2x_bf16_burst": achieved / (2 * peaks["bf16_tflops"]) if peaks.get("bf16_tflops") else None,
         "kernel_ms": kernel_ms, "algorithmic_ops_per_launch": ops_launch,
-        "traffic": TRAFFIC_8192 if full_shape_one_gpu else None,
+        "traffic": TRAFFIC_8192[step_path][0] if full_shape_one_gpu else None,
         "traffic_source": ("constant from an earlier capture, not measured in this run: dram__bytes_read.sum + "
-                           "dram__bytes_write.sum per launch, profiles/tc5_gemm_pair_kernel_gemm_w1a2_8192.md")
+                           "dram__bytes_write.sum per launch, " + TRAFFIC_8192[step_path][1])
         if full_shape_one_gpu else None,
         "algorithmic_bytes_per_launch": operand_bytes + 4 * M * N,
     }
