@@ -674,7 +674,7 @@ def allgather_block(torch, dist, ap, cabi, dev, world, rank, args):
     ms = timed(pipe, sg.barrier)   # every rank's tiles have landed before the next step overwrites them
     check(sg.buffer, sg.local_slot())
     egress = (world - 1) * M * N * 4
-    out["fused_int32"] = {"ms_per_step": ms, "bytes_leaving_each_gpu": egress, "egress_gb_s": egress / (ms * 1e-3) / 1e9,
+    out["fused_int32"] = {"path": pipe.path, "ms_per_step": ms, "bytes_leaving_each_gpu": egress, "egress_gb_s": egress / (ms * 1e-3) / 1e9,
                           "tops": world * 2.0 * M * N * K / (ms * 1e-3) / 1e12, "verified_against_nccl": True}
     # int32 slices, NCCL after the GEMM
     gathered = torch.empty((world, M, N), dtype=torch.int32, device=dev)
@@ -686,12 +686,14 @@ def allgather_block(torch, dist, ap, cabi, dev, world, rank, args):
     torch.cuda.empty_cache()
     # the 2-bit packed output [2][M][N/32] (low bits, the reference's fused decompose kernels), fused
     sgp = shard.SymmetricGather(2 * M, N // 32, dev)
-    pipe3 = GemmPipeline(torch, ap, cabi, dev, rank, D=sgp.local_slot(),
+    # (int8 kernel: its 256-wide tiles give every row 32 contiguous bytes of packed words, one store per destination;
+    # the 224-wide tiles of the e2m1 kernel would scatter 4-byte words over NVLink)
+    pipe3 = GemmPipeline(torch, ap, cabi, dev, rank, D=sgp.local_slot(), path="int8",
                          epilogue=ap.make_epilogue("lowbits", 2, peer_out=sgp.peer_destinations()))
     ms = timed(pipe3, sgp.barrier)
     check(sgp.buffer, sgp.local_slot())
     egress = (world - 1) * 2 * M * (N // 32) * 4
-    out["fused_packed_2bit"] = {"ms_per_step": ms, "bytes_leaving_each_gpu": egress,
+    out["fused_packed_2bit"] = {"path": "int8", "ms_per_step": ms, "bytes_leaving_each_gpu": egress,
                                 "egress_gb_s": egress / (ms * 1e-3) / 1e9,
                                 "tops": world * 2.0 * M * N * K / (ms * 1e-3) / 1e12, "verified_against_nccl": True}
     out["link"] = "NVLink 5 through NVSwitch; 770 GB/s per direction measured peer copy on this pool (900 nominal)"
