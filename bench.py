@@ -428,9 +428,18 @@ def run_ours(args) -> None:
         p8 = GemmPipeline(torch, ap, _cabi, dev, rank, algo=algo, path="int8")
         e8, k8, _ = timed_gemm_steps(torch, dist, p8, args.steps, args.warmup, None)
         e8, k8 = max_over_ranks(e8, k8)
+        # all 2^26 outputs of one operand set, e2m1 path against int8 path (same synthetic weights, this rank's activations)
+        p8.Xs[0].copy_(pipe.Xs[0])
+        pipe.step(0)
+        p8.step(0)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(pipe.D, p8.D))
+        if not same:
+            raise SystemExit("the e2m1 path and the int8 path disagree")
         int8_block = {"ms_per_step": e8 / args.steps, "tops": world * flops_step / (e8 / args.steps * 1e-3) / 1e12,
                       "kernel_ms": k8, "kernel_tops": flops_step / (k8 * 1e-3) / 1e12,
-                      "kernel": "tc5_gemm_pair_kernel (cta_group::2, kind::i8)"}
+                      "kernel": "tc5_gemm_pair_kernel (cta_group::2, kind::i8)",
+                      "e2m1_output_equal_on_all_elements": same}
         del p8
         torch.cuda.empty_cache()
 
