@@ -1040,6 +1040,26 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               if (col0 + j < p.N) D[j] = (int32_t)v[j];
           }
         } else if (!C_INT32 && row_ok) {
+          if constexpr (C_I8THR) {
+            // thresholds -> the next layer's int8 operand in one pass: element j of this 32-column group goes to byte
+            // 4*((31-j)&7) + ((31-j)>>3) (the order apnn_expand_planes writes); its level, the number of thresholds it
+            // reaches, is added to that byte by up to three predicated adds (a byte never exceeds 3)
+            uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              const int4 q4 = thr_s[j];
+              const int x = (int)v[j];
+              const uint32_t inc = 1u << (8 * ((31 - j) >> 3));
+              if (x >= q4.x) r[(31 - j) & 7] += inc;
+              if (x >= q4.y) r[(31 - j) & 7] += inc;
+              if (x >= q4.z) r[(31 - j) & 7] += inc;
+            }
+            uint8_t* O8 = reinterpret_cast<uint8_t*>(p.out) + row * p.N + col0;
+            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(O8), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                         "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                         : "memory");
+            continue;
+          }
           // packed modes need N % 32 == 0, so this word is whole
           uint32_t lv[32];
           if (!C_I8THR && p.out_mode == OUT_LOWBITS) {
