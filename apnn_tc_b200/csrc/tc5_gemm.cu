@@ -928,9 +928,15 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (whole) {
             // int32 rows move through the transposition block so that global accesses are
             // 64 contiguous bytes per row, 8 rows per instruction
-            auto lo16 = [](uint32_t w) { return (uint32_t)(int)(short)(w & 0xffffu); };
-            auto hi16 = [](uint32_t w) { return (uint32_t)((int)w >> 16); };
-            auto sat16 = [](uint32_t x) { return (uint32_t)min(max((int)x, -32768), 32767) & 0xffffu; };
+            // acc + the signed low / high half of w in one instruction each (a two-way dot product with (1, 0) / (0, 1))
+            auto add_lo16 = [](uint32_t acc, uint32_t w) { return (uint32_t)__dp2a_lo((int)w, 0x00000001, (int)acc); };
+            auto add_hi16 = [](uint32_t acc, uint32_t w) { return (uint32_t)__dp2a_lo((int)w, 0x00000100, (int)acc); };
+            // two int32 -> two saturated int16 in one word (lo in the low half)
+            auto sat_pack = [](uint32_t lo, uint32_t hi) {
+              uint32_t d;
+              asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(d) : "r"((int)hi), "r"((int)lo));
+              return d;
+            };
             if (p.residual_in != nullptr && (C_RES16 || p.res16_in)) {
 #pragma unroll
               for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(xp + swz(8 * i + sub_r, grp)) = rin[i];
@@ -938,8 +944,10 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
               for (int j = 0; j < 4; j++) {
                 const uint4 x = *reinterpret_cast<const uint4*>(xp + swz(lane, j));
-                v[8 * j] += lo16(x.x); v[8 * j + 1] += hi16(x.x); v[8 * j + 2] += lo16(x.y); v[8 * j + 3] += hi16(x.y);
-                v[8 * j + 4] += lo16(x.z); v[8 * j + 5] += hi16(x.z); v[8 * j + 6] += lo16(x.w); v[8 * j + 7] += hi16(x.w);
+                v[8 * j] = add_lo16(v[8 * j], x.x); v[8 * j + 1] = add_hi16(v[8 * j + 1], x.x);
+                v[8 * j + 2] = add_lo16(v[8 * j + 2], x.y); v[8 * j + 3] = add_hi16(v[8 * j + 3], x.y);
+                v[8 * j + 4] = add_lo16(v[8 * j + 4], x.z); v[8 * j + 5] = add_hi16(v[8 * j + 5], x.z);
+                v[8 * j + 6] = add_lo16(v[8 * j + 6], x.w); v[8 * j + 7] = add_hi16(v[8 * j + 7], x.w);
               }
               __syncwarp();
               if (c + 2 < c_end) fetch_residual(cur, c + 2);
@@ -966,8 +974,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
               for (int j = 0; j < 4; j++)
                 *reinterpret_cast<uint4*>(xp + swz(lane, j)) =
-                    make_uint4(sat16(v[8 * j]) | (sat16(v[8 * j + 1]) << 16), sat16(v[8 * j + 2]) | (sat16(v[8 * j + 3]) << 16),
-                               sat16(v[8 * j + 4]) | (sat16(v[8 * j + 5]) << 16), sat16(v[8 * j + 6]) | (sat16(v[8 * j + 7]) << 16));
+                    make_uint4(sat_pack(v[8 * j], v[8 * j + 1]), sat_pack(v[8 * j + 2], v[8 * j + 3]),
+                               sat_pack(v[8 * j + 4], v[8 * j + 5]), sat_pack(v[8 * j + 6], v[8 * j + 7]));
               __syncwarp();
 #pragma unroll
               for (int i = 0; i < 4; i++) {
