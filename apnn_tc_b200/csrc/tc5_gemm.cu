@@ -177,6 +177,10 @@ struct Tc5Params {
   // descriptors, so the activations enter shared memory once per tile instead of once per tap.
   int flat_wp;           // Wp
   int flat_hpwp;         // Hp * Wp
+  // floor(n / flat_hpwp) and floor(n / flat_wp) for 0 <= n < 2^31 as (n * magic) >> shift: the epilogue warps turn
+  // a tile row into (image, row, column) once per tile, and a division costs them some twenty instructions
+  unsigned long long magic_hpwp, magic_wp;
+  int shift_hpwp, shift_wp;
   int flat_nblk;         // row blocks per channel block: 1 (all taps in one box) or R (one per filter row)
   int flat_blk_rows;     // rows per block (multiple of 8, at most 256)
   int flat_na, flat_nb;  // A-buffer ring depth; B-tile ring depth (0 when the filter is resident)
@@ -214,9 +218,9 @@ __device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, in
   int b, ho, wo;
   if (p.is_conv == 2) {
     const int pos = tm * BM + r;   // below 2^31: the host checks the flattened row count
-    b = pos / p.flat_hpwp;
+    b = (int)(((unsigned long long)(uint32_t)pos * p.magic_hpwp) >> p.shift_hpwp);
     const int rem = pos - b * p.flat_hpwp;
-    ho = rem / p.flat_wp;
+    ho = (int)(((unsigned long long)(uint32_t)rem * p.magic_wp) >> p.shift_wp);
     wo = rem - ho * p.flat_wp;
     d.valid = b < p.Bn && ho < p.Ho && wo < p.Wo;
   } else {
@@ -240,6 +244,11 @@ __device__ __forceinline__ RowDst row_destination(const Tc5Params& p, int tm, in
 }
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  if (tiles_n == 1) {   // one tile column: the band walk below is the identity
+    tm = tile;
+    tn = 0;
+    return;
+  }
   const int band = GROUP_M * tiles_n;
   const int g = tile / band;
   const int first = g * GROUP_M;
@@ -1194,6 +1203,15 @@ bool make_activation_map(CUtensorMap* map, const void* base, int B, int Hp, int 
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// floor(n / d) == (n * magic) >> shift for every 0 <= n < 2^31 (d >= 1): with L = ceil(log2 d),
+// magic = floor(2^(31+L) / d) + 1 and shift = 31 + L; magic <= 2^32, the product stays below 2^63.
+void division_magic(int d, unsigned long long* magic, int* shift) {
+  int L = 0;
+  while ((1ll << L) < d) L++;
+  *shift = 31 + L;
+  *magic = ((1ull << (31 + L)) / (unsigned long long)d) + 1ull;
+}
+
 // Shared-memory plan: keep the whole B operand resident when the problem has one tile column
 // and its K blocks leave room for at least three A stages; otherwise a ring of A+B stages.
 template <int BN, int BKB, bool PAIR>
@@ -1703,6 +1721,8 @@ apnn_status tc5_conv_i8(cudaStream_t s, const uint8_t* X8, const uint8_t* W8, vo
       p.is_conv = 2;
       p.flat_wp = Wp;
       p.flat_hpwp = Hp * Wp;
+      division_magic(Wp, &p.magic_wp, &p.shift_wp);
+      division_magic(Hp * Wp, &p.magic_hpwp, &p.shift_hpwp);
       p.tiles_m = (int)flat_tiles_m;
       p.flat_nblk = nblk;
       p.flat_blk_rows = blk_rows;
