@@ -559,3 +559,28 @@ def test_fp4_path_long_k_sums_stay_exact(cuda_device, extreme):
     torch.cuda.synchronize()
     assert int(flag.item()) == 0
     assert np.array_equal(to_host(out, np.int32).astype(np.int64), want)
+
+
+@pytest.mark.parametrize("bits,signed", [(1, False), (1, True), (2, False)])
+def test_fp4_nibble_image(cuda_device, bits, signed):
+    """apnn_expand_planes_fp4 writes what the header says: two e2m1 codes per byte, the element whose bit sits
+    at position p of a 32-k plane word in nibble p >> 2 of output word p & 3, levels 0..3 as 0 / 1 / 2 / 3 and
+    a signed plane as -1 / +1."""
+    import apnn_tc_b200 as ap
+    rows, K = 37, 512
+    rng = np.random.default_rng(40 + bits + int(signed))
+    P, lv = oracle.value_planes(rng, rows, K, bits)
+    img = ap.expand_planes_fp4(to_dev(P), signed=signed).cpu().numpy()          # [rows, K/2] bytes
+    assert img.shape == (rows, K // 2)
+    e2m1 = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.0, -0.5, -1, -1.5, -2, -3, -4, -6])
+    words = img.reshape(rows, K // 32, 4, 4).astype(np.uint32)                      # [row][group][word q][byte]
+    w32 = words[..., 0] | (words[..., 1] << 8) | (words[..., 2] << 16) | (words[..., 3] << 24)
+    got = np.zeros((rows, K // 32, 32))
+    for q in range(4):
+        for i in range(8):
+            got[:, :, 4 * i + q] = e2m1[(w32[:, :, q] >> (4 * i)) & 15]             # bit position p = 4*i + q
+    # element j of a 32-k group sits in bit 31 - j of the plane word (the packed layout of the reference)
+    want = lv.reshape(rows, K // 32, 32)[:, :, ::-1].astype(np.float64)
+    if signed:
+        want = 2 * want - 1
+    assert np.array_equal(got, want)
