@@ -669,16 +669,29 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 // group of 32 k, the same for both operands.
 __global__ void __launch_bounds__(256) expand_nibbles_kernel(const uint32_t* __restrict__ planes, uint8_t* __restrict__ out,
                                                              long long total, int bits, int is_signed) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const uint32_t w0 = __ldg(planes + i);
-    const uint32_t w1 = bits > 1 ? __ldg(planes + total + i) : 0u;
-    uint32_t o[4];
+  // four words per thread and trip, their loads issued together
+  constexpr int U = 4;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += U * step) {
+    uint32_t w0[U], w1[U];
 #pragma unroll
-    for (int q = 0; q < 4; q++) {
-      const uint32_t t0 = (w0 >> q) & 0x11111111u, t1 = (w1 >> q) & 0x11111111u;
-      o[q] = is_signed ? (0x22222222u | ((t0 ^ 0x11111111u) << 3)) : ((t1 << 2) | ((t0 & ~t1) << 1) | (t0 & t1));
+    for (int u = 0; u < U; u++) {
+      const long long i = i0 + u * step;
+      w0[u] = i < total ? __ldg(planes + i) : 0u;
+      w1[u] = (bits > 1 && i < total) ? __ldg(planes + total + i) : 0u;
     }
-    *reinterpret_cast<uint4*>(out + i * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const long long i = i0 + u * step;
+      if (i >= total) break;
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const uint32_t t0 = (w0[u] >> q) & 0x11111111u, t1 = (w1[u] >> q) & 0x11111111u;
+        o[q] = is_signed ? (0x22222222u | ((t0 ^ 0x11111111u) << 3)) : ((t1 << 2) | ((t0 & ~t1) << 1) | (t0 & t1));
+      }
+      *reinterpret_cast<uint4*>(out + i * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
   }
 }
 
@@ -808,7 +821,7 @@ apnn_status tc5_gemm_i8_pair(cudaStream_t s, const uint8_t* A8, const uint8_t* B
 apnn_status tc5_expand_fp4(cudaStream_t s, const uint32_t* planes, uint8_t* out, long long rows, int K, int bits,
                            bool is_signed) {
   const long long total = rows * (K / 32);
-  long long blocks = (total + 255) / 256, cap = (long long)device_sm_count() * 16;
+  long long blocks = (total + 4 * 256 - 1) / (4 * 256), cap = (long long)device_sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   expand_nibbles_kernel<<<(int)blocks, 256, 0, s>>>(planes, out, total, bits, is_signed ? 1 : 0);

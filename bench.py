@@ -809,6 +809,21 @@ def kernel_cases(torch, ap, cabi):
         out = torch.empty((8192, 8192), dtype=torch.uint8, device="cuda")
         return (lambda: ap.expand_planes(P, out=out)), 2 * 8192 * 8192 // 8 + 8192 * 8192, 0.0
 
+    def expand_fp4():
+        # 16384 rows so that the output (64 MiB) and the L2 flush between calls keep the case above L2
+        P = words(torch, (2, 16384, 8192 // 32), gen)
+        out = torch.empty((16384, 8192 // 2), dtype=torch.uint8, device="cuda")
+        return (lambda: ap.expand_planes_fp4(P, out=out)), 2 * 16384 * 8192 // 8 + 16384 * 8192 // 2, 0.0
+
+    def gemm_fp4(M_, N_, K_):
+        def setup():
+            W4 = ap.expand_planes_fp4(words(torch, (1, M_, K_ // 32), gen), signed=True)
+            X4 = ap.expand_planes_fp4(words(torch, (2, N_, K_ // 32), gen))
+            D = torch.empty((M_, N_), dtype=torch.int32, device="cuda")
+            flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+            return (lambda: ap.gemm_fp4(W4, X4, D, status_flag=flag)), (M_ * K_ + N_ * K_) // 2 + 4 * M_ * N_, 2.0 * M_ * N_ * K_
+        return setup
+
     def window_rows():
         B_ = 128
         img = (torch.rand((B_, 224, 224, 3), device="cuda", generator=gen) * 20 - 10).contiguous()
@@ -858,6 +873,8 @@ def kernel_cases(torch, ap, cabi):
         "pack_planes": ("pack_planes_kernel<levels>", pack(False)),
         "quantize_pack": ("pack_planes_kernel<float>", pack(True)),
         "expand_planes": ("expand_planes_kernel", expand),
+        "expand_planes_fp4": ("expand_nibbles_kernel", expand_fp4),
+        "pair_gemm_fp4_4096": ("tc5_gemm_pair_kernel<MX> (kind::mxf4)", gemm_fp4(4096, 4096, 4096)),
         "window_rows": ("quantize_window_rows_i8_kernel (ResNet-18 first layer, 128 images, centred 8-bit)", window_rows),
         "maxpool": ("maxpool2x2_i8_kernel", maxpool),
         "requantize": ("requantize_i32_kernel", requantize),
