@@ -24,7 +24,7 @@ EXPORTS = (
     "apnn_status_string", "apnn_last_cuda_error", "apnn_version", "apnn_gemm", "apnn_gemm_ex",
     "apnn_gemm_workspace_bytes", "apnn_gemm_check", "apnn_expand_planes", "apnn_expand_planes_pair", "apnn_gemm_i8", "apnn_gemm_w8", "apnn_expand_planes_fp4", "apnn_gemm_fp4", "apnn_gemm_static_scratch", "apnn_conv2d", "apnn_conv2d_ex",
     "apnn_conv2d_workspace_bytes", "apnn_conv2d_check", "apnn_conv2d_i8", "apnn_bit_compress", "apnn_quantize_pack", "apnn_quantize_im2col", "apnn_create",
-    "apnn_destroy", "apnn_gemm_host", "apnn_conv2d_host", "apnn_probe_peak", "apnn_quantize_im2col_i8", "apnn_quantize_window_rows_i8", "apnn_maxpool2x2_i8", "apnn_requantize_i32",
+    "apnn_destroy", "apnn_gemm_host", "apnn_conv2d_host", "apnn_probe_peak", "apnn_quantize_im2col_i8", "apnn_quantize_window_rows_i8", "apnn_quantize_blocks_i8", "apnn_maxpool2x2_i8", "apnn_requantize_i32",
 )
 
 
@@ -101,6 +101,7 @@ def lib() -> ctypes.CDLL:
     L.apnn_quantize_im2col.argtypes = [vp, vp, vp, i, i, i, i, i, i, i]
     L.apnn_quantize_im2col_i8.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i]
     L.apnn_quantize_window_rows_i8.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i]
+    L.apnn_quantize_blocks_i8.argtypes = [vp, vp, vp, i, i, i, i, i, i, i, i]
     L.apnn_maxpool2x2_i8.argtypes = [vp, vp, vp, i, i, i, i, i, i]
     L.apnn_requantize_i32.argtypes = [vp, vp, vp, ctypes.c_long, i, vp]
     L.apnn_create.argtypes = [ctypes.POINTER(vp), i]

@@ -643,6 +643,53 @@ __global__ void __launch_bounds__(256) maxpool2x2_i8_kernel(const uint8_t* __res
   }
 }
 
+// First layer with a stride: the image regrouped into stride x stride pixel blocks ("space to depth").  Block
+// (hb, wb) of image b becomes one pixel of cpad bytes, byte (di*stride + dj)*C + c = level of pixel
+// (stride*hb + di, stride*wb + dj), channel c; bytes from stride*stride*C on are 0.  The strided RxR convolution of
+// the image is then a stride-1 convolution with 2*ceil(pad/stride)+1 taps a side over these pixels (taps the filter
+// does not reach carry weight 0), which the flat tcgen05 convolution runs like any other layer -- and the quantised
+// image is written once (cpad bytes per block) instead of once per window (R*R*C bytes per output pixel).
+// A thread owns 16 bytes of a block (one aligned store; a warp writes 512 contiguous bytes): four groups of four
+// bytes, each group four consecutive floats of one image row because stride*C is a multiple of 4.
+__global__ void __launch_bounds__(256) quantize_blocks_i8_kernel(const float* __restrict__ img, uint8_t* __restrict__ out,
+                                                                 int B, int H, int W, int C, int stride, int bits,
+                                                                 int halo, int cpad, const QuantSteps qs, uint32_t xormask) {
+  const int Hb = H / stride, Wb = W / stride;
+  const int seg = stride * C;                 // floats (and bytes) of a block row; a multiple of 4
+  const int used = stride * seg;              // bytes of a block that hold levels
+  const int chunks = cpad >> 4;
+  const float steps = (float)(1 << bits);
+  const uint32_t maxlv = (1u << bits) - 1u;
+  const long long row_pitch = (long long)(Wb + 2 * halo) * cpad;
+  // one row of blocks per (blockIdx.y, blockIdx.z) = (hb, b): no 64-bit index arithmetic per thread
+  const int hb = (int)blockIdx.y, b = (int)blockIdx.z;
+  for (int t = (int)(blockIdx.x * blockDim.x + threadIdx.x); t < Wb * chunks; t += (int)(gridDim.x * blockDim.x)) {
+    const int wb = t / chunks, j = t - wb * chunks;
+    const float* blk = img + (((long long)b * H + (long long)hb * stride) * W + (long long)wb * stride) * C;
+    uint32_t w4[4];
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+      const int k = 16 * j + 4 * g;   // first byte of the group inside the block
+      w4[g] = 0u;
+      if (k < used) {
+        const int row = k / seg, off = k - row * seg;
+        const float4 f = __ldg(reinterpret_cast<const float4*>(blk + (long long)row * W * C + off));
+        uint32_t packed;
+        if (qs.n)
+          packed = quantize4_by_steps(f, qs);
+        else if (bits == 8)
+          packed = quantize_level8(f.x) | (quantize_level8(f.y) << 8) | (quantize_level8(f.z) << 16) | (quantize_level8(f.w) << 24);
+        else
+          packed = quantize_level(f.x, steps, maxlv) | (quantize_level(f.y, steps, maxlv) << 8) |
+                   (quantize_level(f.z, steps, maxlv) << 16) | (quantize_level(f.w, steps, maxlv) << 24);
+        w4[g] = packed ^ xormask;
+      }
+    }
+    uint8_t* dst = out + ((long long)b * (Hb + 2 * halo) + hb + halo) * row_pitch + (long long)(wb + halo) * cpad + 16 * j;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+  }
+}
+
 // int32 values [rows][N] -> levels (low bits, or count of per-channel thresholds reached) ->
 // packed planes [bits][rows][N/32] or int8 rows [rows][N] in the operand byte order.
 // A warp owns one 32-column group and walks rows: a lane keeps its column's thresholds in
@@ -866,6 +913,28 @@ apnn_status apnn_quantize_window_rows_i8(void* stream, const float* images, void
       make_quant_steps(bits), xormask, centred ? 0.0f : -100.0f);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "quantize_window_rows_i8 launch");
+  return APNN_OK;
+}
+
+apnn_status apnn_quantize_blocks_i8(void* stream, const float* images, void* out_i8, int B, int H, int W, int C, int stride,
+                                    int bits, int halo, int cpad) {
+  using namespace apnn;
+  if (!images || !out_i8) return APNN_ERR_INVALID_ARG;
+  const bool centred = (bits & APNN_QUANT_CENTRED) != 0;
+  bits &= ~APNN_QUANT_CENTRED;
+  if (centred && bits != 8) return APNN_ERR_INVALID_ARG;
+  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || bits < 1 || bits > 8 || halo < 0 || halo > 8) return APNN_ERR_INVALID_ARG;
+  if (stride < 2 || stride > 4 || H % stride || W % stride || (stride * C) % 4 || stride * stride * C > cpad || cpad % 16)
+    return APNN_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(images) & 15u) || (reinterpret_cast<uintptr_t>(out_i8) & 15u)) return APNN_ERR_ALIGNMENT;
+  const int per_row = (W / stride) * (cpad / 16);
+  if (H / stride > 65535 || B > 65535) return APNN_ERR_UNSUPPORTED;
+  const dim3 grid((unsigned)((per_row + 255) / 256), (unsigned)(H / stride), (unsigned)B);
+  quantize_blocks_i8_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      images, reinterpret_cast<uint8_t*>(out_i8), B, H, W, C, stride, bits, halo, cpad, make_quant_steps(bits),
+      centred ? 0x80808080u : 0u);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "quantize_blocks_i8 launch");
   return APNN_OK;
 }
 

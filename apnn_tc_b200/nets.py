@@ -22,6 +22,7 @@ Everything here is host plumbing: every tensor operation is a call into ``libapn
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
@@ -167,6 +168,34 @@ def _window_row_planes(bits: np.ndarray, narrow: bool) -> np.ndarray:
     byte_of = 4 * (f & 7) + (f >> 3)
     packed_order = rows.reshape(cout, kp // 32, 32)[:, :, byte_of].reshape(cout, kp)
     return np.ascontiguousarray(_pack_bits_msb(packed_order)[None])
+
+
+def _block_filter(im2col_planes: np.ndarray, R: int, stride: int, C: int, cpad: int) -> np.ndarray:
+    """The first layer's +-1 filter (bits [1][COUT][PAD(R*R*C)/32], k = (i*R + j)*C + c) as the int8 rows of the
+    stride-1 convolution over stride x stride pixel blocks (apnn_quantize_blocks_i8): [COUT][taps*taps*cpad] with
+    the weight of image tap (ti, tj, c), ti = stride*(bi - halo) + di + pad, at block tap (bi, bj), byte
+    (di*stride + dj)*C + c, and 0 where the filter does not reach."""
+    words = np.ascontiguousarray(im2col_planes[0]).astype(np.uint32)
+    cout = words.shape[0]
+    shifts = np.arange(31, -1, -1, dtype=np.uint32)
+    bits = ((words[:, :, None] >> shifts) & 1).reshape(cout, -1)[:, : R * R * C].reshape(cout, R, R, C).astype(np.int8)
+    w = 2 * bits - 1
+    pad = (R - 1) // 2
+    halo = -(-pad // stride)
+    taps = 2 * halo + 1
+    out = np.zeros((cout, taps, taps, cpad), dtype=np.int8)
+    for bi in range(taps):
+        for di in range(stride):
+            ti = stride * (bi - halo) + di + pad
+            if not 0 <= ti < R:
+                continue
+            for bj in range(taps):
+                for dj in range(stride):
+                    tj = stride * (bj - halo) + dj + pad
+                    if 0 <= tj < R:
+                        ch = (di * stride + dj) * C
+                        out[:, bi, bj, ch:ch + C] = w[:, ti, tj, :]
+    return np.ascontiguousarray(out.reshape(cout, -1).view(np.uint8))
 
 
 def window_rows_supported(W: int, C: int, R: int, stride: int, kp: int) -> bool:
@@ -324,6 +353,7 @@ class Network:
         self.tc5_ok: Dict[str, bool] = {}
         self.first_im2col = None
         self.first_window_rows = False
+        self.first_blocks = None   # (layer, Hb, Wb, block halo, block taps): the strided first layer on pixel blocks
         self.affine: Dict[str, tuple] = {}
         self.logit_acc = None
         if spec.first_bits not in (0, 8):
@@ -362,6 +392,18 @@ class Network:
                                                         self.device)
                     x8_bytes = max(x8_bytes, B * Hc * Wc * kp)
                     ok = True
+                    # A strided first layer on the centred 8-bit image: stride x stride pixel blocks as the "pixels" of
+                    # a stride-1 convolution (apnn_quantize_blocks_i8), so the quantised image is written once, not
+                    # once per window.
+                    st, C0 = ls.stride, self.spec.image_channels
+                    # Taken when the block convolution has 3 x 3 taps (pad <= stride: 7x7 stride 4): with 5 x 5 taps (11x11
+                    # stride 4) its 50 narrow MMAs per tile cost more than the window copy saves (137 against 59 us for
+                    # 128 AlexNet images).
+                    pad = (ls.R - 1) // 2
+                    if (spec.first_bits == 8 and st >= 2 and st * st * C0 <= 64 and (st * C0) % 4 == 0 and pad <= st
+                            and sh["H"] % st == 0 and sh["W"] % st == 0 and os.environ.get("APNN_FIRST_BLOCKS", "1") != "0"):
+                        bh = -(-pad // st)
+                        self.first_blocks = (ls.name, sh["H"] // st, sh["W"] // st, bh, 2 * bh + 1)
                 self.tc5_ok[ls.name] = ok
                 if not ok and sh["cinp"] % 128:
                     raise ValueError(f"{ls.name}: a {sh['cinp']}-channel input needs the tcgen05 path")
@@ -391,6 +433,11 @@ class Network:
                 _cabi.check(self.L.apnn_expand_planes(_stream_ptr(), wp.data_ptr(), w8.data_ptr(), rows, k, 1, 1),
                             "expand weights")
                 self.w8[ls.name] = w8
+                if self.first_blocks and self.first_blocks[0] == ls.name:
+                    self.w8[ls.name] = torch.from_numpy(_block_filter(p.im2col_planes, ls.R, ls.stride,
+                                                                      self.spec.image_channels, 64)).to(self.device)
+                    _, Hb, Wb, bh, _ = self.first_blocks
+                    self.xblocks = torch.zeros((B, Hb + 2 * bh, Wb + 2 * bh, 64), dtype=torch.uint8, device=self.device)
         if spec.first_bits == 8 and self.first_im2col is None:
             raise ValueError("the 8-bit first layer needs the gathered (im2col) form of the first convolution")
         # a quantised output feeds the next layers as int8 rows, written by the producing kernel's
@@ -497,6 +544,14 @@ class Network:
         return self._launch_conv(ls, sh, X, a, B, epi, out, s)
 
     def _launch_conv(self, ls, sh, X, a, B, epi, out, s) -> int:
+        if self.first_blocks and self.first_blocks[0] == ls.name:
+            _, Hb, Wb, bh, taps = self.first_blocks
+            epi.in_halo = bh
+            # filter bytes -1 / 0 / +1 (bit 0), centred signed image bytes (bit 1)
+            _cabi.check(self.L.apnn_conv2d_i8(s, self.w8[ls.name].data_ptr(), self.xblocks.data_ptr(), out.data_ptr(), B,
+                                              Hb, Wb, 64, sh["coutp"], taps, 1, 3, ctypes.byref(epi), self.flag.data_ptr()),
+                        "apnn_conv2d_i8 " + ls.name)
+            return 1
         if self.first_im2col and self.first_im2col[0] == ls.name:
             _, Hc, Wc, kp = self.first_im2col
             epi.in_halo = 0
@@ -558,7 +613,13 @@ class Network:
         rows = self.batch * self.hw * self.hw
         n = 1
         h0 = self.halo[None]
-        if self.first_im2col:
+        if self.first_blocks:
+            first = self.by_name[self.first_blocks[0]]
+            _cabi.check(self.L.apnn_quantize_blocks_i8(s, images.data_ptr(), self.xblocks.data_ptr(), self.batch, self.hw,
+                                                       self.hw, self.spec.image_channels, first.stride,
+                                                       8 | _cabi.QUANT_CENTRED, self.first_blocks[3], 64),
+                        "first-layer block quantiser")
+        elif self.first_im2col:
             # quantise + gather the first layer's windows straight into the int8 operand buffer
             first = self.by_name[self.first_im2col[0]]
             gather = self.L.apnn_quantize_window_rows_i8 if self.first_window_rows else self.L.apnn_quantize_im2col_i8

@@ -325,6 +325,21 @@ apnn_status apnn_quantize_im2col_i8(void *stream, const float *images, void *out
 apnn_status apnn_quantize_window_rows_i8(void *stream, const float *images, void *out_i8, int B,
                                          int H, int W, int C, int R, int stride, int bits, int kp);
 
+/* A strided first layer without the window copy: the image regrouped into stride x stride pixel blocks.
+ * out_i8[B][H/stride + 2*halo][W/stride + 2*halo][cpad]: block (hb, wb) is one "pixel" of cpad bytes, byte
+ * (di*stride + dj)*C + c = the level of image pixel (stride*hb + di, stride*wb + dj), channel c (plain order,
+ * byte p is channel p), the remaining bytes 0; the ring of halo blocks is not written (zero it once).  The RxR
+ * stride-s convolution (padding p = (R-1)/2) of the image equals the stride-1 convolution of this tensor with
+ * R' = 2*ceil(p/s) + 1 taps a side and in_halo = ceil(p/s), whose filter holds the weight of image tap
+ * (ti, tj, c), ti = s*(bi - ceil(p/s)) + di + p, at block tap (bi, bj), channel (di*s + dj)*C + c, and 0
+ * where ti or tj falls outside 0..R-1 -- run it with apnn_conv2d_i8 like any other layer.  The quantised image
+ * is written once (cpad bytes per block) instead of once per window.  bits as in apnn_quantize_im2col_i8
+ * (APNN_QUANT_CENTRED included).  stride 2..4, H and W multiples of it, stride*C a multiple of 4,
+ * stride*stride*C <= cpad, cpad a multiple of 16; APNN_ERR_UNSUPPORTED otherwise.  No counterpart in the
+ * reference, whose first layer reads the float image directly (NN/kernel.cuh:583-682). */
+apnn_status apnn_quantize_blocks_i8(void *stream, const float *images, void *out_i8, int B, int H, int W,
+                                    int C, int stride, int bits, int halo, int cpad);
+
 /* ---- measurement aid ------------------------------------------------------------
  * Launches an operand-resident issue loop of one contraction instruction on every SM and
  * returns the operations one launch performs; the caller times the launch with events to

@@ -148,3 +148,40 @@ def test_maxpool2x2_i8(cuda_device, B, H, Wd, C, ih, oh):
     assert np.array_equal(got[:, oh:oh + H // 2, oh:oh + Wd // 2], want)
     if oh:
         assert (got[:, 0] == 7).all() and (got[:, :, 0] == 7).all()   # the ring is not written
+
+
+@pytest.mark.parametrize("B,H,Wd,C,stride,bits,centred,halo,cpad", [(2, 32, 32, 3, 4, 8, True, 1, 64), (1, 224, 224, 3, 4, 8, True, 1, 64),
+                                                                    (3, 8, 12, 4, 2, 2, False, 2, 16), (2, 12, 8, 2, 2, 4, False, 0, 32),
+                                                                    (1, 16, 16, 1, 4, 8, True, 1, 16)])
+def test_quantize_blocks_i8(cuda_device, B, H, Wd, C, stride, bits, centred, halo, cpad):
+    """The image as stride x stride pixel blocks: byte (di*stride + dj)*C + c of block (hb, wb) = the oracle's level
+    of pixel (stride*hb + di, stride*wb + dj), channel c (minus 128 in the centred 8-bit form), zero bytes after
+    stride*stride*C, the ring of halo blocks untouched."""
+    from apnn_tc_b200 import _cabi
+    rng = np.random.default_rng(B + H + stride + cpad)
+    x = rng.uniform(-12, 12, size=(B, H, Wd, C)).astype(np.float32)
+    lv = oracle.quantize(x, bits).astype(np.uint8)
+    if centred:
+        lv = lv ^ np.uint8(0x80)
+    Hb, Wb = H // stride, Wd // stride
+    blocks = lv.reshape(B, Hb, stride, Wb, stride, C).transpose(0, 1, 3, 2, 4, 5).reshape(B, Hb, Wb, stride * stride * C)
+    want = np.full((B, Hb + 2 * halo, Wb + 2 * halo, cpad), 0x55, dtype=np.uint8)
+    want[:, halo:halo + Hb, halo:halo + Wb, :] = 0
+    want[:, halo:halo + Hb, halo:halo + Wb, : stride * stride * C] = blocks
+    out = torch.full(want.shape, 0x55, dtype=torch.uint8, device="cuda")
+    xd = torch.from_numpy(x).cuda()
+    st = _cabi.lib().apnn_quantize_blocks_i8(torch.cuda.current_stream().cuda_stream, xd.data_ptr(), out.data_ptr(), B, H, Wd, C,
+                                             stride, bits | (_cabi.QUANT_CENTRED if centred else 0), halo, cpad)
+    _cabi.check(st, "apnn_quantize_blocks_i8")
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_quantize_blocks_i8_refuses_what_it_does_not_cover(cuda_device):
+    from apnn_tc_b200 import _cabi
+    x = torch.zeros((1, 8, 8, 3), dtype=torch.float32, device="cuda")
+    out = torch.zeros((1, 6, 6, 64), dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    L = _cabi.lib()
+    assert L.apnn_quantize_blocks_i8(s, x.data_ptr(), out.data_ptr(), 1, 8, 8, 3, 2, 8, 1, 64) == 2    # stride * C = 6: no whole quads
+    assert L.apnn_quantize_blocks_i8(s, x.data_ptr(), out.data_ptr(), 1, 8, 8, 3, 4, 8, 1, 32) == 2    # 48 level bytes > cpad
+    assert L.apnn_quantize_blocks_i8(s, x.data_ptr(), out.data_ptr(), 1, 7, 8, 3, 4, 8, 1, 64) == 2    # H not a multiple of stride
