@@ -431,7 +431,10 @@ __device__ __forceinline__ bool flat_issue_taps_ring(uint32_t d_tmem, uint32_t a
 // MMA every SM writes and reads a third fewer operand bytes than alone, which is what bounds the wide
 // layers.  With SPLITK the cluster holds `splits` such pairs, and a CTA exchanges partial sums with the
 // CTAs of the other pairs that own the same tile row.
-template <int BN, int BKB, bool SPLITK = false, int EPI = 0, bool PAIR = false>
+// R5: the flat convolution's 5 x 5 taps as straight-line MMAs too (3 x 3 and 1 x 1 always are).  A parameter of its own,
+// instantiated for the hidden-layer epilogue only: with the fifty extra MMAs inlined into every instantiation the code
+// of the other roles moved and the 3 x 3 layers of ResNet-18 ran 1 % slower.
+template <int BN, int BKB, bool SPLITK = false, int EPI = 0, bool PAIR = false, bool R5 = false>
 __global__ void __launch_bounds__(THREADS, 1)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const Tc5Params p) {
@@ -646,7 +649,7 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (!mbar_wait(full_bar(s), ph)) { ok = false; break; }
             tc_fence_after();
             const uint32_t sa = ring + (uint32_t)s * stage_bytes;
-            if (p.R == 3 || p.R == 1) {
+            if (p.R == 3 || p.R == 1 || (R5 && p.R == 5)) {   // straight-line taps; other filters take the loop below
               const uint64_t d0 = make_smem_desc_k<BKB>(0);
               const uint32_t desc_hi = (uint32_t)(d0 >> 32), lo0 = (uint32_t)d0;
               const uint32_t a_lo = lo0 | ((sa & 0x3FFFFu) >> 4);
@@ -655,9 +658,16 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               if (p.b_resident) {
                 const uint32_t b_lo = lo0 | (((base + (uint32_t)cb * B_STAGE_BYTES) & 0x3FFFFu) >> 4);
                 const uint32_t b_step = (uint32_t)p.cblocks * (B_STAGE_BYTES / 16);
-                if (p.R == 3) flat_issue_taps<BKB, 3, PAIR>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
+                if (R5 && p.R == 5) {
+                  if constexpr (R5) flat_issue_taps<BKB, 5, PAIR>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
+                } else if (p.R == 3) flat_issue_taps<BKB, 3, PAIR>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
                 else flat_issue_taps<BKB, 1, PAIR>(d_tmem, a_lo, row_step, b_lo, b_step, desc_hi, p.idesc, enable);
               } else {
+                if (R5 && p.R == 5) {
+                  if constexpr (R5)
+                    ok = flat_issue_taps_ring<BKB, 5, PAIR>(d_tmem, a_lo, row_step, lo0, bring, B_STAGE_BYTES, bfull_bar(0),
+                                                            bempty_bar(0), p.flat_nb, sb, phb, desc_hi, p.idesc, enable, pair_mask);
+                } else
                 ok = p.R == 3 ? flat_issue_taps_ring<BKB, 3, PAIR>(d_tmem, a_lo, row_step, lo0, bring, B_STAGE_BYTES, bfull_bar(0),
                                                                    bempty_bar(0), p.flat_nb, sb, phb, desc_hi, p.idesc, enable,
                                                                    pair_mask)
@@ -1321,6 +1331,10 @@ cudaError_t launch_tc5_p(cudaStream_t s, const CUtensorMap& map_a, const CUtenso
   const bool int32_only = p.out_mode == APNN_OUT_INT32 && p.pool == APNN_POOL_NONE && !residuals;
   const int epi = int32_only ? 5 : !quantising ? 0 : (thr_i8 ? (residuals ? (all16 ? 4 : 3) : 2) : (residuals ? 0 : 1));
   if (epi == 1) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 1, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
+  if constexpr (!PAIR) {
+    if (epi == 2 && p.is_conv == 2 && p.R == 5)
+      return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 2, false, true>, s, grid, smem, pair_ctas, map_a, map_b, p);
+  }
   if (epi == 2) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 2, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
   if (epi == 3) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 3, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);
   if (epi == 4) return launch_kernel(tc5_gemm_kernel<BN, BKB, false, 4, PAIR>, s, grid, smem, pair_ctas, map_a, map_b, p);

@@ -396,11 +396,10 @@ class Network:
                     # a stride-1 convolution (apnn_quantize_blocks_i8), so the quantised image is written once, not
                     # once per window.
                     st, C0 = ls.stride, self.spec.image_channels
-                    # Taken when the block convolution has 3 x 3 taps (pad <= stride: 7x7 stride 4): with 5 x 5 taps (11x11
-                    # stride 4) its 50 narrow MMAs per tile cost more than the window copy saves (137 against 59 us for
-                    # 128 AlexNet images).
+                    # Taken when the block convolution has 3 x 3 or 5 x 5 taps (7x7 and 11x11 filters at stride 4): those
+                    # tap counts have straight-line MMA sequences in the flat convolution.
                     pad = (ls.R - 1) // 2
-                    if (spec.first_bits == 8 and st >= 2 and st * st * C0 <= 64 and (st * C0) % 4 == 0 and pad <= st
+                    if (spec.first_bits == 8 and st >= 2 and st * st * C0 <= 64 and (st * C0) % 4 == 0 and pad <= 2 * st
                             and sh["H"] % st == 0 and sh["W"] % st == 0 and os.environ.get("APNN_FIRST_BLOCKS", "1") != "0"):
                         bh = -(-pad // st)
                         self.first_blocks = (ls.name, sh["H"] // st, sh["W"] // st, bh, 2 * bh + 1)
